@@ -1,0 +1,69 @@
+"""Build recipes for the checker libraries.  TEST INFRASTRUCTURE ONLY.
+
+`build_oracle()` compiles the C restatement beside this file into `libq8_oracle.so`.
+`build_ref()` compiles the reference's own sources, from where they lie in a reference tree,
+into `_ref/libaotx_ref.so`; it needs that tree and is skipped (returns None) without it.
+Nothing here is imported by the product package.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libq8_oracle.so")
+REF_DIR = os.path.join(HERE, "_ref")
+REF_SO = os.path.join(REF_DIR, "libaotx_ref.so")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return False
+    stamp = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= stamp for s in sources)
+
+
+def build_oracle(force=False):
+    src = os.path.join(HERE, "q8_oracle.c")
+    if not force and _newer(ORACLE_SO, [src]):
+        return ORACLE_SO
+    cmd = ["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-shared", "-std=c11",
+           "-ffp-contract=off", "-o", ORACLE_SO, src, "-lm"]
+    subprocess.run(cmd, check=True)
+    return ORACLE_SO
+
+
+def reference_root():
+    root = os.environ.get("AOTX_REFERENCE_ROOT", "/root/reference")
+    probe = os.path.join(root, "tests", "matrix_test.cu")
+    return root if os.path.exists(probe) else None
+
+
+def build_ref(force=False):
+    """Compile the reference's matrix kernels and host checks, unmodified, for sm_100a."""
+    root = reference_root()
+    if root is None or shutil.which("nvcc") is None:
+        return REF_SO if os.path.exists(REF_SO) else None
+    wrap = os.path.join(HERE, "ref_wrap.cu")
+    stubs = os.path.join(HERE, "ref_stubs.c")
+    if not force and _newer(REF_SO, [wrap, stubs]):
+        return REF_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    stub_obj = os.path.join(REF_DIR, "ref_stubs.o")
+    subprocess.run(["gcc", "-O2", "-fPIC", "-c", stubs, "-o", stub_obj], check=True)
+    model = os.path.join(root, "cuda", "model")
+    cmd = ["nvcc", "-std=c++17", *ARCH, "-rdc=true", "-O2", "-Xcompiler", "-fPIC", "-shared",
+           "-diag-suppress", "20044",
+           "-I" + os.path.join(root, "cuda"), "-I" + root, "-I" + os.path.join(root, "tests"),
+           '-DAOTX_PTX_DIR="%s"' % os.path.join(root, "ptx"),
+           "-o", REF_SO, wrap,
+           os.path.join(model, "gemv.cu"), os.path.join(model, "gemm.cu"),
+           os.path.join(model, "dequant.cu"), stub_obj]
+    subprocess.run(cmd, check=True)
+    return REF_SO
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="--force" in sys.argv))
+    print(build_ref(force="--force" in sys.argv))
