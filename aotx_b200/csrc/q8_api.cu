@@ -1,0 +1,294 @@
+// The C ABI of the Q8_0 path: argument checks, the per-device context and the choice of
+// kernel family.  Declarations and the reference interfaces they replace are in
+// include/aotx_q8_b200.h.
+#include "../../include/aotx_q8_b200.h"
+
+#include <cuda_runtime.h>
+#include <new>
+
+#include "q8_common.cuh"
+#include "q8_launch.h"
+
+struct aotx_q8_ctx {
+    int device;
+    unsigned int sm_count;
+    int path;
+    int last_cuda;
+    q8::UmmaScratch scratch;
+};
+
+namespace {
+
+const unsigned int kMaxTokenTile = 256u;
+const unsigned int kMaxExperts = 256u; /* cuda/model/kinds_data.h:36 */
+
+int cuda_fail(aotx_q8_ctx *ctx, cudaError_t err)
+{
+    ctx->last_cuda = (int)err;
+    return AOTX_Q8_ERR_CUDA;
+}
+
+bool dtype_16(int dtype)
+{
+    return dtype == AOTX_Q8_F16 || dtype == AOTX_Q8_BF16;
+}
+
+bool dtype_out(int dtype)
+{
+    return dtype == AOTX_Q8_F32 || dtype == AOTX_Q8_F16 || dtype == AOTX_Q8_BF16;
+}
+
+bool aligned(const void *p, uintptr_t to)
+{
+    return (reinterpret_cast<uintptr_t>(p) & (to - 1u)) == 0u;
+}
+
+size_t round_up(size_t v, size_t to)
+{
+    return (v + to - 1u) / to * to;
+}
+
+} // namespace
+
+extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
+{
+    if (out == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    *out = nullptr;
+    aotx_q8_ctx *ctx = new (std::nothrow) aotx_q8_ctx();
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    ctx->device = device;
+    ctx->path = AOTX_Q8_PATH_AUTO;
+    ctx->last_cuda = 0;
+    cudaError_t err = cudaSetDevice(device);
+    int sms = 0;
+    if (err == cudaSuccess) {
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    int major = 0;
+    if (err == cudaSuccess) {
+        err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    }
+    if (err != cudaSuccess) {
+        int code = cuda_fail(ctx, err);
+        delete ctx;
+        return code;
+    }
+    if (major != 10) {
+        /* The kernels are sm_100a only; there is no other path. */
+        delete ctx;
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    ctx->sm_count = (unsigned int)sms;
+    ctx->scratch.blocks = ctx->sm_count;
+    ctx->scratch.tile_floats = 128ull * kMaxTokenTile;
+    size_t partial_bytes = (size_t)ctx->scratch.blocks * ctx->scratch.tile_floats * sizeof(float);
+    size_t flag_bytes = (size_t)ctx->scratch.blocks * 4u * sizeof(unsigned int);
+    err = cudaMalloc((void **)&ctx->scratch.partial, partial_bytes);
+    if (err == cudaSuccess) {
+        err = cudaMalloc((void **)&ctx->scratch.flags, flag_bytes + sizeof(unsigned int));
+    }
+    if (err == cudaSuccess) {
+        err = cudaMemset(ctx->scratch.flags, 0, flag_bytes + sizeof(unsigned int));
+    }
+    if (err != cudaSuccess) {
+        int code = cuda_fail(ctx, err);
+        cudaFree(ctx->scratch.partial);
+        cudaFree(ctx->scratch.flags);
+        delete ctx;
+        return code;
+    }
+    ctx->scratch.status = ctx->scratch.flags + (size_t)ctx->scratch.blocks * 4u;
+    *out = ctx;
+    return AOTX_Q8_OK;
+}
+
+extern "C" int aotx_q8_destroy(aotx_q8_ctx *ctx)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_OK;
+    }
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->scratch.partial);
+    cudaFree(ctx->scratch.flags);
+    delete ctx;
+    return AOTX_Q8_OK;
+}
+
+extern "C" int aotx_q8_set_path(aotx_q8_ctx *ctx, int path)
+{
+    if (ctx == nullptr || path < AOTX_Q8_PATH_AUTO || path > AOTX_Q8_PATH_TENSOR) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    ctx->path = path;
+    return AOTX_Q8_OK;
+}
+
+extern "C" int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx)
+{
+    return ctx == nullptr ? 0 : ctx->last_cuda;
+}
+
+extern "C" int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int clear)
+{
+    if (ctx == nullptr || status == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err == cudaSuccess) {
+        err = cudaMemcpy(status, ctx->scratch.status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    }
+    if (err == cudaSuccess && clear) {
+        err = cudaMemset(ctx->scratch.status, 0, sizeof(uint32_t));
+    }
+    if (err != cudaSuccess) {
+        return cuda_fail(ctx, err);
+    }
+    return *status == 0u ? AOTX_Q8_OK : AOTX_Q8_ERR_DEVICE;
+}
+
+extern "C" int aotx_q8_dequant(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t k,
+                               uint32_t first_row, uint32_t rows, void *out_f16)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (rows == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w == nullptr || out_f16 == nullptr || k == 0u || (k % 32u) != 0u || !aligned(w, 2u)
+        || !aligned(out_f16, 4u)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaError_t err = q8::launch_dequant((cudaStream_t)stream, w, k, first_row, rows, out_f16);
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                              uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                              void *y, int y_dtype)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (!dtype_16(x_dtype) || !dtype_out(y_dtype) || k == 0u || (k % 32u) != 0u) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (n == 0u || m == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w == nullptr || x == nullptr || y == nullptr || !aligned(w, 2u) || !aligned(x, 4u)
+        || !aligned(y, y_dtype == AOTX_Q8_F32 ? 4u : 2u) || (m_dev != nullptr && !aligned(m_dev, 4u))) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    bool tensor_ok = q8::umma_supports(w, n, k, x, m);
+    if (ctx->path == AOTX_Q8_PATH_TENSOR && !tensor_ok) {
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    cudaError_t err;
+    if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
+        err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m,
+                              m_dev, y, y_dtype);
+    } else {
+        err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
+    }
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f16, const float *router,
+                                 uint32_t tokens, const uint32_t *tokens_dev, uint32_t hidden,
+                                 uint32_t experts, uint32_t used, float *prob, uint32_t *ids)
+{
+    if (ctx == nullptr || experts == 0u || experts > kMaxExperts || used == 0u || used > experts
+        || hidden == 0u) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (tokens == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (x_f16 == nullptr || router == nullptr || prob == nullptr || ids == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaError_t err = q8::launch_route((cudaStream_t)stream, x_f16, router, tokens, tokens_dev, hidden,
+                                       experts, used, prob, ids);
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" size_t aotx_q8_moe_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidden, uint32_t ffn)
+{
+    size_t pairs = (size_t)tokens * used;
+    size_t act = round_up(pairs * ffn * sizeof(unsigned short), 256u);
+    size_t proj = round_up(pairs * hidden * sizeof(float), 256u);
+    return act + proj;
+}
+
+extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up,
+                               const void *w_down, uint32_t type, uint32_t experts, uint32_t hidden,
+                               uint32_t ffn, const void *x_f16, const float *prob, const uint32_t *ids,
+                               uint32_t tokens, const uint32_t *tokens_dev, uint32_t used, void *out,
+                               int out_dtype, void *workspace, size_t workspace_bytes)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (experts == 0u || used == 0u || used > experts || hidden == 0u || ffn == 0u || (hidden % 32u) != 0u
+        || (ffn % 32u) != 0u || !dtype_out(out_dtype)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (tokens == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w_gate == nullptr || w_up == nullptr || w_down == nullptr || x_f16 == nullptr || prob == nullptr
+        || ids == nullptr || out == nullptr || !aligned(x_f16, 4u)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (workspace == nullptr || !aligned(workspace, 256u)
+        || workspace_bytes < aotx_q8_moe_workspace_bytes(tokens, used, hidden, ffn)) {
+        return AOTX_Q8_ERR_WORKSPACE;
+    }
+    size_t pairs = (size_t)tokens * used;
+    unsigned char *base = static_cast<unsigned char *>(workspace);
+    void *act = base;
+    float *proj = reinterpret_cast<float *>(base + round_up(pairs * ffn * sizeof(unsigned short), 256u));
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, tokens,
+                                                   tokens_dev, used, act, proj);
+    if (err == cudaSuccess) {
+        err = q8::launch_expert_sum(s, proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out,
+                                    out_dtype);
+    }
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" int aotx_q8_moe_combine(aotx_q8_ctx *ctx, void *stream, const float *proj, const float *prob,
+                                   const uint32_t *ids, uint32_t tokens, const uint32_t *tokens_dev,
+                                   uint32_t hidden, uint32_t experts, uint32_t used, void *out,
+                                   int out_dtype)
+{
+    if (ctx == nullptr || experts == 0u || used == 0u || used > experts || hidden == 0u
+        || !dtype_out(out_dtype)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (tokens == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (proj == nullptr || prob == nullptr || ids == nullptr || out == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaError_t err = q8::launch_expert_sum((cudaStream_t)stream, proj, prob, ids, tokens, tokens_dev,
+                                            hidden, experts, used, out, out_dtype);
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}

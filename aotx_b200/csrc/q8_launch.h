@@ -1,0 +1,53 @@
+// Internal launch interface between the C-ABI layer and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace q8 {
+
+// y dtype codes as in the public header: 0 float, 1 half, 2 bfloat16.
+
+cudaError_t launch_dequant(cudaStream_t stream, const void *w, unsigned int k, unsigned int first_row,
+                           unsigned int rows, void *out);
+
+cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n, unsigned int k,
+                             const void *x, int x_bf16, unsigned int m, const unsigned int *m_dev,
+                             void *y, int y_dtype);
+
+cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router, unsigned int tokens,
+                         const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                         unsigned int used, float *prob, unsigned int *ids);
+
+cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
+                                     const void *w_down, unsigned int hidden, unsigned int ffn,
+                                     const void *x, const unsigned int *ids, unsigned int tokens,
+                                     const unsigned int *tokens_dev, unsigned int used, void *act,
+                                     float *proj);
+
+cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
+                              const unsigned int *ids, unsigned int tokens,
+                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                              unsigned int used, void *out, int out_dtype);
+
+// The streaming tensor-core product.  Scratch: `partial` holds one float tile of
+// 128 x token_tile per block of the grid, `flags` four words per block (zero between
+// launches), `status` one word that kernels only ever OR bits into.
+struct UmmaScratch {
+    float *partial;
+    unsigned int *flags;
+    unsigned int *status;
+    unsigned int blocks;          // blocks the scratch was sized for
+    unsigned long long tile_floats; // floats per block in `partial`
+};
+
+// Returns cudaErrorNotSupported when the shape is outside what the kernel takes
+// (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
+cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                        const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
+                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype);
+
+bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m);
+
+unsigned int umma_token_tile(unsigned int m);
+
+} // namespace q8

@@ -1,0 +1,452 @@
+// General-shape kernels of the Q8_0 path on the ordinary cores: dequantisation, the
+// any-shape product (depth any multiple of 32, any alignment the block layout allows), the
+// expert router, the per-pair expert products and the ordered expert sum.
+//
+// The streaming tensor-core kernel in q8_umma.cu takes the shapes it supports (depth a
+// multiple of 256, 16-byte aligned rows); the product here serves every other shape, so
+// that the library covers the whole contract of the reference's kernels:
+//   cuda/model/dequant.cu:9-70      -> q8_dequant_kernel
+//   cuda/model/gemv.cuh:33-145      -> q8_gemv_simt_kernel
+//   cuda/model/experts.cu:10-75     -> q8_route_kernel
+//   cuda/model/expert_matrix.cu:8-27, cuda/model/norm.cu:92-105 -> q8_expert_feed_kernel / q8_expert_down_kernel
+//   cuda/model/experts.cu:77-98     -> q8_expert_sum_kernel
+#include "q8_common.cuh"
+#include "q8_launch.h"
+
+#include <math_constants.h>
+
+namespace q8 {
+
+// ---------------------------------------------------------------------------------------
+// Dequantisation.  The rows [first, first + rows) are one contiguous run of 34-byte
+// blocks, so the kernel walks blocks, not rows: one thread turns 8 weights of one block
+// into 8 halves and stores them with one 16-byte store.
+// ---------------------------------------------------------------------------------------
+__global__ void q8_dequant_kernel(const unsigned char *__restrict__ w, unsigned long long blocks,
+                                  __half *__restrict__ out, int wide_store)
+{
+    unsigned long long total = blocks * 4ull;
+    unsigned long long step = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long at = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; at < total;
+         at += step) {
+        unsigned long long block = at >> 2;
+        unsigned int part = (unsigned int)(at & 3ull);
+        const unsigned char *one = w + block * Q8_BLOCK_BYTES;
+        __half d = *reinterpret_cast<const __half *>(one);
+        __half2 d2 = __half2half2(d);
+        const unsigned short *src = reinterpret_cast<const unsigned short *>(one + 2u + part * 8u);
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t flipped = (uint32_t)src[i] ^ 0x8080u;
+            packed[i] = dequant_pair<0>(flipped, d2);
+        }
+        __half *dst = out + block * Q8_BLOCK + part * 8u;
+        if (wide_store) {
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                *reinterpret_cast<__half2 *>(dst + 2 * i) = *reinterpret_cast<__half2 *>(&packed[i]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Two activations from one 32-bit word.
+// ---------------------------------------------------------------------------------------
+template <typename XT>
+__device__ __forceinline__ float2 unpack2(uint32_t word);
+
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t word)
+{
+    return __half22float2(*reinterpret_cast<__half2 *>(&word));
+}
+
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t word)
+{
+    return make_float2(__uint_as_float(word << 16), __uint_as_float(word & 0xFFFF0000u));
+}
+
+#define Q8_SIMT_TAKE 8u
+#define Q8_SIMT_WARPS 8u
+
+// One warp, one row of w, up to 8 rows of x: the lanes take blocks 32 apart, keep the product
+// of a weight and its scale in float like the reference's memory-bound kernel
+// (cuda/model/matrix.cuh:498-512), and add their parts with a shuffle tree.
+template <typename XT>
+__device__ __forceinline__ void simt_row(const unsigned char *__restrict__ row, unsigned int k,
+                                         const XT *__restrict__ x, size_t x_stride, unsigned int take,
+                                         float *acc)
+{
+    unsigned int lane = threadIdx.x & 31u;
+    unsigned int blocks = k / Q8_BLOCK;
+#pragma unroll
+    for (unsigned int t = 0; t < Q8_SIMT_TAKE; ++t) {
+        acc[t] = 0.0f;
+    }
+    for (unsigned int b = lane; b < blocks; b += 32u) {
+        const unsigned char *one = row + (size_t)b * Q8_BLOCK_BYTES;
+        float d = __half2float(*reinterpret_cast<const __half *>(one));
+        const unsigned short *src = reinterpret_cast<const unsigned short *>(one + 2u);
+#pragma unroll 4
+        for (unsigned int i = 0; i < 16u; ++i) {
+            unsigned int v = src[i];
+            float w0 = (float)(int)(signed char)(v & 0xFFu) * d;
+            float w1 = (float)(int)(signed char)(v >> 8) * d;
+#pragma unroll
+            for (unsigned int t = 0; t < Q8_SIMT_TAKE; ++t) {
+                if (t < take) {
+                    const uint32_t *xr = reinterpret_cast<const uint32_t *>(x + (size_t)t * x_stride
+                                                                            + (size_t)b * Q8_BLOCK);
+                    float2 xv = unpack2<XT>(xr[i]);
+                    acc[t] = fmaf(w0, xv.x, acc[t]);
+                    acc[t] = fmaf(w1, xv.y, acc[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (unsigned int step = 16u; step > 0u; step >>= 1) {
+#pragma unroll
+        for (unsigned int t = 0; t < Q8_SIMT_TAKE; ++t) {
+            acc[t] += __shfl_down_sync(0xFFFFFFFFu, acc[t], step);
+        }
+    }
+}
+
+// y[i][j] = sum_c x[i][c] * w[j][c] for i < m, j < n; nothing else is written.  The batch m is
+// the smaller of `m_max` and the device word `m_dev` when that is given.
+template <typename XT, typename YT>
+__global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
+q8_gemv_simt_kernel(const unsigned char *__restrict__ w, unsigned int n, unsigned int k,
+                    const XT *__restrict__ x, unsigned int m_max, const unsigned int *m_dev,
+                    YT *__restrict__ y)
+{
+    unsigned int m = m_max;
+    if (m_dev != nullptr) {
+        unsigned int live = *m_dev;
+        m = live < m_max ? live : m_max;
+    }
+    unsigned int lane = threadIdx.x & 31u;
+    unsigned int warp = threadIdx.x >> 5;
+    unsigned long long stride = row_bytes(k);
+    for (unsigned int j = blockIdx.x * Q8_SIMT_WARPS + warp; j < n; j += gridDim.x * Q8_SIMT_WARPS) {
+        const unsigned char *row = w + stride * j;
+        for (unsigned int m0 = 0; m0 < m; m0 += Q8_SIMT_TAKE) {
+            unsigned int take = m - m0 < Q8_SIMT_TAKE ? m - m0 : Q8_SIMT_TAKE;
+            float acc[Q8_SIMT_TAKE];
+            simt_row<XT>(row, k, x + (size_t)m0 * k, k, take, acc);
+            if (lane == 0u) {
+#pragma unroll
+                for (unsigned int t = 0; t < Q8_SIMT_TAKE; ++t) {
+                    if (t < take) {
+                        store_out<YT>(y, (size_t)(m0 + t) * n + j, acc[t]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Expert router.  One block per token (stepping by the grid), 256 threads.  Logits are float
+// dot products of the float router rows with the half activations, one warp per expert with
+// lanes 32 apart and a shuffle tree; the softmax takes the maximum away; the rank of an
+// expert is the count of experts with a larger probability, or an equal one and a lower
+// index.  The sums run in the same order as the reference kernel's, so the probabilities
+// are the same floats.
+// ---------------------------------------------------------------------------------------
+#define Q8_ROUTE_THREADS 256u
+
+__global__ void __launch_bounds__(Q8_ROUTE_THREADS)
+q8_route_kernel(const __half *__restrict__ x, const float *__restrict__ router, unsigned int tokens_max,
+                const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                unsigned int used, float *__restrict__ prob, unsigned int *__restrict__ ids)
+{
+    __shared__ float probability[Q8_ROUTE_THREADS];
+    __shared__ float reduce[Q8_ROUTE_THREADS];
+    unsigned int tokens = tokens_max;
+    if (tokens_dev != nullptr) {
+        unsigned int live = *tokens_dev;
+        tokens = live < tokens_max ? live : tokens_max;
+    }
+    unsigned int lane = threadIdx.x & 31u;
+    unsigned int warp = threadIdx.x >> 5;
+    unsigned int e = threadIdx.x;
+    for (unsigned int t = blockIdx.x; t < tokens; t += gridDim.x) {
+        const __half *xt = x + (size_t)t * hidden;
+        for (unsigned int ex = warp; ex < experts; ex += Q8_ROUTE_THREADS / 32u) {
+            const float *row = router + (size_t)ex * hidden;
+            float dot = 0.0f;
+            for (unsigned int d = lane; d < hidden; d += 32u) {
+                dot += row[d] * __half2float(xt[d]);
+            }
+            for (unsigned int step = 16u; step != 0u; step >>= 1) {
+                dot += __shfl_down_sync(0xFFFFFFFFu, dot, step);
+            }
+            if (lane == 0u) {
+                probability[ex] = dot;
+            }
+        }
+        __syncthreads();
+        reduce[e] = e < experts ? probability[e] : -CUDART_INF_F;
+        __syncthreads();
+        for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
+            if (e < step) {
+                reduce[e] = fmaxf(reduce[e], reduce[e + step]);
+            }
+            __syncthreads();
+        }
+        float value = e < experts ? expf(probability[e] - reduce[0]) : 0.0f;
+        __syncthreads();
+        reduce[e] = value;
+        __syncthreads();
+        for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
+            if (e < step) {
+                reduce[e] += reduce[e + step];
+            }
+            __syncthreads();
+        }
+        if (e < experts) {
+            value /= reduce[0];
+            probability[e] = value;
+            prob[(size_t)t * experts + e] = value;
+        }
+        __syncthreads();
+        if (e < experts) {
+            unsigned int rank = 0u;
+            for (unsigned int other = 0u; other < experts; ++other) {
+                float candidate = probability[other];
+                rank += (candidate > value || (candidate == value && other < e)) ? 1u : 0u;
+            }
+            if (rank < used) {
+                ids[(size_t)t * used + rank] = e;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Per-pair expert products (pair = token t, rank r; index t * used + r).  These re-read an
+// expert's slice for every pair, like the reference's per-token kernel; the grouped
+// tensor-core kernels replace them for the shapes those support.
+// ---------------------------------------------------------------------------------------
+
+// act[pair][f] = half(silu(gate) * up), gate = x[t] . Wg[e][f], up = x[t] . Wu[e][f].
+__global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
+q8_expert_feed_kernel(const unsigned char *__restrict__ w_gate, const unsigned char *__restrict__ w_up,
+                      unsigned int hidden, unsigned int ffn, const __half *__restrict__ x,
+                      const unsigned int *__restrict__ ids, unsigned int tokens_max,
+                      const unsigned int *tokens_dev, unsigned int used, __half *__restrict__ act)
+{
+    unsigned int tokens = tokens_max;
+    if (tokens_dev != nullptr) {
+        unsigned int live = *tokens_dev;
+        tokens = live < tokens_max ? live : tokens_max;
+    }
+    unsigned int lane = threadIdx.x & 31u;
+    unsigned int warp = threadIdx.x >> 5;
+    unsigned long long stride = row_bytes(hidden);
+    unsigned int f = blockIdx.x * Q8_SIMT_WARPS + warp;
+    if (f >= ffn) {
+        return;
+    }
+    for (unsigned int pair = blockIdx.y; pair < tokens * used; pair += gridDim.y) {
+        unsigned int t = pair / used;
+        unsigned int expert = ids[pair];
+        const unsigned char *gate_row = w_gate + ((unsigned long long)expert * ffn + f) * stride;
+        const unsigned char *up_row = w_up + ((unsigned long long)expert * ffn + f) * stride;
+        float gate[Q8_SIMT_TAKE];
+        float up[Q8_SIMT_TAKE];
+        simt_row<__half>(gate_row, hidden, x + (size_t)t * hidden, hidden, 1u, gate);
+        simt_row<__half>(up_row, hidden, x + (size_t)t * hidden, hidden, 1u, up);
+        if (lane == 0u) {
+            float unit = gate[0] / (1.0f + expf(-gate[0]));
+            act[(size_t)pair * ffn + f] = __float2half_rn(unit * up[0]);
+        }
+    }
+}
+
+// proj[pair][d] = act[pair] . Wd[e][d]
+__global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
+q8_expert_down_kernel(const unsigned char *__restrict__ w_down, unsigned int hidden, unsigned int ffn,
+                      const __half *__restrict__ act, const unsigned int *__restrict__ ids,
+                      unsigned int tokens_max, const unsigned int *tokens_dev, unsigned int used,
+                      float *__restrict__ proj)
+{
+    unsigned int tokens = tokens_max;
+    if (tokens_dev != nullptr) {
+        unsigned int live = *tokens_dev;
+        tokens = live < tokens_max ? live : tokens_max;
+    }
+    unsigned int lane = threadIdx.x & 31u;
+    unsigned int warp = threadIdx.x >> 5;
+    unsigned long long stride = row_bytes(ffn);
+    unsigned int d = blockIdx.x * Q8_SIMT_WARPS + warp;
+    if (d >= hidden) {
+        return;
+    }
+    for (unsigned int pair = blockIdx.y; pair < tokens * used; pair += gridDim.y) {
+        unsigned int expert = ids[pair];
+        const unsigned char *row = w_down + ((unsigned long long)expert * hidden + d) * stride;
+        float sum[Q8_SIMT_TAKE];
+        simt_row<__half>(row, ffn, act + (size_t)pair * ffn, ffn, 1u, sum);
+        if (lane == 0u) {
+            proj[(size_t)pair * hidden + d] = sum[0];
+        }
+    }
+}
+
+// out[t][d] = the ordered sum over ranks: rank 0 gives fmul(proj, p); each later rank adds
+// fmul(proj, p) with a separate rounding of the product and of the sum.
+template <typename YT>
+__global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float *__restrict__ prob,
+                                     const unsigned int *__restrict__ ids, unsigned int tokens_max,
+                                     const unsigned int *tokens_dev, unsigned int hidden,
+                                     unsigned int experts, unsigned int used, YT *__restrict__ out)
+{
+    unsigned int tokens = tokens_max;
+    if (tokens_dev != nullptr) {
+        unsigned int live = *tokens_dev;
+        tokens = live < tokens_max ? live : tokens_max;
+    }
+    for (unsigned int t = blockIdx.x; t < tokens; t += gridDim.x) {
+        for (unsigned int d = threadIdx.x; d < hidden; d += blockDim.x) {
+            float sum = 0.0f;
+            for (unsigned int r = 0; r < used; ++r) {
+                unsigned int expert = ids[(size_t)t * used + r];
+                float p = prob[(size_t)t * experts + expert];
+                float value = __fmul_rn(proj[((size_t)t * used + r) * hidden + d], p);
+                sum = (r == 0u) ? value : __fadd_rn(sum, value);
+            }
+            store_out<YT>(out, (size_t)t * hidden + d, sum);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Launchers.
+// ---------------------------------------------------------------------------------------
+cudaError_t launch_dequant(cudaStream_t stream, const void *w, unsigned int k, unsigned int first_row,
+                           unsigned int rows, void *out)
+{
+    unsigned long long blocks = (unsigned long long)rows * (k / Q8_BLOCK);
+    if (blocks == 0ull) {
+        return cudaSuccess;
+    }
+    const unsigned char *base = static_cast<const unsigned char *>(w) + row_bytes(k) * first_row;
+    unsigned long long threads = blocks * 4ull;
+    unsigned long long want = (threads + 255ull) / 256ull;
+    unsigned int grid = (unsigned int)(want < 148ull * 16ull ? want : 148ull * 16ull);
+    int wide = (reinterpret_cast<uintptr_t>(out) & 15u) == 0u;
+    q8_dequant_kernel<<<grid, 256, 0, stream>>>(base, blocks, static_cast<__half *>(out), wide);
+    return cudaGetLastError();
+}
+
+template <typename XT, typename YT>
+static cudaError_t launch_gemv_simt_typed(cudaStream_t stream, const void *w, unsigned int n,
+                                          unsigned int k, const void *x, unsigned int m,
+                                          const unsigned int *m_dev, void *y)
+{
+    unsigned int want = (n + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS;
+    unsigned int grid = want < 148u * 8u ? want : 148u * 8u;
+    q8_gemv_simt_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
+        static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
+        static_cast<YT *>(y));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n, unsigned int k,
+                             const void *x, int x_bf16, unsigned int m, const unsigned int *m_dev,
+                             void *y, int y_dtype)
+{
+    if (n == 0u || m == 0u) {
+        return cudaSuccess;
+    }
+#define Q8_CASE(XT, YD, YT)                                                                      \
+    if (y_dtype == (YD)) {                                                                       \
+        return launch_gemv_simt_typed<XT, YT>(stream, w, n, k, x, m, m_dev, y);                  \
+    }
+    if (x_bf16) {
+        Q8_CASE(__nv_bfloat16, 0, float)
+        Q8_CASE(__nv_bfloat16, 1, __half)
+        Q8_CASE(__nv_bfloat16, 2, __nv_bfloat16)
+    } else {
+        Q8_CASE(__half, 0, float)
+        Q8_CASE(__half, 1, __half)
+        Q8_CASE(__half, 2, __nv_bfloat16)
+    }
+#undef Q8_CASE
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router, unsigned int tokens,
+                         const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                         unsigned int used, float *prob, unsigned int *ids)
+{
+    if (tokens == 0u) {
+        return cudaSuccess;
+    }
+    unsigned int grid = tokens < 148u * 8u ? tokens : 148u * 8u;
+    q8_route_kernel<<<grid, Q8_ROUTE_THREADS, 0, stream>>>(static_cast<const __half *>(x), router,
+                                                           tokens, tokens_dev, hidden, experts, used,
+                                                           prob, ids);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
+                                     const void *w_down, unsigned int hidden, unsigned int ffn,
+                                     const void *x, const unsigned int *ids, unsigned int tokens,
+                                     const unsigned int *tokens_dev, unsigned int used, void *act,
+                                     float *proj)
+{
+    unsigned int pairs = tokens * used;
+    if (pairs == 0u) {
+        return cudaSuccess;
+    }
+    unsigned int wave = pairs < 4096u ? pairs : 4096u;
+    dim3 feed((ffn + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, wave);
+    dim3 down((hidden + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, wave);
+    q8_expert_feed_kernel<<<feed, Q8_SIMT_WARPS * 32u, 0, stream>>>(
+        static_cast<const unsigned char *>(w_gate), static_cast<const unsigned char *>(w_up), hidden,
+        ffn, static_cast<const __half *>(x), ids, tokens, tokens_dev, used, static_cast<__half *>(act));
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        return err;
+    }
+    q8_expert_down_kernel<<<down, Q8_SIMT_WARPS * 32u, 0, stream>>>(
+        static_cast<const unsigned char *>(w_down), hidden, ffn, static_cast<const __half *>(act), ids,
+        tokens, tokens_dev, used, proj);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
+                              const unsigned int *ids, unsigned int tokens,
+                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                              unsigned int used, void *out, int out_dtype)
+{
+    if (tokens == 0u) {
+        return cudaSuccess;
+    }
+    unsigned int grid = tokens < 148u * 8u ? tokens : 148u * 8u;
+    if (out_dtype == 0) {
+        q8_expert_sum_kernel<float><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden,
+                                                              experts, used, static_cast<float *>(out));
+    } else if (out_dtype == 1) {
+        q8_expert_sum_kernel<__half><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden,
+                                                               experts, used, static_cast<__half *>(out));
+    } else if (out_dtype == 2) {
+        q8_expert_sum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+            proj, prob, ids, tokens, tokens_dev, hidden, experts, used, static_cast<__nv_bfloat16 *>(out));
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+} // namespace q8

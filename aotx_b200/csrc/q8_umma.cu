@@ -1,0 +1,714 @@
+// The streaming tensor-core product of the Q8_0 path for sm_100a:
+//     y[i][j] = sum_c x[i][c] * half(q[j][c] * d[j][c/32]),   float sums,
+// for every batch size, over the reference's own 34-byte interleaved block layout.
+//
+// It replaces, behind one launch, the three kernels the reference puts on a projection
+// (ptx/gemv_q8.ptx:18-223 for one row, cuda/model/gemv.cuh:33-145 for 2..16 rows,
+// cuda/model/gemm.cuh:55-189 for 17 rows and more; the regime switch is
+// cuda/model/product.cu:24-49).  Its weights are the half-rounded ones of the reference's
+// tensor-core kernel (cuda/model/gemm.cuh:108-113), bit for bit.
+//
+// Shape of the work.  The weight rows are the M side of the MMA: a tile is 128 rows of w by
+// NTOK rows of x (NTOK = 16..256, chosen from the batch), so a decode batch costs one pass
+// over the weights whatever its size, and the 34-byte blocks never need a transpose.  The
+// depth is cut into segments of 256 weights (8 blocks = 272 bytes per row, the smallest
+// run of blocks that is a multiple of 16 bytes).  All (tile, segment) units are dealt out
+// evenly over one persistent block per SM; a tile that is shared between blocks is summed
+// through a scratch slot per block, in a fixed order, by the block that holds its last
+// segment.
+//
+// Pipeline inside a block (15 warps):
+//   warp 12   bulk tensor copies of raw weight segments  [128 rows x 272 B]  -> shared
+//   warp 13   bulk tensor copies of x tiles [NTOK x 64], 128-byte swizzle    -> shared
+//   warps 4-11 read a raw row (one thread per row and half segment), dequantise exactly
+//             (see q8_common.cuh) and store halves in the K-major 128-byte-swizzled
+//             operand layout
+//   warp 14   one thread issues tcgen05.mma 128 x NTOK x 16, float accumulators in TMEM,
+//             two accumulator buffers
+//   warps 0-3 read the accumulators from TMEM and store y (or the partial sums)
+// All waits are bounded; a wait that runs out raises a status bit and the block runs to
+// its end.
+#include <cuda.h>
+
+#include "q8_common.cuh"
+#include "q8_launch.h"
+
+namespace q8 {
+
+constexpr uint32_t kRows = 128;                          // rows of w per tile (MMA M)
+constexpr uint32_t kSegK = 256;                          // weights per row per segment
+constexpr uint32_t kSegBytes = 272;                      // bytes per row per segment
+constexpr uint32_t kSegWords = kSegBytes / 4;            // 68
+constexpr uint32_t kRawStageBytes = kRows * kSegBytes;   // 34816
+constexpr uint32_t kSubK = 64;                           // weights per row per MMA stage
+constexpr uint32_t kSubs = kSegK / kSubK;                // 4 MMA stages per segment
+constexpr uint32_t kAStageBytes = kRows * kSubK * 2;     // 16384
+constexpr uint32_t kThreads = 15 * 32;
+constexpr uint32_t kEpilogueWarps = 4;
+constexpr uint32_t kConvertWarp0 = 4;
+constexpr uint32_t kWeightWarp = 12;
+constexpr uint32_t kInputWarp = 13;
+constexpr uint32_t kMmaWarp = 14;
+
+template <int NTOK>
+struct Shape {
+    static constexpr uint32_t raw_stages = NTOK <= 64 ? 3 : 2;
+    static constexpr uint32_t mma_stages = NTOK <= 128 ? 4 : 3;
+    static constexpr uint32_t x_stage_bytes = NTOK * kSubK * 2;
+    static constexpr uint32_t tmem_columns = 2 * NTOK < 32 ? 32 : 2 * NTOK;
+    static constexpr uint32_t a_offset = 0;
+    static constexpr uint32_t x_offset = a_offset + mma_stages * kAStageBytes;
+    static constexpr uint32_t raw_offset = x_offset + mma_stages * x_stage_bytes;
+    static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
+    static constexpr uint32_t bar_count = 2 * raw_stages + 3 * mma_stages + 4 + 1;
+    static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    static constexpr uint32_t chunk = NTOK < 32 ? 16 : 32; // accumulator columns per TMEM read
+};
+
+struct UmmaArgs {
+    unsigned int n;
+    unsigned int k;
+    unsigned int m_max;
+    const unsigned int *m_dev;
+    void *y;
+    float *partial;
+    unsigned int *flags;
+    unsigned int *status;
+    unsigned long long tile_floats;
+    unsigned int b_bf16;
+};
+
+// The units [begin, end) of block `b` out of `blocks`, of `units` in all.
+__device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks, unsigned long long units,
+                                           unsigned long long *begin, unsigned long long *end)
+{
+    *begin = (unsigned long long)b * units / blocks;
+    *end = (unsigned long long)(b + 1u) * units / blocks;
+}
+
+// Dequantise the two blocks of one MMA stage that this thread owns and store them as 8
+// chunks of 16 bytes in the swizzled operand layout.  `raw` holds 36 words: bytes
+// [H * 128, H * 128 + 144) of the thread's 272-byte row segment.  The thread's four blocks
+// start at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
+template <int H, int JJ>
+__device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_t a_stage, uint32_t row)
+{
+    const uint32_t row_base = a_stage + (row >> 3) * 1024u + (row & 7u) * 128u;
+    const uint32_t phase = row & 7u;
+#pragma unroll
+    for (int jb = 0; jb < 2; ++jb) {
+        constexpr int kDummy = 0;
+        (void)kDummy;
+        const int lb = 2 * JJ + jb;
+        const int byte_off = (H ? 8 : 0) + 34 * lb;
+        const int wi = byte_off / 4;
+        const bool odd = (byte_off % 4) == 2;
+        // scale in both halves of a word
+        uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
+        __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t out[4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+                const int p = 4 * c + pp; // pair index 0..15: weights 2p, 2p+1
+                if (odd) {
+                    // payload starts at the next word boundary
+                    const int word = wi + 1 + p / 2;
+                    uint32_t flipped = raw[word] ^ 0x80808080u;
+                    out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                } else {
+                    // payload starts in the high half of the scale's word
+                    const int word = wi + (p + 1) / 2;
+                    uint32_t flipped = raw[word] ^ 0x80808080u;
+                    out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                }
+            }
+            const uint32_t kc = (uint32_t)(4 * jb + c);
+            const uint32_t addr = row_base + ((kc ^ phase) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[0]), "r"(out[1]),
+                         "r"(out[2]), "r"(out[3])
+                         : "memory");
+        }
+    }
+}
+
+template <int H>
+__device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
+{
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
+                     : "r"(raw_row + (uint32_t)(H * 128 + 16 * i))
+                     : "memory");
+    }
+}
+
+template <int NTOK, typename YT>
+__global__ void __launch_bounds__(kThreads, 1)
+q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const UmmaArgs args)
+{
+    using S = Shape<NTOK>;
+    extern __shared__ unsigned char smem_raw_[];
+    const uint32_t smem0 = (smem_u32(smem_raw_) + 1023u) & ~1023u;
+    const uint32_t a_base = smem0 + S::a_offset;
+    const uint32_t x_base = smem0 + S::x_offset;
+    const uint32_t raw_base = smem0 + S::raw_offset;
+    const uint32_t bar_base = smem0 + S::bar_offset;
+    // barrier table
+    const uint32_t raw_full = bar_base;
+    const uint32_t raw_empty = raw_full + 8u * S::raw_stages;
+    const uint32_t x_full = raw_empty + 8u * S::raw_stages;
+    const uint32_t a_full = x_full + 8u * S::mma_stages;
+    const uint32_t mma_empty = a_full + 8u * S::mma_stages;
+    const uint32_t acc_full = mma_empty + 8u * S::mma_stages;
+    const uint32_t acc_empty = acc_full + 16u;
+    const uint32_t drain_bar = acc_empty + 16u;
+    const uint32_t tmem_slot = drain_bar + 8u;
+    unsigned char *generic0 = smem_raw_ + (smem0 - smem_u32(smem_raw_));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(generic0 + (tmem_slot - smem0));
+    volatile uint32_t *abort_flag = tmem_slot_ptr + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+
+    // The live batch and the schedule; the same in every block.
+    unsigned int m = args.m_max;
+    if (args.m_dev != nullptr) {
+        unsigned int live = *args.m_dev;
+        m = live < m ? live : m;
+    }
+    if (m == 0u) {
+        return;
+    }
+    const uint32_t segs = args.k / kSegK;
+    const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
+    const uint32_t tok_tiles = (m + (uint32_t)NTOK - 1u) / (uint32_t)NTOK;
+    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
+    unsigned long long u_begin, u_end;
+    unit_range(blockIdx.x, gridDim.x, units, &u_begin, &u_end);
+    if (u_begin >= u_end) {
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < S::raw_stages; ++i) {
+            mbar_init(raw_full + 8u * i, 1u);
+            mbar_init(raw_empty + 8u * i, 8u);
+        }
+        for (uint32_t i = 0; i < S::mma_stages; ++i) {
+            mbar_init(x_full + 8u * i, 1u);
+            mbar_init(a_full + 8u * i, 4u);
+            mbar_init(mma_empty + 8u * i, 1u);
+        }
+        for (uint32_t i = 0; i < 2u; ++i) {
+            mbar_init(acc_full + 8u * i, 1u);
+            mbar_init(acc_empty + 8u * i, kEpilogueWarps);
+        }
+        mbar_init(drain_bar, 1u);
+        *abort_flag = 0u;
+        mbar_init_fence();
+    }
+    if (warp == kWeightWarp && lane == 0u) {
+        tma_prefetch_desc(&tmap_w);
+    }
+    if (warp == kInputWarp && lane == 0u) {
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(tmem_slot, S::tmem_columns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == kWeightWarp) {
+        // ---------------------------------------------------------------- raw weight copies
+        if (lane == 0u) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (unsigned long long u = u_begin; ok && u < u_end;) {
+                const uint32_t tile = (uint32_t)(u / segs);
+                const uint32_t s0 = (uint32_t)(u % segs);
+                const unsigned long long left = u_end - u;
+                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+                const uint32_t row_tile = tile / tok_tiles;
+                for (uint32_t s = s0; s < s1; ++s, ++g) {
+                    const uint32_t st = g % S::raw_stages;
+                    const uint32_t ph = (g / S::raw_stages) & 1u;
+                    if (!mbar_wait(raw_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(raw_full + 8u * st, kRawStageBytes);
+                    tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
+                                (int)(s * kSegWords), (int)(row_tile * kRows));
+                }
+                u += (s1 - s0);
+            }
+            // Let every copy this thread started land before the block ends.
+            uint32_t local_abort = 0;
+            const uint32_t first = g > S::raw_stages ? g - S::raw_stages : 0u;
+            for (uint32_t i = first; i < g; ++i) {
+                mbar_wait(raw_full + 8u * (i % S::raw_stages), (i / S::raw_stages) & 1u, &local_abort,
+                          nullptr);
+            }
+        }
+    } else if (warp == kInputWarp) {
+        // ---------------------------------------------------------------- x tile copies
+        if (lane == 0u) {
+            uint32_t q = 0;
+            bool ok = true;
+            for (unsigned long long u = u_begin; ok && u < u_end;) {
+                const uint32_t tile = (uint32_t)(u / segs);
+                const uint32_t s0 = (uint32_t)(u % segs);
+                const unsigned long long left = u_end - u;
+                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+                const uint32_t tok_tile = tile % tok_tiles;
+                for (uint32_t s = s0; ok && s < s1; ++s) {
+                    for (uint32_t j = 0; j < kSubs; ++j, ++q) {
+                        const uint32_t st = q % S::mma_stages;
+                        const uint32_t ph = (q / S::mma_stages) & 1u;
+                        if (!mbar_wait(mma_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(x_full + 8u * st, S::x_stage_bytes);
+                        tma_load_2d(x_base + st * S::x_stage_bytes, &tmap_x, x_full + 8u * st,
+                                    (int)(s * kSegK + j * kSubK), (int)(tok_tile * (uint32_t)NTOK));
+                    }
+                }
+                u += (s1 - s0);
+            }
+            uint32_t local_abort = 0;
+            const uint32_t first = q > S::mma_stages ? q - S::mma_stages : 0u;
+            for (uint32_t i = first; i < q; ++i) {
+                mbar_wait(x_full + 8u * (i % S::mma_stages), (i / S::mma_stages) & 1u, &local_abort,
+                          nullptr);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0u) {
+            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, args.b_bf16);
+            uint32_t q = 0;
+            uint32_t tc = 0;
+            bool ok = true;
+            for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
+                const uint32_t s0 = (uint32_t)(u % segs);
+                const unsigned long long left = u_end - u;
+                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+                const uint32_t buf = tc & 1u;
+                const uint32_t aph = (tc >> 1) & 1u;
+                if (!mbar_wait(acc_empty + 8u * buf, aph ^ 1u, abort_flag, args.status)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * (uint32_t)NTOK;
+                uint32_t accumulate = 0u;
+                for (uint32_t s = s0; ok && s < s1; ++s) {
+                    for (uint32_t j = 0; j < kSubs; ++j, ++q) {
+                        const uint32_t st = q % S::mma_stages;
+                        const uint32_t ph = (q / S::mma_stages) & 1u;
+                        if (!mbar_wait(a_full + 8u * st, ph, abort_flag, args.status)
+                            || !mbar_wait(x_full + 8u * st, ph, abort_flag, args.status)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
+                        const uint64_t b_desc = umma_desc_sw128(x_base + st * S::x_stage_bytes);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
+                            // 16 halves = 32 bytes further along the swizzled row
+                            umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, accumulate);
+                            accumulate = 1u;
+                        }
+                        umma_commit(mma_empty + 8u * st);
+                    }
+                }
+                if (ok) {
+                    umma_commit(acc_full + 8u * buf);
+                }
+                u += (s1 - s0);
+            }
+            if (!ok) {
+                // Outstanding MMAs must finish before the tensor memory goes back.
+                uint32_t local_abort = 0;
+                umma_commit(drain_bar);
+                mbar_wait(drain_bar, 0u, &local_abort, nullptr);
+            }
+        }
+    } else if (warp >= kConvertWarp0) {
+        // ---------------------------------------------------------------- dequantise
+        const uint32_t cw = warp - kConvertWarp0;
+        const uint32_t half_id = cw >> 2;
+        const uint32_t row = (cw & 3u) * 32u + lane;
+        uint32_t g = 0;
+        bool ok = true;
+        for (unsigned long long u = u_begin; ok && u < u_end;) {
+            const uint32_t s0 = (uint32_t)(u % segs);
+            const unsigned long long left = u_end - u;
+            const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
+                const uint32_t rst = g % S::raw_stages;
+                const uint32_t rph = (g / S::raw_stages) & 1u;
+                if (!mbar_wait(raw_full + 8u * rst, rph, abort_flag, args.status)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t raw[36];
+                const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
+                if (half_id == 0u) {
+                    load_raw<0>(raw_row, raw);
+                } else {
+                    load_raw<1>(raw_row, raw);
+                }
+                __syncwarp();
+                if (lane == 0u) {
+                    mbar_arrive(raw_empty + 8u * rst);
+                }
+#pragma unroll
+                for (uint32_t jj = 0; jj < 2u; ++jj) {
+                    const uint32_t q = g * kSubs + half_id * 2u + jj;
+                    const uint32_t st = q % S::mma_stages;
+                    const uint32_t ph = (q / S::mma_stages) & 1u;
+                    if (!mbar_wait(mma_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_stage = a_base + st * kAStageBytes;
+                    if (half_id == 0u) {
+                        if (jj == 0u) {
+                            convert_stage<0, 0>(raw, a_stage, row);
+                        } else {
+                            convert_stage<0, 1>(raw, a_stage, row);
+                        }
+                    } else {
+                        if (jj == 0u) {
+                            convert_stage<1, 0>(raw, a_stage, row);
+                        } else {
+                            convert_stage<1, 1>(raw, a_stage, row);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0u) {
+                        mbar_arrive(a_full + 8u * st);
+                    }
+                }
+            }
+            u += (s1 - s0);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const uint32_t wq = warp; // 0..3: this warp reads TMEM lanes [32 wq, 32 wq + 32)
+        YT *y = static_cast<YT *>(args.y);
+        uint32_t tc = 0;
+        bool ok = true;
+        for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
+            const uint32_t tile = (uint32_t)(u / segs);
+            const uint32_t s0 = (uint32_t)(u % segs);
+            const unsigned long long left = u_end - u;
+            const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            const uint32_t row_tile = tile / tok_tiles;
+            const uint32_t tok_tile = tile % tok_tiles;
+            const uint32_t buf = tc & 1u;
+            const uint32_t aph = (tc >> 1) & 1u;
+            if (!mbar_wait(acc_full + 8u * buf, aph, abort_flag, args.status)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t lane_row = wq * 32u + lane;
+            const uint32_t j = row_tile * kRows + lane_row;      // row of w = column of y
+            const uint32_t i0 = tok_tile * (uint32_t)NTOK;       // first row of x of the tile
+            const uint32_t taddr = tmem_base + ((wq * 32u) << 16) + buf * (uint32_t)NTOK;
+            const bool whole = (s0 == 0u && s1 == segs);
+            const bool last = (s1 == segs);
+            float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
+
+            if (!whole && last) {
+                // Wait for the blocks that hold the earlier segments of this tile.
+                const unsigned long long tile_first = (unsigned long long)tile * segs;
+                for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+                    unsigned long long ob, oe;
+                    unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
+                    if (oe <= tile_first) {
+                        break;
+                    }
+                    if (lane == 0u) {
+                        const unsigned int *flag = args.flags + 4u * (unsigned int)cc + wq;
+                        uint32_t spin = 0;
+                        while (ld_acquire_gpu(flag) == 0u) {
+                            if (++spin > (1u << 22)) {
+                                atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                    __syncwarp();
+                    if (ob <= tile_first) {
+                        break;
+                    }
+                }
+            }
+
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += S::chunk) {
+                uint32_t v[S::chunk];
+                if (S::chunk == 32u) {
+                    tmem_ld_32x32(taddr + c0, v);
+                } else {
+                    tmem_ld_32x16(taddr + c0, v);
+                }
+                tmem_ld_wait();
+                if (!last) {
+#pragma unroll
+                    for (uint32_t i = 0; i < S::chunk; ++i) {
+                        __stcg(own_slot + (unsigned long long)(c0 + i) * kRows + lane_row, __uint_as_float(v[i]));
+                    }
+                } else {
+                    if (!whole) {
+                        const unsigned long long tile_first = (unsigned long long)tile * segs;
+                        for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+                            unsigned long long ob, oe;
+                            unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
+                            if (oe <= tile_first) {
+                                break;
+                            }
+                            const float *slot = args.partial + (unsigned long long)cc * args.tile_floats;
+#pragma unroll
+                            for (uint32_t i = 0; i < S::chunk; ++i) {
+                                float add = __ldcg(slot + (unsigned long long)(c0 + i) * kRows + lane_row);
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) + add);
+                            }
+                            if (ob <= tile_first) {
+                                break;
+                            }
+                        }
+                    }
+                    if (j < args.n) {
+#pragma unroll
+                        for (uint32_t i = 0; i < S::chunk; ++i) {
+                            const uint32_t row_x = i0 + c0 + i;
+                            if (row_x < m) {
+                                store_out<YT>(y, (size_t)row_x * args.n + j, __uint_as_float(v[i]));
+                            }
+                        }
+                    }
+                }
+            }
+            // The accumulator buffer is free again.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0u) {
+                mbar_arrive(acc_empty + 8u * buf);
+            }
+            if (!last) {
+                // Publish this warp's quarter of the partial tile.
+                __threadfence();
+                __syncwarp();
+                if (lane == 0u) {
+                    st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
+                }
+            } else if (!whole) {
+                // Hand the consumed slots back for the next launch.
+                const unsigned long long tile_first = (unsigned long long)tile * segs;
+                __syncwarp();
+                for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+                    unsigned long long ob, oe;
+                    unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
+                    if (oe <= tile_first) {
+                        break;
+                    }
+                    if (lane == 0u) {
+                        st_release_gpu(args.flags + 4u * (unsigned int)cc + wq, 0u);
+                    }
+                    if (ob <= tile_first) {
+                        break;
+                    }
+                }
+            }
+            u += (s1 - s0);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, S::tmem_columns);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side.
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess
+            && result == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    }
+    return fn;
+}
+
+unsigned int umma_token_tile(unsigned int m)
+{
+    if (m <= 16u) {
+        return 16u;
+    }
+    if (m <= 32u) {
+        return 32u;
+    }
+    if (m <= 64u) {
+        return 64u;
+    }
+    if (m <= 128u) {
+        return 128u;
+    }
+    return 256u;
+}
+
+bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m)
+{
+    if (n == 0u || m == 0u || k == 0u || (k % kSegK) != 0u) {
+        return false;
+    }
+    if ((reinterpret_cast<uintptr_t>(w) & 15u) != 0u || (reinterpret_cast<uintptr_t>(x) & 15u) != 0u) {
+        return false;
+    }
+    return true;
+}
+
+template <int NTOK, typename YT>
+static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                                const UmmaArgs &args, unsigned int grid)
+{
+    using S = Shape<NTOK>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(q8_umma_kernel<NTOK, YT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)S::smem_bytes);
+        if (err != cudaSuccess) {
+            return err;
+        }
+        configured = true;
+    }
+    q8_umma_kernel<NTOK, YT><<<grid, kThreads, S::smem_bytes, stream>>>(tw, tx, args);
+    return cudaGetLastError();
+}
+
+template <int NTOK>
+static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                               const UmmaArgs &args, unsigned int grid, int y_dtype)
+{
+    switch (y_dtype) {
+    case 0:
+        return launch_typed<NTOK, float>(stream, tw, tx, args, grid);
+    case 1:
+        return launch_typed<NTOK, __half>(stream, tw, tx, args, grid);
+    case 2:
+        return launch_typed<NTOK, __nv_bfloat16>(stream, tw, tx, args, grid);
+    default:
+        return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                        const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
+                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype)
+{
+    if (!umma_supports(w, n, k, x, m)) {
+        return cudaErrorNotSupported;
+    }
+    EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr) {
+        return cudaErrorNotSupported;
+    }
+    const unsigned int ntok = umma_token_tile(m);
+    const unsigned long long row_b = row_bytes(k);
+
+    CUtensorMap tw, tx;
+    {
+        cuuint64_t dims[2] = {row_b / 4ull, n};
+        cuuint64_t strides[1] = {row_b};
+        cuuint32_t box[2] = {kSegWords, kRows};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(w), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        cuuint64_t dims[2] = {k, m};
+        cuuint64_t strides[1] = {(cuuint64_t)k * 2ull};
+        cuuint32_t box[2] = {kSubK, ntok};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&tx, x_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                            const_cast<void *>(x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+
+    const unsigned long long row_tiles = (n + kRows - 1u) / kRows;
+    const unsigned long long tok_tiles = (m + ntok - 1u) / ntok;
+    const unsigned long long units = row_tiles * tok_tiles * (k / kSegK);
+    unsigned int grid = sm_count < scratch.blocks ? sm_count : scratch.blocks;
+    if (units < grid) {
+        grid = (unsigned int)units;
+    }
+    if (scratch.tile_floats < (unsigned long long)kRows * ntok) {
+        return cudaErrorInvalidValue;
+    }
+
+    UmmaArgs args;
+    args.n = n;
+    args.k = k;
+    args.m_max = m;
+    args.m_dev = m_dev;
+    args.y = y;
+    args.partial = scratch.partial;
+    args.flags = scratch.flags;
+    args.status = scratch.status;
+    args.tile_floats = scratch.tile_floats;
+    args.b_bf16 = x_bf16 ? 1u : 0u;
+
+    switch (ntok) {
+    case 16:
+        return launch_tile<16>(stream, tw, tx, args, grid, y_dtype);
+    case 32:
+        return launch_tile<32>(stream, tw, tx, args, grid, y_dtype);
+    case 64:
+        return launch_tile<64>(stream, tw, tx, args, grid, y_dtype);
+    case 128:
+        return launch_tile<128>(stream, tw, tx, args, grid, y_dtype);
+    default:
+        return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
+    }
+}
+
+} // namespace q8

@@ -1,0 +1,409 @@
+#!/usr/bin/env python
+"""Benchmark of the Q8_0 weight-matrix path.
+
+Default workload (`decode_m32_llama3_8b_layer`): one step = the four Q8_0 projections of a
+Llama-3-8B-shaped layer at a batch of 32 rows (fused QKV 4096->6144, O 4096->4096, fused
+gate+up 4096->28672, down 14336->4096), bf16 activations, float sums, bf16 results, on
+seeded synthetic weights (uniform int8, one half scale per 32 weights).  The metric is
+algorithmic bytes moved per second: every weight byte once plus the activations in and the
+results out.  Weight copies rotate between steps so that no step finds its weights in L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints one JSON line (rank 0).  `value` is timed with inputs resident in device memory;
+`e2e` runs the same steps through the library call with activations and results in pinned
+host memory, copies inside the timed region.  `--impl reference` times the reference's own
+host implementation of the product on this machine's cores over a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (rows of x, [(projection, k, n)], x dtype, y dtype)
+    "decode_m32_llama3_8b_layer": (32, [("qkv", 4096, 6144), ("o", 4096, 4096),
+                                        ("gate_up", 4096, 28672), ("down", 14336, 4096)],
+                                   "bfloat16", "bfloat16"),
+    "gemv_m1_4096": (1, [("w", 4096, 4096)], "float16", "float16"),
+    "prefill_m2048_llama3_8b_layer": (2048, [("qkv", 4096, 6144), ("o", 4096, 4096),
+                                             ("gate_up", 4096, 28672), ("down", 14336, 4096)],
+                                      "bfloat16", "bfloat16"),
+}
+TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer"}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+        return peaks.get("hbm_gbs", 6650.0), peaks.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def algorithmic_bytes(m, projections, x_bytes, y_bytes):
+    total = 0
+    for _, k, n in projections:
+        total += n * (k // 32) * 34 + m * k * x_bytes + m * n * y_bytes
+    return total
+
+
+def flops(m, projections):
+    return sum(2 * m * n * k for _, k, n in projections)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                mhz = self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+                util = self.nvml.nvmlDeviceGetUtilizationRates(self.handle).gpu
+                mask = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((mhz, util))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "samples": 0}
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def device_index(local_rank):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        try:
+            return int(visible.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def make_inputs(torch, m, projections, x_dtype, copies, seed):
+    import aotx_b200
+    rng = np.random.Generator(np.random.PCG64(seed))
+    tensors = []
+    for index, (name, k, n) in enumerate(projections):
+        weights = []
+        for c in range(copies):
+            host = aotx_b200.synth_q8_0(n, k, seed * 1000 + index * 10 + c)
+            dev = torch.empty(host.size, dtype=torch.uint8, device="cuda")
+            dev.copy_(torch.from_numpy(host))
+            weights.append(dev)
+        x_host = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(x_dtype)
+        tensors.append({"name": name, "k": k, "n": n, "w": weights, "x_host": x_host.pin_memory()})
+    return tensors
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import aotx_b200
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m, projections, x_name, y_name = WORKLOADS[args.workload]
+    x_dtype, y_dtype = getattr(torch, x_name), getattr(torch, y_name)
+    ctx = aotx_b200.Q8Context(local_rank)
+    weight_bytes = sum(n * (k // 32) * 34 for _, k, n in projections)
+    copies = max(2, int(np.ceil(3 * 126e6 / weight_bytes)) + 1)
+    copies = min(copies, 24)
+    tensors = make_inputs(torch, m, projections, x_dtype, copies, seed=1 + rank)
+    for t in tensors:
+        t["x"] = t["x_host"].cuda()
+        t["y"] = torch.empty((m, t["n"]), dtype=y_dtype, device="cuda")
+        t["y_host"] = torch.empty((m, t["n"]), dtype=y_dtype).pin_memory()
+
+    def step(c):
+        for t in tensors:
+            ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
+
+    def step_e2e(c):
+        for t in tensors:
+            ctx.matmul_host(t["w"][c], t["n"], t["k"], t["x_host"], t["y_host"], t["x"], t["y"])
+
+    # One graph per weight copy: the step is launch-bound on the host otherwise.
+    step(0)
+    torch.cuda.synchronize()
+    graphs = []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for c in range(copies):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                step(c)
+            graphs.append(g)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        graphs[i % copies].replay()
+    barrier()
+
+    sampler = ClockSampler(device_index(local_rank))
+    sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for i in range(args.steps):
+        starts[i].record()
+        graphs[i % copies].replay()
+        stops[i].record()
+    barrier()
+    total_ms = starts[0].elapsed_time(stops[-1])
+    step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    # A short timed region gives the sampler nothing to see: keep the same load running,
+    # untimed, until it has a few samples under load.
+    extended = False
+    if len(sampler.samples) < 8:
+        extended = True
+        deadline = time.time() + 1.0
+        i = 0
+        while time.time() < deadline:
+            for _ in range(50):
+                graphs[i % copies].replay()
+                i += 1
+            torch.cuda.synchronize()
+    sampler.stop_flag.set()
+    sampler.join()
+    status = ctx.device_status()
+
+    # end to end: host buffers, copies inside the timed region
+    for i in range(3):
+        step_e2e(i % copies)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step_e2e(i % copies)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    if world > 1:
+        import torch.distributed as dist
+        both = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(both, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = both.tolist()
+
+    x_bytes = y_bytes = 2
+    step_bytes = algorithmic_bytes(m, projections, x_bytes, y_bytes)
+    step_flops = flops(m, projections)
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    launches = len(projections)
+    kernel_ms = statistics.mean(step_ms) / launches
+    tensor_bound = args.workload in TENSOR_BOUND
+    if tensor_bound:
+        achieved = step_flops / launches / (kernel_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": achieved / tensor_peak, "traffic": None}
+        value = world * step_flops * args.steps / (total_ms * 1e-3) / 1e12
+        e2e_value = world * step_flops * args.steps / (e2e_ms * 1e-3) / 1e12
+        metric, unit = "q8_prefill_gemm_tflops", "TFLOP/s"
+    else:
+        achieved = step_bytes / launches / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "traffic": None}
+        value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+        e2e_value = world * step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
+        metric, unit = "q8_decode_gemm_hbm_gbs", "GB/s"
+    roofline["peak_source"] = peak_kind
+    roofline["kernel"] = "q8_umma_kernel"
+    roofline["launches_timed"] = launches * args.steps
+    roofline["avg_launch_us"] = kernel_ms * 1e3
+    roofline["bytes_per_launch"] = step_bytes / launches
+    roofline["tokens_per_s"] = world * m * args.steps / (total_ms * 1e-3)
+
+    h2d = sum(t["x_host"].numel() * 2 for t in tensors)
+    d2h = sum(t["y_host"].numel() * 2 for t in tensors)
+    clocks = sampler.summary()
+    clocks["probe"] = "extended" if extended else "timed_region"
+
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "rows": m, "x": x_name, "y": y_name,
+                   "projections": {name: [k, n] for name, k, n in projections},
+                   "weight_copies_rotated": copies, "l2": "weight copies rotate; total > 3x L2",
+                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True},
+        "roofline": roofline,
+        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches * args.steps,
+        "clocks": clocks,
+        "device_status": status,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_sample(workload, fraction):
+    """A bounded sample of the workload for the host cores: the first `fraction` of the rows
+    of every projection, at the full batch and depth, fp16 activations (the reference's host
+    code reads halves only)."""
+    import aotx_b200
+    m, projections, _, _ = WORKLOADS[workload]
+    rng = np.random.Generator(np.random.PCG64(99))
+    parts = []
+    for index, (name, k, n) in enumerate(projections):
+        rows = max(8, int(n * fraction) // 8 * 8)
+        w = aotx_b200.synth_q8_0(rows, k, 900 + index)
+        x = rng.standard_normal((m, k)).astype(np.float16).view(np.uint16)
+        parts.append((name, k, rows, w, x))
+    return m, parts
+
+
+def time_cpu(workload, fraction, want_reference=True):
+    """One pass of the sample on all host cores.  Uses the reference's own compiled host
+    product when that library is present, else the oracle's restatement of it."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle.binding import Oracle, Reference
+    cores = os.cpu_count() or 1
+    m, parts = cpu_sample(workload, fraction)
+    ref = Reference() if want_reference else None
+    kind = "reference" if (ref is not None and ref.available) else "port"
+    oracle = Oracle()
+    begin = time.perf_counter()
+    for name, k, rows, w, x in parts:
+        if kind == "reference":
+            # the reference's product is one thread; split the rows over the cores
+            per = max(1, (rows + cores - 1) // cores)
+            slices = [(r0, min(rows, r0 + per)) for r0 in range(0, rows, per)]
+            stride = (k // 32) * 34
+
+            def one(span):
+                r0, r1 = span
+                return ref.product(w[r0 * stride:r1 * stride], r1 - r0, k, x, m)
+
+            with ThreadPoolExecutor(cores) as pool:
+                list(pool.map(one, slices))
+        else:
+            oracle.product(w, rows, k, x, m, threads=cores)
+    seconds = time.perf_counter() - begin
+    sample_bytes = sum(rows * (k // 32) * 34 + m * k * 2 + m * rows * 4 for _, k, rows, _, _ in parts)
+    sample_flops = sum(2 * m * rows * k for _, k, rows, _, _ in parts)
+    return kind, cores, seconds, sample_bytes, sample_flops
+
+
+def cpu_baseline(workload, budget_s):
+    kind, cores, seconds, sample_bytes, sample_flops = time_cpu(workload, 1.0 / 64.0)
+    # grow the sample toward the budget, once
+    fraction = min(1.0, (1.0 / 64.0) * max(1.0, budget_s / max(seconds, 1e-3) / 2.0))
+    kind, cores, seconds, sample_bytes, sample_flops = time_cpu(workload, fraction)
+    tensor_bound = workload in TENSOR_BOUND
+    value = sample_flops / seconds / 1e12 if tensor_bound else sample_bytes / seconds / 1e9
+    return {"value": value, "unit": "TFLOP/s" if tensor_bound else "GB/s", "cores": cores, "kind": kind,
+            "sample": "first %.4f of the rows of each projection, full batch and depth, fp16 x, "
+                      "double sums; %.2f s" % (fraction, seconds),
+            "gflops": sample_flops / seconds / 1e9}
+
+
+def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the product (its host check code), all host
+    threads, on a bounded sample of the same workload per step."""
+    if rank != 0:
+        return
+    tensor_bound = args.workload in TENSOR_BOUND
+    # size one step to about a second
+    kind, cores, seconds, sample_bytes, sample_flops = time_cpu(args.workload, 1.0 / 128.0)
+    fraction = min(1.0, (1.0 / 128.0) * max(1.0, 1.0 / max(seconds, 1e-3)))
+    for _ in range(max(args.warmup, 1)):
+        time_cpu(args.workload, fraction)
+    total = 0.0
+    for _ in range(args.steps):
+        kind, cores, seconds, sample_bytes, sample_flops = time_cpu(args.workload, fraction)
+        total += seconds
+    value = (sample_flops * args.steps / total / 1e12) if tensor_bound \
+        else (sample_bytes * args.steps / total / 1e9)
+    unit = "TFLOP/s" if tensor_bound else "GB/s"
+    m, projections, x_name, y_name = WORKLOADS[args.workload]
+    sample = ("first %.4f of the rows of each projection, full batch and depth, per step" % fraction)
+    line = {
+        "impl": "reference",
+        "metric": "q8_prefill_gemm_tflops" if tensor_bound else "q8_decode_gemm_hbm_gbs",
+        "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1),
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64 sums over f16", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": m, "x": "float16", "y": "float64",
+                   "projections": {name: [k, n] for name, k, n in projections}},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=2000)
+    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--workload", default="decode_m32_llama3_8b_layer", choices=sorted(WORKLOADS))
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,129 @@
+/* aotx_q8_b200 - C ABI of the B200-native Q8_0 weight-matrix path.
+ *
+ * A drop-in for the matrix kernels of AOTX's model module.  Every entry point takes plain
+ * pointers to device memory that the caller owns, enqueues its work on the caller's stream
+ * and returns without synchronising, so it can be called inside a stream capture exactly
+ * where the reference launches its own kernels.  Nothing is allocated by a call: scratch
+ * memory lives in the context (made once, outside any capture) or is passed in.
+ *
+ * Weight layout (unchanged from the model file; reference cuda/model/matrix.cuh:6-7,26,77-82):
+ * w[n][k] row-major, each row k/32 blocks of 34 bytes = little-endian binary16 scale then 32
+ * signed bytes.  `type` is the model file's block type id; only 8 (Q8_0) is served
+ * (reference cuda/model/model.cuh:31).
+ *
+ * Return value: 0 on success, one of the AOTX_Q8_ERR_* codes otherwise.  On an error nothing
+ * is enqueued and no output is written (the reference's kernels likewise write nothing for a
+ * type they do not know: cuda/model/dequant.cu:24-25, cuda/model/gemm.cuh:236-237).
+ *
+ * Paths are relative to the reference's source root.
+ */
+#ifndef AOTX_Q8_B200_H
+#define AOTX_Q8_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AOTX_Q8_OK 0
+#define AOTX_Q8_ERR_ARGUMENT 1    /* null pointer, k not a multiple of 32, bad dtype, misaligned */
+#define AOTX_Q8_ERR_TYPE 2        /* block type other than Q8_0 */
+#define AOTX_Q8_ERR_CUDA 3        /* a CUDA call failed; see aotx_q8_last_cuda_error */
+#define AOTX_Q8_ERR_UNSUPPORTED 4 /* forced kernel family cannot take this shape */
+#define AOTX_Q8_ERR_WORKSPACE 5   /* workspace null or too small */
+#define AOTX_Q8_ERR_DEVICE 6      /* a device-side wait ran out (see aotx_q8_device_status) */
+
+#define AOTX_Q8_TYPE_Q8_0 8u
+
+/* element types of activations and outputs */
+#define AOTX_Q8_F32 0
+#define AOTX_Q8_F16 1
+#define AOTX_Q8_BF16 2
+
+/* kernel family, for aotx_q8_set_path */
+#define AOTX_Q8_PATH_AUTO 0    /* tensor-core streaming kernel where it applies, else general */
+#define AOTX_Q8_PATH_GENERAL 1 /* the any-shape kernel on the ordinary cores */
+#define AOTX_Q8_PATH_TENSOR 2  /* the tcgen05 streaming kernel; ERR_UNSUPPORTED if it cannot run */
+
+/* bits of the device status word */
+#define AOTX_Q8_DEVICE_BARRIER_TIMEOUT 1u
+#define AOTX_Q8_DEVICE_FLAG_TIMEOUT 2u
+
+typedef struct aotx_q8_ctx aotx_q8_ctx;
+
+/* Make / release the per-device context: SM count, the scratch tiles and flags of the
+ * streaming kernel (about 20 MB) and a device status word.  Call outside stream capture.
+ * No counterpart in the reference, whose kernels need no scratch; it takes the place of the
+ * buffers that cuda/model/model_host.cu:95-153 makes before its capture starts. */
+int aotx_q8_init(aotx_q8_ctx **ctx, int device);
+int aotx_q8_destroy(aotx_q8_ctx *ctx);
+
+/* Choose the kernel family for later calls on this context (tests and measurements). */
+int aotx_q8_set_path(aotx_q8_ctx *ctx, int path);
+
+/* The last CUDA error code an entry point of this context saw (cudaError_t as int). */
+int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx);
+
+/* Synchronise the device and read the status word that kernels raise instead of hanging;
+ * 0 means every bounded wait completed.  `clear` != 0 zeroes it afterwards. */
+int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int clear);
+
+/* Rows [first_row, first_row + rows) of w as binary16: out[r][j] = half(float(q) * float(d)),
+ * bit-exact.  Replaces aotx_model_dequant (cuda/model/dequant.cu:26-70; declaration
+ * cuda/model/model.cuh:112-116). */
+int aotx_q8_dequant(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t k,
+                    uint32_t first_row, uint32_t rows, void *out_f16);
+
+/* y[i][j] = sum_c x[i][c] * w[j][c], float sums, for i < m and j < n; no other element of y
+ * is written.  x is [m][k] of x_dtype (F16 or BF16), y is [m][n] of y_dtype.
+ * If m_dev is not null it points to a device word holding the live batch; the product then
+ * covers min(*m_dev, m) rows, read on the device at run time, so one captured node serves
+ * every batch up to m.  With x F16, y F32 and m_dev this is the whole of
+ * aotx_model_matrix's work (cuda/model/graph_host.cu:20-40): it stands in for
+ * aotx_model_gemm (cuda/model/gemm.cu:7-14), aotx_model_gemv (cuda/model/gemv.cu:7-11),
+ * aotx_model_line and aotx_model_product (cuda/model/product.cu:24-49) and the PTX module
+ * aotx_gemv_q8 (ptx/gemv_q8.ptx:18-223). */
+int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                   uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                   void *y, int y_dtype);
+
+/* Router of a routed-expert layer: prob[t][e] = softmax over all experts of
+ * router[e] . x[t] (float router rows, binary16 x), ids[t][r] = the expert of rank r < used,
+ * ties to the lower index.  experts <= 256.  Replaces aotx_model_expert_route
+ * (cuda/model/experts.cu:10-75). */
+int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f16, const float *router,
+                      uint32_t tokens, const uint32_t *tokens_dev, uint32_t hidden,
+                      uint32_t experts, uint32_t used, float *prob, uint32_t *ids);
+
+/* Bytes of workspace aotx_q8_moe_ffn needs for this shape. */
+size_t aotx_q8_moe_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidden, uint32_t ffn);
+
+/* The routed feed-forward step for given selections.  For each token t and rank r in
+ * ascending order, with e = ids[t][r]: gate = x[t] . Wg[e], up = x[t] . Wu[e],
+ * act = half(silu(gate) * up), proj = act . Wd[e]; out[t] = the rank-ordered sum of
+ * float(proj * prob[t][e]) (product and sum rounded separately).  Wg, Wu are
+ * [experts][ffn][hidden], Wd is [experts][hidden][ffn], all Q8_0.  Replaces the loop of
+ * aotx_model_capture_experts (cuda/model/experts_host.cu:99-111): aotx_model_expert_matrix
+ * (cuda/model/expert_matrix.cu:8-63), aotx_model_swiglu (cuda/model/norm.cu:92-105) and
+ * aotx_model_expert_add (cuda/model/experts.cu:77-98). */
+int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up,
+                    const void *w_down, uint32_t type, uint32_t experts, uint32_t hidden,
+                    uint32_t ffn, const void *x_f16, const float *prob, const uint32_t *ids,
+                    uint32_t tokens, const uint32_t *tokens_dev, uint32_t used, void *out,
+                    int out_dtype, void *workspace, size_t workspace_bytes);
+
+/* The rank-ordered weighted sum alone: proj is float [tokens][used][hidden] (the output of
+ * the selected experts, rank-major inside a token); out[t] = fmul(proj[t][0], p0), then for each
+ * later rank fadd(out[t], fmul(proj[t][r], pr)), pr = prob[t][ids[t][r]].  Bit-exact with
+ * aotx_model_expert_add run for rank 0..used-1 (cuda/model/experts.cu:77-98). */
+int aotx_q8_moe_combine(aotx_q8_ctx *ctx, void *stream, const float *proj, const float *prob,
+                        const uint32_t *ids, uint32_t tokens, const uint32_t *tokens_dev,
+                        uint32_t hidden, uint32_t experts, uint32_t used, void *out, int out_dtype);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,69 @@
+"""CPU-side checks: the library exports what the header declares, the layout helpers are
+right, and the package refuses to run without a device (no fallback)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built():
+    from aotx_b200 import build
+    return build.build()
+
+
+def test_library_exports_every_declared_symbol(built):
+    header = open(os.path.join(ROOT, "include", "aotx_q8_b200.h")).read()
+    declared = set(re.findall(r"\b(aotx_q8_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 10
+    lib = C.CDLL(built)
+    for name in sorted(declared):
+        assert hasattr(lib, name), name
+    from aotx_b200.library import SYMBOLS
+    assert declared == set(SYMBOLS)
+
+
+def test_pack_unpack_round_trip_and_oracle_agreement(oracle):
+    import aotx_b200
+    rng = np.random.default_rng(1)
+    n, k = 9, 128
+    q = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    d = (rng.random((n, k // 32)) * 0.01).astype(np.float16)
+    w = aotx_b200.pack_q8_0(q, d)
+    assert w.size == n * aotx_b200.row_bytes(k) == n * 4 * 34
+    q2, d2 = aotx_b200.unpack_q8_0(w, n, k)
+    assert np.array_equal(q, q2) and np.array_equal(d.view(np.uint16), d2.view(np.uint16))
+    want = (q.astype(np.float32).reshape(n, k // 32, 32) * d.astype(np.float32)[..., None])
+    got = oracle.dequant(w, k, 0, n).view(np.float16)
+    assert np.array_equal(got, want.astype(np.float16).reshape(n, k))
+
+
+def test_synthetic_distribution():
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(64, 1024, 0)
+    q, d = aotx_b200.unpack_q8_0(w, 64, 1024)
+    assert q.min() == -127 and q.max() == 127
+    share = (d.astype(np.float32) < 6.1e-5).mean()
+    assert 0.2 < share < 0.45
+    assert np.array_equal(w, aotx_b200.synth_q8_0(64, 1024, 0))
+
+
+def test_no_device_means_no_result():
+    import torch
+    import aotx_b200
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    with pytest.raises(RuntimeError):
+        aotx_b200.Q8Context(0)
+
+
+def test_product_package_never_touches_the_oracle():
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "aotx_b200")):
+        for name in files:
+            if name.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                text = open(os.path.join(dirpath, name)).read()
+                assert "oracle" not in text.replace("no CPU or PyTorch fallback", ""), name
