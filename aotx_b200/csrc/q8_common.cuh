@@ -105,17 +105,29 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Every wait is bounded.  When the bound runs out the waiter raises `*abort_flag` (shared)
 // and the device status word, and the caller leaves its loop; the kernel then runs to its
 // end with a wrong result rather than holding the GPU.
-#define Q8_WAIT_SPINS (1u << 24)
+#define Q8_WAIT_CYCLES 4000000000ll /* about two seconds of SM clock */
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                           unsigned int *status)
 {
-    for (uint32_t spin = 0; spin < Q8_WAIT_SPINS; ++spin) {
+    // The common case: the phase completes within a few thousand polls; no clock is read.
+    for (uint32_t spin = 0; spin < 4096u; ++spin) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
-        if ((spin & 1023u) == 1023u && *abort_flag != 0u) {
-            return false;
+    }
+    const long long begin = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((spin & 255u) == 0u) {
+            if (*abort_flag != 0u) {
+                return false;
+            }
+            if (clock64() - begin > Q8_WAIT_CYCLES) {
+                break;
+            }
         }
     }
     *abort_flag = 1u;

@@ -14,7 +14,7 @@
 // depth is cut into segments of 256 weights (8 blocks = 272 bytes per row, the smallest
 // run of blocks that is a multiple of 16 bytes).  All (tile, segment) units are dealt out
 // evenly over one persistent block per SM; a tile that is shared between blocks is summed
-// through a scratch slot per block, in a fixed order, by the block that holds its last
+// through a scratch slot per block, in a fixed order, by the block that holds its first
 // segment.
 //
 // Pipeline inside a block (15 warps):
@@ -54,13 +54,14 @@ template <int NTOK>
 struct Shape {
     static constexpr uint32_t raw_stages = NTOK <= 64 ? 3 : 2;
     static constexpr uint32_t mma_stages = NTOK <= 128 ? 4 : 3;
+    static constexpr uint32_t x_stages = NTOK <= 32 ? 8 : (NTOK == 64 ? 6 : (NTOK == 128 ? 4 : 3));
     static constexpr uint32_t x_stage_bytes = NTOK * kSubK * 2;
     static constexpr uint32_t tmem_columns = 2 * NTOK < 32 ? 32 : 2 * NTOK;
     static constexpr uint32_t a_offset = 0;
     static constexpr uint32_t x_offset = a_offset + mma_stages * kAStageBytes;
-    static constexpr uint32_t raw_offset = x_offset + mma_stages * x_stage_bytes;
+    static constexpr uint32_t raw_offset = x_offset + x_stages * x_stage_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
-    static constexpr uint32_t bar_count = 2 * raw_stages + 3 * mma_stages + 4 + 1;
+    static constexpr uint32_t bar_count = 2 * raw_stages + 2 * mma_stages + 2 * x_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
     static constexpr uint32_t chunk = NTOK < 32 ? 16 : 32; // accumulator columns per TMEM read
 };
@@ -161,7 +162,8 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t raw_full = bar_base;
     const uint32_t raw_empty = raw_full + 8u * S::raw_stages;
     const uint32_t x_full = raw_empty + 8u * S::raw_stages;
-    const uint32_t a_full = x_full + 8u * S::mma_stages;
+    const uint32_t x_empty = x_full + 8u * S::x_stages;
+    const uint32_t a_full = x_empty + 8u * S::x_stages;
     const uint32_t mma_empty = a_full + 8u * S::mma_stages;
     const uint32_t acc_full = mma_empty + 8u * S::mma_stages;
     const uint32_t acc_empty = acc_full + 16u;
@@ -198,8 +200,11 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             mbar_init(raw_full + 8u * i, 1u);
             mbar_init(raw_empty + 8u * i, 8u);
         }
-        for (uint32_t i = 0; i < S::mma_stages; ++i) {
+        for (uint32_t i = 0; i < S::x_stages; ++i) {
             mbar_init(x_full + 8u * i, 1u);
+            mbar_init(x_empty + 8u * i, 1u);
+        }
+        for (uint32_t i = 0; i < S::mma_stages; ++i) {
             mbar_init(a_full + 8u * i, 4u);
             mbar_init(mma_empty + 8u * i, 1u);
         }
@@ -271,9 +276,9 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 const uint32_t tok_tile = tile % tok_tiles;
                 for (uint32_t s = s0; ok && s < s1; ++s) {
                     for (uint32_t j = 0; j < kSubs; ++j, ++q) {
-                        const uint32_t st = q % S::mma_stages;
-                        const uint32_t ph = (q / S::mma_stages) & 1u;
-                        if (!mbar_wait(mma_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
+                        const uint32_t st = q % S::x_stages;
+                        const uint32_t ph = (q / S::x_stages) & 1u;
+                        if (!mbar_wait(x_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
                             ok = false;
                             break;
                         }
@@ -285,9 +290,9 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 u += (s1 - s0);
             }
             uint32_t local_abort = 0;
-            const uint32_t first = q > S::mma_stages ? q - S::mma_stages : 0u;
+            const uint32_t first = q > S::x_stages ? q - S::x_stages : 0u;
             for (uint32_t i = first; i < q; ++i) {
-                mbar_wait(x_full + 8u * (i % S::mma_stages), (i / S::mma_stages) & 1u, &local_abort,
+                mbar_wait(x_full + 8u * (i % S::x_stages), (i / S::x_stages) & 1u, &local_abort,
                           nullptr);
             }
         }
@@ -315,14 +320,16 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     for (uint32_t j = 0; j < kSubs; ++j, ++q) {
                         const uint32_t st = q % S::mma_stages;
                         const uint32_t ph = (q / S::mma_stages) & 1u;
+                        const uint32_t xst = q % S::x_stages;
+                        const uint32_t xph = (q / S::x_stages) & 1u;
                         if (!mbar_wait(a_full + 8u * st, ph, abort_flag, args.status)
-                            || !mbar_wait(x_full + 8u * st, ph, abort_flag, args.status)) {
+                            || !mbar_wait(x_full + 8u * xst, xph, abort_flag, args.status)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
                         const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
-                        const uint64_t b_desc = umma_desc_sw128(x_base + st * S::x_stage_bytes);
+                        const uint64_t b_desc = umma_desc_sw128(x_base + xst * S::x_stage_bytes);
 #pragma unroll
                         for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
                             // 16 halves = 32 bytes further along the swizzled row
@@ -330,6 +337,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             accumulate = 1u;
                         }
                         umma_commit(mma_empty + 8u * st);
+                        umma_commit(x_empty + 8u * xst);
                     }
                 }
                 if (ok) {
@@ -429,24 +437,28 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             const uint32_t j = row_tile * kRows + lane_row;      // row of w = column of y
             const uint32_t i0 = tok_tile * (uint32_t)NTOK;       // first row of x of the tile
             const uint32_t taddr = tmem_base + ((wq * 32u) << 16) + buf * (uint32_t)NTOK;
+            // A tile that is cut between blocks belongs to the block that holds its first
+            // segment.  That is the owner's last piece of work, while the other holders meet
+            // the tile at the very start of their ranges, so their partial sums are published
+            // long before the owner asks for them.
             const bool whole = (s0 == 0u && s1 == segs);
-            const bool last = (s1 == segs);
+            const bool owner = (s0 == 0u);
+            const unsigned long long tile_end = ((unsigned long long)tile + 1ull) * segs;
             float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
 
-            if (!whole && last) {
-                // Wait for the blocks that hold the earlier segments of this tile.
-                const unsigned long long tile_first = (unsigned long long)tile * segs;
-                for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+            if (owner && !whole) {
+                // Wait for the blocks that hold the later segments of this tile.
+                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
                     unsigned long long ob, oe;
-                    unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
-                    if (oe <= tile_first) {
+                    unit_range(cc, gridDim.x, units, &ob, &oe);
+                    if (ob >= tile_end) {
                         break;
                     }
                     if (lane == 0u) {
-                        const unsigned int *flag = args.flags + 4u * (unsigned int)cc + wq;
-                        uint32_t spin = 0;
+                        const unsigned int *flag = args.flags + 4u * cc + wq;
+                        const long long begin = clock64();
                         while (ld_acquire_gpu(flag) == 0u) {
-                            if (++spin > (1u << 22)) {
+                            if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
                                 atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
                                 break;
                             }
@@ -454,7 +466,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         }
                     }
                     __syncwarp();
-                    if (ob <= tile_first) {
+                    if (oe >= tile_end) {
                         break;
                     }
                 }
@@ -469,18 +481,17 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     tmem_ld_32x16(taddr + c0, v);
                 }
                 tmem_ld_wait();
-                if (!last) {
+                if (!owner) {
 #pragma unroll
                     for (uint32_t i = 0; i < S::chunk; ++i) {
                         __stcg(own_slot + (unsigned long long)(c0 + i) * kRows + lane_row, __uint_as_float(v[i]));
                     }
                 } else {
                     if (!whole) {
-                        const unsigned long long tile_first = (unsigned long long)tile * segs;
-                        for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+                        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
                             unsigned long long ob, oe;
-                            unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
-                            if (oe <= tile_first) {
+                            unit_range(cc, gridDim.x, units, &ob, &oe);
+                            if (ob >= tile_end) {
                                 break;
                             }
                             const float *slot = args.partial + (unsigned long long)cc * args.tile_floats;
@@ -489,7 +500,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                                 float add = __ldcg(slot + (unsigned long long)(c0 + i) * kRows + lane_row);
                                 v[i] = __float_as_uint(__uint_as_float(v[i]) + add);
                             }
-                            if (ob <= tile_first) {
+                            if (oe >= tile_end) {
                                 break;
                             }
                         }
@@ -511,7 +522,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (lane == 0u) {
                 mbar_arrive(acc_empty + 8u * buf);
             }
-            if (!last) {
+            if (!owner) {
                 // Publish this warp's quarter of the partial tile.
                 __threadfence();
                 __syncwarp();
@@ -520,18 +531,17 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 }
             } else if (!whole) {
                 // Hand the consumed slots back for the next launch.
-                const unsigned long long tile_first = (unsigned long long)tile * segs;
                 __syncwarp();
-                for (int cc = (int)blockIdx.x - 1; cc >= 0; --cc) {
+                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
                     unsigned long long ob, oe;
-                    unit_range((unsigned int)cc, gridDim.x, units, &ob, &oe);
-                    if (oe <= tile_first) {
+                    unit_range(cc, gridDim.x, units, &ob, &oe);
+                    if (ob >= tile_end) {
                         break;
                     }
                     if (lane == 0u) {
-                        st_release_gpu(args.flags + 4u * (unsigned int)cc + wq, 0u);
+                        st_release_gpu(args.flags + 4u * cc + wq, 0u);
                     }
-                    if (ob <= tile_first) {
+                    if (oe >= tile_end) {
                         break;
                     }
                 }

@@ -32,11 +32,11 @@ WORKLOADS = {
     # name: (rows of x, [(projection, k, n)], x dtype, y dtype)
     "decode_m32_llama3_8b_layer": (32, [("qkv", 4096, 6144), ("o", 4096, 4096),
                                         ("gate_up", 4096, 28672), ("down", 14336, 4096)],
-                                   "bfloat16", "bfloat16"),
+                                   "float16", "bfloat16"),
     "gemv_m1_4096": (1, [("w", 4096, 4096)], "float16", "float16"),
     "prefill_m2048_llama3_8b_layer": (2048, [("qkv", 4096, 6144), ("o", 4096, 4096),
                                              ("gate_up", 4096, 28672), ("down", 14336, 4096)],
-                                      "bfloat16", "bfloat16"),
+                                      "float16", "bfloat16"),
 }
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer"}
 

@@ -17,7 +17,7 @@ def ctx():
     c.close()
 
 
-@pytest.mark.parametrize("path_name", ["PATH_GENERAL", "PATH_TENSOR"])
+@pytest.mark.parametrize("path_name", ["PATH_GENERAL", "PATH_AUTO"])
 @pytest.mark.parametrize("n,k,m", [(256, 512, 1), (640, 1024, 32), (512, 768, 130)])
 def test_bf16_activations(ctx, oracle, path_name, n, k, m):
     import aotx_b200
@@ -26,9 +26,11 @@ def test_bf16_activations(ctx, oracle, path_name, n, k, m):
     x, bits = x_bf16_bits(m, k, 31 + m)
     ctx.set_path(getattr(aotx_b200, path_name))
     y = torch.full((m + 1, n), GUARD, dtype=torch.bfloat16, device="cuda")
-    ctx.matmul(dev_weights(w), n, k, x.cuda(), y=y[:m])
-    torch.cuda.synchronize()
-    ctx.set_path(0)
+    try:
+        ctx.matmul(dev_weights(w), n, k, x.cuda(), y=y[:m])
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_path(0)
     got = y.float().cpu().numpy()
     want = oracle.product(w, n, k, bits, m, bf16=True)
     ok, err, bound = oracle.within_bound(got[:m], want)

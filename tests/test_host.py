@@ -67,3 +67,27 @@ def test_product_package_never_touches_the_oracle():
             if name.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, name)).read()
                 assert "oracle" not in text.replace("no CPU or PyTorch fallback", ""), name
+
+
+def test_cpp_seam_compiles_and_links(built, tmp_path):
+    """The C++ mirror of the reference's matrix seam builds against the header and links with
+    the library (no device call is made)."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    src = tmp_path / "seam.cpp"
+    src.write_text(
+        '#include "aotx_b200_seam.hpp"\n'
+        "int main(int argc, char **) {\n"
+        "    aotx_b200_hold hold = {};\n"
+        "    if (argc > 100) { aotx_model_matrix(&hold, 0, 8, 1, 32, 0, 1, 0, AOTX_B200_BATCH_TOKENS); }\n"
+        "    return aotx_q8_set_path(0, 0) == AOTX_Q8_ERR_ARGUMENT ? 0 : 1;\n"
+        "}\n")
+    exe = tmp_path / "seam"
+    cuda_inc = "/usr/local/cuda/include"
+    lib_dir = os.path.dirname(built)
+    subprocess.run(["g++", "-std=c++17", "-I" + os.path.join(ROOT, "include"), "-I" + cuda_inc, str(src),
+                    "-o", str(exe), "-L" + lib_dir, "-laotx_q8_b200", "-Wl,-rpath," + lib_dir,
+                    "-L/usr/local/cuda/lib64", "-lcudart"], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
