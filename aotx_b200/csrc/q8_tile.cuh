@@ -1,0 +1,274 @@
+// Pieces shared by the two tensor-core kernels of the Q8_0 product: tile constants, the
+// kernel arguments, the unit schedule, the raw-row loader, the exact converters (to shared
+// memory in the swizzled operand layout, or to tensor memory) and the epilogue that stores a
+// finished tile or hands a partial one to the tile's owner.
+#pragma once
+
+#include <cuda.h>
+
+#include "q8_common.cuh"
+
+namespace q8 {
+
+constexpr uint32_t kRows = 128;                          // rows of w per tile (MMA M)
+constexpr uint32_t kSegK = 256;                          // weights per row per segment
+constexpr uint32_t kSegBytes = 272;                      // bytes per row per segment
+constexpr uint32_t kSegWords = kSegBytes / 4;            // 68
+constexpr uint32_t kRawStageBytes = kRows * kSegBytes;   // 34816
+constexpr uint32_t kSubK = 64;                           // weights per row per MMA stage
+constexpr uint32_t kSubs = kSegK / kSubK;                // 4 MMA stages per segment
+constexpr uint32_t kAStageBytes = kRows * kSubK * 2;     // 16384
+constexpr uint32_t kThreads = 15 * 32;
+constexpr uint32_t kEpilogueWarps = 4;
+constexpr uint32_t kConvertWarp0 = 4;
+constexpr uint32_t kWeightWarp = 12;
+constexpr uint32_t kInputWarp = 13;
+constexpr uint32_t kMmaWarp = 14;
+
+struct UmmaArgs {
+    unsigned int n;
+    unsigned int k;
+    unsigned int m_max;
+    const unsigned int *m_dev;
+    void *y;
+    float *partial;
+    unsigned int *flags;
+    unsigned int *status;
+    unsigned long long tile_floats;
+    unsigned int b_bf16;
+#ifdef Q8_EXPERIMENT
+    unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
+#endif
+};
+
+// The units [begin, end) of block `b` out of `blocks`, of `units` in all.
+__device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks, unsigned long long units,
+                                           unsigned long long *begin, unsigned long long *end)
+{
+    *begin = (unsigned long long)b * units / blocks;
+    *end = (unsigned long long)(b + 1u) * units / blocks;
+}
+
+// Dequantise the two blocks of one MMA stage that this thread owns and store them as 8
+// chunks of 16 bytes in the swizzled operand layout.  `raw` holds 36 words: bytes
+// [H * 128, H * 128 + 144) of the thread's 272-byte row segment.  The thread's four blocks
+// start at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
+template <int H, int JJ>
+__device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_t a_stage, uint32_t row)
+{
+    const uint32_t row_base = a_stage + (row >> 3) * 1024u + (row & 7u) * 128u;
+    const uint32_t phase = row & 7u;
+#pragma unroll
+    for (int jb = 0; jb < 2; ++jb) {
+        constexpr int kDummy = 0;
+        (void)kDummy;
+        const int lb = 2 * JJ + jb;
+        const int byte_off = (H ? 8 : 0) + 34 * lb;
+        const int wi = byte_off / 4;
+        const bool odd = (byte_off % 4) == 2;
+        // scale in both halves of a word
+        uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
+        __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t out[4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+                const int p = 4 * c + pp; // pair index 0..15: weights 2p, 2p+1
+                if (odd) {
+                    // payload starts at the next word boundary
+                    const int word = wi + 1 + p / 2;
+                    uint32_t flipped = raw[word] ^ 0x80808080u;
+                    out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                } else {
+                    // payload starts in the high half of the scale's word
+                    const int word = wi + (p + 1) / 2;
+                    uint32_t flipped = raw[word] ^ 0x80808080u;
+                    out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                }
+            }
+            const uint32_t kc = (uint32_t)(4 * jb + c);
+            const uint32_t addr = row_base + ((kc ^ phase) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[0]), "r"(out[1]),
+                         "r"(out[2]), "r"(out[3])
+                         : "memory");
+        }
+    }
+}
+
+// The same two blocks as 32 packed words (64 halves in order of k), written to this thread's
+// lane of tensor memory: column c of the stage holds weights 2c and 2c+1 of the stage.
+template <int H, int JJ>
+__device__ __forceinline__ void convert_stage_tmem(const uint32_t (&raw)[36], uint32_t taddr)
+{
+    uint32_t out[32];
+#pragma unroll
+    for (int jb = 0; jb < 2; ++jb) {
+        const int lb = 2 * JJ + jb;
+        const int byte_off = (H ? 8 : 0) + 34 * lb;
+        const int wi = byte_off / 4;
+        const bool odd = (byte_off % 4) == 2;
+        uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
+        __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {
+            if (odd) {
+                const int word = wi + 1 + p / 2;
+                uint32_t flipped = raw[word] ^ 0x80808080u;
+                out[16 * jb + p] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+            } else {
+                const int word = wi + (p + 1) / 2;
+                uint32_t flipped = raw[word] ^ 0x80808080u;
+                out[16 * jb + p] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+            }
+        }
+    }
+    tmem_st_32x32(taddr, out);
+}
+
+template <int H>
+__device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
+{
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
+                     : "r"(raw_row + (uint32_t)(H * 128 + 16 * i))
+                     : "memory");
+    }
+}
+
+// One piece of a tile is in the accumulator at `taddr_acc` (column base of the buffer).  The
+// warp `wq` of the four epilogue warps owns TMEM lanes [32 wq, 32 wq + 32).  `chunk` columns are
+// read per TMEM load.
+template <int NTOK, typename YT>
+__device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t taddr_acc, uint32_t wq,
+                                               uint32_t lane, uint32_t tile, uint32_t s0, uint32_t s1,
+                                               uint32_t segs, uint32_t tok_tiles,
+                                               unsigned long long units, unsigned int m,
+                                               volatile uint32_t *abort_flag, uint32_t acc_empty_bar)
+{
+    constexpr uint32_t kChunk = NTOK < 32 ? 16 : 32;
+    YT *y = static_cast<YT *>(args.y);
+    const uint32_t row_tile = tile / tok_tiles;
+    const uint32_t tok_tile = tile % tok_tiles;
+    const uint32_t lane_row = wq * 32u + lane;
+    const uint32_t j = row_tile * kRows + lane_row;      // row of w = column of y
+    const uint32_t i0 = tok_tile * (uint32_t)NTOK;       // first row of x of the tile
+    const uint32_t taddr = taddr_acc + ((wq * 32u) << 16);
+    // A tile that is cut between blocks belongs to the block that holds its first
+    // segment.  That is the owner's last piece of work, while the other holders meet
+    // the tile at the very start of their ranges, so their partial sums are published
+    // long before the owner asks for them.
+    const bool whole = (s0 == 0u && s1 == segs);
+    const bool owner = (s0 == 0u);
+    const unsigned long long tile_end = ((unsigned long long)tile + 1ull) * segs;
+    float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
+
+    if (owner && !whole) {
+        // Wait for the blocks that hold the later segments of this tile.
+        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
+            unsigned long long ob, oe;
+            unit_range(cc, gridDim.x, units, &ob, &oe);
+            if (ob >= tile_end) {
+                break;
+            }
+            if (lane == 0u) {
+                const unsigned int *flag = args.flags + 4u * cc + wq;
+                const long long begin = clock64();
+                while (ld_acquire_gpu(flag) == 0u) {
+                    if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
+                        atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            __syncwarp();
+            if (oe >= tile_end) {
+                break;
+            }
+        }
+    }
+
+#pragma unroll 1
+    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += kChunk) {
+        uint32_t v[kChunk];
+        if (kChunk == 32u) {
+            tmem_ld_32x32(taddr + c0, v);
+        } else {
+            tmem_ld_32x16(taddr + c0, v);
+        }
+        tmem_ld_wait();
+        if (!owner) {
+#pragma unroll
+            for (uint32_t i = 0; i < kChunk; ++i) {
+                __stcg(own_slot + (unsigned long long)(c0 + i) * kRows + lane_row, __uint_as_float(v[i]));
+            }
+        } else {
+            if (!whole) {
+                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
+                    unsigned long long ob, oe;
+                    unit_range(cc, gridDim.x, units, &ob, &oe);
+                    if (ob >= tile_end) {
+                        break;
+                    }
+                    const float *slot = args.partial + (unsigned long long)cc * args.tile_floats;
+#pragma unroll
+                    for (uint32_t i = 0; i < kChunk; ++i) {
+                        float add = __ldcg(slot + (unsigned long long)(c0 + i) * kRows + lane_row);
+                        v[i] = __float_as_uint(__uint_as_float(v[i]) + add);
+                    }
+                    if (oe >= tile_end) {
+                        break;
+                    }
+                }
+            }
+            if (j < args.n) {
+#pragma unroll
+                for (uint32_t i = 0; i < kChunk; ++i) {
+                    const uint32_t row_x = i0 + c0 + i;
+                    if (row_x < m) {
+                        store_out<YT>(y, (size_t)row_x * args.n + j, __uint_as_float(v[i]));
+                    }
+                }
+            }
+        }
+    }
+    // The accumulator buffer is free again.
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0u) {
+        mbar_arrive(acc_empty_bar);
+    }
+    if (!owner) {
+        // Publish this warp's quarter of the partial tile.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0u) {
+            st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
+        }
+    } else if (!whole) {
+        // Hand the consumed slots back for the next launch.
+        __syncwarp();
+        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
+            unsigned long long ob, oe;
+            unit_range(cc, gridDim.x, units, &ob, &oe);
+            if (ob >= tile_end) {
+                break;
+            }
+            if (lane == 0u) {
+                st_release_gpu(args.flags + 4u * cc + wq, 0u);
+            }
+            if (oe >= tile_end) {
+                break;
+            }
+        }
+    }
+}
+
+// Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.
+cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                                 const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
+
+} // namespace q8

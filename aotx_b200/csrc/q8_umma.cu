@@ -29,36 +29,29 @@
 // All waits are bounded; a wait that runs out raises a status bit and the block runs to
 // its end.
 #include <cuda.h>
+#include <stdlib.h>
 
-#include "q8_common.cuh"
 #include "q8_launch.h"
+#include "q8_tile.cuh"
 
 namespace q8 {
 
-constexpr uint32_t kRows = 128;                          // rows of w per tile (MMA M)
-constexpr uint32_t kSegK = 256;                          // weights per row per segment
-constexpr uint32_t kSegBytes = 272;                      // bytes per row per segment
-constexpr uint32_t kSegWords = kSegBytes / 4;            // 68
-constexpr uint32_t kRawStageBytes = kRows * kSegBytes;   // 34816
-constexpr uint32_t kSubK = 64;                           // weights per row per MMA stage
-constexpr uint32_t kSubs = kSegK / kSubK;                // 4 MMA stages per segment
-constexpr uint32_t kAStageBytes = kRows * kSubK * 2;     // 16384
-constexpr uint32_t kThreads = 15 * 32;
-constexpr uint32_t kEpilogueWarps = 4;
-constexpr uint32_t kConvertWarp0 = 4;
-constexpr uint32_t kWeightWarp = 12;
-constexpr uint32_t kInputWarp = 13;
-constexpr uint32_t kMmaWarp = 14;
-
-template <int NTOK>
+// TS = true keeps the dequantised weight tile in tensor memory (the MMA reads A from TMEM):
+// the converters write it with tcgen05.st, no shared memory is spent on it, and the raw ring
+// gets the space.  TS = false keeps it in shared memory (both accumulators then fit beside a
+// 256-wide token tile).
+template <int NTOK, bool TS>
 struct Shape {
-    static constexpr uint32_t raw_stages = NTOK <= 64 ? 3 : 2;
-    static constexpr uint32_t mma_stages = NTOK <= 128 ? 4 : 3;
+    static constexpr uint32_t raw_stages = TS ? (NTOK <= 64 ? 5 : 4) : (NTOK <= 64 ? 3 : 2);
+    static constexpr uint32_t mma_stages = TS ? 8 : (NTOK <= 128 ? 4 : 3);
     static constexpr uint32_t x_stages = NTOK <= 32 ? 8 : (NTOK == 64 ? 6 : (NTOK == 128 ? 4 : 3));
     static constexpr uint32_t x_stage_bytes = NTOK * kSubK * 2;
-    static constexpr uint32_t tmem_columns = 2 * NTOK < 32 ? 32 : 2 * NTOK;
+    static constexpr uint32_t acc_columns = 2 * NTOK;
+    static constexpr uint32_t a_column0 = NTOK <= 64 ? 128 : 256;       // TS only
+    static constexpr uint32_t a_stage_columns = kSubK / 2;               // 32 words per row
+    static constexpr uint32_t tmem_columns = TS ? 512 : (2 * NTOK < 32 ? 32 : 2 * NTOK);
     static constexpr uint32_t a_offset = 0;
-    static constexpr uint32_t x_offset = a_offset + mma_stages * kAStageBytes;
+    static constexpr uint32_t x_offset = a_offset + (TS ? 0 : mma_stages * kAStageBytes);
     static constexpr uint32_t raw_offset = x_offset + x_stages * x_stage_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * mma_stages + 2 * x_stages + 4 + 1;
@@ -66,92 +59,13 @@ struct Shape {
     static constexpr uint32_t chunk = NTOK < 32 ? 16 : 32; // accumulator columns per TMEM read
 };
 
-struct UmmaArgs {
-    unsigned int n;
-    unsigned int k;
-    unsigned int m_max;
-    const unsigned int *m_dev;
-    void *y;
-    float *partial;
-    unsigned int *flags;
-    unsigned int *status;
-    unsigned long long tile_floats;
-    unsigned int b_bf16;
-};
 
-// The units [begin, end) of block `b` out of `blocks`, of `units` in all.
-__device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks, unsigned long long units,
-                                           unsigned long long *begin, unsigned long long *end)
-{
-    *begin = (unsigned long long)b * units / blocks;
-    *end = (unsigned long long)(b + 1u) * units / blocks;
-}
-
-// Dequantise the two blocks of one MMA stage that this thread owns and store them as 8
-// chunks of 16 bytes in the swizzled operand layout.  `raw` holds 36 words: bytes
-// [H * 128, H * 128 + 144) of the thread's 272-byte row segment.  The thread's four blocks
-// start at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
-template <int H, int JJ>
-__device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_t a_stage, uint32_t row)
-{
-    const uint32_t row_base = a_stage + (row >> 3) * 1024u + (row & 7u) * 128u;
-    const uint32_t phase = row & 7u;
-#pragma unroll
-    for (int jb = 0; jb < 2; ++jb) {
-        constexpr int kDummy = 0;
-        (void)kDummy;
-        const int lb = 2 * JJ + jb;
-        const int byte_off = (H ? 8 : 0) + 34 * lb;
-        const int wi = byte_off / 4;
-        const bool odd = (byte_off % 4) == 2;
-        // scale in both halves of a word
-        uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
-        __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint32_t out[4];
-#pragma unroll
-            for (int pp = 0; pp < 4; ++pp) {
-                const int p = 4 * c + pp; // pair index 0..15: weights 2p, 2p+1
-                if (odd) {
-                    // payload starts at the next word boundary
-                    const int word = wi + 1 + p / 2;
-                    uint32_t flipped = raw[word] ^ 0x80808080u;
-                    out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
-                } else {
-                    // payload starts in the high half of the scale's word
-                    const int word = wi + (p + 1) / 2;
-                    uint32_t flipped = raw[word] ^ 0x80808080u;
-                    out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
-                }
-            }
-            const uint32_t kc = (uint32_t)(4 * jb + c);
-            const uint32_t addr = row_base + ((kc ^ phase) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[0]), "r"(out[1]),
-                         "r"(out[2]), "r"(out[3])
-                         : "memory");
-        }
-    }
-}
-
-template <int H>
-__device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
-{
-#pragma unroll
-    for (int i = 0; i < 9; ++i) {
-        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
-                     : "r"(raw_row + (uint32_t)(H * 128 + 16 * i))
-                     : "memory");
-    }
-}
-
-template <int NTOK, typename YT>
+template <int NTOK, typename YT, bool TS>
 __global__ void __launch_bounds__(kThreads, 1)
 q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const UmmaArgs args)
 {
-    using S = Shape<NTOK>;
+    using S = Shape<NTOK, TS>;
     extern __shared__ unsigned char smem_raw_[];
     const uint32_t smem0 = (smem_u32(smem_raw_) + 1023u) & ~1023u;
     const uint32_t a_base = smem0 + S::a_offset;
@@ -249,6 +163,12 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         ok = false;
                         break;
                     }
+#ifdef Q8_EXPERIMENT
+                    if (args.debug & 1u) {
+                        mbar_arrive(raw_full + 8u * st);
+                        continue;
+                    }
+#endif
                     mbar_expect_tx(raw_full + 8u * st, kRawStageBytes);
                     tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
                                 (int)(s * kSegWords), (int)(row_tile * kRows));
@@ -282,6 +202,12 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             ok = false;
                             break;
                         }
+#ifdef Q8_EXPERIMENT
+                        if (args.debug & 8u) {
+                            mbar_arrive(x_full + 8u * st);
+                            continue;
+                        }
+#endif
                         mbar_expect_tx(x_full + 8u * st, S::x_stage_bytes);
                         tma_load_2d(x_base + st * S::x_stage_bytes, &tmap_x, x_full + 8u * st,
                                     (int)(s * kSegK + j * kSubK), (int)(tok_tile * (uint32_t)NTOK));
@@ -328,13 +254,30 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
                         const uint64_t b_desc = umma_desc_sw128(x_base + xst * S::x_stage_bytes);
+#ifdef Q8_EXPERIMENT
+                        if (args.debug & 4u) {
+                            umma_commit(mma_empty + 8u * st);
+                            umma_commit(x_empty + 8u * xst);
+                            continue;
+                        }
+#endif
+                        if constexpr (TS) {
+                            const uint32_t a_tmem = tmem_base + S::a_column0 + st * S::a_stage_columns;
 #pragma unroll
-                        for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
-                            // 16 halves = 32 bytes further along the swizzled row
-                            umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, accumulate);
-                            accumulate = 1u;
+                            for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
+                                // 16 halves = 8 columns of A, 32 bytes along the swizzled row of B
+                                umma_f16_ts(d_tmem, a_tmem + 8u * kk, b_desc + 2u * kk, idesc, accumulate);
+                                accumulate = 1u;
+                            }
+                        } else {
+                            const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
+#pragma unroll
+                            for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
+                                // 16 halves = 32 bytes further along the swizzled row
+                                umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, accumulate);
+                                accumulate = 1u;
+                            }
                         }
                         umma_commit(mma_empty + 8u * st);
                         umma_commit(x_empty + 8u * xst);
@@ -372,6 +315,14 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 }
                 uint32_t raw[36];
                 const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
+#ifdef Q8_EXPERIMENT
+                if (args.debug & 2u) {
+#pragma unroll
+                    for (int i = 0; i < 36; ++i) {
+                        raw[i] = 0u;
+                    }
+                } else
+#endif
                 if (half_id == 0u) {
                     load_raw<0>(raw_row, raw);
                 } else {
@@ -390,21 +341,52 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         ok = false;
                         break;
                     }
-                    const uint32_t a_stage = a_base + st * kAStageBytes;
-                    if (half_id == 0u) {
-                        if (jj == 0u) {
-                            convert_stage<0, 0>(raw, a_stage, row);
-                        } else {
-                            convert_stage<0, 1>(raw, a_stage, row);
+#ifdef Q8_EXPERIMENT
+                    if (args.debug & 2u) {
+                        __syncwarp();
+                        if (lane == 0u) {
+                            mbar_arrive(a_full + 8u * st);
                         }
-                    } else {
-                        if (jj == 0u) {
-                            convert_stage<1, 0>(raw, a_stage, row);
-                        } else {
-                            convert_stage<1, 1>(raw, a_stage, row);
-                        }
+                        continue;
                     }
-                    fence_proxy_async_smem();
+#endif
+                    if constexpr (TS) {
+                        // this warp owns TMEM lanes [32 (cw & 3), +32): its rows of the tile
+                        const uint32_t taddr = tmem_base + (((cw & 3u) * 32u) << 16) + S::a_column0
+                                             + st * S::a_stage_columns;
+                        tc_fence_after_sync();
+                        if (half_id == 0u) {
+                            if (jj == 0u) {
+                                convert_stage_tmem<0, 0>(raw, taddr);
+                            } else {
+                                convert_stage_tmem<0, 1>(raw, taddr);
+                            }
+                        } else {
+                            if (jj == 0u) {
+                                convert_stage_tmem<1, 0>(raw, taddr);
+                            } else {
+                                convert_stage_tmem<1, 1>(raw, taddr);
+                            }
+                        }
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                    } else {
+                        const uint32_t a_stage = a_base + st * kAStageBytes;
+                        if (half_id == 0u) {
+                            if (jj == 0u) {
+                                convert_stage<0, 0>(raw, a_stage, row);
+                            } else {
+                                convert_stage<0, 1>(raw, a_stage, row);
+                            }
+                        } else {
+                            if (jj == 0u) {
+                                convert_stage<1, 0>(raw, a_stage, row);
+                            } else {
+                                convert_stage<1, 1>(raw, a_stage, row);
+                            }
+                        }
+                        fence_proxy_async_smem();
+                    }
                     __syncwarp();
                     if (lane == 0u) {
                         mbar_arrive(a_full + 8u * st);
@@ -433,119 +415,8 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t lane_row = wq * 32u + lane;
-            const uint32_t j = row_tile * kRows + lane_row;      // row of w = column of y
-            const uint32_t i0 = tok_tile * (uint32_t)NTOK;       // first row of x of the tile
-            const uint32_t taddr = tmem_base + ((wq * 32u) << 16) + buf * (uint32_t)NTOK;
-            // A tile that is cut between blocks belongs to the block that holds its first
-            // segment.  That is the owner's last piece of work, while the other holders meet
-            // the tile at the very start of their ranges, so their partial sums are published
-            // long before the owner asks for them.
-            const bool whole = (s0 == 0u && s1 == segs);
-            const bool owner = (s0 == 0u);
-            const unsigned long long tile_end = ((unsigned long long)tile + 1ull) * segs;
-            float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
-
-            if (owner && !whole) {
-                // Wait for the blocks that hold the later segments of this tile.
-                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
-                    unsigned long long ob, oe;
-                    unit_range(cc, gridDim.x, units, &ob, &oe);
-                    if (ob >= tile_end) {
-                        break;
-                    }
-                    if (lane == 0u) {
-                        const unsigned int *flag = args.flags + 4u * cc + wq;
-                        const long long begin = clock64();
-                        while (ld_acquire_gpu(flag) == 0u) {
-                            if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
-                                atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
-                                break;
-                            }
-                            __nanosleep(64);
-                        }
-                    }
-                    __syncwarp();
-                    if (oe >= tile_end) {
-                        break;
-                    }
-                }
-            }
-
-#pragma unroll 1
-            for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += S::chunk) {
-                uint32_t v[S::chunk];
-                if (S::chunk == 32u) {
-                    tmem_ld_32x32(taddr + c0, v);
-                } else {
-                    tmem_ld_32x16(taddr + c0, v);
-                }
-                tmem_ld_wait();
-                if (!owner) {
-#pragma unroll
-                    for (uint32_t i = 0; i < S::chunk; ++i) {
-                        __stcg(own_slot + (unsigned long long)(c0 + i) * kRows + lane_row, __uint_as_float(v[i]));
-                    }
-                } else {
-                    if (!whole) {
-                        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
-                            unsigned long long ob, oe;
-                            unit_range(cc, gridDim.x, units, &ob, &oe);
-                            if (ob >= tile_end) {
-                                break;
-                            }
-                            const float *slot = args.partial + (unsigned long long)cc * args.tile_floats;
-#pragma unroll
-                            for (uint32_t i = 0; i < S::chunk; ++i) {
-                                float add = __ldcg(slot + (unsigned long long)(c0 + i) * kRows + lane_row);
-                                v[i] = __float_as_uint(__uint_as_float(v[i]) + add);
-                            }
-                            if (oe >= tile_end) {
-                                break;
-                            }
-                        }
-                    }
-                    if (j < args.n) {
-#pragma unroll
-                        for (uint32_t i = 0; i < S::chunk; ++i) {
-                            const uint32_t row_x = i0 + c0 + i;
-                            if (row_x < m) {
-                                store_out<YT>(y, (size_t)row_x * args.n + j, __uint_as_float(v[i]));
-                            }
-                        }
-                    }
-                }
-            }
-            // The accumulator buffer is free again.
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0u) {
-                mbar_arrive(acc_empty + 8u * buf);
-            }
-            if (!owner) {
-                // Publish this warp's quarter of the partial tile.
-                __threadfence();
-                __syncwarp();
-                if (lane == 0u) {
-                    st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
-                }
-            } else if (!whole) {
-                // Hand the consumed slots back for the next launch.
-                __syncwarp();
-                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
-                    unsigned long long ob, oe;
-                    unit_range(cc, gridDim.x, units, &ob, &oe);
-                    if (ob >= tile_end) {
-                        break;
-                    }
-                    if (lane == 0u) {
-                        st_release_gpu(args.flags + 4u * cc + wq, 0u);
-                    }
-                    if (oe >= tile_end) {
-                        break;
-                    }
-                }
-            }
+            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, s0, s1, segs,
+                                     tok_tiles, units, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }
     }
@@ -608,14 +479,14 @@ bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x,
     return true;
 }
 
-template <int NTOK, typename YT>
+template <int NTOK, typename YT, bool TS>
 static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                 const UmmaArgs &args, unsigned int grid)
 {
-    using S = Shape<NTOK>;
+    using S = Shape<NTOK, TS>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(q8_umma_kernel<NTOK, YT>,
+        cudaError_t err = cudaFuncSetAttribute(q8_umma_kernel<NTOK, YT, TS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)S::smem_bytes);
         if (err != cudaSuccess) {
@@ -623,7 +494,7 @@ static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, cons
         }
         configured = true;
     }
-    q8_umma_kernel<NTOK, YT><<<grid, kThreads, S::smem_bytes, stream>>>(tw, tx, args);
+    q8_umma_kernel<NTOK, YT, TS><<<grid, kThreads, S::smem_bytes, stream>>>(tw, tx, args);
     return cudaGetLastError();
 }
 
@@ -631,13 +502,14 @@ template <int NTOK>
 static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                const UmmaArgs &args, unsigned int grid, int y_dtype)
 {
+    constexpr bool TS = false;
     switch (y_dtype) {
     case 0:
-        return launch_typed<NTOK, float>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, float, TS>(stream, tw, tx, args, grid);
     case 1:
-        return launch_typed<NTOK, __half>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, __half, TS>(stream, tw, tx, args, grid);
     case 2:
-        return launch_typed<NTOK, __nv_bfloat16>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, __nv_bfloat16, TS>(stream, tw, tx, args, grid);
     default:
         return cudaErrorInvalidValue;
     }
@@ -706,19 +578,17 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.status = scratch.status;
     args.tile_floats = scratch.tile_floats;
     args.b_bf16 = x_bf16 ? 1u : 0u;
-
-    switch (ntok) {
-    case 16:
-        return launch_tile<16>(stream, tw, tx, args, grid, y_dtype);
-    case 32:
-        return launch_tile<32>(stream, tw, tx, args, grid, y_dtype);
-    case 64:
-        return launch_tile<64>(stream, tw, tx, args, grid, y_dtype);
-    case 128:
-        return launch_tile<128>(stream, tw, tx, args, grid, y_dtype);
-    default:
-        return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
+#ifdef Q8_EXPERIMENT
+    {
+        const char *env = getenv("Q8_EXPERIMENT");
+        args.debug = env != nullptr ? (unsigned int)atoi(env) : 0u;
     }
+#endif
+
+    if (ntok <= 128u) {
+        return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
+    }
+    return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
 }
 
 } // namespace q8
