@@ -14,6 +14,8 @@ struct aotx_q8_ctx {
     unsigned int sm_count;
     int path;
     int last_cuda;
+    int overlap;
+    unsigned int launches;
     q8::UmmaScratch scratch;
 };
 
@@ -63,6 +65,8 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     ctx->device = device;
     ctx->path = AOTX_Q8_PATH_AUTO;
     ctx->last_cuda = 0;
+    ctx->overlap = 1;
+    ctx->launches = 0;
     cudaError_t err = cudaSetDevice(device);
     int sms = 0;
     if (err == cudaSuccess) {
@@ -85,8 +89,8 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     ctx->sm_count = (unsigned int)sms;
     ctx->scratch.blocks = ctx->sm_count;
     ctx->scratch.tile_floats = 128ull * kMaxTokenTile;
-    size_t partial_bytes = (size_t)ctx->scratch.blocks * ctx->scratch.tile_floats * sizeof(float);
-    size_t flag_bytes = (size_t)ctx->scratch.blocks * 4u * sizeof(unsigned int);
+    size_t partial_bytes = 2u * (size_t)ctx->scratch.blocks * ctx->scratch.tile_floats * sizeof(float);
+    size_t flag_bytes = 2u * (size_t)ctx->scratch.blocks * 4u * sizeof(unsigned int);
     err = cudaMalloc((void **)&ctx->scratch.partial, partial_bytes);
     if (err == cudaSuccess) {
         err = cudaMalloc((void **)&ctx->scratch.flags, flag_bytes + sizeof(unsigned int));
@@ -101,7 +105,7 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
         delete ctx;
         return code;
     }
-    ctx->scratch.status = ctx->scratch.flags + (size_t)ctx->scratch.blocks * 4u;
+    ctx->scratch.status = ctx->scratch.flags + 2u * (size_t)ctx->scratch.blocks * 4u;
     *out = ctx;
     return AOTX_Q8_OK;
 }
@@ -124,6 +128,15 @@ extern "C" int aotx_q8_set_path(aotx_q8_ctx *ctx, int path)
         return AOTX_Q8_ERR_ARGUMENT;
     }
     ctx->path = path;
+    return AOTX_Q8_OK;
+}
+
+extern "C" int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    ctx->overlap = enabled != 0;
     return AOTX_Q8_OK;
 }
 
@@ -201,7 +214,7 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     cudaError_t err;
     if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
         err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m,
-                              m_dev, y, y_dtype);
+                              m_dev, y, y_dtype, ctx->launches++, ctx->overlap != 0);
     } else {
         err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
     }

@@ -302,6 +302,19 @@ __host__ __device__ inline uint32_t umma_idesc(unsigned int m, unsigned int n, u
     return d;
 }
 
+// Programmatic dependent launch: let the next kernel on the stream start its blocks early,
+// and wait (in that next kernel) until everything before it on the stream has finished and
+// its memory is visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

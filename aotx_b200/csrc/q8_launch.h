@@ -29,9 +29,9 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
                               const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                               unsigned int used, void *out, int out_dtype);
 
-// The streaming tensor-core product.  Scratch: `partial` holds one float tile of
-// 128 x token_tile per block of the grid, `flags` four words per block (zero between
-// launches), `status` one word that kernels only ever OR bits into.
+// The streaming tensor-core product.  Scratch, in two sets that alternate between launches:
+// `partial` holds one float tile of 128 x token_tile per block of the grid, `flags` four words
+// per block (zero between launches); `status` is one word that kernels only ever OR bits into.
 struct UmmaScratch {
     float *partial;
     unsigned int *flags;
@@ -44,7 +44,8 @@ struct UmmaScratch {
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
-                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype);
+                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
+                        bool overlap);
 
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m);
 

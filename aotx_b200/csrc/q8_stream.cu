@@ -65,9 +65,20 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
+#ifdef Q8_EXPERIMENT
+    unsigned long long t_start = 0;
+    if (args.trace != nullptr && threadIdx.x == 0) {
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
+    }
+#endif
 
+    // The next kernel on the stream may start its blocks as this one's finish.  Work that only
+    // reads the weights runs ahead of the kernels before this one; everything that reads x or
+    // the live batch, or writes y or the scratch slots, first waits for them to finish.
+    grid_launch_dependents();
     unsigned int m = args.m_max;
     if (args.m_dev != nullptr) {
+        grid_dependency_wait();
         unsigned int live = *args.m_dev;
         m = live < m ? live : m;
     }
@@ -116,6 +127,14 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 0u] = t_start;
+        args.trace[blockIdx.x * 8u + 1u] = t;
+    }
+#endif
 
     if (warp == kWeightWarp) {
         // ---------------------------------------------------------------- raw weight copies
@@ -159,6 +178,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // ---------------------------------------------------------------- x copies
         if (lane == 0u) {
             uint32_t g = 0;
+            grid_dependency_wait();
             bool ok = true;
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
@@ -327,6 +347,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // ---------------------------------------------------------------- epilogue
         const uint32_t wq = warp;
         uint32_t tc = 0;
+        grid_dependency_wait();
         bool ok = true;
         for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
             const uint32_t tile = (uint32_t)(u / segs);
@@ -348,10 +369,24 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     tc_fence_before_sync();
     __syncthreads();
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 2u] = t;
+    }
+#endif
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, S::tmem_columns);
     }
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && threadIdx.x == 14 * 32) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 3u] = t;
+    }
+#endif
 }
 
 template <int NTOK, typename YT>
@@ -369,8 +404,8 @@ static cudaError_t launch_stream_typed(cudaStream_t stream, const CUtensorMap &t
         }
         configured = true;
     }
-    q8_stream_kernel<NTOK, YT><<<grid, kThreads, S::smem_bytes, stream>>>(tw, tx, args);
-    return cudaGetLastError();
+    return launch_tile_kernel(q8_stream_kernel<NTOK, YT>, grid, S::smem_bytes, stream, args.overlap != 0u, tw,
+                              tx, args);
 }
 
 template <int NTOK>

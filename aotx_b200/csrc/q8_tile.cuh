@@ -36,8 +36,10 @@ struct UmmaArgs {
     unsigned int *status;
     unsigned long long tile_floats;
     unsigned int b_bf16;
+    unsigned int overlap; // launched with the programmatic-dependent-launch attribute
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
+    unsigned long long *trace; // [launch][block][4] timestamps, or null
 #endif
 };
 
@@ -165,15 +167,32 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     const unsigned long long tile_end = ((unsigned long long)tile + 1ull) * segs;
     float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
 
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && wq == 0u && lane == 0u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 4u] = t;
+        args.trace[blockIdx.x * 8u + 7u] = (owner ? 1u : 0u) | (whole ? 2u : 0u);
+    }
+#endif
+    // The other holders of this tile are the blocks right after this one, up to `last_cc`.
+    unsigned int last_cc = blockIdx.x;
     if (owner && !whole) {
-        // Wait for the blocks that hold the later segments of this tile.
         for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
             unsigned long long ob, oe;
             unit_range(cc, gridDim.x, units, &ob, &oe);
             if (ob >= tile_end) {
                 break;
             }
-            if (lane == 0u) {
+            last_cc = cc;
+            if (oe >= tile_end) {
+                break;
+            }
+        }
+        // Wait for their partial sums; each lane watches one of them.
+        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+            const unsigned int cc = base + lane;
+            if (cc <= last_cc) {
                 const unsigned int *flag = args.flags + 4u * cc + wq;
                 const long long begin = clock64();
                 while (ld_acquire_gpu(flag) == 0u) {
@@ -181,16 +200,19 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                         atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
                         break;
                     }
-                    __nanosleep(64);
                 }
             }
-            __syncwarp();
-            if (oe >= tile_end) {
-                break;
-            }
         }
+        __syncwarp();
     }
 
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && wq == 0u && lane == 0u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 5u] = t;
+    }
+#endif
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += kChunk) {
         uint32_t v[kChunk];
@@ -206,22 +228,29 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                 __stcg(own_slot + (unsigned long long)(c0 + i) * kRows + lane_row, __uint_as_float(v[i]));
             }
         } else {
-            if (!whole) {
-                for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
-                    unsigned long long ob, oe;
-                    unit_range(cc, gridDim.x, units, &ob, &oe);
-                    if (ob >= tile_end) {
-                        break;
-                    }
-                    const float *slot = args.partial + (unsigned long long)cc * args.tile_floats;
+            // Add the partial sums in block order, two blocks' loads in flight at a time.
+            for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; cc += 2u) {
+                const float *slot0 = args.partial + (unsigned long long)cc * args.tile_floats
+                                   + (unsigned long long)c0 * kRows + lane_row;
+                const bool two = cc + 1u <= last_cc;
+                const float *slot1 = two ? slot0 + args.tile_floats : slot0;
+                float a0[kChunk];
+                float a1[kChunk];
 #pragma unroll
-                    for (uint32_t i = 0; i < kChunk; ++i) {
-                        float add = __ldcg(slot + (unsigned long long)(c0 + i) * kRows + lane_row);
-                        v[i] = __float_as_uint(__uint_as_float(v[i]) + add);
+                for (uint32_t i = 0; i < kChunk; ++i) {
+                    a0[i] = __ldcg(slot0 + (unsigned long long)i * kRows);
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < kChunk; ++i) {
+                    a1[i] = two ? __ldcg(slot1 + (unsigned long long)i * kRows) : 0.0f;
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < kChunk; ++i) {
+                    float sum = __uint_as_float(v[i]) + a0[i];
+                    if (two) {
+                        sum += a1[i];
                     }
-                    if (oe >= tile_end) {
-                        break;
-                    }
+                    v[i] = __float_as_uint(sum);
                 }
             }
             if (j < args.n) {
@@ -235,6 +264,13 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             }
         }
     }
+#ifdef Q8_EXPERIMENT
+    if (args.trace != nullptr && wq == 0u && lane == 0u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.trace[blockIdx.x * 8u + 6u] = t;
+    }
+#endif
     // The accumulator buffer is free again.
     tc_fence_before_sync();
     __syncwarp();
@@ -242,29 +278,41 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
         mbar_arrive(acc_empty_bar);
     }
     if (!owner) {
-        // Publish this warp's quarter of the partial tile.
+        // Publish this warp's quarter of the partial tile.  Every lane makes its own stores
+        // visible first; this happens at the start of a block's range, off the critical path.
         __threadfence();
         __syncwarp();
         if (lane == 0u) {
             st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
         }
     } else if (!whole) {
-        // Hand the consumed slots back for the next launch.
-        __syncwarp();
-        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
-            unsigned long long ob, oe;
-            unit_range(cc, gridDim.x, units, &ob, &oe);
-            if (ob >= tile_end) {
-                break;
-            }
-            if (lane == 0u) {
-                st_release_gpu(args.flags + 4u * cc + wq, 0u);
-            }
-            if (oe >= tile_end) {
-                break;
+        // Hand the consumed slots back for the next launch (ordered by the end of the kernel).
+        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+            const unsigned int cc = base + lane;
+            if (cc <= last_cc) {
+                *reinterpret_cast<volatile unsigned int *>(args.flags + 4u * cc + wq) = 0u;
             }
         }
     }
+}
+
+// Launch with or without the programmatic-dependent-launch attribute.
+template <typename Kernel>
+inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned int smem_bytes,
+                                      cudaStream_t stream, bool overlap, const CUtensorMap &tw,
+                                      const CUtensorMap &tx, const UmmaArgs &args)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid, 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, tw, tx, args);
 }
 
 // Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.

@@ -36,6 +36,11 @@
 
 namespace q8 {
 
+#ifdef Q8_EXPERIMENT
+static unsigned long long *g_trace_base = nullptr;
+static unsigned int g_trace_launches = 0;
+#endif
+
 // TS = true keeps the dequantised weight tile in tensor memory (the MMA reads A from TMEM):
 // the converters write it with tcgen05.st, no shared memory is spent on it, and the raw ring
 // gets the space.  TS = false keeps it in shared memory (both accumulators then fit beside a
@@ -91,8 +96,13 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t lane = threadIdx.x & 31u;
 
     // The live batch and the schedule; the same in every block.
+    // The next kernel on the stream may start its blocks as this one's finish.  Work that only
+    // reads the weights runs ahead of the kernels before this one; everything that reads x or
+    // the live batch, or writes y or the scratch slots, first waits for them to finish.
+    grid_launch_dependents();
     unsigned int m = args.m_max;
     if (args.m_dev != nullptr) {
+        grid_dependency_wait();
         unsigned int live = *args.m_dev;
         m = live < m ? live : m;
     }
@@ -187,6 +197,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         // ---------------------------------------------------------------- x tile copies
         if (lane == 0u) {
             uint32_t q = 0;
+            grid_dependency_wait();
             bool ok = true;
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
@@ -398,16 +409,14 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else {
         // ---------------------------------------------------------------- epilogue
         const uint32_t wq = warp; // 0..3: this warp reads TMEM lanes [32 wq, 32 wq + 32)
-        YT *y = static_cast<YT *>(args.y);
         uint32_t tc = 0;
+        grid_dependency_wait();
         bool ok = true;
         for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
             const uint32_t tile = (uint32_t)(u / segs);
             const uint32_t s0 = (uint32_t)(u % segs);
             const unsigned long long left = u_end - u;
             const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-            const uint32_t row_tile = tile / tok_tiles;
-            const uint32_t tok_tile = tile % tok_tiles;
             const uint32_t buf = tc & 1u;
             const uint32_t aph = (tc >> 1) & 1u;
             if (!mbar_wait(acc_full + 8u * buf, aph, abort_flag, args.status)) {
@@ -494,8 +503,8 @@ static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, cons
         }
         configured = true;
     }
-    q8_umma_kernel<NTOK, YT, TS><<<grid, kThreads, S::smem_bytes, stream>>>(tw, tx, args);
-    return cudaGetLastError();
+    return launch_tile_kernel(q8_umma_kernel<NTOK, YT, TS>, grid, S::smem_bytes, stream, args.overlap != 0u,
+                              tw, tx, args);
 }
 
 template <int NTOK>
@@ -517,7 +526,8 @@ static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const
 
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
-                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype)
+                        unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
+                        bool overlap)
 {
     if (!umma_supports(w, n, k, x, m)) {
         return cudaErrorNotSupported;
@@ -573,8 +583,11 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.m_max = m;
     args.m_dev = m_dev;
     args.y = y;
-    args.partial = scratch.partial;
-    args.flags = scratch.flags;
+    // Two sets of slots and flags alternate between launches, so that a launch whose blocks
+    // start early never meets the slots of the launch before it.
+    args.partial = scratch.partial + (unsigned long long)(set & 1u) * scratch.blocks * scratch.tile_floats;
+    args.flags = scratch.flags + (unsigned long long)(set & 1u) * scratch.blocks * 4u;
+    args.overlap = overlap ? 1u : 0u;
     args.status = scratch.status;
     args.tile_floats = scratch.tile_floats;
     args.b_bf16 = x_bf16 ? 1u : 0u;
@@ -582,6 +595,16 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     {
         const char *env = getenv("Q8_EXPERIMENT");
         args.debug = env != nullptr ? (unsigned int)atoi(env) : 0u;
+        if (getenv("Q8_TRACE") != nullptr) {
+            if (g_trace_base == nullptr) {
+                cudaMalloc((void **)&g_trace_base, 256ull * 160ull * 8ull * 8ull);
+                cudaMemset(g_trace_base, 0, 256ull * 160ull * 8ull * 8ull);
+            }
+            args.trace = g_trace_base + (unsigned long long)(g_trace_launches % 256u) * 160ull * 8ull;
+            g_trace_launches += 1;
+        } else {
+            args.trace = nullptr;
+        }
     }
 #endif
 
@@ -592,3 +615,13 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
 }
 
 } // namespace q8
+
+#ifdef Q8_EXPERIMENT
+extern "C" unsigned int q8_trace_read(unsigned long long *host)
+{
+    if (q8::g_trace_base != nullptr) {
+        cudaMemcpy(host, q8::g_trace_base, 256ull * 160ull * 8ull * 8ull, cudaMemcpyDeviceToHost);
+    }
+    return q8::g_trace_launches;
+}
+#endif

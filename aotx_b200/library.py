@@ -8,7 +8,7 @@ LIB_PATH = os.path.join(HERE, "libaotx_q8_b200.so")
 
 # every symbol include/aotx_q8_b200.h declares
 SYMBOLS = (
-    "aotx_q8_init", "aotx_q8_destroy", "aotx_q8_set_path", "aotx_q8_last_cuda_error",
+    "aotx_q8_init", "aotx_q8_destroy", "aotx_q8_set_path", "aotx_q8_set_overlap", "aotx_q8_last_cuda_error",
     "aotx_q8_device_status", "aotx_q8_dequant", "aotx_q8_matmul", "aotx_q8_moe_route",
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine",
 )
@@ -34,6 +34,7 @@ def load_library():
     lib.aotx_q8_init.argtypes = [C.POINTER(vp), i32]
     lib.aotx_q8_destroy.argtypes = [vp]
     lib.aotx_q8_set_path.argtypes = [vp, i32]
+    lib.aotx_q8_set_overlap.argtypes = [vp, i32]
     lib.aotx_q8_last_cuda_error.argtypes = [vp]
     lib.aotx_q8_device_status.argtypes = [vp, C.POINTER(u32), i32]
     lib.aotx_q8_dequant.argtypes = [vp, vp, vp, u32, u32, u32, u32, vp]

@@ -105,6 +105,9 @@ class Q8Context:
     def set_path(self, path):
         self._check(self.lib.aotx_q8_set_path(self.handle, path))
 
+    def set_overlap(self, enabled):
+        self._check(self.lib.aotx_q8_set_overlap(self.handle, int(bool(enabled))))
+
     def device_status(self, clear=True):
         status = C.c_uint32(0)
         code = self.lib.aotx_q8_device_status(self.handle, C.byref(status), int(clear))

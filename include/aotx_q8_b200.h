@@ -54,7 +54,7 @@ extern "C" {
 typedef struct aotx_q8_ctx aotx_q8_ctx;
 
 /* Make / release the per-device context: SM count, the scratch tiles and flags of the
- * streaming kernel (about 20 MB) and a device status word.  Call outside stream capture.
+ * streaming kernel (about 40 MB) and a device status word.  Call outside stream capture.
  * No counterpart in the reference, whose kernels need no scratch; it takes the place of the
  * buffers that cuda/model/model_host.cu:95-153 makes before its capture starts. */
 int aotx_q8_init(aotx_q8_ctx **ctx, int device);
@@ -62,6 +62,14 @@ int aotx_q8_destroy(aotx_q8_ctx *ctx);
 
 /* Choose the kernel family for later calls on this context (tests and measurements). */
 int aotx_q8_set_path(aotx_q8_ctx *ctx, int path);
+
+/* Let consecutive products on one stream overlap (default on).  The tensor-core kernels are
+ * launched as programmatic dependents: the blocks of a product may start, and stream weight
+ * bytes, while the work before it on the stream is still finishing; they wait for that work
+ * before they read x or the live batch or write y.  The weight tensor itself must therefore
+ * not be written by the operation just before the product on the same stream; switch the
+ * overlap off around such a sequence.  No counterpart in the reference. */
+int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled);
 
 /* The last CUDA error code an entry point of this context saw (cudaError_t as int). */
 int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx);
