@@ -204,10 +204,11 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
         return AOTX_Q8_ERR_ARGUMENT;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    /* One MMA takes both operands in one 16-bit format: binary16 weights against bfloat16
-     * activations raise an illegal-instruction fault on sm_100a.  bfloat16 activations go to
-     * the general kernel. */
-    bool tensor_ok = x_dtype == AOTX_Q8_F16 && q8::umma_supports(w, n, k, x, m);
+    /* One MMA takes both operands in one 16-bit format (binary16 weights against bfloat16
+     * activations raise an illegal-instruction fault on sm_100a), so for bfloat16 activations
+     * the decode kernel turns the x tiles into binary16 in shared memory and the 256-row
+     * kernel dequantises the weights to bfloat16. */
+    bool tensor_ok = q8::umma_supports(w, n, k, x, m);
     if (ctx->path == AOTX_Q8_PATH_TENSOR && !tensor_ok) {
         return AOTX_Q8_ERR_UNSUPPORTED;
     }

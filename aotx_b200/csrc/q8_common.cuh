@@ -55,6 +55,42 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t flipped, __half2 d2)
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// The same two weights as bfloat16: float(q) * float(d) is exact in float, so the pack is the
+// single rounding bfloat16(q * d).  Used where the activations are bfloat16, because one MMA
+// takes both operands in one 16-bit format.
+template <int HIGH>
+__device__ __forceinline__ uint32_t dequant_pair_bf16(uint32_t flipped, float d)
+{
+    uint32_t magic = prmt(flipped, 0x64646464u, HIGH ? 0x4342u : 0x4140u);
+    __half2 v = *reinterpret_cast<__half2 *>(&magic);
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480)); // 1152.0
+    float2 q = __half22float2(__hsub2(v, bias));
+    uint32_t out;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(q.y * d), "f"(q.x * d));
+    return out;
+}
+
+// Eight bfloat16 values in shared memory become eight binary16 values in place.  Every
+// bfloat16 of magnitude between 2^-14 and 65504 converts exactly; larger ones saturate to the
+// largest half, smaller ones round to the half subnormals.
+__device__ __forceinline__ void bf16_chunk_to_f16_inplace(uint32_t addr)
+{
+    uint32_t w[4];
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "r"(addr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float lo = __uint_as_float(w[i] << 16);
+        float hi = __uint_as_float(w[i] & 0xFFFF0000u);
+        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(hi), "f"(lo));
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3])
+                 : "memory");
+}
+
 __device__ __forceinline__ __half dequant_one(int q, __half d)
 {
     return __float2half_rn((float)q * __half2float(d));

@@ -218,7 +218,8 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (warp == kMmaWarp) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0u) {
-            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, args.b_bf16);
+            // bfloat16 activations were turned into binary16 in shared memory by the converters
+            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
             uint32_t g = 0;
             uint32_t tc = 0;
             bool ok = true;
@@ -335,6 +336,20 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                     tmem_st_wait();
                     tc_fence_before_sync();
+                }
+                if (args.b_bf16 != 0u) {
+                    // One MMA takes both operands in one format: turn this segment's x tile into
+                    // binary16 where it lies (the swizzle moves whole 16-byte chunks, so the
+                    // conversion is chunk by chunk whatever the layout).
+                    if (!mbar_wait(x_full + 8u * st, ph, abort_flag, args.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t x_seg = x_base + st * S::x_seg_bytes;
+                    for (uint32_t c = cw * 32u + lane; c < S::x_seg_bytes / 16u; c += 256u) {
+                        bf16_chunk_to_f16_inplace(x_seg + 16u * c);
+                    }
+                    fence_proxy_async_smem();
                 }
                 __syncwarp();
                 if (lane == 0u) {

@@ -55,15 +55,13 @@ __device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks, 
 // chunks of 16 bytes in the swizzled operand layout.  `raw` holds 36 words: bytes
 // [H * 128, H * 128 + 144) of the thread's 272-byte row segment.  The thread's four blocks
 // start at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
-template <int H, int JJ>
+template <int H, int JJ, bool BF>
 __device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_t a_stage, uint32_t row)
 {
     const uint32_t row_base = a_stage + (row >> 3) * 1024u + (row & 7u) * 128u;
     const uint32_t phase = row & 7u;
 #pragma unroll
     for (int jb = 0; jb < 2; ++jb) {
-        constexpr int kDummy = 0;
-        (void)kDummy;
         const int lb = 2 * JJ + jb;
         const int byte_off = (H ? 8 : 0) + 34 * lb;
         const int wi = byte_off / 4;
@@ -71,6 +69,8 @@ __device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_
         // scale in both halves of a word
         uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
         __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
+        const float d = __low2float(d2);
+        (void)d;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t out[4];
@@ -81,12 +81,21 @@ __device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_
                     // payload starts at the next word boundary
                     const int word = wi + 1 + p / 2;
                     uint32_t flipped = raw[word] ^ 0x80808080u;
-                    out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                    if constexpr (BF) {
+                        out[pp] = (p % 2) ? dequant_pair_bf16<1>(flipped, d) : dequant_pair_bf16<0>(flipped, d);
+                    } else {
+                        out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                    }
                 } else {
                     // payload starts in the high half of the scale's word
                     const int word = wi + (p + 1) / 2;
                     uint32_t flipped = raw[word] ^ 0x80808080u;
-                    out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                    if constexpr (BF) {
+                        out[pp] = ((p + 1) % 2) ? dequant_pair_bf16<1>(flipped, d)
+                                                : dequant_pair_bf16<0>(flipped, d);
+                    } else {
+                        out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                    }
                 }
             }
             const uint32_t kc = (uint32_t)(4 * jb + c);

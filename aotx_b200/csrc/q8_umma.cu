@@ -236,7 +236,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else if (warp == kMmaWarp) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0u) {
-            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, args.b_bf16);
+            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, args.b_bf16, args.b_bf16);
             uint32_t q = 0;
             uint32_t tc = 0;
             bool ok = true;
@@ -383,17 +383,32 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         tc_fence_before_sync();
                     } else {
                         const uint32_t a_stage = a_base + st * kAStageBytes;
-                        if (half_id == 0u) {
-                            if (jj == 0u) {
-                                convert_stage<0, 0>(raw, a_stage, row);
+                        if (args.b_bf16 != 0u) {
+                            // bfloat16 activations: the weights go to bfloat16 as well
+                            if (half_id == 0u) {
+                                if (jj == 0u) {
+                                    convert_stage<0, 0, true>(raw, a_stage, row);
+                                } else {
+                                    convert_stage<0, 1, true>(raw, a_stage, row);
+                                }
                             } else {
-                                convert_stage<0, 1>(raw, a_stage, row);
+                                if (jj == 0u) {
+                                    convert_stage<1, 0, true>(raw, a_stage, row);
+                                } else {
+                                    convert_stage<1, 1, true>(raw, a_stage, row);
+                                }
+                            }
+                        } else if (half_id == 0u) {
+                            if (jj == 0u) {
+                                convert_stage<0, 0, false>(raw, a_stage, row);
+                            } else {
+                                convert_stage<0, 1, false>(raw, a_stage, row);
                             }
                         } else {
                             if (jj == 0u) {
-                                convert_stage<1, 0>(raw, a_stage, row);
+                                convert_stage<1, 0, false>(raw, a_stage, row);
                             } else {
-                                convert_stage<1, 1>(raw, a_stage, row);
+                                convert_stage<1, 1, false>(raw, a_stage, row);
                             }
                         }
                         fence_proxy_async_smem();

@@ -32,11 +32,11 @@ WORKLOADS = {
     # name: (rows of x, [(projection, k, n)], x dtype, y dtype)
     "decode_m32_llama3_8b_layer": (32, [("qkv", 4096, 6144), ("o", 4096, 4096),
                                         ("gate_up", 4096, 28672), ("down", 14336, 4096)],
-                                   "float16", "bfloat16"),
+                                   "bfloat16", "bfloat16"),
     "gemv_m1_4096": (1, [("w", 4096, 4096)], "float16", "float16"),
     "prefill_m2048_llama3_8b_layer": (2048, [("qkv", 4096, 6144), ("o", 4096, 4096),
                                              ("gate_up", 4096, 28672), ("down", 14336, 4096)],
-                                      "float16", "bfloat16"),
+                                      "bfloat16", "bfloat16"),
 }
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer"}
 
@@ -268,7 +268,7 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 operands, f32 sums",
         "data": "synthetic",
         "config": {"workload": args.workload, "rows": m, "x": x_name, "y": y_name,
                    "projections": {name: [k, n] for name, k, n in projections},

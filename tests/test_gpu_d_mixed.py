@@ -1,5 +1,5 @@
-"""bfloat16 activations against binary16 weights in one MMA (mixed operand formats), and
-the benchmark's decode and prefill shapes."""
+"""bfloat16 activations through both kernel families, and the benchmark's decode and prefill
+shapes."""
 import numpy as np
 import pytest
 
@@ -17,8 +17,8 @@ def ctx():
     c.close()
 
 
-@pytest.mark.parametrize("path_name", ["PATH_GENERAL", "PATH_AUTO"])
-@pytest.mark.parametrize("n,k,m", [(256, 512, 1), (640, 1024, 32), (512, 768, 130)])
+@pytest.mark.parametrize("path_name", ["PATH_GENERAL", "PATH_TENSOR"])
+@pytest.mark.parametrize("n,k,m", [(256, 512, 1), (640, 1024, 32), (512, 768, 130), (384, 1024, 300)])
 def test_bf16_activations(ctx, oracle, path_name, n, k, m):
     import aotx_b200
     torch = torch_mod()
