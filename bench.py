@@ -34,11 +34,13 @@ WORKLOADS = {
                                         ("gate_up", 4096, 28672), ("down", 14336, 4096)],
                                    "bfloat16", "bfloat16"),
     "gemv_m1_4096": (1, [("w", 4096, 4096)], "float16", "float16"),
+    "decode_m32_gate_up": (32, [("gate_up", 4096, 28672)], "bfloat16", "bfloat16"),
+    "prefill_m2048_gate_up": (2048, [("gate_up", 4096, 28672)], "bfloat16", "bfloat16"),
     "prefill_m2048_llama3_8b_layer": (2048, [("qkv", 4096, 6144), ("o", 4096, 4096),
                                              ("gate_up", 4096, 28672), ("down", 14336, 4096)],
                                       "bfloat16", "bfloat16"),
 }
-TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer"}
+TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up"}
 
 
 def measured_peaks():
