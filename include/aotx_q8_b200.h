@@ -130,6 +130,20 @@ int aotx_q8_moe_combine(aotx_q8_ctx *ctx, void *stream, const float *proj, const
                         const uint32_t *ids, uint32_t tokens, const uint32_t *tokens_dev,
                         uint32_t hidden, uint32_t experts, uint32_t used, void *out, int out_dtype);
 
+/* The product without a context, for callers that cannot allocate device memory (a frozen
+ * memory plan, a process whose device footprint must not grow, a plug-in that only gets a
+ * stream and buffers).  Same arguments and result as aotx_q8_matmul; the scratch the kernel
+ * needs is a fixed array inside the library (about 5.3 MB on every GPU that loads it, held
+ * until the process exits), which limits a call to m <= 64 rows of x: more returns
+ * AOTX_Q8_ERR_WORKSPACE and enqueues nothing.  It calls no cudaMalloc or cudaFree.  The first
+ * call on each device looks the array up (cudaGetSymbolAddress): make that call before any
+ * stream capture.  All calls share the array and clear the part that must start at zero; two
+ * calls that overlap on the GPU (different streams, no ordering) race on it.
+ * It has no counterpart in the reference. */
+int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type, uint32_t n, uint32_t k,
+                          const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev, void *y,
+                          int y_dtype);
+
 #ifdef __cplusplus
 }
 #endif
