@@ -243,10 +243,7 @@ extern "C" int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f
 
 extern "C" size_t aotx_q8_moe_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidden, uint32_t ffn)
 {
-    size_t pairs = (size_t)tokens * used;
-    size_t act = round_up(pairs * ffn * sizeof(unsigned short), 256u);
-    size_t proj = round_up(pairs * hidden * sizeof(float), 256u);
-    return act + proj;
+    return q8::moe_workspace_layout(tokens, used, hidden, ffn, kMaxExperts).bytes;
 }
 
 extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up,
@@ -261,8 +258,8 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
-    if (experts == 0u || used == 0u || used > experts || hidden == 0u || ffn == 0u || (hidden % 32u) != 0u
-        || (ffn % 32u) != 0u || !dtype_out(out_dtype)) {
+    if (experts == 0u || experts > kMaxExperts || used == 0u || used > experts || hidden == 0u || ffn == 0u
+        || (hidden % 32u) != 0u || (ffn % 32u) != 0u || !dtype_out(out_dtype)) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
     if (tokens == 0u) {
@@ -272,17 +269,26 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
         || ids == nullptr || out == nullptr || !aligned(x_f16, 4u)) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    if (workspace == nullptr || !aligned(workspace, 256u)
-        || workspace_bytes < aotx_q8_moe_workspace_bytes(tokens, used, hidden, ffn)) {
+    q8::MoeWorkspace ws = q8::moe_workspace_layout(tokens, used, hidden, ffn, kMaxExperts);
+    if (workspace == nullptr || !aligned(workspace, 256u) || workspace_bytes < ws.bytes) {
         return AOTX_Q8_ERR_WORKSPACE;
     }
-    size_t pairs = (size_t)tokens * used;
     unsigned char *base = static_cast<unsigned char *>(workspace);
-    void *act = base;
-    float *proj = reinterpret_cast<float *>(base + round_up(pairs * ffn * sizeof(unsigned short), 256u));
+    float *proj = reinterpret_cast<float *>(base + ws.proj);
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, tokens,
-                                                   tokens_dev, used, act, proj);
+    bool grouped = q8::moe_grouped_supports(w_gate, w_up, w_down, x_f16, hidden, ffn, experts);
+    if (ctx->path == AOTX_Q8_PATH_TENSOR && !grouped) {
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    cudaError_t err;
+    if (grouped && ctx->path != AOTX_Q8_PATH_GENERAL) {
+        err = q8::launch_moe_grouped(s, ctx->scratch, ctx->sm_count, &ctx->launches, ctx->overlap != 0, w_gate,
+                                     w_up, w_down, experts, hidden, ffn, x_f16, ids, tokens, tokens_dev, used,
+                                     base, ws);
+    } else {
+        err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, tokens, tokens_dev,
+                                           used, base + ws.act, proj);
+    }
     if (err == cudaSuccess) {
         err = q8::launch_expert_sum(s, proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out,
                                     out_dtype);

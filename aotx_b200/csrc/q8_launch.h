@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 
 namespace q8 {
 
@@ -46,6 +47,31 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
                         bool overlap);
+
+// Grouped mode of the decode-regime kernel: tiles from a device table (see q8_tile.cuh).
+struct GroupTile;
+cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                                const void *w_stacked, unsigned int total_rows, unsigned int k,
+                                const void *x_sorted, unsigned int x_rows, unsigned int ntok,
+                                const GroupTile *tiles, const unsigned int *count_dev, unsigned int max_tiles,
+                                const unsigned int *row_map, void *y, unsigned int ldy, int y_dtype,
+                                unsigned int set, bool overlap);
+
+// Routed experts as grouped products (q8_moe.cu).  Offsets are bytes into the workspace.
+struct MoeWorkspace {
+    size_t act, proj, sorted_pair, counts, tiles_feed, tiles_down, x_sorted, gate, up, bytes;
+    unsigned int max_feed, max_down;
+};
+MoeWorkspace moe_workspace_layout(unsigned int tokens, unsigned int used, unsigned int hidden,
+                                  unsigned int ffn, unsigned int experts);
+bool moe_grouped_supports(const void *w_gate, const void *w_up, const void *w_down, const void *x,
+                          unsigned int hidden, unsigned int ffn, unsigned int experts);
+cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                               unsigned int *launches, bool overlap, const void *w_gate, const void *w_up,
+                               const void *w_down, unsigned int experts, unsigned int hidden,
+                               unsigned int ffn, const void *x, const unsigned int *ids, unsigned int tokens,
+                               const unsigned int *tokens_dev, unsigned int used, unsigned char *workspace,
+                               const MoeWorkspace &ws);
 
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m);
 

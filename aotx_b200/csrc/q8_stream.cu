@@ -88,12 +88,19 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t segs = args.k / kSegK;
     const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
     const uint32_t tok_tiles = (m + (uint32_t)NTOK - 1u) / (uint32_t)NTOK;
-    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
-    unsigned long long u_begin, u_end;
-    unit_range(blockIdx.x, gridDim.x, units, &u_begin, &u_end);
-    if (u_begin >= u_end) {
+    unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
+    if (args.group_tiles != nullptr) {
+        // the table was built by the kernel before this one on the stream
+        grid_dependency_wait();
+        units = (unsigned long long)(*args.group_count) * segs;
+    }
+    // No more blocks than units take part, so that every block in the schedule has work.
+    const unsigned int blocks = units < gridDim.x ? (unsigned int)units : gridDim.x;
+    if (blockIdx.x >= blocks) {
         return;
     }
+    unsigned long long u_begin, u_end;
+    unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
@@ -146,7 +153,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t s0 = (uint32_t)(u % segs);
                 const unsigned long long left = u_end - u;
                 const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t row_tile = tile / tok_tiles;
+                const uint32_t w_row = tile_place<NTOK>(args, tile, tok_tiles, m).w_row;
                 for (uint32_t s = s0; s < s1; ++s, ++g) {
                     const uint32_t st = g % S::raw_stages;
                     const uint32_t ph = (g / S::raw_stages) & 1u;
@@ -162,7 +169,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #endif
                     mbar_expect_tx(raw_full + 8u * st, kRawStageBytes);
                     tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
-                                (int)(s * kSegWords), (int)(row_tile * kRows));
+                                (int)(s * kSegWords), (int)w_row);
                 }
                 u += (s1 - s0);
             }
@@ -185,7 +192,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t s0 = (uint32_t)(u % segs);
                 const unsigned long long left = u_end - u;
                 const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t tok_tile = tile % tok_tiles;
+                const uint32_t tok0 = tile_place<NTOK>(args, tile, tok_tiles, m).i0;
                 for (uint32_t s = s0; s < s1; ++s, ++g) {
                     const uint32_t st = g % S::depth;
                     const uint32_t ph = (g / S::depth) & 1u;
@@ -204,7 +211,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     for (uint32_t j = 0; j < kSubs; ++j) {
                         tma_load_2d(x_base + st * S::x_seg_bytes + j * S::x_sub_bytes, &tmap_x,
                                     x_full + 8u * st, (int)(s * kSegK + j * kSubK),
-                                    (int)(tok_tile * (uint32_t)NTOK));
+                                    (int)tok0);
                     }
                 }
                 u += (s1 - s0);
@@ -377,7 +384,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
             tc_fence_after_sync();
             epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, s0, s1, segs,
-                                     tok_tiles, units, m, abort_flag, acc_empty + 8u * buf);
+                                     tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }
     }

@@ -25,6 +25,23 @@ constexpr uint32_t kWeightWarp = 12;
 constexpr uint32_t kInputWarp = 13;
 constexpr uint32_t kMmaWarp = 14;
 
+struct GroupTile {
+    unsigned int w_row;     // first row of the tile in the stacked weight tensor
+    unsigned int j0;        // first column of y the tile produces
+    unsigned int j_limit;   // columns of y of this expert's tensor (store j < j_limit)
+    unsigned int tok0;      // first row of the sorted activations
+    unsigned int tok_limit; // one past the last row that belongs to the tile
+};
+
+// Where a tile reads and writes.
+struct TilePlace {
+    unsigned int w_row;
+    unsigned int j0;
+    unsigned int j_limit;
+    unsigned int i0;
+    unsigned int i_limit;
+};
+
 struct UmmaArgs {
     unsigned int n;
     unsigned int k;
@@ -37,6 +54,13 @@ struct UmmaArgs {
     unsigned long long tile_floats;
     unsigned int b_bf16;
     unsigned int overlap; // launched with the programmatic-dependent-launch attribute
+    // Grouped mode (routed experts): the tiles come from a table built on the device, one
+    // entry per (expert, token tile, row tile); w is then all experts' rows stacked, x the
+    // activation rows sorted by expert, and a result row i goes to y row row_map[i].
+    const GroupTile *group_tiles;      // null outside grouped mode
+    const unsigned int *group_count;   // device word: number of table entries
+    const unsigned int *row_map;       // may be null
+    unsigned int ldy;                  // row stride of y in elements
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null
@@ -152,20 +176,44 @@ __device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
 // One piece of a tile is in the accumulator at `taddr_acc` (column base of the buffer).  The
 // warp `wq` of the four epilogue warps owns TMEM lanes [32 wq, 32 wq + 32).  `chunk` columns are
 // read per TMEM load.
+template <int NTOK>
+__device__ __forceinline__ TilePlace tile_place(const UmmaArgs &args, uint32_t tile, uint32_t tok_tiles,
+                                                unsigned int m)
+{
+    TilePlace place;
+    if (args.group_tiles != nullptr) {
+        const GroupTile entry = args.group_tiles[tile];
+        place.w_row = entry.w_row;
+        place.j0 = entry.j0;
+        place.j_limit = entry.j_limit;
+        place.i0 = entry.tok0;
+        place.i_limit = entry.tok_limit;
+    } else {
+        const uint32_t row_tile = tile / tok_tiles;
+        const uint32_t tok_tile = tile % tok_tiles;
+        place.w_row = row_tile * kRows;
+        place.j0 = row_tile * kRows;
+        place.j_limit = args.n;
+        place.i0 = tok_tile * (uint32_t)NTOK;
+        place.i_limit = m;
+    }
+    return place;
+}
+
 template <int NTOK, typename YT>
 __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t taddr_acc, uint32_t wq,
                                                uint32_t lane, uint32_t tile, uint32_t s0, uint32_t s1,
                                                uint32_t segs, uint32_t tok_tiles,
-                                               unsigned long long units, unsigned int m,
-                                               volatile uint32_t *abort_flag, uint32_t acc_empty_bar)
+                                               unsigned long long units, unsigned int blocks,
+                                               unsigned int m, volatile uint32_t *abort_flag,
+                                               uint32_t acc_empty_bar)
 {
     constexpr uint32_t kChunk = NTOK < 32 ? 16 : 32;
     YT *y = static_cast<YT *>(args.y);
-    const uint32_t row_tile = tile / tok_tiles;
-    const uint32_t tok_tile = tile % tok_tiles;
+    const TilePlace place = tile_place<NTOK>(args, tile, tok_tiles, m);
     const uint32_t lane_row = wq * 32u + lane;
-    const uint32_t j = row_tile * kRows + lane_row;      // row of w = column of y
-    const uint32_t i0 = tok_tile * (uint32_t)NTOK;       // first row of x of the tile
+    const uint32_t j = place.j0 + lane_row;              // row of w = column of y
+    const uint32_t i0 = place.i0;                        // first row of x of the tile
     const uint32_t taddr = taddr_acc + ((wq * 32u) << 16);
     // A tile that is cut between blocks belongs to the block that holds its first
     // segment.  That is the owner's last piece of work, while the other holders meet
@@ -187,9 +235,9 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     // The other holders of this tile are the blocks right after this one, up to `last_cc`.
     unsigned int last_cc = blockIdx.x;
     if (owner && !whole) {
-        for (unsigned int cc = blockIdx.x + 1u; cc < gridDim.x; ++cc) {
+        for (unsigned int cc = blockIdx.x + 1u; cc < blocks; ++cc) {
             unsigned long long ob, oe;
-            unit_range(cc, gridDim.x, units, &ob, &oe);
+            unit_range(cc, blocks, units, &ob, &oe);
             if (ob >= tile_end) {
                 break;
             }
@@ -262,12 +310,13 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                     v[i] = __float_as_uint(sum);
                 }
             }
-            if (j < args.n) {
+            if (j < place.j_limit) {
 #pragma unroll
                 for (uint32_t i = 0; i < kChunk; ++i) {
                     const uint32_t row_x = i0 + c0 + i;
-                    if (row_x < m) {
-                        store_out<YT>(y, (size_t)row_x * args.n + j, __uint_as_float(v[i]));
+                    if (row_x < place.i_limit) {
+                        const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
+                        store_out<YT>(y, (size_t)row_y * args.ldy + j, __uint_as_float(v[i]));
                     }
                 }
             }

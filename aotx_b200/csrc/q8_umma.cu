@@ -113,11 +113,13 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
     const uint32_t tok_tiles = (m + (uint32_t)NTOK - 1u) / (uint32_t)NTOK;
     const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
-    unsigned long long u_begin, u_end;
-    unit_range(blockIdx.x, gridDim.x, units, &u_begin, &u_end);
-    if (u_begin >= u_end) {
+    // No more blocks than units take part, so that every block in the schedule has work.
+    const unsigned int blocks = units < gridDim.x ? (unsigned int)units : gridDim.x;
+    if (blockIdx.x >= blocks) {
         return;
     }
+    unsigned long long u_begin, u_end;
+    unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
@@ -440,7 +442,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             }
             tc_fence_after_sync();
             epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, s0, s1, segs,
-                                     tok_tiles, units, m, abort_flag, acc_empty + 8u * buf);
+                                     tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }
     }
@@ -603,6 +605,10 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.partial = scratch.partial + (unsigned long long)(set & 1u) * scratch.blocks * scratch.tile_floats;
     args.flags = scratch.flags + (unsigned long long)(set & 1u) * scratch.blocks * 4u;
     args.overlap = overlap ? 1u : 0u;
+    args.group_tiles = nullptr;
+    args.group_count = nullptr;
+    args.row_map = nullptr;
+    args.ldy = n;
     args.status = scratch.status;
     args.tile_floats = scratch.tile_floats;
     args.b_bf16 = x_bf16 ? 1u : 0u;
@@ -627,6 +633,74 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
         return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
     }
     return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
+}
+
+cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                                const void *w_stacked, unsigned int total_rows, unsigned int k,
+                                const void *x_sorted, unsigned int x_rows, unsigned int ntok,
+                                const GroupTile *tiles, const unsigned int *count_dev, unsigned int max_tiles,
+                                const unsigned int *row_map, void *y, unsigned int ldy, int y_dtype,
+                                unsigned int set, bool overlap)
+{
+    EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr || (k % kSegK) != 0u || ntok > 128u) {
+        return cudaErrorNotSupported;
+    }
+    if (max_tiles == 0u || x_rows == 0u) {
+        return cudaSuccess;
+    }
+    const unsigned long long row_b = row_bytes(k);
+    CUtensorMap tw, tx;
+    {
+        cuuint64_t dims[2] = {row_b / 4ull, total_rows};
+        cuuint64_t strides[1] = {row_b};
+        cuuint32_t box[2] = {kSegWords, kRows};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(w_stacked), dims, strides,
+                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        cuuint64_t dims[2] = {k, x_rows};
+        cuuint64_t strides[1] = {(cuuint64_t)k * 2ull};
+        cuuint32_t box[2] = {kSubK, ntok};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_sorted), dims, strides,
+                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    const unsigned long long units = (unsigned long long)max_tiles * (k / kSegK);
+    unsigned int grid = sm_count < scratch.blocks ? sm_count : scratch.blocks;
+    if (units < grid) {
+        grid = (unsigned int)units;
+    }
+    UmmaArgs args;
+    args.n = total_rows;
+    args.k = k;
+    args.m_max = x_rows;
+    args.m_dev = nullptr;
+    args.y = y;
+    args.partial = scratch.partial + (unsigned long long)(set & 1u) * scratch.blocks * scratch.tile_floats;
+    args.flags = scratch.flags + (unsigned long long)(set & 1u) * scratch.blocks * 4u;
+    args.status = scratch.status;
+    args.tile_floats = scratch.tile_floats;
+    args.b_bf16 = 0u;
+    args.overlap = overlap ? 1u : 0u;
+    args.group_tiles = tiles;
+    args.group_count = count_dev;
+    args.row_map = row_map;
+    args.ldy = ldy;
+#ifdef Q8_EXPERIMENT
+    args.debug = 0u;
+    args.trace = nullptr;
+#endif
+    return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
 }
 
 } // namespace q8

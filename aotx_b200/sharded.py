@@ -1,0 +1,145 @@
+"""The two places where the Q8_0 path shards over the GPUs of one box.
+
+The reference is single-GPU, so nothing here mirrors reference code; the single-GPU results
+are the contract.  One process per GPU, `torch.distributed` (NCCL over NVLink on GPUs, gloo in
+the CPU tests) for the exchange steps.
+
+* `ColumnSplit`: a large projection `y = x . w^T` split by rows of w (= columns of y).  Rows
+  are independent and contiguous in the block layout, so a rank's shard is a plain byte range
+  of the tensor; x is replicated; one all-gather of the y slices ends the step.
+* `ExpertParallel`: routed experts with whole experts placed on ranks.  Tokens are sharded,
+  routing is local, (token, rank) pairs travel to the expert's owner in one all-to-all, the
+  owner runs the grouped expert products, the float results travel back in a second
+  all-to-all, and the home rank forms the rank-ordered weighted sum exactly as on one GPU.
+
+The compute step is injected (`product` / `experts`) so that the exchange logic runs on CPU
+ranks in the tests; on GPUs it is the library's own kernels.
+"""
+
+
+def shard_rows(n, world, rank):
+    """Rows [first, last) of an n-row tensor owned by `rank`: as even as possible, the first
+    n % world ranks hold one row more."""
+    base, extra = divmod(n, world)
+    first = rank * base + min(rank, extra)
+    return first, first + base + (1 if rank < extra else 0)
+
+
+def expert_owner(expert, experts, world):
+    """The rank that holds `expert` under the same even split."""
+    base, extra = divmod(experts, world)
+    edge = extra * (base + 1)
+    if expert < edge:
+        return expert // (base + 1)
+    return extra + (expert - edge) // base
+
+
+def _dist():
+    import torch.distributed as dist
+    return dist
+
+
+class ColumnSplit:
+    """y[m][n] = x[m][k] . w[n][k]^T with the rows of w split over the ranks.
+
+    `product(x, m) -> y_local[m][rows]` computes this rank's slice (on GPUs:
+    `Q8Context.matmul` on the rank's byte range of w)."""
+
+    def __init__(self, n, k, world, rank, product, group=None):
+        self.n, self.k, self.world, self.rank = n, k, world, rank
+        self.first, self.last = shard_rows(n, world, rank)
+        self.rows = self.last - self.first
+        self.max_rows = shard_rows(n, world, 0)[1]
+        self.product = product
+        self.group = group
+
+    @staticmethod
+    def shard_bytes(n, k, world, rank):
+        """Byte range of this rank's rows in the Q8_0 tensor."""
+        first, last = shard_rows(n, world, rank)
+        stride = (k // 32) * 34
+        return first * stride, last * stride
+
+    def matmul(self, x, m, out=None):
+        """Returns y[m][n], the same on every rank."""
+        import torch
+        y_local = self.product(x, m)
+        if self.world == 1:
+            return y_local
+        even = self.n % self.world == 0
+        if even:
+            padded = y_local.contiguous()
+        else:
+            padded = y_local.new_zeros((m, self.max_rows))
+            padded[:, :self.rows] = y_local
+        gathered = y_local.new_empty((self.world, m, self.max_rows))
+        _dist().all_gather(list(gathered.unbind(0)), padded, group=self.group)
+        if out is None:
+            out = y_local.new_empty((m, self.n))
+        for r in range(self.world):
+            first, last = shard_rows(self.n, self.world, r)
+            out[:, first:last] = gathered[r, :, :last - first]
+        return out
+
+
+class ExpertParallel:
+    """Routed feed-forward step with experts placed on ranks.
+
+    `experts(x_pairs, local_expert_of_pair) -> proj[pairs][hidden]` (float) runs the expert
+    products of this rank for the pairs it received (on GPUs: `Q8Context.moe_ffn` with one
+    selection per row and weight 1).  `combine(proj[tokens][used][hidden], prob, ids) -> out`
+    is the rank-ordered weighted sum (`Q8Context.moe_combine`)."""
+
+    def __init__(self, experts_total, used, hidden, world, rank, experts, combine, group=None):
+        self.experts_total, self.used, self.hidden = experts_total, used, hidden
+        self.world, self.rank = world, rank
+        self.first, self.last = shard_rows(experts_total, world, rank)
+        self.experts = experts
+        self.combine = combine
+        self.group = group
+
+    def ffn(self, x, prob, ids):
+        """x: [tokens_local][hidden] half, prob: [tokens_local][experts_total] float,
+        ids: [tokens_local][used] int32.  Returns out[tokens_local][hidden]."""
+        import torch
+        dist = _dist()
+        tokens = x.shape[0]
+        pairs = tokens * self.used
+        flat = ids.reshape(-1).long()
+        owner = torch.empty_like(flat)
+        base, extra = divmod(self.experts_total, self.world)
+        edge = extra * (base + 1)
+        low = flat < edge
+        owner[low] = flat[low] // (base + 1)
+        if base > 0:
+            owner[~low] = extra + (flat[~low] - edge) // base
+        # pairs grouped by destination rank, stable, so that the way back is the inverse
+        order = torch.argsort(owner, stable=True)
+        send_counts = torch.bincount(owner, minlength=self.world)
+        recv_counts = torch.empty_like(send_counts)
+        if self.world > 1:
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        else:
+            recv_counts.copy_(send_counts)
+        send_list = send_counts.tolist()
+        recv_list = recv_counts.tolist()
+        rows_out = x[(order // self.used)]
+        expert_out = flat[order].to(torch.int32)
+        got = int(sum(recv_list))
+        rows_in = x.new_empty((got, self.hidden))
+        expert_in = expert_out.new_empty((got,))
+        if self.world > 1:
+            dist.all_to_all_single(rows_in, rows_out.contiguous(), recv_list, send_list, group=self.group)
+            dist.all_to_all_single(expert_in, expert_out.contiguous(), recv_list, send_list, group=self.group)
+        else:
+            rows_in.copy_(rows_out)
+            expert_in.copy_(expert_out)
+        proj_in = self.experts(rows_in, expert_in - self.first)
+        proj_back = proj_in.new_empty((pairs, self.hidden))
+        if self.world > 1:
+            dist.all_to_all_single(proj_back, proj_in.contiguous(), send_list, recv_list, group=self.group)
+        else:
+            proj_back.copy_(proj_in)
+        proj = proj_back.new_empty((pairs, self.hidden))
+        proj[order] = proj_back
+        return self.combine(proj.reshape(tokens, self.used, self.hidden), prob, ids)

@@ -80,7 +80,8 @@ def _moe_case(oracle, tokens, experts, used, hidden, ffn, seed):
 
 
 @pytest.mark.parametrize("tokens,experts,used,hidden,ffn", [(1, 5, 3, 512, 64), (64, 5, 3, 512, 96),
-                                                            (33, 16, 4, 256, 256)])
+                                                            (33, 16, 4, 256, 256), (200, 7, 2, 512, 256),
+                                                            (64, 128, 8, 2048, 768)])
 def test_moe_ffn_matches_oracle(ctx, oracle, tokens, experts, used, hidden, ffn):
     torch = torch_mod()
     wg, wu, wd, x, router = _moe_case(oracle, tokens, experts, used, hidden, ffn, 40 + tokens)
@@ -116,3 +117,30 @@ def test_ordered_sum_bit_exact(ctx, oracle):
         got = out.cpu().numpy()
         assert np.array_equal(got[:tokens].view(np.uint32), want.view(np.uint32))
         assert (got[tokens:] == GUARD).all()
+
+
+def test_grouped_path_equals_per_pair_path_at_full_size(ctx, oracle):
+    """The benchmark's routed-expert shape (512 tokens, 128 experts, top 8, 2048 -> 768 -> 2048):
+    the grouped tensor-core path and the per-pair path give the same result within the product
+    bound, and the same selections feed both."""
+    import aotx_b200
+    torch = torch_mod()
+    tokens, experts, used, hidden, ffn = 512, 128, 8, 2048, 768
+    wg, wu, wd, x, router = _moe_case(oracle, tokens, experts, used, hidden, ffn, 900)
+    xd = dev(x)
+    prob, ids = ctx.moe_route(xd, dev(router), used)
+    dwg, dwu, dwd = dev_weights(wg), dev_weights(wu), dev_weights(wd)
+    outs = []
+    for path in (aotx_b200.PATH_TENSOR, aotx_b200.PATH_GENERAL):
+        ctx.set_path(path)
+        try:
+            outs.append(ctx.moe_ffn(dwg, dwu, dwd, experts, hidden, ffn, xd, prob, ids).cpu().numpy())
+        finally:
+            ctx.set_path(0)
+    torch.cuda.synchronize()
+    a, b = outs
+    assert np.isfinite(a).all()
+    assert np.abs(a - b).max() <= 1e-2 * np.abs(b).max() + 1e-3
+    counts = np.bincount(ids.cpu().numpy().reshape(-1), minlength=experts)
+    assert counts.sum() == tokens * used and counts.max() > 32
+    assert ctx.device_status() == 0
