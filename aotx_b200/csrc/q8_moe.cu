@@ -7,6 +7,8 @@
 // (cuda/model/expert_matrix.cu:8-27, loop cuda/model/experts_host.cu:99-111), which re-reads an
 // expert's weights for every token routed to it.  The results are the same products; the
 // rank-ordered weighted sum (cuda/model/experts.cu:77-98) is kept as it is.
+#include <stdlib.h>
+
 #include "q8_launch.h"
 #include "q8_tile.cuh"
 
@@ -14,7 +16,18 @@ namespace q8 {
 
 #define Q8_GROUP_THREADS 1024u
 #define Q8_GROUP_MAX_EXPERTS 256u
-#define Q8_GROUP_TOKENS 64u /* token tile of the grouped products */
+#define Q8_GROUP_TOKENS_MAX 64u /* largest token tile of the grouped products */
+
+static unsigned int group_tokens()
+{
+#ifdef Q8_EXPERIMENT
+    const char *env = getenv("Q8_GROUP_TOKENS");
+    if (env != nullptr) {
+        return (unsigned int)atoi(env);
+    }
+#endif
+    return 64u;
+}
 
 // One block.  Counts the pairs of every expert, places each pair in its expert's run of
 // `sorted_pair` (order inside a run is not fixed and does not affect any result: every column
@@ -24,7 +37,7 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
                       const unsigned int *tokens_dev, unsigned int used, unsigned int experts,
                       unsigned int ffn, unsigned int hidden, unsigned int *__restrict__ sorted_pair,
                       GroupTile *__restrict__ tiles_feed, GroupTile *__restrict__ tiles_down,
-                      unsigned int *__restrict__ counts)
+                      unsigned int *__restrict__ counts, unsigned int tile_tokens)
 {
     __shared__ unsigned int count[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int offset[Q8_GROUP_MAX_EXPERTS];
@@ -56,7 +69,7 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
             offset[e] = at;
             feed_base[e] = feed;
             down_base[e] = down;
-            unsigned int tok_tiles = (count[e] + Q8_GROUP_TOKENS - 1u) / Q8_GROUP_TOKENS;
+            unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
             at += count[e];
             feed += tok_tiles * feed_rows;
             down += tok_tiles * down_rows;
@@ -71,12 +84,12 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
         sorted_pair[at] = p;
     }
     for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
-        unsigned int tok_tiles = (count[e] + Q8_GROUP_TOKENS - 1u) / Q8_GROUP_TOKENS;
+        unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
         for (unsigned int tt = 0u; tt < tok_tiles; ++tt) {
-            unsigned int tok0 = offset[e] + tt * Q8_GROUP_TOKENS;
+            unsigned int tok0 = offset[e] + tt * tile_tokens;
             unsigned int tok_limit = offset[e] + count[e];
-            if (tok_limit > tok0 + Q8_GROUP_TOKENS) {
-                tok_limit = tok0 + Q8_GROUP_TOKENS;
+            if (tok_limit > tok0 + tile_tokens) {
+                tok_limit = tok0 + tile_tokens;
             }
             for (unsigned int r = 0u; r < feed_rows; ++r) {
                 GroupTile t;
@@ -156,7 +169,7 @@ MoeWorkspace moe_workspace_layout(unsigned int tokens, unsigned int used, unsign
 {
     MoeWorkspace ws;
     const size_t pairs = (size_t)tokens * used;
-    const size_t tok_tiles = pairs / Q8_GROUP_TOKENS + experts;
+    const size_t tok_tiles = pairs / 16u + experts; /* room for the smallest token tile */
     ws.max_feed = (unsigned int)(tok_tiles * ((ffn + kRows - 1u) / kRows));
     ws.max_down = (unsigned int)(tok_tiles * ((hidden + kRows - 1u) / kRows));
     size_t at = 0;
@@ -190,6 +203,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
                                const MoeWorkspace &ws)
 {
     const unsigned int pairs = tokens * used;
+    const unsigned int tile_tokens = group_tokens();
     unsigned int *sorted_pair = reinterpret_cast<unsigned int *>(workspace + ws.sorted_pair);
     unsigned int *counts = reinterpret_cast<unsigned int *>(workspace + ws.counts);
     GroupTile *tiles_feed = reinterpret_cast<GroupTile *>(workspace + ws.tiles_feed);
@@ -201,7 +215,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
     float *proj = reinterpret_cast<float *>(workspace + ws.proj);
 
     q8_group_build_kernel<<<1, Q8_GROUP_THREADS, 0, stream>>>(ids, tokens, tokens_dev, used, experts, ffn, hidden,
-                                                              sorted_pair, tiles_feed, tiles_down, counts);
+                                                              sorted_pair, tiles_feed, tiles_down, counts, tile_tokens);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
         return err;
@@ -214,13 +228,13 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
         return err;
     }
     err = launch_umma_grouped(stream, scratch, sm_count, w_gate, experts * ffn, hidden, x_sorted, pairs,
-                              Q8_GROUP_TOKENS, tiles_feed, counts + 0, ws.max_feed, nullptr, gate, ffn, 0,
+                              tile_tokens, tiles_feed, counts + 0, ws.max_feed, nullptr, gate, ffn, 0,
                               (*launches)++, overlap);
     if (err != cudaSuccess) {
         return err;
     }
     err = launch_umma_grouped(stream, scratch, sm_count, w_up, experts * ffn, hidden, x_sorted, pairs,
-                              Q8_GROUP_TOKENS, tiles_feed, counts + 0, ws.max_feed, nullptr, up, ffn, 0,
+                              tile_tokens, tiles_feed, counts + 0, ws.max_feed, nullptr, up, ffn, 0,
                               (*launches)++, overlap);
     if (err != cudaSuccess) {
         return err;
@@ -231,7 +245,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
         return err;
     }
     return launch_umma_grouped(stream, scratch, sm_count, w_down, experts * hidden, ffn, act, pairs,
-                               Q8_GROUP_TOKENS, tiles_down, counts + 1, ws.max_down, sorted_pair, proj, hidden,
+                               tile_tokens, tiles_down, counts + 1, ws.max_down, sorted_pair, proj, hidden,
                                0, (*launches)++, overlap);
 }
 

@@ -161,13 +161,19 @@ q8_gemv_simt_kernel(const unsigned char *__restrict__ w, unsigned int n, unsigne
 // are the same floats.
 // ---------------------------------------------------------------------------------------
 #define Q8_ROUTE_THREADS 256u
+#define Q8_ROUTE_TOKENS 4u /* tokens that share one pass over the router rows */
 
+// One block takes Q8_ROUTE_TOKENS tokens at a time: a warp reads a router row once and forms
+// the dot product of every token of the group with it.  Each (token, expert) sum still adds
+// the same products in the same order as one warp of the reference kernel does (lanes 32
+// apart, then the shuffle tree), so the probabilities are the same floats.
 __global__ void __launch_bounds__(Q8_ROUTE_THREADS)
 q8_route_kernel(const __half *__restrict__ x, const float *__restrict__ router, unsigned int tokens_max,
                 const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                 unsigned int used, float *__restrict__ prob, unsigned int *__restrict__ ids)
 {
-    __shared__ float probability[Q8_ROUTE_THREADS];
+    extern __shared__ float route_x[]; // the group's activations as float: [Q8_ROUTE_TOKENS][hidden]
+    __shared__ float probability[Q8_ROUTE_TOKENS][Q8_ROUTE_THREADS];
     __shared__ float reduce[Q8_ROUTE_THREADS];
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
@@ -177,57 +183,78 @@ q8_route_kernel(const __half *__restrict__ x, const float *__restrict__ router, 
     unsigned int lane = threadIdx.x & 31u;
     unsigned int warp = threadIdx.x >> 5;
     unsigned int e = threadIdx.x;
-    for (unsigned int t = blockIdx.x; t < tokens; t += gridDim.x) {
-        const __half *xt = x + (size_t)t * hidden;
+    for (unsigned int t0 = blockIdx.x * Q8_ROUTE_TOKENS; t0 < tokens; t0 += gridDim.x * Q8_ROUTE_TOKENS) {
+        unsigned int group = tokens - t0 < Q8_ROUTE_TOKENS ? tokens - t0 : Q8_ROUTE_TOKENS;
+        for (unsigned int at = threadIdx.x; at < Q8_ROUTE_TOKENS * hidden; at += Q8_ROUTE_THREADS) {
+            unsigned int g = at / hidden;
+            route_x[at] = g < group ? __half2float(x[(size_t)(t0 + g) * hidden + (at - g * hidden)]) : 0.0f;
+        }
+        __syncthreads();
         for (unsigned int ex = warp; ex < experts; ex += Q8_ROUTE_THREADS / 32u) {
             const float *row = router + (size_t)ex * hidden;
-            float dot = 0.0f;
+            float dot[Q8_ROUTE_TOKENS];
+#pragma unroll
+            for (unsigned int g = 0; g < Q8_ROUTE_TOKENS; ++g) {
+                dot[g] = 0.0f;
+            }
+#pragma unroll 8
             for (unsigned int d = lane; d < hidden; d += 32u) {
-                dot += row[d] * __half2float(xt[d]);
+                float r = row[d];
+#pragma unroll
+                for (unsigned int g = 0; g < Q8_ROUTE_TOKENS; ++g) {
+                    // the reference's own expression; both compile to one fused multiply-add
+                    dot[g] += r * route_x[g * hidden + d];
+                }
             }
-            for (unsigned int step = 16u; step != 0u; step >>= 1) {
-                dot += __shfl_down_sync(0xFFFFFFFFu, dot, step);
-            }
-            if (lane == 0u) {
-                probability[ex] = dot;
+#pragma unroll
+            for (unsigned int g = 0; g < Q8_ROUTE_TOKENS; ++g) {
+                for (unsigned int step = 16u; step != 0u; step >>= 1) {
+                    dot[g] += __shfl_down_sync(0xFFFFFFFFu, dot[g], step);
+                }
+                if (lane == 0u) {
+                    probability[g][ex] = dot[g];
+                }
             }
         }
         __syncthreads();
-        reduce[e] = e < experts ? probability[e] : -CUDART_INF_F;
-        __syncthreads();
-        for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
-            if (e < step) {
-                reduce[e] = fmaxf(reduce[e], reduce[e + step]);
+        for (unsigned int g = 0; g < group; ++g) {
+            unsigned int t = t0 + g;
+            reduce[e] = e < experts ? probability[g][e] : -CUDART_INF_F;
+            __syncthreads();
+            for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
+                if (e < step) {
+                    reduce[e] = fmaxf(reduce[e], reduce[e + step]);
+                }
+                __syncthreads();
+            }
+            float value = e < experts ? expf(probability[g][e] - reduce[0]) : 0.0f;
+            __syncthreads();
+            reduce[e] = value;
+            __syncthreads();
+            for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
+                if (e < step) {
+                    reduce[e] += reduce[e + step];
+                }
+                __syncthreads();
+            }
+            if (e < experts) {
+                value /= reduce[0];
+                probability[g][e] = value;
+                prob[(size_t)t * experts + e] = value;
+            }
+            __syncthreads();
+            if (e < experts) {
+                unsigned int rank = 0u;
+                for (unsigned int other = 0u; other < experts; ++other) {
+                    float candidate = probability[g][other];
+                    rank += (candidate > value || (candidate == value && other < e)) ? 1u : 0u;
+                }
+                if (rank < used) {
+                    ids[(size_t)t * used + rank] = e;
+                }
             }
             __syncthreads();
         }
-        float value = e < experts ? expf(probability[e] - reduce[0]) : 0.0f;
-        __syncthreads();
-        reduce[e] = value;
-        __syncthreads();
-        for (unsigned int step = Q8_ROUTE_THREADS / 2u; step != 0u; step >>= 1) {
-            if (e < step) {
-                reduce[e] += reduce[e + step];
-            }
-            __syncthreads();
-        }
-        if (e < experts) {
-            value /= reduce[0];
-            probability[e] = value;
-            prob[(size_t)t * experts + e] = value;
-        }
-        __syncthreads();
-        if (e < experts) {
-            unsigned int rank = 0u;
-            for (unsigned int other = 0u; other < experts; ++other) {
-                float candidate = probability[other];
-                rank += (candidate > value || (candidate == value && other < e)) ? 1u : 0u;
-            }
-            if (rank < used) {
-                ids[(size_t)t * used + rank] = e;
-            }
-        }
-        __syncthreads();
     }
 }
 
@@ -392,8 +419,22 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
     if (tokens == 0u) {
         return cudaSuccess;
     }
-    unsigned int grid = tokens < 148u * 8u ? tokens : 148u * 8u;
-    q8_route_kernel<<<grid, Q8_ROUTE_THREADS, 0, stream>>>(static_cast<const __half *>(x), router,
+    unsigned int groups = (tokens + Q8_ROUTE_TOKENS - 1u) / Q8_ROUTE_TOKENS;
+    unsigned int grid = groups < 148u * 8u ? groups : 148u * 8u;
+    size_t smem = (size_t)Q8_ROUTE_TOKENS * hidden * sizeof(float);
+    if (smem > 160u * 1024u) {
+        return cudaErrorInvalidValue;
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(q8_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               160 * 1024);
+        if (err != cudaSuccess) {
+            return err;
+        }
+        configured = true;
+    }
+    q8_route_kernel<<<grid, Q8_ROUTE_THREADS, smem, stream>>>(static_cast<const __half *>(x), router,
                                                            tokens, tokens_dev, hidden, experts, used,
                                                            prob, ids);
     return cudaGetLastError();
