@@ -143,3 +143,37 @@ class ExpertParallel:
         proj = proj_back.new_empty((pairs, self.hidden))
         proj[order] = proj_back
         return self.combine(proj.reshape(tokens, self.used, self.hidden), prob, ids)
+
+
+def column_split_on_gpu(ctx, w_local, n, k, world, rank, y_dtype=None, group=None):
+    """`ColumnSplit` whose local step is the library's product on this rank's rows of w
+    (`w_local`: device tensor holding the byte range `ColumnSplit.shard_bytes`)."""
+    first, last = shard_rows(n, world, rank)
+
+    def product(x, m):
+        return ctx.matmul(w_local, last - first, k, x, m=m, y_dtype=y_dtype)
+
+    return ColumnSplit(n, k, world, rank, product, group=group)
+
+
+def expert_parallel_on_gpu(ctx, w_gate, w_up, w_down, experts_total, used, hidden, ffn, world, rank,
+                           group=None):
+    """`ExpertParallel` whose local step is the library's grouped expert products on this
+    rank's experts (`w_*`: device tensors holding only those experts' slices)."""
+    import torch
+    first, last = shard_rows(experts_total, world, rank)
+    local = last - first
+
+    def experts(rows, local_expert):
+        count = rows.shape[0]
+        if count == 0:
+            return torch.zeros((0, hidden), dtype=torch.float32, device=rows.device)
+        ones = torch.ones((count, local), dtype=torch.float32, device=rows.device)
+        ids = local_expert.to(torch.int32).reshape(count, 1).contiguous()
+        return ctx.moe_ffn(w_gate, w_up, w_down, local, hidden, ffn, rows.contiguous(), ones, ids,
+                           tokens=count)
+
+    def combine(proj, prob, ids):
+        return ctx.moe_combine(proj.contiguous(), prob, ids)
+
+    return ExpertParallel(experts_total, used, hidden, world, rank, experts, combine, group=group)
