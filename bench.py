@@ -40,6 +40,10 @@ WORKLOADS = {
                                              ("gate_up", 4096, 28672), ("down", 14336, 4096)],
                                       "bfloat16", "bfloat16"),
 }
+# DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures
+# summarised under profiles/ (gate+up projection; scaled to the average launch by bytes).
+TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.0565, "decode_m32_gate_up": 1.0565,
+                 "prefill_m2048_llama3_8b_layer": 4.14, "prefill_m2048_gate_up": 4.14}
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up"}
 
 
@@ -255,6 +259,8 @@ def run_ours(args, rank, world, local_rank):
         value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
         e2e_value = world * step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
         metric, unit = "q8_decode_gemm_hbm_gbs", "GB/s"
+    ratio = TRAFFIC_RATIO.get(args.workload)
+    roofline["traffic"] = ratio * step_bytes / launches if ratio else None
     roofline["peak_source"] = peak_kind
     roofline["kernel"] = "q8_umma_kernel"
     roofline["launches_timed"] = launches * args.steps
@@ -285,6 +291,147 @@ def run_ours(args, rank, world, local_rank):
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+SHARDED = {
+    # BASELINE config 4: LM head 8192 -> 151936, rows of w split over the ranks, all-gather of y
+    "lm_head_colsplit": {"n": 151936, "k": 8192},
+    # BASELINE config 3: Qwen3-30B-A3B-shaped routed experts, expert parallel over the ranks
+    "moe_qwen3_30b_a3b": {"tokens": 512, "experts": 128, "used": 8, "hidden": 2048, "ffn": 768},
+}
+
+
+def run_sharded(args, rank, world, local_rank):
+    """Strong-scaling workloads: the total work is fixed, the ranks split it."""
+    import torch
+    import aotx_b200
+    from aotx_b200.sharded import (ColumnSplit, column_split_on_gpu, expert_parallel_on_gpu, shard_rows)
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = aotx_b200.Q8Context(local_rank)
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    spec = SHARDED[args.workload]
+    copies = 2
+    if args.workload == "lm_head_colsplit":
+        n, k, m = spec["n"], spec["k"], args.rows
+        first, last = shard_rows(n, world, rank)
+        rows = last - first
+        shards = []
+        for c in range(copies):
+            host = aotx_b200.synth_q8_0(rows, k, 7000 + 10 * rank + c)
+            shards.append(torch.from_numpy(host).cuda())
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+        def step(c):
+            splits[c].matmul(x, m, out=out)
+
+        step_bytes = n * (k // 32) * 34 + m * k * 2 + m * n * 2
+        launches = 1
+        config = {"workload": args.workload, "rows": m, "n": n, "k": k, "x": "bfloat16", "y": "bfloat16",
+                  "parallelism": "column split x%d + all-gather" % world}
+    else:
+        tokens, experts, used = spec["tokens"], spec["experts"], spec["used"]
+        hidden, ffn = spec["hidden"], spec["ffn"]
+        e0, e1 = shard_rows(experts, world, rank)
+        t0, t1 = shard_rows(tokens, world, rank)
+        local = e1 - e0
+        sets = []
+        for c in range(copies):
+            sets.append(tuple(torch.from_numpy(aotx_b200.synth_q8_0(local * r, kk, 8000 + 100 * c + 10 * rank + i)).cuda()
+                              for i, (r, kk) in enumerate(((ffn, hidden), (ffn, hidden), (hidden, ffn)))))
+        gen = torch.Generator(device="cuda").manual_seed(11)
+        x_all = torch.randn(tokens, hidden, device="cuda", generator=gen).half()
+        router = (torch.randn(experts, hidden, device="cuda", generator=gen) / hidden ** 0.5).float()
+        prob_all, ids_all = ctx.moe_route(x_all, router, used)
+        x_loc, prob, ids = x_all[t0:t1].contiguous(), prob_all[t0:t1].contiguous(), ids_all[t0:t1].contiguous()
+        if world == 1:
+            ws = ctx.moe_workspace(tokens, used, hidden, ffn)
+            out = torch.empty((tokens, hidden), dtype=torch.float32, device="cuda")
+
+            def step(c):
+                ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
+        else:
+            eps = [expert_parallel_on_gpu(ctx, *sets[c], experts, used, hidden, ffn, world, rank)
+                   for c in range(copies)]
+
+            def step(c):
+                eps[c].ffn(x_loc, prob, ids)
+
+        hit = int((torch.bincount(ids_all.reshape(-1).long(), minlength=experts) > 0).sum())
+        slice_bytes = 2 * ffn * (hidden // 32) * 34 + hidden * (ffn // 32) * 34
+        step_bytes = hit * slice_bytes + tokens * hidden * 2 + tokens * hidden * 4
+        launches = 8
+        config = {"workload": args.workload, "tokens": tokens, "experts": experts, "used": used,
+                  "hidden": hidden, "ffn": ffn, "experts_hit": hit, "x": "float16", "y": "float32",
+                  "router": "selections made once outside the timed region",
+                  "parallelism": "expert parallel x%d + all-to-all" % world if world > 1 else "single"}
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step(0)
+    barrier()
+    graphs = None
+    if args.workload == "lm_head_colsplit" or world == 1:
+        try:
+            graphs = []
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for c in range(copies):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        step(c)
+                    graphs.append(g)
+            torch.cuda.synchronize()
+        except Exception:
+            graphs = None
+    run = (lambda c: graphs[c].replay()) if graphs else step
+    for i in range(max(args.warmup, 3)):
+        run(i % copies)
+    barrier()
+    sampler = ClockSampler(device_index(local_rank))
+    sampler.start()
+    e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0_.record()
+    for i in range(args.steps):
+        run(i % copies)
+    e1_.record()
+    barrier()
+    total_ms = e0_.elapsed_time(e1_)
+    sampler.stop_flag.set()
+    sampler.join()
+    status = ctx.device_status()
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t[0])
+    value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+    config["cuda_graph"] = bool(graphs)
+    config["l2"] = "two weight copies rotate; each larger than L2 at N=1"
+    line = {
+        "metric": "q8_decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16/bf16 operands, f32 sums", "data": "synthetic", "config": config,
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": value / world / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                     "note": "per GPU, whole step including the exchange"},
+        "gpu_launches": launches * args.steps, "clocks": sampler.summary(), "device_status": status,
+    }
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -392,7 +539,9 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
-    parser.add_argument("--workload", default="decode_m32_llama3_8b_layer", choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default="decode_m32_llama3_8b_layer",
+                        choices=sorted(WORKLOADS) + sorted(SHARDED))
+    parser.add_argument("--rows", type=int, default=8, help="rows of x for lm_head_colsplit")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
@@ -403,6 +552,9 @@ def main():
         if args.steps > 20:
             args.steps = 20
         run_reference(args, rank, world)
+        return
+    if args.workload in SHARDED:
+        run_sharded(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 
