@@ -383,7 +383,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 break;
             }
             tc_fence_after_sync();
-            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, s0, s1, segs,
+            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, tile, s0, s1, segs,
                                      tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }

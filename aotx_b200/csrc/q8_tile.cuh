@@ -173,6 +173,39 @@ __device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
     }
 }
 
+// The order of work of one block: first its share [u, u_end) of the units of the tiles that
+// are cut between blocks (tile ids from sk_tile0), then whole tiles dp_first + i * dp_stride.
+struct WorkIter {
+    unsigned long long u;
+    unsigned long long u_end;
+    uint32_t segs;
+    uint32_t sk_tile0;
+    uint32_t dp_next;
+    uint32_t dp_count;
+    uint32_t dp_first;
+    uint32_t dp_stride;
+
+    __device__ __forceinline__ bool next(uint32_t &tile, uint32_t &s0, uint32_t &s1)
+    {
+        if (u < u_end) {
+            tile = sk_tile0 + (uint32_t)(u / segs);
+            s0 = (uint32_t)(u % segs);
+            const unsigned long long left = u_end - u;
+            s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            u += (s1 - s0);
+            return true;
+        }
+        if (dp_next < dp_count) {
+            tile = dp_first + dp_next * dp_stride;
+            s0 = 0;
+            s1 = segs;
+            dp_next += 1;
+            return true;
+        }
+        return false;
+    }
+};
+
 // One piece of a tile is in the accumulator at `taddr_acc` (column base of the buffer).  The
 // warp `wq` of the four epilogue warps owns TMEM lanes [32 wq, 32 wq + 32).  `chunk` columns are
 // read per TMEM load.
@@ -202,7 +235,8 @@ __device__ __forceinline__ TilePlace tile_place(const UmmaArgs &args, uint32_t t
 
 template <int NTOK, typename YT>
 __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t taddr_acc, uint32_t wq,
-                                               uint32_t lane, uint32_t tile, uint32_t s0, uint32_t s1,
+                                               uint32_t lane, uint32_t tile, uint32_t cut_tile, uint32_t s0,
+                                               uint32_t s1,
                                                uint32_t segs, uint32_t tok_tiles,
                                                unsigned long long units, unsigned int blocks,
                                                unsigned int m, volatile uint32_t *abort_flag,
@@ -221,7 +255,8 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     // long before the owner asks for them.
     const bool whole = (s0 == 0u && s1 == segs);
     const bool owner = (s0 == 0u);
-    const unsigned long long tile_end = ((unsigned long long)tile + 1ull) * segs;
+    // `cut_tile` counts the tile among those that are cut into units (`units` of them in all)
+    const unsigned long long tile_end = ((unsigned long long)cut_tile + 1ull) * segs;
     float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
 
 #ifdef Q8_EXPERIMENT

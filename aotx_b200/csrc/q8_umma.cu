@@ -112,14 +112,31 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t segs = args.k / kSegK;
     const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
     const uint32_t tok_tiles = (m + (uint32_t)NTOK - 1u) / (uint32_t)NTOK;
-    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
-    // No more blocks than units take part, so that every block in the schedule has work.
+    unsigned long long units = 0;
+    // Whole waves of tiles are dealt round-robin (block b takes tiles b, b + G, ...: the token
+    // tiles of one weight row tile then run at the same time on neighbouring SMs and share its
+    // bytes in L2); the tiles of the last, partial wave are cut into units and spread evenly
+    // over all blocks, first in every block's order of work.
+    const unsigned long long tiles = (unsigned long long)row_tiles * tok_tiles;
+    const uint32_t waves = (uint32_t)(tiles / gridDim.x);
+    const uint32_t dp_tiles = waves * gridDim.x;
+    units = (tiles - dp_tiles) * segs;                        // units of the partial wave
     const unsigned int blocks = units < gridDim.x ? (unsigned int)units : gridDim.x;
-    if (blockIdx.x >= blocks) {
+    WorkIter first_work;
+    first_work.segs = segs;
+    first_work.u = 0;
+    first_work.u_end = 0;
+    if (blockIdx.x < blocks) {
+        unit_range(blockIdx.x, blocks, units, &first_work.u, &first_work.u_end);
+    }
+    first_work.sk_tile0 = dp_tiles;
+    first_work.dp_next = 0;
+    first_work.dp_count = waves;
+    first_work.dp_first = blockIdx.x;
+    first_work.dp_stride = gridDim.x;
+    if (first_work.u >= first_work.u_end && waves == 0u) {
         return;
     }
-    unsigned long long u_begin, u_end;
-    unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
@@ -162,11 +179,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (lane == 0u) {
             uint32_t g = 0;
             bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end;) {
-                const uint32_t tile = (uint32_t)(u / segs);
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            WorkIter work = first_work;
+            uint32_t tile = 0, s0 = 0, s1 = 0;
+            for (; ok && work.next(tile, s0, s1);) {
+                (void)tile;
                 const uint32_t row_tile = tile / tok_tiles;
                 for (uint32_t s = s0; s < s1; ++s, ++g) {
                     const uint32_t st = g % S::raw_stages;
@@ -185,7 +201,6 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
                                 (int)(s * kSegWords), (int)(row_tile * kRows));
                 }
-                u += (s1 - s0);
             }
             // Let every copy this thread started land before the block ends.
             uint32_t local_abort = 0;
@@ -201,11 +216,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             uint32_t q = 0;
             grid_dependency_wait();
             bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end;) {
-                const uint32_t tile = (uint32_t)(u / segs);
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            WorkIter work = first_work;
+            uint32_t tile = 0, s0 = 0, s1 = 0;
+            for (; ok && work.next(tile, s0, s1);) {
+                (void)tile;
                 const uint32_t tok_tile = tile % tok_tiles;
                 for (uint32_t s = s0; ok && s < s1; ++s) {
                     for (uint32_t j = 0; j < kSubs; ++j, ++q) {
@@ -226,7 +240,6 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                                     (int)(s * kSegK + j * kSubK), (int)(tok_tile * (uint32_t)NTOK));
                     }
                 }
-                u += (s1 - s0);
             }
             uint32_t local_abort = 0;
             const uint32_t first = q > S::x_stages ? q - S::x_stages : 0u;
@@ -242,10 +255,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             uint32_t q = 0;
             uint32_t tc = 0;
             bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            WorkIter work = first_work;
+            uint32_t tile = 0, s0 = 0, s1 = 0;
+            for (; ok && work.next(tile, s0, s1); ++tc) {
+                (void)tile;
                 const uint32_t buf = tc & 1u;
                 const uint32_t aph = (tc >> 1) & 1u;
                 if (!mbar_wait(acc_empty + 8u * buf, aph ^ 1u, abort_flag, args.status)) {
@@ -299,7 +312,6 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 if (ok) {
                     umma_commit(acc_full + 8u * buf);
                 }
-                u += (s1 - s0);
             }
             if (!ok) {
                 // Outstanding MMAs must finish before the tensor memory goes back.
@@ -315,10 +327,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t row = (cw & 3u) * 32u + lane;
         uint32_t g = 0;
         bool ok = true;
-        for (unsigned long long u = u_begin; ok && u < u_end;) {
-            const uint32_t s0 = (uint32_t)(u % segs);
-            const unsigned long long left = u_end - u;
-            const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+        WorkIter work = first_work;
+        uint32_t tile = 0, s0 = 0, s1 = 0;
+        for (; ok && work.next(tile, s0, s1);) {
+            (void)tile;
             for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
                 const uint32_t rst = g % S::raw_stages;
                 const uint32_t rph = (g / S::raw_stages) & 1u;
@@ -421,7 +433,6 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     }
                 }
             }
-            u += (s1 - s0);
         }
     } else {
         // ---------------------------------------------------------------- epilogue
@@ -429,11 +440,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         uint32_t tc = 0;
         grid_dependency_wait();
         bool ok = true;
-        for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
-            const uint32_t tile = (uint32_t)(u / segs);
-            const uint32_t s0 = (uint32_t)(u % segs);
-            const unsigned long long left = u_end - u;
-            const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+        WorkIter work = first_work;
+        uint32_t tile = 0, s0 = 0, s1 = 0;
+        for (; ok && work.next(tile, s0, s1); ++tc) {
+            (void)tile;
             const uint32_t buf = tc & 1u;
             const uint32_t aph = (tc >> 1) & 1u;
             if (!mbar_wait(acc_full + 8u * buf, aph, abort_flag, args.status)) {
@@ -441,9 +451,9 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 break;
             }
             tc_fence_after_sync();
-            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, s0, s1, segs,
+            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile,
+                                     tile >= first_work.sk_tile0 ? tile - first_work.sk_tile0 : 0u, s0, s1, segs,
                                      tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
-            u += (s1 - s0);
         }
     }
 

@@ -64,6 +64,22 @@ def test_prefill_shape_m2048_spot(ctx, oracle):
     check_product(oracle, w, n, k, x.view(np.uint16), m, y.cpu().numpy(), full_limit=0, spots=2048)
 
 
+@pytest.mark.parametrize("n,k,m", [(1280, 512, 700), (2560, 256, 2048), (2432, 768, 1100)])
+def test_wide_batches_full_compare(ctx, oracle, n, k, m):
+    """Batches above 128 rows (the 256-row kernel): fewer tiles than SMs, one whole wave plus a
+    cut tail, and a ragged last token tile, each against the whole oracle product."""
+    import aotx_b200
+    torch = torch_mod()
+    w = aotx_b200.synth_q8_0(n, k, n + m)
+    x = x_fp16(m, k, m)
+    y = torch.full((m + 1, n), GUARD, dtype=torch.float32, device="cuda")
+    ctx.matmul(dev_weights(w), n, k, dev(x), y=y[:m])
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    check_product(oracle, w, n, k, x.view(np.uint16), m, got[:m])
+    assert (got[m:] == GUARD).all()
+
+
 def test_linearity_at_full_size(ctx):
     """A size-independent property at the benchmark's largest decode shape: the product is
     linear in x, so y(x1 + x2) = y(x1) + y(x2) to float rounding when the sums of inputs are
