@@ -437,10 +437,18 @@ def run_sharded(args, rank, world, local_rank):
         "gpu_launches": launches * args.steps, "clocks": sampler.summary(), "device_status": status,
     }
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # Graphs that hold captured collectives must go before the process group does; tearing the
+    # group down first left every rank waiting at exit.
+    graphs = None
+    run = None
+    torch.cuda.synchronize()
     if world > 1:
         import torch.distributed as dist
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def cpu_sample(workload, fraction):
