@@ -219,18 +219,64 @@ def run_ours(args, rank, world, local_rank):
     sampler.join()
     status = ctx.device_status()
 
-    # end to end: host buffers, copies inside the timed region
+    # End to end: activations start in pinned host memory and results end there, every step,
+    # copies inside the timed region.  The step is captured like the resident one (the
+    # reference runs its passes as graphs too): the uploads run on a copy stream ahead of the
+    # products, each result goes back on a second copy stream while the next product runs.
+    e2e_mode = "graph, copies overlapped on two copy streams"
+    e2e_graphs = []
+    try:
+        main_stream = torch.cuda.Stream()
+        up_stream = torch.cuda.Stream()
+        down_stream = torch.cuda.Stream()
+        with torch.cuda.stream(main_stream):
+            for c in range(copies):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=main_stream):
+                    up_stream.wait_stream(main_stream)
+                    ready = []
+                    with torch.cuda.stream(up_stream):
+                        for t in tensors:
+                            t["x"].copy_(t["x_host"], non_blocking=True)
+                            event = torch.cuda.Event()
+                            event.record(up_stream)
+                            ready.append(event)
+                    down_stream.wait_stream(main_stream)
+                    for t, event in zip(tensors, ready):
+                        main_stream.wait_event(event)
+                        ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
+                        done = torch.cuda.Event()
+                        done.record(main_stream)
+                        with torch.cuda.stream(down_stream):
+                            down_stream.wait_event(done)
+                            t["y_host"].copy_(t["y"], non_blocking=True)
+                    main_stream.wait_stream(up_stream)
+                    main_stream.wait_stream(down_stream)
+                e2e_graphs.append(g)
+        torch.cuda.synchronize()
+    except Exception as error:
+        e2e_graphs = []
+        e2e_mode = "eager calls (graph capture failed: %s)" % str(error)[:80]
+
+    def run_e2e(c):
+        if e2e_graphs:
+            e2e_graphs[c].replay()
+        else:
+            step_e2e(c)
+
     for i in range(3):
-        step_e2e(i % copies)
+        run_e2e(i % copies)
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        step_e2e(i % copies)
+        run_e2e(i % copies)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # the results that came back are the device results
+    check = all(bool(torch.equal(t["y_host"], t["y"].cpu())) for t in tensors)
 
     if world > 1:
         import torch.distributed as dist
@@ -284,7 +330,7 @@ def run_ours(args, rank, world, local_rank):
                    "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+                "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode, "host_result_matches_device": check},
         "gpu_launches": launches * args.steps,
         "clocks": clocks,
         "device_status": status,
