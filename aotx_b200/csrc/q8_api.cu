@@ -315,3 +315,41 @@ extern "C" int aotx_q8_moe_combine(aotx_q8_ctx *ctx, void *stream, const float *
                                             hidden, experts, used, out, out_dtype);
     return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
 }
+
+extern "C" int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                                    uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                                    void *const *y_peers, uint32_t peers, uint32_t ldy, uint32_t col0,
+                                    int y_dtype)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (!dtype_16(x_dtype) || !dtype_out(y_dtype) || k == 0u || (k % 32u) != 0u || peers == 0u || peers > 8u
+        || y_peers == nullptr || (unsigned long long)col0 + n > ldy) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (n == 0u || m == 0u) {
+        return AOTX_Q8_OK;
+    }
+    q8::PeerOut out;
+    out.peers = peers;
+    out.col0 = col0;
+    out.ldy = ldy;
+    for (uint32_t i = 0; i < 8u; ++i) {
+        out.y_peer[i] = i < peers ? y_peers[i] : nullptr;
+        if (i < peers && (y_peers[i] == nullptr || !aligned(y_peers[i], y_dtype == AOTX_Q8_F32 ? 4u : 2u))) {
+            return AOTX_Q8_ERR_ARGUMENT;
+        }
+    }
+    if (w == nullptr || x == nullptr || !q8::umma_supports(w, n, k, x, m)) {
+        /* only the tensor-core kernels store into peers */
+        return w == nullptr || x == nullptr ? AOTX_Q8_ERR_ARGUMENT : AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    cudaError_t err = q8::launch_umma((cudaStream_t)stream, ctx->scratch, ctx->sm_count, w, n, k, x,
+                                      x_dtype == AOTX_Q8_BF16, m, m_dev, out.y_peer[0], y_dtype, ctx->launches++,
+                                      ctx->overlap != 0, &out);
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}

@@ -41,12 +41,21 @@ struct UmmaScratch {
     unsigned long long tile_floats; // floats per block in `partial`
 };
 
+// Column-split output: the product is columns [col0, col0 + n) of a y with row stride ldy,
+// stored into every buffer of y_peer (own and peer-mapped).
+struct PeerOut {
+    void *y_peer[8];
+    unsigned int peers;
+    unsigned int col0;
+    unsigned int ldy;
+};
+
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap);
+                        bool overlap, const PeerOut *out = nullptr);
 
 // Grouped mode of the decode-regime kernel: tiles from a device table (see q8_tile.cuh).
 struct GroupTile;

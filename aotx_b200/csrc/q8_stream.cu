@@ -416,15 +416,10 @@ static cudaError_t launch_stream_typed(cudaStream_t stream, const CUtensorMap &t
                                        const UmmaArgs &args, unsigned int grid)
 {
     using S = StreamShape<NTOK>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(q8_stream_kernel<NTOK, YT>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)S::smem_bytes);
-        if (err != cudaSuccess) {
-            return err;
-        }
-        configured = true;
+    static unsigned long long configured = 0ull;
+    cudaError_t err = allow_shared_memory(q8_stream_kernel<NTOK, YT>, S::smem_bytes, &configured);
+    if (err != cudaSuccess) {
+        return err;
     }
     return launch_tile_kernel(q8_stream_kernel<NTOK, YT>, grid, S::smem_bytes, stream, args.overlap != 0u, tw,
                               tx, args);

@@ -61,6 +61,12 @@ struct UmmaArgs {
     const unsigned int *group_count;   // device word: number of table entries
     const unsigned int *row_map;       // may be null
     unsigned int ldy;                  // row stride of y in elements
+    // Column-split mode: this launch computes columns [col0, col0 + n) of a wider y and stores
+    // its tiles into `peers` copies of it (this GPU's own and the peers' buffers, reached by
+    // ordinary stores through peer-mapped addresses).  peers == 0: store into `y` only.
+    void *y_peer[8];
+    unsigned int peers;
+    unsigned int col0;
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null
@@ -346,12 +352,16 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                 }
             }
             if (j < place.j_limit) {
+                const uint32_t copies = args.peers == 0u ? 1u : args.peers;
+                for (uint32_t peer = 0; peer < copies; ++peer) {
+                    YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
 #pragma unroll
-                for (uint32_t i = 0; i < kChunk; ++i) {
-                    const uint32_t row_x = i0 + c0 + i;
-                    if (row_x < place.i_limit) {
-                        const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
-                        store_out<YT>(y, (size_t)row_y * args.ldy + j, __uint_as_float(v[i]));
+                    for (uint32_t i = 0; i < kChunk; ++i) {
+                        const uint32_t row_x = i0 + c0 + i;
+                        if (row_x < place.i_limit) {
+                            const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
+                            store_out<YT>(out, (size_t)row_y * args.ldy + args.col0 + j, __uint_as_float(v[i]));
+                        }
                     }
                 }
             }
@@ -387,6 +397,26 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             }
         }
     }
+}
+
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
+template <typename Kernel>
+inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask)
+{
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        return err;
+    }
+    const unsigned long long bit = 1ull << (device & 63);
+    if ((*done_mask & bit) == 0ull) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err != cudaSuccess) {
+            return err;
+        }
+        *done_mask |= bit;
+    }
+    return cudaSuccess;
 }
 
 // Launch with or without the programmatic-dependent-launch attribute.

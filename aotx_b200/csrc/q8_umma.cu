@@ -520,15 +520,10 @@ static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, cons
                                 const UmmaArgs &args, unsigned int grid)
 {
     using S = Shape<NTOK, TS>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(q8_umma_kernel<NTOK, YT, TS>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)S::smem_bytes);
-        if (err != cudaSuccess) {
-            return err;
-        }
-        configured = true;
+    static unsigned long long configured = 0ull;
+    cudaError_t err = allow_shared_memory(q8_umma_kernel<NTOK, YT, TS>, S::smem_bytes, &configured);
+    if (err != cudaSuccess) {
+        return err;
     }
     return launch_tile_kernel(q8_umma_kernel<NTOK, YT, TS>, grid, S::smem_bytes, stream, args.overlap != 0u,
                               tw, tx, args);
@@ -554,7 +549,7 @@ static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap)
+                        bool overlap, const PeerOut *out)
 {
     if (!umma_supports(w, n, k, x, m)) {
         return cudaErrorNotSupported;
@@ -619,6 +614,16 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.group_count = nullptr;
     args.row_map = nullptr;
     args.ldy = n;
+    args.peers = 0u;
+    args.col0 = 0u;
+    if (out != nullptr) {
+        args.ldy = out->ldy;
+        args.col0 = out->col0;
+        args.peers = out->peers;
+        for (unsigned int i = 0; i < 8u; ++i) {
+            args.y_peer[i] = i < out->peers ? out->y_peer[i] : nullptr;
+        }
+    }
     args.status = scratch.status;
     args.tile_floats = scratch.tile_floats;
     args.b_bf16 = x_bf16 ? 1u : 0u;
@@ -706,6 +711,8 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     args.group_count = count_dev;
     args.row_map = row_map;
     args.ldy = ldy;
+    args.peers = 0u;
+    args.col0 = 0u;
 #ifdef Q8_EXPERIMENT
     args.debug = 0u;
     args.trace = nullptr;

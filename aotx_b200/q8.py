@@ -139,6 +139,15 @@ class Q8Context:
             y.data_ptr(), _dtype_code(y.dtype)))
         return y
 
+    def matmul_peers(self, w, n, k, x, m, y_ptrs, ldy, col0, y_dtype, m_dev=None, type=Q8_0):
+        """Column-split product: columns [col0, col0 + n) of y[m][ldy], stored into every buffer
+        of `y_ptrs` (device addresses: this GPU's y and the peers', peer-mapped)."""
+        array = (C.c_void_p * len(y_ptrs))(*[C.c_void_p(int(p)) for p in y_ptrs])
+        self._check(self.lib.aotx_q8_matmul_peers(
+            self.handle, self._stream(), w.data_ptr(), type, n, k, x.data_ptr(), _dtype_code(x.dtype), m,
+            m_dev.data_ptr() if m_dev is not None else None, array, len(y_ptrs), ldy, col0,
+            _dtype_code(y_dtype)))
+
     def matmul_host(self, w, n, k, x_host, y_host, x_dev, y_dev):
         """The same product with the activations and the result in pinned host memory: copy
         in, multiply, copy out, all on the current stream (weights stay resident on the

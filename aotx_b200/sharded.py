@@ -177,3 +177,33 @@ def expert_parallel_on_gpu(ctx, w_gate, w_up, w_down, experts_total, used, hidde
         return ctx.moe_combine(proj.contiguous(), prob, ids)
 
     return ExpertParallel(experts_total, used, hidden, world, rank, experts, combine, group=group)
+
+
+class ColumnSplitFused:
+    """Column-split projection whose gather happens in the product's own stores.
+
+    y lives in symmetric memory (`torch.distributed._symmetric_memory`): every rank can store
+    into every rank's copy.  The kernel of rank r writes its column slice of each tile into all
+    copies (plain stores over NVLink, no multicast loads), and one device-side barrier orders
+    the ranks before anyone reads y.  A barrier also opens the step, so that no rank overwrites
+    a y that a peer is still reading from the step before."""
+
+    def __init__(self, ctx, w_local, n, k, world, rank, m_max, y_dtype, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.ctx, self.w_local = ctx, w_local
+        self.n, self.k, self.world, self.rank = n, k, world, rank
+        self.first, self.last = shard_rows(n, world, rank)
+        self.y_dtype = y_dtype
+        group = group if group is not None else dist.group.WORLD
+        self.y = symm.empty((m_max, n), dtype=y_dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.y, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def matmul(self, x, m):
+        self.handle.barrier(channel=0)
+        self.ctx.matmul_peers(self.w_local, self.last - self.first, self.k, x, m, self.ptrs, self.n,
+                              self.first, self.y_dtype)
+        self.handle.barrier(channel=1)
+        return self.y[:m]

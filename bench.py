@@ -379,16 +379,24 @@ def run_sharded(args, rank, world, local_rank):
             host = aotx_b200.synth_q8_0(rows, k, 7000 + 10 * rank + c)
             shards.append(torch.from_numpy(host).cuda())
         x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
-        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        if args.fused and world > 1:
+            from aotx_b200.sharded import ColumnSplitFused
+            fused = [ColumnSplitFused(ctx, w, n, k, world, rank, m, torch.bfloat16) for w in shards]
 
-        def step(c):
-            splits[c].matmul(x, m, out=out)
+            def step(c):
+                fused[c].matmul(x, m)
+        else:
+            splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
+            out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+            def step(c):
+                splits[c].matmul(x, m, out=out)
 
         step_bytes = n * (k // 32) * 34 + m * k * 2 + m * n * 2
         launches = 1
         config = {"workload": args.workload, "rows": m, "n": n, "k": k, "x": "bfloat16", "y": "bfloat16",
-                  "parallelism": "column split x%d + all-gather" % world}
+                  "parallelism": ("column split x%d, slices stored into peers by the kernel" if args.fused
+                                  else "column split x%d + all-gather") % world}
     else:
         tokens, experts, used = spec["tokens"], spec["experts"], spec["used"]
         hidden, ffn = spec["hidden"], spec["ffn"]
@@ -643,6 +651,8 @@ def main():
     parser.add_argument("--workload", default="decode_m32_llama3_8b_layer",
                         choices=sorted(WORKLOADS) + sorted(SHARDED))
     parser.add_argument("--rows", type=int, default=8, help="rows of x for lm_head_colsplit")
+    parser.add_argument("--fused", action="store_true",
+                        help="lm_head_colsplit: store the slices into the peers instead of an all-gather")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()

@@ -130,6 +130,18 @@ int aotx_q8_moe_combine(aotx_q8_ctx *ctx, void *stream, const float *proj, const
                         const uint32_t *ids, uint32_t tokens, const uint32_t *tokens_dev,
                         uint32_t hidden, uint32_t experts, uint32_t used, void *out, int out_dtype);
 
+/* Column-split product for several GPUs of one box: w holds this GPU's n rows of a wider tensor,
+ * the result is columns [col0, col0 + n) of y[m][ldy], and every tile is stored into all of
+ * y_peers[0..peers) - this GPU's copy of y and the peers' copies, given as device addresses
+ * that this GPU can store through (peer-mapped or symmetric memory).  The gather of the
+ * column slices thus happens in the kernel's own stores; the caller only has to order the
+ * GPUs afterwards (a barrier) before anyone reads y.  Only the tensor-core kernels serve it
+ * (k % 256 == 0, 16-byte aligned w and x); peers <= 8.  The reference is single-GPU and has no
+ * counterpart. */
+int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                         uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                         void *const *y_peers, uint32_t peers, uint32_t ldy, uint32_t col0, int y_dtype);
+
 /* The product without a context, for callers that cannot allocate device memory (a frozen
  * memory plan, a process whose device footprint must not grow, a plug-in that only gets a
  * stream and buffers).  Same arguments and result as aotx_q8_matmul; the scratch the kernel

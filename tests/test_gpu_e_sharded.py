@@ -43,6 +43,19 @@ def _worker(rank, world, port, result):
     # a different split of the rows changes where tiles are cut between blocks, hence the
     # order of a few float additions: equal to float rounding, not bit for bit
     ok = ok and bool((y - want).abs().max() <= 1e-4 * want.abs().max())
+    # the same split with the gather fused into the product's stores (symmetric memory)
+    from aotx_b200.sharded import ColumnSplitFused
+    nf, kf = 3072, 1024
+    wf = aotx_b200.synth_q8_0(nf, kf, 15)
+    f0, f1 = ColumnSplit.shard_bytes(nf, kf, world, rank)
+    fused = ColumnSplitFused(ctx, torch.from_numpy(wf[f0:f1].copy()).cuda(), nf, kf, world, rank, 16,
+                             torch.float32)
+    xf = x[:, :kf].contiguous()
+    for _ in range(2):
+        yf = fused.matmul(xf, m)
+    wantf = ctx.matmul(torch.from_numpy(wf).cuda(), nf, kf, xf)
+    torch.cuda.synchronize()
+    ok = ok and bool((yf - wantf).abs().max() <= 1e-4 * wantf.abs().max())
     # expert parallel
     experts, used, hidden, ffn, tokens_all = 16, 4, 512, 256, 40
     wg = aotx_b200.synth_q8_0(experts * ffn, hidden, 1)
