@@ -57,8 +57,13 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
         cursor[e] = 0u;
     }
     __syncthreads();
+    // A selection outside the expert table is left out of both passes (its result row is then
+    // never written), rather than indexing past the tables.
     for (unsigned int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        atomicAdd(&count[ids[p]], 1u);
+        unsigned int e = ids[p];
+        if (e < experts) {
+            atomicAdd(&count[e], 1u);
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0u) {
@@ -80,8 +85,10 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
     __syncthreads();
     for (unsigned int p = threadIdx.x; p < pairs; p += blockDim.x) {
         unsigned int e = ids[p];
-        unsigned int at = offset[e] + atomicAdd(&cursor[e], 1u);
-        sorted_pair[at] = p;
+        if (e < experts) {
+            unsigned int at = offset[e] + atomicAdd(&cursor[e], 1u);
+            sorted_pair[at] = p;
+        }
     }
     for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
         unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;

@@ -58,6 +58,17 @@ def test_every_scale_and_byte(ctx, oracle):
     assert np.array_equal(got, oracle.dequant(w_host, k, 0, n))
 
 
+def test_whole_projection(ctx, oracle):
+    """A whole 4096 x 4096 tensor of the benchmark's distribution, 16.8 M values, bit for bit."""
+    import aotx_b200
+    torch = torch_mod()
+    n = k = 4096
+    w_host = aotx_b200.synth_q8_0(n, k, 33)
+    out = ctx.dequant(dev_weights(w_host), k, 0, n)
+    got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, oracle.dequant(w_host, k, 0, n))
+
+
 def test_row_window_and_unaligned_output(ctx, oracle):
     import aotx_b200
     torch = torch_mod()

@@ -101,6 +101,20 @@ def test_reference_fixture_recipe_tensor_path(ctx, oracle):
     assert bad == 0, worst
 
 
+@pytest.mark.parametrize("n,k,m", [(9728, 2560, 1), (2560, 9728, 8), (2560, 2560, 1)])
+def test_reference_rate_shapes(ctx, oracle, n, k, m):
+    """The other shapes of the reference's rate cases (tests/matrix_test.cu:754-760), its own
+    generator, both kernel families against each other and against sampled oracle sums."""
+    import aotx_b200
+    w = oracle.build(n, k, SEED + 640)
+    x = oracle.input(m, k, SEED + 642)
+    tensor = _run(ctx, w, n, k, x.view(np.float16), m, path=aotx_b200.PATH_TENSOR)[:m]
+    general = _run(ctx, w, n, k, x.view(np.float16), m, path=aotx_b200.PATH_GENERAL)[:m]
+    assert oracle.spot(w, n, k, x, m, tensor, count=256)[0] == 0
+    assert oracle.spot(w, n, k, x, m, general, count=256)[0] == 0
+    assert np.abs(tensor - general).max() <= 1e-2 * np.abs(general).max() + 1e-3
+
+
 def test_live_batch_from_device_word(ctx, oracle):
     """One call shape, several live batches: rows at and past the live batch stay as they
     were (the contract of cuda/model/product.cu:24-49)."""
