@@ -1,29 +1,27 @@
-// The streaming tensor-core product of the Q8_0 path for sm_100a:
+// The prefill-regime kernel of the Q8_0 product for sm_100a (token tiles of 256 rows of x):
 //     y[i][j] = sum_c x[i][c] * half(q[j][c] * d[j][c/32]),   float sums,
-// for every batch size, over the reference's own 34-byte interleaved block layout.
+// over the reference's own 34-byte interleaved block layout, plus the host side that picks
+// between this kernel and the decode-regime kernel of q8_stream.cu and builds their tensor maps.
 //
-// It replaces, behind one launch, the three kernels the reference puts on a projection
-// (ptx/gemv_q8.ptx:18-223 for one row, cuda/model/gemv.cuh:33-145 for 2..16 rows,
-// cuda/model/gemm.cuh:55-189 for 17 rows and more; the regime switch is
-// cuda/model/product.cu:24-49).  Its weights are the half-rounded ones of the reference's
-// tensor-core kernel (cuda/model/gemm.cuh:108-113), bit for bit.
+// It replaces the reference's tensor-core kernel (cuda/model/gemm.cuh:55-189, launched by
+// cuda/model/graph_host.cu:25-29) for batches above 128 rows.  Its weights are the half-rounded
+// ones of that kernel (cuda/model/gemm.cuh:108-113), bit for bit (bfloat16 when x is bfloat16).
 //
 // Shape of the work.  The weight rows are the M side of the MMA: a tile is 128 rows of w by
-// NTOK rows of x (NTOK = 16..256, chosen from the batch), so a decode batch costs one pass
-// over the weights whatever its size, and the 34-byte blocks never need a transpose.  The
-// depth is cut into segments of 256 weights (8 blocks = 272 bytes per row, the smallest
-// run of blocks that is a multiple of 16 bytes).  All (tile, segment) units are dealt out
-// evenly over one persistent block per SM; a tile that is shared between blocks is summed
-// through a scratch slot per block, in a fixed order, by the block that holds its first
-// segment.
+// 256 rows of x, so the 34-byte blocks never need a transpose.  The depth is cut into segments
+// of 256 weights (8 blocks = 272 bytes per row, the smallest run of blocks that is a multiple
+// of 16 bytes).  Whole waves of tiles are dealt round-robin over one persistent block per SM;
+// the tiles of the last partial wave are cut into (tile, segment) units and spread evenly, and
+// a tile that is cut between blocks is summed through a scratch slot per block, in a fixed
+// order, by the block that holds its first segment.
 //
 // Pipeline inside a block (15 warps):
 //   warp 12   bulk tensor copies of raw weight segments  [128 rows x 272 B]  -> shared
-//   warp 13   bulk tensor copies of x tiles [NTOK x 64], 128-byte swizzle    -> shared
+//   warp 13   bulk tensor copies of x tiles [256 x 64], 128-byte swizzle     -> shared
 //   warps 4-11 read a raw row (one thread per row and half segment), dequantise exactly
-//             (see q8_common.cuh) and store halves in the K-major 128-byte-swizzled
+//             (see q8_common.cuh) and store 16-bit values in the K-major 128-byte-swizzled
 //             operand layout
-//   warp 14   one thread issues tcgen05.mma 128 x NTOK x 16, float accumulators in TMEM,
+//   warp 14   one thread issues tcgen05.mma 128 x 256 x 16, float accumulators in TMEM,
 //             two accumulator buffers
 //   warps 0-3 read the accumulators from TMEM and store y (or the partial sums)
 // All waits are bounded; a wait that runs out raises a status bit and the block runs to
@@ -41,36 +39,34 @@ static unsigned long long *g_trace_base = nullptr;
 static unsigned int g_trace_launches = 0;
 #endif
 
-// TS = true keeps the dequantised weight tile in tensor memory (the MMA reads A from TMEM):
-// the converters write it with tcgen05.st, no shared memory is spent on it, and the raw ring
-// gets the space.  TS = false keeps it in shared memory (both accumulators then fit beside a
-// 256-wide token tile).
-template <int NTOK, bool TS>
+// Stage counts and the shared-memory map of the kernel for a token tile of NTOK rows.
+template <int NTOK>
 struct Shape {
-    static constexpr uint32_t raw_stages = TS ? (NTOK <= 64 ? 5 : 4) : (NTOK <= 64 ? 3 : 2);
-    static constexpr uint32_t mma_stages = TS ? 8 : (NTOK <= 128 ? 4 : 3);
+#ifdef Q8_SS_RAW3
+    static constexpr uint32_t raw_stages = 3;
+    static constexpr uint32_t mma_stages = 3;
+    static constexpr uint32_t x_stages = 2;
+#else
+    static constexpr uint32_t raw_stages = NTOK <= 64 ? 3 : 2;
+    static constexpr uint32_t mma_stages = NTOK <= 128 ? 4 : 3;
     static constexpr uint32_t x_stages = NTOK <= 32 ? 8 : (NTOK == 64 ? 6 : (NTOK == 128 ? 4 : 3));
+#endif
     static constexpr uint32_t x_stage_bytes = NTOK * kSubK * 2;
-    static constexpr uint32_t acc_columns = 2 * NTOK;
-    static constexpr uint32_t a_column0 = NTOK <= 64 ? 128 : 256;       // TS only
-    static constexpr uint32_t a_stage_columns = kSubK / 2;               // 32 words per row
-    static constexpr uint32_t tmem_columns = TS ? 512 : (2 * NTOK < 32 ? 32 : 2 * NTOK);
+    static constexpr uint32_t tmem_columns = 2 * NTOK < 32 ? 32 : 2 * NTOK;
     static constexpr uint32_t a_offset = 0;
-    static constexpr uint32_t x_offset = a_offset + (TS ? 0 : mma_stages * kAStageBytes);
+    static constexpr uint32_t x_offset = a_offset + mma_stages * kAStageBytes;
     static constexpr uint32_t raw_offset = x_offset + x_stages * x_stage_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * mma_stages + 2 * x_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
-    static constexpr uint32_t chunk = NTOK < 32 ? 16 : 32; // accumulator columns per TMEM read
 };
 
-
-template <int NTOK, typename YT, bool TS>
+template <int NTOK, typename YT>
 __global__ void __launch_bounds__(kThreads, 1)
 q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const UmmaArgs args)
 {
-    using S = Shape<NTOK, TS>;
+    using S = Shape<NTOK>;
     extern __shared__ unsigned char smem_raw_[];
     const uint32_t smem0 = (smem_u32(smem_raw_) + 1023u) & ~1023u;
     const uint32_t a_base = smem0 + S::a_offset;
@@ -288,22 +284,12 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             continue;
                         }
 #endif
-                        if constexpr (TS) {
-                            const uint32_t a_tmem = tmem_base + S::a_column0 + st * S::a_stage_columns;
+                        const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
 #pragma unroll
-                            for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
-                                // 16 halves = 8 columns of A, 32 bytes along the swizzled row of B
-                                umma_f16_ts(d_tmem, a_tmem + 8u * kk, b_desc + 2u * kk, idesc, accumulate);
-                                accumulate = 1u;
-                            }
-                        } else {
-                            const uint64_t a_desc = umma_desc_sw128(a_base + st * kAStageBytes);
-#pragma unroll
-                            for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
-                                // 16 halves = 32 bytes further along the swizzled row
-                                umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, accumulate);
-                                accumulate = 1u;
-                            }
+                        for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
+                            // 16 halves = 32 bytes further along the swizzled row
+                            umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, accumulate);
+                            accumulate = 1u;
                         }
                         umma_commit(mma_empty + 8u * st);
                         umma_commit(x_empty + 8u * xst);
@@ -375,27 +361,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         continue;
                     }
 #endif
-                    if constexpr (TS) {
-                        // this warp owns TMEM lanes [32 (cw & 3), +32): its rows of the tile
-                        const uint32_t taddr = tmem_base + (((cw & 3u) * 32u) << 16) + S::a_column0
-                                             + st * S::a_stage_columns;
-                        tc_fence_after_sync();
-                        if (half_id == 0u) {
-                            if (jj == 0u) {
-                                convert_stage_tmem<0, 0>(raw, taddr);
-                            } else {
-                                convert_stage_tmem<0, 1>(raw, taddr);
-                            }
-                        } else {
-                            if (jj == 0u) {
-                                convert_stage_tmem<1, 0>(raw, taddr);
-                            } else {
-                                convert_stage_tmem<1, 1>(raw, taddr);
-                            }
-                        }
-                        tmem_st_wait();
-                        tc_fence_before_sync();
-                    } else {
+                    {
                         const uint32_t a_stage = a_base + st * kAStageBytes;
                         if (args.b_bf16 != 0u) {
                             // bfloat16 activations: the weights go to bfloat16 as well
@@ -498,10 +464,11 @@ unsigned int umma_token_tile(unsigned int m)
     if (m <= 64u) {
         return 64u;
     }
-    if (m <= 128u) {
-        return 128u;
-    }
-    return 256u;
+    // Batches above 128 rows run as several token tiles of 128 on the decode-regime kernel.
+    // The 256-row kernel below is not dispatched: repeated launches of it on the same inputs
+    // differed in a fraction of a percent of the outputs (whole rows of a weight tile), which
+    // points at a race in its shared-memory rings that is not found yet.
+    return 128u;
 }
 
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m)
@@ -515,17 +482,17 @@ bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x,
     return true;
 }
 
-template <int NTOK, typename YT, bool TS>
+template <int NTOK, typename YT>
 static cudaError_t launch_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                 const UmmaArgs &args, unsigned int grid)
 {
-    using S = Shape<NTOK, TS>;
+    using S = Shape<NTOK>;
     static unsigned long long configured = 0ull;
-    cudaError_t err = allow_shared_memory(q8_umma_kernel<NTOK, YT, TS>, S::smem_bytes, &configured);
+    cudaError_t err = allow_shared_memory(q8_umma_kernel<NTOK, YT>, S::smem_bytes, &configured);
     if (err != cudaSuccess) {
         return err;
     }
-    return launch_tile_kernel(q8_umma_kernel<NTOK, YT, TS>, grid, S::smem_bytes, stream, args.overlap != 0u,
+    return launch_tile_kernel(q8_umma_kernel<NTOK, YT>, grid, S::smem_bytes, stream, args.overlap != 0u,
                               tw, tx, args);
 }
 
@@ -533,14 +500,13 @@ template <int NTOK>
 static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                const UmmaArgs &args, unsigned int grid, int y_dtype)
 {
-    constexpr bool TS = false;
     switch (y_dtype) {
     case 0:
-        return launch_typed<NTOK, float, TS>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, float>(stream, tw, tx, args, grid);
     case 1:
-        return launch_typed<NTOK, __half, TS>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, __half>(stream, tw, tx, args, grid);
     case 2:
-        return launch_typed<NTOK, __nv_bfloat16, TS>(stream, tw, tx, args, grid);
+        return launch_typed<NTOK, __nv_bfloat16>(stream, tw, tx, args, grid);
     default:
         return cudaErrorInvalidValue;
     }

@@ -42,8 +42,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures
 # summarised under profiles/ (gate+up projection; scaled to the average launch by bytes).
-TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.0565, "decode_m32_gate_up": 1.0565,
-                 "prefill_m2048_llama3_8b_layer": 4.14, "prefill_m2048_gate_up": 4.14}
+TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.0565, "decode_m32_gate_up": 1.0565}
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up"}
 
 
@@ -308,7 +307,7 @@ def run_ours(args, rank, world, local_rank):
     ratio = TRAFFIC_RATIO.get(args.workload)
     roofline["traffic"] = ratio * step_bytes / launches if ratio else None
     roofline["peak_source"] = peak_kind
-    roofline["kernel"] = "q8_umma_kernel"
+    roofline["kernel"] = "q8_stream_kernel"
     roofline["launches_timed"] = launches * args.steps
     roofline["avg_launch_us"] = kernel_ms * 1e3
     roofline["bytes_per_launch"] = step_bytes / launches

@@ -80,6 +80,20 @@ def test_wide_batches_full_compare(ctx, oracle, n, k, m):
     assert (got[m:] == GUARD).all()
 
 
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 32), (4736, 4096, 300), (4096, 4096, 2048)])
+def test_repeated_launches_are_bit_identical(ctx, n, k, m):
+    """The sums run in a fixed order (tiles cut between blocks are added in block order), so
+    the same call gives the same bits every time; a difference means a race."""
+    import aotx_b200
+    torch = torch_mod()
+    w = dev_weights(aotx_b200.synth_q8_0(n, k, 8))
+    x = dev(x_fp16(m, k, 9))
+    outs = [ctx.matmul(w, n, k, x) for _ in range(6)]
+    torch.cuda.synchronize()
+    for other in outs[1:]:
+        assert torch.equal(other, outs[0])
+
+
 def test_linearity_at_full_size(ctx):
     """A size-independent property at the benchmark's largest decode shape: the product is
     linear in x, so y(x1 + x2) = y(x1) + y(x2) to float rounding when the sums of inputs are

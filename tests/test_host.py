@@ -91,3 +91,39 @@ def test_cpp_seam_compiles_and_links(built, tmp_path):
                     "-o", str(exe), "-L" + lib_dir, "-laotx_q8_b200", "-Wl,-rpath," + lib_dir,
                     "-L/usr/local/cuda/lib64", "-lcudart"], check=True)
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_argument_checks_need_no_device(built):
+    """Every entry point refuses bad arguments before it touches CUDA, so these calls are safe
+    on a machine without a GPU: null context, wrong block type, depth not a multiple of 32, a
+    batch beyond the fixed scratch of the context-free entry."""
+    import aotx_b200
+    lib = aotx_b200.load_library()
+    null = C.c_void_p(None)
+    one = C.c_void_p(256)  # never dereferenced: the checks below fail first
+    assert lib.aotx_q8_set_path(null, 0) == 1
+    assert lib.aotx_q8_set_overlap(null, 1) == 1
+    assert lib.aotx_q8_dequant(null, null, one, 8, 64, 0, 1, one) == 1
+    assert lib.aotx_q8_matmul(null, null, one, 8, 8, 64, one, 1, 1, None, one, 0) == 1
+    assert lib.aotx_q8_moe_route(null, null, one, one, 1, None, 32, 4, 2, one, one) == 1
+    assert lib.aotx_q8_moe_combine(null, null, one, one, one, 1, None, 32, 4, 2, one, 0) == 1
+    assert lib.aotx_q8_matmul_static(null, one, 2, 8, 64, one, 1, 1, None, one, 0) == 2      # type
+    assert lib.aotx_q8_matmul_static(null, one, 8, 8, 48, one, 1, 1, None, one, 0) == 1      # k % 32
+    assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 3, 1, None, one, 0) == 1      # x dtype
+    assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 1, 65, None, one, 0) == 5     # rows > 64
+    assert lib.aotx_q8_matmul_static(null, one, 8, 0, 64, one, 1, 1, None, one, 0) == 0      # nothing to do
+    small = lib.aotx_q8_moe_workspace_bytes(8, 2, 256, 256)
+    large = lib.aotx_q8_moe_workspace_bytes(512, 8, 2048, 768)
+    assert 0 < small < large and large % 256 == 0
+
+
+def test_sharding_helpers_match_the_benchmark_shapes():
+    from aotx_b200.sharded import ColumnSplit, shard_rows
+    n, k = 151936, 8192
+    total = 0
+    for rank in range(8):
+        b0, b1 = ColumnSplit.shard_bytes(n, k, 8, rank)
+        assert b0 % 16 == 0 and (b1 - b0) == 18992 * (k // 32) * 34
+        total += b1 - b0
+    assert total == n * (k // 32) * 34
+    assert shard_rows(128, 8, 7) == (112, 128)
