@@ -21,6 +21,7 @@ constexpr uint32_t kAStageBytes = kRows * kSubK * 2;     // 16384
 constexpr uint32_t kThreads = 15 * 32;
 constexpr uint32_t kEpilogueWarps = 4;
 constexpr uint32_t kConvertWarp0 = 4;
+constexpr uint32_t kConvertThreads = 8 * 32;                // warps 4..11
 constexpr uint32_t kWeightWarp = 12;
 constexpr uint32_t kInputWarp = 13;
 constexpr uint32_t kMmaWarp = 14;

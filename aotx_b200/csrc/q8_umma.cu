@@ -42,15 +42,9 @@ static unsigned int g_trace_launches = 0;
 // Stage counts and the shared-memory map of the kernel for a token tile of NTOK rows.
 template <int NTOK>
 struct Shape {
-#ifdef Q8_SS_RAW3
-    static constexpr uint32_t raw_stages = 3;
-    static constexpr uint32_t mma_stages = 3;
-    static constexpr uint32_t x_stages = 2;
-#else
     static constexpr uint32_t raw_stages = NTOK <= 64 ? 3 : 2;
     static constexpr uint32_t mma_stages = NTOK <= 128 ? 4 : 3;
     static constexpr uint32_t x_stages = NTOK <= 32 ? 8 : (NTOK == 64 ? 6 : (NTOK == 128 ? 4 : 3));
-#endif
     static constexpr uint32_t x_stage_bytes = NTOK * kSubK * 2;
     static constexpr uint32_t tmem_columns = 2 * NTOK < 32 ? 32 : 2 * NTOK;
     static constexpr uint32_t a_offset = 0;
@@ -137,14 +131,14 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
             mbar_init(raw_full + 8u * i, 1u);
-            mbar_init(raw_empty + 8u * i, 8u);
+            mbar_init(raw_empty + 8u * i, kConvertThreads);
         }
         for (uint32_t i = 0; i < S::x_stages; ++i) {
             mbar_init(x_full + 8u * i, 1u);
             mbar_init(x_empty + 8u * i, 1u);
         }
         for (uint32_t i = 0; i < S::mma_stages; ++i) {
-            mbar_init(a_full + 8u * i, 4u);
+            mbar_init(a_full + 8u * i, kConvertThreads / 2u);
             mbar_init(mma_empty + 8u * i, 1u);
         }
         for (uint32_t i = 0; i < 2u; ++i) {
@@ -339,10 +333,8 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 } else {
                     load_raw<1>(raw_row, raw);
                 }
-                __syncwarp();
-                if (lane == 0u) {
-                    mbar_arrive(raw_empty + 8u * rst);
-                }
+                // every thread releases the stage itself, after its own loads
+                mbar_arrive(raw_empty + 8u * rst);
 #pragma unroll
                 for (uint32_t jj = 0; jj < 2u; ++jj) {
                     const uint32_t q = g * kSubs + half_id * 2u + jj;
@@ -352,12 +344,10 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         ok = false;
                         break;
                     }
+                    tc_fence_after_sync();
 #ifdef Q8_EXPERIMENT
                     if (args.debug & 2u) {
-                        __syncwarp();
-                        if (lane == 0u) {
-                            mbar_arrive(a_full + 8u * st);
-                        }
+                        mbar_arrive(a_full + 8u * st);
                         continue;
                     }
 #endif
@@ -393,10 +383,8 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         }
                         fence_proxy_async_smem();
                     }
-                    __syncwarp();
-                    if (lane == 0u) {
-                        mbar_arrive(a_full + 8u * st);
-                    }
+                    // every thread publishes its own row: its stores, its proxy fence, its arrival
+                    mbar_arrive(a_full + 8u * st);
                 }
             }
         }
@@ -468,6 +456,11 @@ unsigned int umma_token_tile(unsigned int m)
     // The 256-row kernel below is not dispatched: repeated launches of it on the same inputs
     // differed in a fraction of a percent of the outputs (whole rows of a weight tile), which
     // points at a race in its shared-memory rings that is not found yet.
+#ifdef Q8_EXPERIMENT
+    if (m > 128u && getenv("Q8_WIDE_TILE") != nullptr) {
+        return 256u;
+    }
+#endif
     return 128u;
 }
 
