@@ -75,11 +75,34 @@ struct UmmaArgs {
 };
 
 // The units [begin, end) of block `b` out of `blocks`, of `units` in all.
-__device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks, unsigned long long units,
-                                           unsigned long long *begin, unsigned long long *end)
+__host__ __device__ __forceinline__ void unit_range(unsigned int b, unsigned int blocks,
+                                                    unsigned long long units, unsigned long long *begin,
+                                                    unsigned long long *end)
 {
     *begin = (unsigned long long)b * units / blocks;
     *end = (unsigned long long)(b + 1u) * units / blocks;
+}
+
+// A tile that is cut between blocks is finished by block `b`, which holds its first segment.
+// Returns the last of the blocks after `b` that hold later segments of the tile, whose units
+// end at `tile_end` (b itself if there is none).
+__host__ __device__ __forceinline__ unsigned int last_holder(unsigned int b, unsigned int blocks,
+                                                             unsigned long long units,
+                                                             unsigned long long tile_end)
+{
+    unsigned int last_cc = b;
+    for (unsigned int cc = b + 1u; cc < blocks; ++cc) {
+        unsigned long long ob, oe;
+        unit_range(cc, blocks, units, &ob, &oe);
+        if (ob >= tile_end) {
+            break;
+        }
+        last_cc = cc;
+        if (oe >= tile_end) {
+            break;
+        }
+    }
+    return last_cc;
 }
 
 // Dequantise the two blocks of one MMA stage that this thread owns and store them as 8
@@ -192,7 +215,7 @@ struct WorkIter {
     uint32_t dp_first;
     uint32_t dp_stride;
 
-    __device__ __forceinline__ bool next(uint32_t &tile, uint32_t &s0, uint32_t &s1)
+    __host__ __device__ __forceinline__ bool next(uint32_t &tile, uint32_t &s0, uint32_t &s1)
     {
         if (u < u_end) {
             tile = sk_tile0 + (uint32_t)(u / segs);
@@ -277,17 +300,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     // The other holders of this tile are the blocks right after this one, up to `last_cc`.
     unsigned int last_cc = blockIdx.x;
     if (owner && !whole) {
-        for (unsigned int cc = blockIdx.x + 1u; cc < blocks; ++cc) {
-            unsigned long long ob, oe;
-            unit_range(cc, blocks, units, &ob, &oe);
-            if (ob >= tile_end) {
-                break;
-            }
-            last_cc = cc;
-            if (oe >= tile_end) {
-                break;
-            }
-        }
+        last_cc = last_holder(blockIdx.x, blocks, units, tile_end);
         // Wait for their partial sums; each lane watches one of them.
         for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
             const unsigned int cc = base + lane;
