@@ -206,8 +206,8 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     cudaStream_t s = (cudaStream_t)stream;
     /* One MMA takes both operands in one 16-bit format (binary16 weights against bfloat16
      * activations raise an illegal-instruction fault on sm_100a), so for bfloat16 activations
-     * the decode kernel turns the x tiles into binary16 in shared memory and the 256-row
-     * kernel dequantises the weights to bfloat16. */
+     * the streaming kernel turns the x tiles into binary16 in shared memory (values beyond the
+     * binary16 range saturate). */
     bool tensor_ok = q8::umma_supports(w, n, k, x, m);
     if (ctx->path == AOTX_Q8_PATH_TENSOR && !tensor_ok) {
         return AOTX_Q8_ERR_UNSUPPORTED;

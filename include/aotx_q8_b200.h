@@ -15,6 +15,12 @@
  * is enqueued and no output is written (the reference's kernels likewise write nothing for a
  * type they do not know: cuda/model/dequant.cu:24-25, cuda/model/gemm.cuh:236-237).
  *
+ * Devices and threads: a context belongs to the device it was made for; the caller keeps that
+ * device current in the calling thread and passes one of its streams, as the reference does
+ * for its own launches.  A context keeps a launch counter and alternating scratch sets, so
+ * calls on one context come from one thread at a time, and products on one context that run
+ * on different streams at the same time need a context each (they would share the scratch).
+ *
  * Paths are relative to the reference's source root.
  */
 #ifndef AOTX_Q8_B200_H
@@ -86,6 +92,9 @@ int aotx_q8_dequant(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type
 
 /* y[i][j] = sum_c x[i][c] * w[j][c], float sums, for i < m and j < n; no other element of y
  * is written.  x is [m][k] of x_dtype (F16 or BF16), y is [m][n] of y_dtype.
+ * BF16 activations enter the tensor-core kernel as binary16: exact for magnitudes from 2^-14
+ * to 65504, rounded below that range and saturated above it (activations after a norm layer
+ * are far inside it); the general kernel reads them as they are.
  * If m_dev is not null it points to a device word holding the live batch; the product then
  * covers min(*m_dev, m) rows, read on the device at run time, so one captured node serves
  * every batch up to m.  With x F16, y F32 and m_dev this is the whole of
