@@ -93,6 +93,28 @@ def test_cpp_seam_compiles_and_links(built, tmp_path):
     assert subprocess.run([str(exe)]).returncode == 0
 
 
+def test_cpp_seam_program_builds_and_fails_loudly_without_a_device(built, tmp_path):
+    """The C++ parity program of the seam (run on the GPU by test_gpu_g_seam.py) compiles and
+    links here; on a machine without a GPU its first call reports the CUDA error and stops."""
+    import shutil
+    import subprocess
+    import torch
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    exe = tmp_path / "seam_check"
+    lib_dir = os.path.dirname(built)
+    subprocess.run([nvcc, "-O1", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+                    "-I", os.path.join(ROOT, "include"), "-o", str(exe),
+                    os.path.join(ROOT, "tests", "seam_check.cu"), "-L", lib_dir, "-laotx_q8_b200",
+                    "-Xlinker", "-rpath", "-Xlinker", lib_dir], check=True, timeout=900)
+    if torch.cuda.is_available():
+        return
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 1
+    assert "aotx_q8_init" in run.stderr
+
+
 def test_argument_checks_need_no_device(built):
     """Every entry point refuses bad arguments before it touches CUDA, so these calls are safe
     on a machine without a GPU: null context, wrong block type, depth not a multiple of 32, a
