@@ -13,6 +13,22 @@ SYMBOLS = (
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_matmul_peers",
 )
 
+# every symbol include/aotx_gguf_b200.h declares
+GGUF_SYMBOLS = (
+    "aotx_gguf_open", "aotx_gguf_close", "aotx_gguf_file_bytes", "aotx_gguf_header_bytes",
+    "aotx_gguf_data_bytes", "aotx_gguf_alignment", "aotx_gguf_tensor_count", "aotx_gguf_tensor",
+    "aotx_gguf_find", "aotx_gguf_u32", "aotx_gguf_u64", "aotx_gguf_f32", "aotx_gguf_string",
+    "aotx_gguf_array", "aotx_gguf_read", "aotx_gguf_read_threads", "aotx_gguf_row_bytes", "aotx_gguf_row_range",
+    "aotx_gguf_loader_init", "aotx_gguf_loader_destroy", "aotx_gguf_loader_last_cuda_error",
+    "aotx_gguf_upload",
+)
+
+
+class TensorInfo(C.Structure):
+    """aotx_gguf_tensor_info of include/aotx_gguf_b200.h."""
+    _fields_ = [("name", C.c_char * 128), ("dim_count", C.c_uint32), ("type", C.c_uint32),
+                ("dims", C.c_uint64 * 4), ("offset", C.c_uint64), ("bytes", C.c_uint64)]
+
 
 class LibraryMissing(RuntimeError):
     pass
@@ -52,5 +68,31 @@ def load_library():
         fn = getattr(lib, name)
         if name != "aotx_q8_moe_workspace_bytes":
             fn.restype = i32
+    u64, info = C.c_uint64, C.POINTER(TensorInfo)
+    lib.aotx_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.aotx_gguf_close.argtypes = [vp]
+    lib.aotx_gguf_close.restype = None
+    for name in ("aotx_gguf_file_bytes", "aotx_gguf_header_bytes", "aotx_gguf_data_bytes",
+                 "aotx_gguf_tensor_count"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = u64
+    lib.aotx_gguf_alignment.argtypes = [vp]
+    lib.aotx_gguf_alignment.restype = u32
+    lib.aotx_gguf_tensor.argtypes = [vp, u64, info]
+    lib.aotx_gguf_find.argtypes = [vp, C.c_char_p, info]
+    lib.aotx_gguf_u32.argtypes = [vp, C.c_char_p, C.POINTER(u32)]
+    lib.aotx_gguf_u64.argtypes = [vp, C.c_char_p, C.POINTER(u64)]
+    lib.aotx_gguf_f32.argtypes = [vp, C.c_char_p, C.POINTER(C.c_float)]
+    lib.aotx_gguf_string.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
+    lib.aotx_gguf_array.argtypes = [vp, C.c_char_p, C.POINTER(u32), C.POINTER(u64)]
+    lib.aotx_gguf_read.argtypes = [vp, u64, u64, vp]
+    lib.aotx_gguf_read_threads.argtypes = [vp, u64, u64, vp, u32]
+    lib.aotx_gguf_row_bytes.argtypes = [u32, u64]
+    lib.aotx_gguf_row_bytes.restype = u64
+    lib.aotx_gguf_row_range.argtypes = [info, u64, u64, C.POINTER(u64), C.POINTER(u64)]
+    lib.aotx_gguf_loader_init.argtypes = [C.POINTER(vp), i32, C.c_size_t]
+    lib.aotx_gguf_loader_destroy.argtypes = [vp]
+    lib.aotx_gguf_loader_last_cuda_error.argtypes = [vp]
+    lib.aotx_gguf_upload.argtypes = [vp, vp, u64, u64, vp, vp]
     _lib = lib
     return lib

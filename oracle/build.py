@@ -2,7 +2,8 @@
 
 `build_oracle()` compiles the C restatement beside this file into `libq8_oracle.so`.
 `build_ref()` compiles the reference's own sources, from where they lie in a reference tree,
-into `_ref/libaotx_ref.so`; it needs that tree and is skipped (returns None) without it.
+into `_ref/libaotx_ref.so`, `build_gguf_ref()` the reference's model-file reader into
+`_ref/libgguf_ref.so`; both need that tree and are skipped (return None) without it.
 Nothing here is imported by the product package.
 """
 import os
@@ -64,6 +65,25 @@ def build_ref(force=False):
     return REF_SO
 
 
+GGUF_REF_SO = os.path.join(REF_DIR, "libgguf_ref.so")
+
+
+def build_gguf_ref(force=False):
+    """Compile the reference's model-file reader (disk/modelfile/gguf.c and meta.c, plain C, no
+    dependency outside its own headers), unmodified, from where it lies in the reference tree.
+    It is the checker of the product's own reader (aotx_b200/csrc/gguf_table.cpp)."""
+    root = reference_root()
+    if root is None or shutil.which("gcc") is None:
+        return GGUF_REF_SO if os.path.exists(GGUF_REF_SO) else None
+    sources = [os.path.join(root, "disk", "modelfile", name) for name in ("gguf.c", "meta.c")]
+    if not force and os.path.exists(GGUF_REF_SO):
+        return GGUF_REF_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-I" + root, "-o", GGUF_REF_SO, *sources], check=True)
+    return GGUF_REF_SO
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    print(build_gguf_ref(force="--force" in sys.argv))
