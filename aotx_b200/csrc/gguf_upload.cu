@@ -152,3 +152,49 @@ extern "C" int aotx_gguf_upload(aotx_gguf_loader *loader, const aotx_gguf *file,
     }
     return AOTX_GGUF_OK;
 }
+
+extern "C" int aotx_gguf_upload_rows(aotx_gguf_loader *loader, const aotx_gguf *file, uint64_t offset,
+                                     uint64_t row_bytes, uint64_t rows, void *device_dst, uint64_t dst_pitch,
+                                     void *stream)
+{
+    if (loader == nullptr || file == nullptr || (device_dst == nullptr && rows > 0) || row_bytes == 0
+        || dst_pitch < row_bytes) {
+        return AOTX_GGUF_ERR_READ;
+    }
+    const uint64_t have = aotx_gguf_data_bytes(file);
+    if (rows > have / row_bytes || offset > have - rows * row_bytes) {
+        return AOTX_GGUF_ERR_FORMAT;
+    }
+    const uint64_t per_piece = loader->piece / row_bytes; // whole rows per pinned buffer
+    if (per_piece == 0) {
+        return AOTX_GGUF_ERR_READ;
+    }
+    DeviceScope scope(loader->device);
+    if (scope.error() != cudaSuccess) {
+        return cuda_fail(loader, scope.error());
+    }
+    unsigned char *dst = static_cast<unsigned char *>(device_dst);
+    for (uint64_t row = 0; row < rows; row += per_piece) {
+        const uint64_t count = rows - row < per_piece ? rows - row : per_piece;
+        const unsigned int slot = loader->turn & 1u;
+        cudaError_t err = cudaEventSynchronize(loader->done[slot]);
+        if (err != cudaSuccess) {
+            return cuda_fail(loader, err);
+        }
+        int code = aotx_gguf_read_threads(file, offset + row * row_bytes, count * row_bytes, loader->host[slot],
+                                          loader->threads);
+        if (code != 0) {
+            return code;
+        }
+        err = cudaMemcpy2DAsync(dst + row * dst_pitch, (size_t)dst_pitch, loader->host[slot], (size_t)row_bytes,
+                                (size_t)row_bytes, (size_t)count, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+        if (err == cudaSuccess) {
+            err = cudaEventRecord(loader->done[slot], (cudaStream_t)stream);
+        }
+        if (err != cudaSuccess) {
+            return cuda_fail(loader, err);
+        }
+        loader->turn += 1u;
+    }
+    return AOTX_GGUF_OK;
+}

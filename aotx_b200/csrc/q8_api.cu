@@ -222,6 +222,50 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
 }
 
+extern "C" int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                                    uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                                    void *y, int y_dtype, int epilogue)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (epilogue == AOTX_Q8_EPILOGUE_STORE) {
+        return aotx_q8_matmul(ctx, stream, w, type, n, k, x, x_dtype, m, m_dev, y, y_dtype);
+    }
+    if (epilogue != AOTX_Q8_EPILOGUE_ADD && epilogue != AOTX_Q8_EPILOGUE_SWIGLU) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (!dtype_16(x_dtype) || !dtype_out(y_dtype) || k == 0u || (k % 32u) != 0u
+        || (epilogue == AOTX_Q8_EPILOGUE_ADD && y_dtype != AOTX_Q8_F32)
+        || (epilogue == AOTX_Q8_EPILOGUE_SWIGLU && (n & 1u) != 0u)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (n == 0u || m == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w == nullptr || x == nullptr || y == nullptr || !aligned(w, 2u) || !aligned(x, 4u)
+        || !aligned(y, y_dtype == AOTX_Q8_F32 ? 4u : 2u) || (m_dev != nullptr && !aligned(m_dev, 4u))) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    bool tensor_ok = q8::umma_supports(w, n, k, x, m);
+    if (ctx->path == AOTX_Q8_PATH_TENSOR && !tensor_ok) {
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    cudaError_t err;
+    if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
+        err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y,
+                              y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, (unsigned int)epilogue);
+    } else {
+        err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype,
+                                   (unsigned int)epilogue);
+    }
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
 extern "C" int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f16, const float *router,
                                  uint32_t tokens, const uint32_t *tokens_dev, uint32_t hidden,
                                  uint32_t experts, uint32_t used, float *prob, uint32_t *ids)
@@ -289,6 +333,51 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
         err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, tokens, tokens_dev,
                                            used, base + ws.act, proj);
     }
+    if (err == cudaSuccess) {
+        err = q8::launch_expert_sum(s, proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out,
+                                    out_dtype);
+    }
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" int aotx_q8_moe_ffn_fused(aotx_q8_ctx *ctx, void *stream, const void *w_gate_up, const void *w_down,
+                                     uint32_t type, uint32_t experts, uint32_t hidden, uint32_t ffn,
+                                     const void *x_f16, const float *prob, const uint32_t *ids, uint32_t tokens,
+                                     const uint32_t *tokens_dev, uint32_t used, void *out, int out_dtype,
+                                     void *workspace, size_t workspace_bytes)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    if (experts == 0u || experts > kMaxExperts || used == 0u || used > experts || hidden == 0u || ffn == 0u
+        || (hidden % 32u) != 0u || (ffn % 32u) != 0u || !dtype_out(out_dtype)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (tokens == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w_gate_up == nullptr || w_down == nullptr || x_f16 == nullptr || prob == nullptr || ids == nullptr
+        || out == nullptr || !aligned(x_f16, 4u)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    q8::MoeWorkspace ws = q8::moe_workspace_layout(tokens, used, hidden, ffn, kMaxExperts);
+    if (workspace == nullptr || !aligned(workspace, 256u) || workspace_bytes < ws.bytes) {
+        return AOTX_Q8_ERR_WORKSPACE;
+    }
+    /* only the grouped tensor-core products take the interleaved tensor */
+    if (ctx->path == AOTX_Q8_PATH_GENERAL
+        || !q8::moe_grouped_supports(w_gate_up, w_gate_up, w_down, x_f16, hidden, ffn, experts)) {
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    unsigned char *base = static_cast<unsigned char *>(workspace);
+    float *proj = reinterpret_cast<float *>(base + ws.proj);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t err = q8::launch_moe_grouped_fused(s, ctx->scratch, ctx->sm_count, &ctx->launches,
+                                                   ctx->overlap != 0, w_gate_up, w_down, experts, hidden, ffn,
+                                                   x_f16, ids, tokens, tokens_dev, used, base, ws);
     if (err == cudaSuccess) {
         err = q8::launch_expert_sum(s, proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out,
                                     out_dtype);

@@ -8,12 +8,19 @@ namespace q8 {
 
 // y dtype codes as in the public header: 0 float, 1 half, 2 bfloat16.
 
+// What a product does with a finished sum (the epilogue codes of the public header).
+constexpr unsigned int kEpilogueStore = 0u;
+constexpr unsigned int kEpilogueAdd = 1u;    // y is float and the sum is added to it
+constexpr unsigned int kEpilogueSwiglu = 2u; // rows 2p, 2p+1 of w are gate and up of column p
+
 cudaError_t launch_dequant(cudaStream_t stream, const void *w, unsigned int k, unsigned int first_row,
                            unsigned int rows, void *out);
 
+// `epilogue`: 0 store, 1 add into a float y, 2 silu(gate) * up over row pairs of w into a y of
+// n / 2 columns (the same three modes as the tensor-core kernel, see q8_tile.cuh).
 cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n, unsigned int k,
                              const void *x, int x_bf16, unsigned int m, const unsigned int *m_dev,
-                             void *y, int y_dtype);
+                             void *y, int y_dtype, unsigned int epilogue = 0u);
 
 cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router, unsigned int tokens,
                          const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
@@ -55,7 +62,7 @@ struct PeerOut {
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap, const PeerOut *out = nullptr);
+                        bool overlap, const PeerOut *out = nullptr, unsigned int epilogue = 0u);
 
 // Grouped mode of the decode-regime kernel: tiles from a device table (see q8_tile.cuh).
 struct GroupTile;
@@ -64,7 +71,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
                                 const void *x_sorted, unsigned int x_rows, unsigned int ntok,
                                 const GroupTile *tiles, const unsigned int *count_dev, unsigned int max_tiles,
                                 const unsigned int *row_map, void *y, unsigned int ldy, int y_dtype,
-                                unsigned int set, bool overlap);
+                                unsigned int set, bool overlap, unsigned int epilogue = 0u);
 
 // Routed experts as grouped products (q8_moe.cu).  Offsets are bytes into the workspace.
 struct MoeWorkspace {
@@ -81,6 +88,13 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
                                unsigned int ffn, const void *x, const unsigned int *ids, unsigned int tokens,
                                const unsigned int *tokens_dev, unsigned int used, unsigned char *workspace,
                                const MoeWorkspace &ws);
+
+cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                                     unsigned int *launches, bool overlap, const void *w_gate_up,
+                                     const void *w_down, unsigned int experts, unsigned int hidden,
+                                     unsigned int ffn, const void *x, const unsigned int *ids,
+                                     unsigned int tokens, const unsigned int *tokens_dev, unsigned int used,
+                                     unsigned char *workspace, const MoeWorkspace &ws);
 
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m);
 

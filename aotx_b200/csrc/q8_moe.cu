@@ -177,7 +177,8 @@ MoeWorkspace moe_workspace_layout(unsigned int tokens, unsigned int used, unsign
     MoeWorkspace ws;
     const size_t pairs = (size_t)tokens * used;
     const size_t tok_tiles = pairs / 16u + experts; /* room for the smallest token tile */
-    ws.max_feed = (unsigned int)(tok_tiles * ((ffn + kRows - 1u) / kRows));
+    /* room for the interleaved gate+up form as well, which has twice the rows */
+    ws.max_feed = (unsigned int)(tok_tiles * ((2u * ffn + kRows - 1u) / kRows));
     ws.max_down = (unsigned int)(tok_tiles * ((hidden + kRows - 1u) / kRows));
     size_t at = 0;
     ws.act = at;
@@ -248,6 +249,53 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
     }
     q8_swiglu_kernel<<<148 * 8, 256, 0, stream>>>(gate, up, tokens, tokens_dev, used, ffn, act);
     err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        return err;
+    }
+    return launch_umma_grouped(stream, scratch, sm_count, w_down, experts * hidden, ffn, act, pairs,
+                               tile_tokens, tiles_down, counts + 1, ws.max_down, sorted_pair, proj, hidden,
+                               0, (*launches)++, overlap);
+}
+
+// The same step with gate and up in one tensor, rows interleaved (row 2r of an expert is its
+// gate row r, row 2r + 1 its up row r): one grouped product whose store applies the gated unit
+// and writes the half activations, then the down product.  Two tensor-core launches instead of
+// three and an elementwise kernel, and no float gate / up round trip.
+cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
+                                     unsigned int *launches, bool overlap, const void *w_gate_up,
+                                     const void *w_down, unsigned int experts, unsigned int hidden,
+                                     unsigned int ffn, const void *x, const unsigned int *ids,
+                                     unsigned int tokens, const unsigned int *tokens_dev, unsigned int used,
+                                     unsigned char *workspace, const MoeWorkspace &ws)
+{
+    const unsigned int pairs = tokens * used;
+    const unsigned int tile_tokens = group_tokens();
+    unsigned int *sorted_pair = reinterpret_cast<unsigned int *>(workspace + ws.sorted_pair);
+    unsigned int *counts = reinterpret_cast<unsigned int *>(workspace + ws.counts);
+    GroupTile *tiles_feed = reinterpret_cast<GroupTile *>(workspace + ws.tiles_feed);
+    GroupTile *tiles_down = reinterpret_cast<GroupTile *>(workspace + ws.tiles_down);
+    __half *x_sorted = reinterpret_cast<__half *>(workspace + ws.x_sorted);
+    __half *act = reinterpret_cast<__half *>(workspace + ws.act);
+    float *proj = reinterpret_cast<float *>(workspace + ws.proj);
+
+    // the feed table is built over the 2 * ffn interleaved rows of every expert
+    q8_group_build_kernel<<<1, Q8_GROUP_THREADS, 0, stream>>>(ids, tokens, tokens_dev, used, experts, 2u * ffn,
+                                                              hidden, sorted_pair, tiles_feed, tiles_down, counts,
+                                                              tile_tokens);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        return err;
+    }
+    const unsigned int wave = pairs < 148u * 16u ? pairs : 148u * 16u;
+    q8_gather_rows_kernel<<<wave, 128, 0, stream>>>(static_cast<const uint4 *>(x), sorted_pair, tokens, tokens_dev,
+                                                    used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
+    err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        return err;
+    }
+    err = launch_umma_grouped(stream, scratch, sm_count, w_gate_up, experts * 2u * ffn, hidden, x_sorted, pairs,
+                              tile_tokens, tiles_feed, counts + 0, ws.max_feed, nullptr, act, ffn, 1,
+                              (*launches)++, overlap, kEpilogueSwiglu);
     if (err != cudaSuccess) {
         return err;
     }

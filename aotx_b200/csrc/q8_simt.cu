@@ -152,6 +152,55 @@ q8_gemv_simt_kernel(const unsigned char *__restrict__ w, unsigned int n, unsigne
     }
 }
 
+// The same product with one of the two fused stores (q8_launch.h): the sum is added to the
+// float that y holds, or the sums of rows 2p and 2p+1 of w (gate and up of column p) leave as
+// silu(gate) * up in column p of a y that is n / 2 wide (arithmetic of
+// cuda/model/norm.cu:78-105).  One warp takes one output column.
+template <typename XT, typename YT>
+__global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
+q8_gemv_simt_fused_kernel(const unsigned char *__restrict__ w, unsigned int n, unsigned int k,
+                          const XT *__restrict__ x, unsigned int m_max, const unsigned int *m_dev,
+                          YT *__restrict__ y, unsigned int epilogue)
+{
+    unsigned int m = m_max;
+    if (m_dev != nullptr) {
+        unsigned int live = *m_dev;
+        m = live < m_max ? live : m_max;
+    }
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned int warp = threadIdx.x >> 5;
+    const unsigned long long stride = row_bytes(k);
+    const bool swiglu = epilogue == kEpilogueSwiglu;
+    const unsigned int columns = swiglu ? n / 2u : n;
+    for (unsigned int p = blockIdx.x * Q8_SIMT_WARPS + warp; p < columns; p += gridDim.x * Q8_SIMT_WARPS) {
+        const unsigned char *row = w + stride * (swiglu ? 2ull * p : (unsigned long long)p);
+        for (unsigned int m0 = 0; m0 < m; m0 += Q8_SIMT_TAKE) {
+            const unsigned int take = m - m0 < Q8_SIMT_TAKE ? m - m0 : Q8_SIMT_TAKE;
+            float first[Q8_SIMT_TAKE];
+            float second[Q8_SIMT_TAKE];
+            simt_row<XT>(row, k, x + (size_t)m0 * k, k, take, first);
+            if (swiglu) {
+                simt_row<XT>(row + stride, k, x + (size_t)m0 * k, k, take, second);
+            }
+            if (lane == 0u) {
+#pragma unroll
+                for (unsigned int t = 0; t < Q8_SIMT_TAKE; ++t) {
+                    if (t < take) {
+                        const size_t at = (size_t)(m0 + t) * columns + p;
+                        if (swiglu) {
+                            const float unit = first[t] / (1.0f + expf(-first[t]));
+                            store_out<YT>(y, at, unit * second[t]);
+                        } else {
+                            float *sum = reinterpret_cast<float *>(y) + at;
+                            *sum = *sum + first[t];
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Expert router.  One block per token (stepping by the grid), 256 threads.  Logits are float
 // dot products of the float router rows with the half activations, one warp per expert with
@@ -378,26 +427,36 @@ cudaError_t launch_dequant(cudaStream_t stream, const void *w, unsigned int k, u
 template <typename XT, typename YT>
 static cudaError_t launch_gemv_simt_typed(cudaStream_t stream, const void *w, unsigned int n,
                                           unsigned int k, const void *x, unsigned int m,
-                                          const unsigned int *m_dev, void *y)
+                                          const unsigned int *m_dev, void *y, unsigned int epilogue)
 {
     unsigned int want = (n + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS;
     unsigned int grid = want < 148u * 8u ? want : 148u * 8u;
-    q8_gemv_simt_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
-        static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
-        static_cast<YT *>(y));
+    if (epilogue == kEpilogueStore) {
+        q8_gemv_simt_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
+            static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
+            static_cast<YT *>(y));
+    } else {
+        q8_gemv_simt_fused_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
+            static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
+            static_cast<YT *>(y), epilogue);
+    }
     return cudaGetLastError();
 }
 
 cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n, unsigned int k,
                              const void *x, int x_bf16, unsigned int m, const unsigned int *m_dev,
-                             void *y, int y_dtype)
+                             void *y, int y_dtype, unsigned int epilogue)
 {
     if (n == 0u || m == 0u) {
         return cudaSuccess;
     }
+    if ((epilogue == kEpilogueAdd && y_dtype != 0) || (epilogue == kEpilogueSwiglu && (n & 1u) != 0u)
+        || epilogue > kEpilogueSwiglu) {
+        return cudaErrorInvalidValue;
+    }
 #define Q8_CASE(XT, YD, YT)                                                                      \
     if (y_dtype == (YD)) {                                                                       \
-        return launch_gemv_simt_typed<XT, YT>(stream, w, n, k, x, m, m_dev, y);                  \
+        return launch_gemv_simt_typed<XT, YT>(stream, w, n, k, x, m, m_dev, y, epilogue);        \
     }
     if (x_bf16) {
         Q8_CASE(__nv_bfloat16, 0, float)

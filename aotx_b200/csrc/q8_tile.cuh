@@ -7,6 +7,7 @@
 #include <cuda.h>
 
 #include "q8_common.cuh"
+#include "q8_launch.h"
 
 namespace q8 {
 
@@ -68,6 +69,10 @@ struct UmmaArgs {
     void *y_peer[8];
     unsigned int peers;
     unsigned int col0;
+    // What the store does with a finished sum (kEpilogue*): write it; add it to the float that
+    // y holds (residual stream); or, with rows 2p and 2p+1 of w being the gate and up rows of
+    // output column p, write silu(gate) * up to column p of a y that is n / 2 wide.
+    unsigned int epilogue;
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null
@@ -365,7 +370,22 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                     v[i] = __float_as_uint(sum);
                 }
             }
-            if (j < place.j_limit) {
+            const bool swiglu = args.epilogue == kEpilogueSwiglu;
+            if (swiglu) {
+                // Gate and up sums of one output column sit in neighbouring lanes (every lane of
+                // the warp is here: the branch conditions above are the same for the whole warp).
+                // The arithmetic is that of the separate kernel (cuda/model/norm.cu:92-105).
+#pragma unroll
+                for (uint32_t i = 0; i < kChunk; ++i) {
+                    const float mine = __uint_as_float(v[i]);
+                    const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1u);
+                    const float unit = mine / (1.0f + expf(-mine));
+                    v[i] = __float_as_uint(unit * other);
+                }
+            }
+            const bool writes = j < place.j_limit && (!swiglu || (lane_row & 1u) == 0u);
+            const uint32_t col = swiglu ? ((args.col0 + j) >> 1) : (args.col0 + j);
+            if (writes) {
                 const uint32_t copies = args.peers == 0u ? 1u : args.peers;
                 for (uint32_t peer = 0; peer < copies; ++peer) {
                     YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
@@ -374,7 +394,15 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                         const uint32_t row_x = i0 + c0 + i;
                         if (row_x < place.i_limit) {
                             const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
-                            store_out<YT>(out, (size_t)row_y * args.ldy + args.col0 + j, __uint_as_float(v[i]));
+                            const size_t at = (size_t)row_y * args.ldy + col;
+                            if (args.epilogue == kEpilogueAdd) {
+                                // y is the float residual stream: one rounded add, as the
+                                // separate kernel does it (cuda/model/norm.cu:78-89)
+                                float *sum = reinterpret_cast<float *>(out) + at;
+                                *sum = *sum + __uint_as_float(v[i]);
+                            } else {
+                                store_out<YT>(out, at, __uint_as_float(v[i]));
+                            }
                         }
                     }
                 }

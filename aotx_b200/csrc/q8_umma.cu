@@ -508,7 +508,7 @@ static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap, const PeerOut *out)
+                        bool overlap, const PeerOut *out, unsigned int epilogue)
 {
     if (!umma_supports(w, n, k, x, m)) {
         return cudaErrorNotSupported;
@@ -572,7 +572,8 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.group_tiles = nullptr;
     args.group_count = nullptr;
     args.row_map = nullptr;
-    args.ldy = n;
+    args.epilogue = epilogue;
+    args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
     args.peers = 0u;
     args.col0 = 0u;
     if (out != nullptr) {
@@ -614,7 +615,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
                                 const void *x_sorted, unsigned int x_rows, unsigned int ntok,
                                 const GroupTile *tiles, const unsigned int *count_dev, unsigned int max_tiles,
                                 const unsigned int *row_map, void *y, unsigned int ldy, int y_dtype,
-                                unsigned int set, bool overlap)
+                                unsigned int set, bool overlap, unsigned int epilogue)
 {
     EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr || (k % kSegK) != 0u || ntok > 128u) {
@@ -672,6 +673,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     args.ldy = ldy;
     args.peers = 0u;
     args.col0 = 0u;
+    args.epilogue = epilogue;
 #ifdef Q8_EXPERIMENT
     args.debug = 0u;
     args.trace = nullptr;

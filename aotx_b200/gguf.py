@@ -198,3 +198,22 @@ class GGUFLoader:
         """One rank's rows of a tensor: the shard of a column-split projection, or a range of
         experts of a stacked expert tensor."""
         return self.upload(gguf, *gguf.row_range(tensor, first_row, rows), out=out)
+
+    def upload_interleaved(self, gguf, gate, up, first_row=0, rows=None):
+        """Rows [first_row, first_row + rows) of two tensors of one shape as one device tensor
+        with the rows interleaved (row 2r from `gate`, row 2r + 1 from `up`)."""
+        import torch
+        if gate.dims != up.dims or gate.type != up.type:
+            raise ValueError("gate and up must have one shape and type")
+        rows = gate.rows - first_row if rows is None else rows
+        stride = row_bytes(gate.type, gate.row_weights)
+        out = torch.empty(2 * rows * stride, dtype=torch.uint8, device=torch.device("cuda", self.device))
+        stream = torch.cuda.current_stream(out.device).cuda_stream
+        for which, tensor in enumerate((gate, up)):
+            offset, _ = gguf.row_range(tensor, first_row, rows)
+            code = self.lib.aotx_gguf_upload_rows(self.handle, gguf.handle, offset, stride, rows,
+                                                  out.data_ptr() + which * stride, 2 * stride, stream)
+            if code != 0:
+                raise GGUFError("aotx_gguf_upload_rows (cuda error %d)"
+                                % self.lib.aotx_gguf_loader_last_cuda_error(self.handle), code)
+        return out

@@ -11,6 +11,7 @@ SYMBOLS = (
     "aotx_q8_init", "aotx_q8_destroy", "aotx_q8_set_path", "aotx_q8_set_overlap", "aotx_q8_last_cuda_error",
     "aotx_q8_device_status", "aotx_q8_dequant", "aotx_q8_matmul", "aotx_q8_moe_route",
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_matmul_peers",
+    "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused",
 )
 
 # every symbol include/aotx_gguf_b200.h declares
@@ -20,7 +21,7 @@ GGUF_SYMBOLS = (
     "aotx_gguf_find", "aotx_gguf_u32", "aotx_gguf_u64", "aotx_gguf_f32", "aotx_gguf_string",
     "aotx_gguf_array", "aotx_gguf_read", "aotx_gguf_read_threads", "aotx_gguf_row_bytes", "aotx_gguf_row_range",
     "aotx_gguf_loader_init", "aotx_gguf_loader_destroy", "aotx_gguf_loader_last_cuda_error",
-    "aotx_gguf_upload",
+    "aotx_gguf_upload", "aotx_gguf_upload_rows",
 )
 
 
@@ -64,6 +65,9 @@ def load_library():
     lib.aotx_q8_matmul_static.argtypes = [vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32]
     lib.aotx_q8_matmul_peers.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), u32,
                                          u32, u32, i32]
+    lib.aotx_q8_matmul_fused.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32, i32]
+    lib.aotx_q8_moe_ffn_fused.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
+                                          u32, vp, i32, vp, C.c_size_t]
     for name in SYMBOLS:
         fn = getattr(lib, name)
         if name != "aotx_q8_moe_workspace_bytes":
@@ -94,5 +98,6 @@ def load_library():
     lib.aotx_gguf_loader_destroy.argtypes = [vp]
     lib.aotx_gguf_loader_last_cuda_error.argtypes = [vp]
     lib.aotx_gguf_upload.argtypes = [vp, vp, u64, u64, vp, vp]
+    lib.aotx_gguf_upload_rows.argtypes = [vp, vp, u64, u64, u64, vp, u64, vp]
     _lib = lib
     return lib

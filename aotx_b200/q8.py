@@ -13,6 +13,7 @@ from .library import load_library
 Q8_0 = 8  # cuda/model/model.cuh:31
 F32, F16, BF16 = 0, 1, 2
 PATH_AUTO, PATH_GENERAL, PATH_TENSOR = 0, 1, 2
+EPILOGUE_STORE, EPILOGUE_ADD, EPILOGUE_SWIGLU = 0, 1, 2
 
 _ERRORS = {1: "bad argument", 2: "block type is not Q8_0", 3: "CUDA call failed",
            4: "shape unsupported by the forced kernel family", 5: "workspace missing or small",
@@ -28,6 +29,22 @@ class Q8Error(RuntimeError):
 def row_bytes(k):
     """Bytes of one row of k weights (cuda/model/matrix.cuh:77-82)."""
     return (k // 32) * 34
+
+
+def interleave_rows(w_gate, w_up, k, groups=1):
+    """Gate and up tensors of the same shape as one tensor with rows interleaved (row 2r = gate
+    row r, row 2r + 1 = up row r), the layout EPILOGUE_SWIGLU and `moe_ffn_fused` read.  Rows are
+    whole runs of row_bytes(k) bytes, so this is a strided byte copy; `groups` experts stacked in
+    each tensor keep their order."""
+    stride = row_bytes(k)
+    gate = np.ascontiguousarray(w_gate).reshape(-1, stride)
+    up = np.ascontiguousarray(w_up).reshape(-1, stride)
+    if gate.shape != up.shape or gate.shape[0] % groups != 0:
+        raise ValueError("gate and up must hold the same rows")
+    out = np.empty((2 * gate.shape[0], stride), dtype=np.uint8)
+    out[0::2] = gate
+    out[1::2] = up
+    return out.reshape(-1)
 
 
 def pack_q8_0(q, d):
@@ -139,6 +156,24 @@ class Q8Context:
             y.data_ptr(), _dtype_code(y.dtype)))
         return y
 
+    def matmul_fused(self, w, n, k, x, epilogue, m=None, m_dev=None, y=None, y_dtype=None, type=Q8_0):
+        """The product with the next step of the layer in its store.  EPILOGUE_ADD: `y` is the
+        float residual stream, the product is added to it.  EPILOGUE_SWIGLU: `w` holds gate and
+        up rows interleaved (`interleave_rows`), the result is silu(gate) * up, [m][n // 2]."""
+        torch = _torch()
+        if m is None:
+            m = x.shape[0]
+        if y is None:
+            if epilogue == EPILOGUE_ADD:
+                raise ValueError("EPILOGUE_ADD adds into a y that the caller gives")
+            width = n // 2 if epilogue == EPILOGUE_SWIGLU else n
+            y = torch.empty((m, width), dtype=y_dtype or torch.float32, device=self.device)
+        self._check(self.lib.aotx_q8_matmul_fused(
+            self.handle, self._stream(), w.data_ptr(), type, n, k, x.data_ptr(),
+            _dtype_code(x.dtype), m, m_dev.data_ptr() if m_dev is not None else None,
+            y.data_ptr(), _dtype_code(y.dtype), epilogue))
+        return y
+
     def matmul_peers(self, w, n, k, x, m, y_ptrs, ldy, col0, y_dtype, m_dev=None, type=Q8_0):
         """Column-split product: columns [col0, col0 + n) of y[m][ldy], stored into every buffer
         of `y_ptrs` (device addresses: this GPU's y and the peers', peer-mapped)."""
@@ -189,6 +224,24 @@ class Q8Context:
         self._check(self.lib.aotx_q8_moe_ffn(
             self.handle, self._stream(), w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(),
             type, experts, hidden, ffn, x.data_ptr(), prob.data_ptr(), ids.data_ptr(), tokens,
+            tokens_dev.data_ptr() if tokens_dev is not None else None, used, out.data_ptr(),
+            _dtype_code(out.dtype), workspace.data_ptr(), workspace.numel()))
+        return out
+
+    def moe_ffn_fused(self, w_gate_up, w_down, experts, hidden, ffn, x, prob, ids, tokens=None,
+                      tokens_dev=None, out=None, out_dtype=None, workspace=None, type=Q8_0):
+        """`moe_ffn` with gate and up of every expert interleaved in one tensor
+        ([experts][2 * ffn][hidden], see `interleave_rows`)."""
+        torch = _torch()
+        tokens = x.shape[0] if tokens is None else tokens
+        used = ids.shape[1]
+        if out is None:
+            out = torch.empty((tokens, hidden), dtype=out_dtype or torch.float32, device=self.device)
+        if workspace is None:
+            workspace = self.moe_workspace(tokens, used, hidden, ffn)
+        self._check(self.lib.aotx_q8_moe_ffn_fused(
+            self.handle, self._stream(), w_gate_up.data_ptr(), w_down.data_ptr(), type, experts, hidden,
+            ffn, x.data_ptr(), prob.data_ptr(), ids.data_ptr(), tokens,
             tokens_dev.data_ptr() if tokens_dev is not None else None, used, out.data_ptr(),
             _dtype_code(out.dtype), workspace.data_ptr(), workspace.numel()))
         return out

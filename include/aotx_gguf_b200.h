@@ -121,6 +121,16 @@ int aotx_gguf_loader_last_cuda_error(const aotx_gguf_loader *loader);
 int aotx_gguf_upload(aotx_gguf_loader *loader, const aotx_gguf *file, uint64_t offset, uint64_t bytes,
                      void *device_dst, void *stream);
 
+/* The same for `rows` rows of `row_bytes` bytes each that lie back to back in the file from
+ * `offset` and land `dst_pitch` bytes apart on the device (dst_pitch >= row_bytes).  Two calls
+ * with dst_pitch = 2 * row_bytes, the second starting row_bytes further, interleave the rows of
+ * a gate and an up tensor: the layout AOTX_Q8_EPILOGUE_SWIGLU and aotx_q8_moe_ffn_fused read
+ * (include/aotx_q8_b200.h).  A piece holds whole rows; row_bytes above the loader's piece size
+ * returns 1.  No counterpart in the reference. */
+int aotx_gguf_upload_rows(aotx_gguf_loader *loader, const aotx_gguf *file, uint64_t offset,
+                          uint64_t row_bytes, uint64_t rows, void *device_dst, uint64_t dst_pitch,
+                          void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,11 @@ extern "C" {
 #define AOTX_Q8_PATH_GENERAL 1 /* the any-shape kernel on the ordinary cores */
 #define AOTX_Q8_PATH_TENSOR 2  /* the tcgen05 streaming kernel; ERR_UNSUPPORTED if it cannot run */
 
+/* what a product does with a finished sum, for aotx_q8_matmul_fused */
+#define AOTX_Q8_EPILOGUE_STORE 0  /* y[i][j] = sum: aotx_q8_matmul */
+#define AOTX_Q8_EPILOGUE_ADD 1    /* y[i][j] = y[i][j] + sum, y float: the residual add */
+#define AOTX_Q8_EPILOGUE_SWIGLU 2 /* y[i][p] = silu(sum over row 2p) * (sum over row 2p + 1) */
+
 /* bits of the device status word */
 #define AOTX_Q8_DEVICE_BARRIER_TIMEOUT 1u
 #define AOTX_Q8_DEVICE_FLAG_TIMEOUT 2u
@@ -106,6 +111,30 @@ int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type,
                    uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
                    void *y, int y_dtype);
 
+/* The product with the step that follows it in a layer folded into its store, so that the
+ * float result never makes a round trip through memory and one launch goes away:
+ *   AOTX_Q8_EPILOGUE_ADD     y is the float residual stream and the product is added to it,
+ *                            y[i][j] = fadd(y[i][j], sum): the O and down projections followed
+ *                            by aotx_model_residual (cuda/model/norm.cu:78-89;
+ *                            cuda/model/graph_host.cu:86,96).  y_dtype must be F32.
+ *   AOTX_Q8_EPILOGUE_SWIGLU  w holds gate and up rows interleaved (row 2p = gate row p,
+ *                            row 2p + 1 = up row p; n even counts both), y is [m][n / 2] and
+ *                            y[i][p] = silu(gate sum) * (up sum), silu(g) = g / (1 + expf(-g)),
+ *                            rounded once to y_dtype: the gate and up projections followed by
+ *                            aotx_model_swiglu (cuda/model/norm.cu:92-105;
+ *                            cuda/model/graph_host.cu:88-92).  With y_dtype F16 this is the
+ *                            reference's `act` buffer.
+ * AOTX_Q8_EPILOGUE_ADD forms the same float sums as aotx_q8_matmul on the same shape and adds
+ * each once, so it equals the two-step form bit for bit.  AOTX_Q8_EPILOGUE_SWIGLU runs over a
+ * tensor of twice the rows, which moves the points where long rows are cut between blocks, so
+ * its gate and up sums can differ from the separate products' in the last bits of a float (the
+ * activations then differ by at most a binary16 rounding step).
+ * AOTX_Q8_EPILOGUE_STORE is aotx_q8_matmul itself.  Every shape is served (tensor-core
+ * kernel or general kernel, as for aotx_q8_matmul). */
+int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                         uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                         void *y, int y_dtype, int epilogue);
+
 /* Router of a routed-expert layer: prob[t][e] = softmax over all experts of
  * router[e] . x[t] (float router rows, binary16 x), ids[t][r] = the expert of rank r < used,
  * ties to the lower index.  experts <= 256.  Replaces aotx_model_expert_route
@@ -130,6 +159,20 @@ int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const vo
                     uint32_t ffn, const void *x_f16, const float *prob, const uint32_t *ids,
                     uint32_t tokens, const uint32_t *tokens_dev, uint32_t used, void *out,
                     int out_dtype, void *workspace, size_t workspace_bytes);
+
+/* aotx_q8_moe_ffn with gate and up of every expert in one tensor, rows interleaved:
+ * w_gate_up is [experts][2 * ffn][hidden] with row 2r of an expert its gate row r and row
+ * 2r + 1 its up row r.  One grouped product applies the gated unit in its store and writes the
+ * binary16 activations, the down product follows: two tensor-core launches where aotx_q8_moe_ffn
+ * has three and an elementwise kernel (result equal up to the float summation order of the gate
+ * and up sums, see aotx_q8_matmul_fused).  Needs the shapes of the
+ * grouped kernels (hidden and ffn multiples of 256, 16-byte aligned tensors), else
+ * AOTX_Q8_ERR_UNSUPPORTED.  Workspace as for aotx_q8_moe_ffn. */
+int aotx_q8_moe_ffn_fused(aotx_q8_ctx *ctx, void *stream, const void *w_gate_up, const void *w_down,
+                          uint32_t type, uint32_t experts, uint32_t hidden, uint32_t ffn,
+                          const void *x_f16, const float *prob, const uint32_t *ids, uint32_t tokens,
+                          const uint32_t *tokens_dev, uint32_t used, void *out, int out_dtype,
+                          void *workspace, size_t workspace_bytes);
 
 /* The rank-ordered weighted sum alone: proj is float [tokens][used][hidden] (the output of
  * the selected experts, rank-major inside a token); out[t] = fmul(proj[t][0], p0), then for each

@@ -88,3 +88,31 @@ def test_product_on_an_uploaded_shard(model, oracle):
     finally:
         loader.close()
         ctx.close()
+
+
+def test_interleaved_upload_of_gate_and_up(tmp_path):
+    """Two tensors uploaded row by row into one with the rows interleaved: the layout the gated
+    store reads, equal to what interleave_rows builds on the host."""
+    import aotx_b200
+    from aotx_b200.gguf import GGUFFile, GGUFLoader
+    torch = torch_mod()
+    k, ffn, experts = 512, 96, 3
+    gate = aotx_b200.synth_q8_0(experts * ffn, k, 31)
+    up = aotx_b200.synth_q8_0(experts * ffn, k, 32)
+    blob, _ = gw.build([], [{"name": "g", "dims": [k, ffn, experts], "type": 8, "data": gate.tobytes()},
+                            {"name": "u", "dims": [k, ffn, experts], "type": 8, "data": up.tobytes()}])
+    path = str(tmp_path / "gu.gguf")
+    with open(path, "wb") as f:
+        f.write(blob)
+    loader = GGUFLoader(0, 20000)  # a piece of 36 rows and a bit
+    try:
+        with GGUFFile(path) as f:
+            got = loader.upload_interleaved(f, f.find("g"), f.find("u"))
+            part = loader.upload_interleaved(f, f.find("g"), f.find("u"), first_row=ffn, rows=ffn)
+        torch.cuda.synchronize()
+        want = aotx_b200.interleave_rows(gate, up, k, groups=experts)
+        assert np.array_equal(got.cpu().numpy(), want)
+        stride = aotx_b200.row_bytes(k)
+        assert np.array_equal(part.cpu().numpy(), want[2 * ffn * stride:4 * ffn * stride])
+    finally:
+        loader.close()

@@ -134,9 +134,26 @@ def test_argument_checks_need_no_device(built):
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 3, 1, None, one, 0) == 1      # x dtype
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 1, 65, None, one, 0) == 5     # rows > 64
     assert lib.aotx_q8_matmul_static(null, one, 8, 0, 64, one, 1, 1, None, one, 0) == 0      # nothing to do
+    assert lib.aotx_q8_matmul_fused(null, null, one, 8, 8, 64, one, 1, 1, None, one, 0, 1) == 1
+    assert lib.aotx_q8_moe_ffn_fused(null, null, one, one, 8, 4, 256, 256, one, one, one, 1, None, 2, one, 0,
+                                     one, 1 << 30) == 1
     small = lib.aotx_q8_moe_workspace_bytes(8, 2, 256, 256)
     large = lib.aotx_q8_moe_workspace_bytes(512, 8, 2048, 768)
     assert 0 < small < large and large % 256 == 0
+
+
+def test_interleaved_rows_layout():
+    """Row 2r of the interleaved tensor is gate row r, row 2r + 1 is up row r, expert by expert."""
+    import aotx_b200
+    k, ffn, experts = 64, 6, 3
+    stride = aotx_b200.row_bytes(k)
+    gate = aotx_b200.synth_q8_0(experts * ffn, k, 1)
+    up = aotx_b200.synth_q8_0(experts * ffn, k, 2)
+    both = aotx_b200.interleave_rows(gate, up, k, groups=experts).reshape(experts, ffn, 2, stride)
+    assert np.array_equal(both[:, :, 0], gate.reshape(experts, ffn, stride))
+    assert np.array_equal(both[:, :, 1], up.reshape(experts, ffn, stride))
+    with pytest.raises(ValueError):
+        aotx_b200.interleave_rows(gate, up[:stride], k)
 
 
 def test_sharding_helpers_match_the_benchmark_shapes():
