@@ -40,10 +40,18 @@ WORKLOADS = {
                                              ("gate_up", 4096, 28672), ("down", 14336, 4096)],
                                       "bfloat16", "bfloat16"),
 }
+# The same layer with the steps that follow the products folded into their stores: O and down add
+# into the float residual stream, gate+up (rows interleaved) leaves as the half activations.
+FUSED = {"decode_m32_llama3_8b_layer_fused": "decode_m32_llama3_8b_layer",
+         "prefill_m2048_llama3_8b_layer_fused": "prefill_m2048_llama3_8b_layer"}
+for _name, _base in FUSED.items():
+    WORKLOADS[_name] = WORKLOADS[_base]
+EPILOGUE_OF = {"o": 1, "down": 1, "gate_up": 2}  # AOTX_Q8_EPILOGUE_ADD / _SWIGLU
+
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures
 # summarised under profiles/ (gate+up projection; scaled to the average launch by bytes).
 TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.0565, "decode_m32_gate_up": 1.0565}
-TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up"}
+TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up", "prefill_m2048_llama3_8b_layer_fused"}
 
 
 def measured_peaks():
@@ -55,10 +63,17 @@ def measured_peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def algorithmic_bytes(m, projections, x_bytes, y_bytes):
+def algorithmic_bytes(m, projections, x_bytes, y_bytes, fused=False):
     total = 0
-    for _, k, n in projections:
-        total += n * (k // 32) * 34 + m * k * x_bytes + m * n * y_bytes
+    for name, k, n in projections:
+        total += n * (k // 32) * 34 + m * k * x_bytes
+        mode = EPILOGUE_OF.get(name, 0) if fused else 0
+        if mode == 1:
+            total += 2 * m * n * 4          # the float residual stream, read and written
+        elif mode == 2:
+            total += m * (n // 2) * 2       # half activations, one per gate/up pair
+        else:
+            total += m * n * y_bytes
     return total
 
 
@@ -155,18 +170,34 @@ def run_ours(args, rank, world, local_rank):
     copies = max(2, int(np.ceil(3 * 126e6 / weight_bytes)) + 1)
     copies = min(copies, 24)
     tensors = make_inputs(torch, m, projections, x_dtype, copies, seed=1 + rank)
+    fused = args.workload in FUSED
     for t in tensors:
         t["x"] = t["x_host"].cuda()
-        t["y"] = torch.empty((m, t["n"]), dtype=y_dtype, device="cuda")
-        t["y_host"] = torch.empty((m, t["n"]), dtype=y_dtype).pin_memory()
+        t["mode"] = EPILOGUE_OF.get(t["name"], 0) if fused else 0
+        if t["mode"] == 1:
+            shape, kind = (m, t["n"]), torch.float32
+        elif t["mode"] == 2:
+            shape, kind = (m, t["n"] // 2), torch.float16
+        else:
+            shape, kind = (m, t["n"]), y_dtype
+        t["y"] = torch.zeros(shape, dtype=kind, device="cuda")
+        t["y_host"] = torch.empty(shape, dtype=kind).pin_memory()
+
+    def product(t, c):
+        if t["mode"]:
+            ctx.matmul_fused(t["w"][c], t["n"], t["k"], t["x"], t["mode"], y=t["y"])
+        else:
+            ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
 
     def step(c):
         for t in tensors:
-            ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
+            product(t, c)
 
     def step_e2e(c):
         for t in tensors:
-            ctx.matmul_host(t["w"][c], t["n"], t["k"], t["x_host"], t["y_host"], t["x"], t["y"])
+            t["x"].copy_(t["x_host"], non_blocking=True)
+            product(t, c)
+            t["y_host"].copy_(t["y"], non_blocking=True)
 
     # One graph per weight copy: the step is launch-bound on the host otherwise.
     step(0)
@@ -243,7 +274,7 @@ def run_ours(args, rank, world, local_rank):
                     down_stream.wait_stream(main_stream)
                     for t, event in zip(tensors, ready):
                         main_stream.wait_event(event)
-                        ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
+                        product(t, c)
                         done = torch.cuda.Event()
                         done.record(main_stream)
                         with torch.cuda.stream(down_stream):
@@ -284,7 +315,7 @@ def run_ours(args, rank, world, local_rank):
         total_ms, e2e_ms = both.tolist()
 
     x_bytes = y_bytes = 2
-    step_bytes = algorithmic_bytes(m, projections, x_bytes, y_bytes)
+    step_bytes = algorithmic_bytes(m, projections, x_bytes, y_bytes, fused=fused)
     step_flops = flops(m, projections)
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     launches = len(projections)
@@ -313,8 +344,8 @@ def run_ours(args, rank, world, local_rank):
     roofline["bytes_per_launch"] = step_bytes / launches
     roofline["tokens_per_s"] = world * m * args.steps / (total_ms * 1e-3)
 
-    h2d = sum(t["x_host"].numel() * 2 for t in tensors)
-    d2h = sum(t["y_host"].numel() * 2 for t in tensors)
+    h2d = sum(t["x_host"].numel() * t["x_host"].element_size() for t in tensors)
+    d2h = sum(t["y_host"].numel() * t["y_host"].element_size() for t in tensors)
     clocks = sampler.summary()
     clocks["probe"] = "extended" if extended else "timed_region"
 
@@ -617,7 +648,8 @@ def run_reference(args, rank, world):
     # size one step to about a second
     kind, cores, seconds, sample_bytes, sample_flops = time_cpu(args.workload, 1.0 / 128.0)
     fraction = min(1.0, (1.0 / 128.0) * max(1.0, 1.0 / max(seconds, 1e-3)))
-    for _ in range(max(args.warmup, 1)):
+    warmups = min(max(args.warmup, 1), 3)  # a pass is about a second of all cores
+    for _ in range(warmups):
         time_cpu(args.workload, fraction)
     total = 0.0
     for _ in range(args.steps):
@@ -631,7 +663,7 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference",
         "metric": "q8_prefill_gemm_tflops" if tensor_bound else "q8_decode_gemm_hbm_gbs",
-        "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1),
+        "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmups,
         "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64 sums over f16", "data": "synthetic",
         "config": {"workload": args.workload, "rows": m, "x": "float16", "y": "float64",
