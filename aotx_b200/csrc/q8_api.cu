@@ -169,17 +169,19 @@ extern "C" int aotx_q8_dequant(aotx_q8_ctx *ctx, void *stream, const void *w, ui
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    if (type != AOTX_Q8_TYPE_Q8_0) {
+    if (!q8::block_type_known(type)) {
         return AOTX_Q8_ERR_TYPE;
     }
     if (rows == 0u) {
         return AOTX_Q8_OK;
     }
-    if (w == nullptr || out_f16 == nullptr || k == 0u || (k % 32u) != 0u || !aligned(w, 2u)
+    if (w == nullptr || out_f16 == nullptr || k == 0u || (k % q8::block_type_run(type)) != 0u || !aligned(w, 2u)
         || !aligned(out_f16, 4u)) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    cudaError_t err = q8::launch_dequant((cudaStream_t)stream, w, k, first_row, rows, out_f16);
+    cudaError_t err = type == AOTX_Q8_TYPE_Q8_0
+        ? q8::launch_dequant((cudaStream_t)stream, w, k, first_row, rows, out_f16)
+        : q8::launch_dequant_any((cudaStream_t)stream, w, type, k, first_row, rows, out_f16);
     return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
 }
 
@@ -190,10 +192,10 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    if (type != AOTX_Q8_TYPE_Q8_0) {
+    if (!q8::block_type_known(type)) {
         return AOTX_Q8_ERR_TYPE;
     }
-    if (!dtype_16(x_dtype) || !dtype_out(y_dtype) || k == 0u || (k % 32u) != 0u) {
+    if (!dtype_16(x_dtype) || !dtype_out(y_dtype) || k == 0u || (k % q8::block_type_run(type)) != 0u) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
     if (n == 0u || m == 0u) {
@@ -204,6 +206,14 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
         return AOTX_Q8_ERR_ARGUMENT;
     }
     cudaStream_t s = (cudaStream_t)stream;
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        /* the other block types of a model file: one decoder, general kernel */
+        if (ctx->path == AOTX_Q8_PATH_TENSOR) {
+            return AOTX_Q8_ERR_UNSUPPORTED;
+        }
+        cudaError_t any = q8::launch_gemv_any(s, w, type, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
+        return any == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, any);
+    }
     /* One MMA takes both operands in one 16-bit format (binary16 weights against bfloat16
      * activations raise an illegal-instruction fault on sm_100a), so for bfloat16 activations
      * the streaming kernel turns the x tiles into binary16 in shared memory (values beyond the

@@ -22,6 +22,15 @@ cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n,
                              const void *x, int x_bf16, unsigned int m, const unsigned int *m_dev,
                              void *y, int y_dtype, unsigned int epilogue = 0u);
 
+// Every other block type of the model file (q_generic.cu, decoder in q_blocks.cuh).
+bool block_type_known(unsigned int type);
+unsigned int block_type_run(unsigned int type); // k must be a multiple of this; 0 for an unknown type
+cudaError_t launch_dequant_any(cudaStream_t stream, const void *w, unsigned int type, unsigned int k,
+                               unsigned int first_row, unsigned int rows, void *out);
+cudaError_t launch_gemv_any(cudaStream_t stream, const void *w, unsigned int type, unsigned int n,
+                            unsigned int k, const void *x, int x_bf16, unsigned int m,
+                            const unsigned int *m_dev, void *y, int y_dtype);
+
 cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router, unsigned int tokens,
                          const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                          unsigned int used, float *prob, unsigned int *ids);

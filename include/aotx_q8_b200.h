@@ -8,8 +8,13 @@
  *
  * Weight layout (unchanged from the model file; reference cuda/model/matrix.cuh:6-7,26,77-82):
  * w[n][k] row-major, each row k/32 blocks of 34 bytes = little-endian binary16 scale then 32
- * signed bytes.  `type` is the model file's block type id; only 8 (Q8_0) is served
- * (reference cuda/model/model.cuh:31).
+ * signed bytes.  `type` is the model file's block type id (reference cuda/model/model.cuh:24-36).
+ * 8 (Q8_0) is the path this library is built for: every entry point takes it, on the
+ * tensor-core kernels where the shape allows.  aotx_q8_dequant and aotx_q8_matmul also take the
+ * other types the reference's kernels read - F32 0, F16 1, Q4_0 2, Q4_1 3, Q5_0 6, Q5_1 7,
+ * Q2_K 10, Q3_K 11, Q4_K 12, Q5_K 13, Q6_K 14 - through one decoder on the ordinary cores (rows
+ * of whole blocks: k a multiple of 32, of 256 for the K types); any other id is
+ * AOTX_Q8_ERR_TYPE.
  *
  * Return value: 0 on success, one of the AOTX_Q8_ERR_* codes otherwise.  On an error nothing
  * is enqueued and no output is written (the reference's kernels likewise write nothing for a
@@ -90,7 +95,9 @@ int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx);
 int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int clear);
 
 /* Rows [first_row, first_row + rows) of w as binary16: out[r][j] = half(float(q) * float(d)),
- * bit-exact.  Replaces aotx_model_dequant (cuda/model/dequant.cu:26-70; declaration
+ * bit-exact; for the other block types half(v) with v the correctly rounded float of the
+ * format's expression (one fused multiply-add after exact products), as the reference's
+ * readers form it (cuda/model/matrix.cuh:163-245, 255-340).  Replaces aotx_model_dequant (cuda/model/dequant.cu:26-70; declaration
  * cuda/model/model.cuh:112-116). */
 int aotx_q8_dequant(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t k,
                     uint32_t first_row, uint32_t rows, void *out_f16);

@@ -83,7 +83,26 @@ def build_gguf_ref(force=False):
     return GGUF_REF_SO
 
 
+KREF_SO = os.path.join(REF_DIR, "libkref_ref.so")
+
+
+def build_kref(force=False):
+    """The reference's host reading of the packed block types (tests/matrix_kref.h), compiled
+    from the reference tree through the two-line wrapper kref_wrap.c."""
+    root = reference_root()
+    if root is None or shutil.which("gcc") is None:
+        return KREF_SO if os.path.exists(KREF_SO) else None
+    wrap = os.path.join(HERE, "kref_wrap.c")
+    if not force and _newer(KREF_SO, [wrap]):
+        return KREF_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-I" + os.path.join(root, "tests"), "-o", KREF_SO, wrap,
+                    "-lm"], check=True)
+    return KREF_SO
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
     print(build_gguf_ref(force="--force" in sys.argv))
+    print(build_kref(force="--force" in sys.argv))
