@@ -94,7 +94,7 @@ def test_cpp_seam_compiles_and_links(built, tmp_path):
 
 
 def test_cpp_seam_program_builds_and_fails_loudly_without_a_device(built, tmp_path):
-    """The C++ parity program of the seam (run on the GPU by test_gpu_g_seam.py) compiles and
+    """The C++ parity program of the seam (run on the GPU by test_gpu_i_seam.py) compiles and
     links here; on a machine without a GPU its first call reports the CUDA error and stops."""
     import shutil
     import subprocess
