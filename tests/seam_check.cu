@@ -165,8 +165,6 @@ int main()
         fill_guard(y_dev, (size_t)rows * c.n, hold.stream);
         hold.decode = 0u;
         aotx_model_matrix(&hold, w_dev, AOTX_Q8_TYPE_Q8_0, c.n, c.k, x_dev, c.m, y_dev, AOTX_B200_BATCH_TOKENS);
-        // a block type the path does not serve must leave y alone (here: every row is already
-        // written, so a second call with another type must change nothing)
         CHECK_CUDA(cudaStreamSynchronize(hold.stream));
         std::vector<float> got((size_t)rows * c.n);
         CHECK_CUDA(cudaMemcpy(got.data(), y_dev, got.size() * sizeof(float), cudaMemcpyDeviceToHost));
@@ -179,8 +177,9 @@ int main()
         if (wrong != 0u || touched != 0u) {
             return 1;
         }
+        // a block type without a layout must leave y alone (cuda/model/gemm.cuh:236-237)
         fill_guard(y_dev, (size_t)rows * c.n, hold.stream);
-        aotx_model_matrix(&hold, w_dev, 2u /* another block type */, c.n, c.k, x_dev, c.m, y_dev,
+        aotx_model_matrix(&hold, w_dev, 9u /* a block type without a layout */, c.n, c.k, x_dev, c.m, y_dev,
                           AOTX_B200_BATCH_TOKENS);
         CHECK_CUDA(cudaStreamSynchronize(hold.stream));
         CHECK_CUDA(cudaMemcpy(got.data(), y_dev, got.size() * sizeof(float), cudaMemcpyDeviceToHost));

@@ -89,6 +89,6 @@ def test_wrong_type_writes_nothing(ctx):
     w = dev_weights(aotx_b200.synth_q8_0(4, 64, 1))
     out = torch.full((4, 64), 3.0, dtype=torch.float16, device="cuda")
     with pytest.raises(aotx_b200.Q8Error) as err:
-        ctx.dequant(w, 64, 0, 4, out=out, type=2)
+        ctx.dequant(w, 64, 0, 4, out=out, type=9)  # Q8_1: no layout here, nor in the reference
     assert err.value.code == 2
     assert (out == 3.0).all()

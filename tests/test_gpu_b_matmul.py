@@ -156,7 +156,7 @@ def test_errors_write_nothing(ctx):
     x = dev(x_fp16(2, 64, 1))
     y = torch.full((2, 8), GUARD, dtype=torch.float32, device="cuda")
     with pytest.raises(aotx_b200.Q8Error) as err:
-        ctx.matmul(w, 8, 64, x, y=y, type=2)
+        ctx.matmul(w, 8, 64, x, y=y, type=9)  # Q8_1: no layout here, nor in the reference
     assert err.value.code == 2
     with pytest.raises(aotx_b200.Q8Error) as err:
         ctx.matmul(w, 8, 48, x, y=y)
