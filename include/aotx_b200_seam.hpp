@@ -59,6 +59,38 @@ static inline void aotx_model_matrix(aotx_b200_hold *hold, const void *w, unsign
     aotx_b200_check(code, "aotx_model_matrix");
 }
 
+// The product of the O or down projection followed by the residual add, as one node:
+// resid[i][j] += sum (aotx_model_matrix(..., work->proj, ...) then aotx_model_residual,
+// cuda/model/graph_host.cu:84-86, 93-96; cuda/model/norm.cu:78-89).
+static inline void aotx_model_matrix_residual(aotx_b200_hold *hold, const void *w, unsigned int type,
+                                              unsigned int n, unsigned int k, const half *x, unsigned int m,
+                                              float *resid, unsigned int which)
+{
+    const unsigned int *live = hold->decode != 0u ? hold->batch[which & 1u] : nullptr;
+    int code = aotx_q8_matmul_fused(hold->q8, (void *)hold->stream, w, type, n, k, x, AOTX_Q8_F16, m, live,
+                                    resid, AOTX_Q8_F32, AOTX_Q8_EPILOGUE_ADD);
+    if (code == AOTX_Q8_ERR_TYPE) {
+        return;
+    }
+    aotx_b200_check(code, "aotx_model_matrix_residual");
+}
+
+// Gate and up projections and the gated unit as one node: `w_gate_up` holds the two tensors'
+// rows interleaved (2 * ffn rows), act[i][p] = half(silu(gate) * up)
+// (cuda/model/graph_host.cu:88-92; cuda/model/norm.cu:92-105).
+static inline void aotx_model_matrix_swiglu(aotx_b200_hold *hold, const void *w_gate_up, unsigned int type,
+                                            unsigned int ffn, unsigned int k, const half *x, unsigned int m,
+                                            half *act, unsigned int which)
+{
+    const unsigned int *live = hold->decode != 0u ? hold->batch[which & 1u] : nullptr;
+    int code = aotx_q8_matmul_fused(hold->q8, (void *)hold->stream, w_gate_up, type, 2u * ffn, k, x, AOTX_Q8_F16,
+                                    m, live, act, AOTX_Q8_F16, AOTX_Q8_EPILOGUE_SWIGLU);
+    if (code == AOTX_Q8_ERR_TYPE) {
+        return;
+    }
+    aotx_b200_check(code, "aotx_model_matrix_swiglu");
+}
+
 // Rows of a tensor as halves (the reference launches aotx_model_dequant directly:
 // tests/matrix_test.cu:363; cuda/model/model.cuh:112-116).
 static inline void aotx_model_dequant_rows(aotx_b200_hold *hold, const void *w, unsigned int type,

@@ -81,7 +81,9 @@ def test_cpp_seam_compiles_and_links(built, tmp_path):
         '#include "aotx_b200_seam.hpp"\n'
         "int main(int argc, char **) {\n"
         "    aotx_b200_hold hold = {};\n"
-        "    if (argc > 100) { aotx_model_matrix(&hold, 0, 8, 1, 32, 0, 1, 0, AOTX_B200_BATCH_TOKENS); }\n"
+        "    if (argc > 100) { aotx_model_matrix(&hold, 0, 8, 1, 32, 0, 1, 0, AOTX_B200_BATCH_TOKENS);\n"
+        "        aotx_model_matrix_residual(&hold, 0, 8, 1, 32, 0, 1, 0, AOTX_B200_BATCH_TOKENS);\n"
+        "        aotx_model_matrix_swiglu(&hold, 0, 8, 1, 32, 0, 1, 0, AOTX_B200_BATCH_TOKENS); }\n"
         "    return aotx_q8_set_path(0, 0) == AOTX_Q8_ERR_ARGUMENT ? 0 : 1;\n"
         "}\n")
     exe = tmp_path / "seam"
