@@ -1,5 +1,6 @@
 // The decode-regime kernel of the Q8_0 product (token tiles of 16 to 128 rows of x): the
-// weights stream through once at memory speed, whatever the batch.
+// weights stream through once at memory speed, whatever the batch.  Batches above 128 rows run
+// on it too, as several token tiles of 128.
 //
 // Same tiling and unit schedule as the kernel in q8_umma.cu (128 rows of w by NTOK rows of
 // x, depth in segments of 256 weights, units dealt evenly over one persistent block per SM),

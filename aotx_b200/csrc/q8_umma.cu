@@ -3,9 +3,15 @@
 // over the reference's own 34-byte interleaved block layout, plus the host side that picks
 // between this kernel and the decode-regime kernel of q8_stream.cu and builds their tensor maps.
 //
-// It replaces the reference's tensor-core kernel (cuda/model/gemm.cuh:55-189, launched by
-// cuda/model/graph_host.cu:25-29) for batches above 128 rows.  Its weights are the half-rounded
-// ones of that kernel (cuda/model/gemm.cuh:108-113), bit for bit (bfloat16 when x is bfloat16).
+// It was written to replace the reference's tensor-core kernel (cuda/model/gemm.cuh:55-189,
+// launched by cuda/model/graph_host.cu:25-29) for batches above 128 rows, with the half-rounded
+// weights of that kernel (cuda/model/gemm.cuh:108-113), bit for bit (bfloat16 when x is
+// bfloat16).  It is NOT DISPATCHED at present: repeated launches on the same inputs differed in
+// a fraction of a percent of the outputs, so batches above 128 rows run as token tiles of 128
+// on the kernel of q8_stream.cu (umma_token_tile below).  The kernel stays in the library so
+// that the fault can be found; only a build with -DQ8_EXPERIMENT and Q8_WIDE_TILE set in the
+// environment reaches it.  (-DQ8_EXPERIMENT also compiles time stamps and switches that leave
+// out one stage of the pipeline at a time; the product library is built without it.)
 //
 // Shape of the work.  The weight rows are the M side of the MMA: a tile is 128 rows of w by
 // 256 rows of x, so the 34-byte blocks never need a transpose.  The depth is cut into segments
