@@ -67,7 +67,7 @@ def test_residual_add_with_a_live_batch_word(ctx):
 @pytest.mark.parametrize("half_n,k,m", [(40, 128, 3), (192, 512, 1), (320, 1024, 32), (256, 768, 130),
                                         (14336, 4096, 32), (128, 1024, 300)])
 @pytest.mark.parametrize("out", ["float16", "float32"])
-def test_gated_unit_equals_two_products_then_swiglu(ctx, half_n, k, m, out):
+def test_gated_unit_equals_two_products_then_swiglu(ctx, oracle, half_n, k, m, out):
     import aotx_b200
     torch = torch_mod()
     wg = aotx_b200.synth_q8_0(half_n, k, 80 + m)
@@ -88,6 +88,14 @@ def test_gated_unit_equals_two_products_then_swiglu(ctx, half_n, k, m, out):
     assert bool(torch.isfinite(got).all())
     assert bool(((got - want).abs() <= step * want.abs() + 1e-5 * scale + 1e-7).all())
     assert bool((y[m:].float() == float(torch.tensor(GUARD).to(dtype))).all())
+    if float(m) * half_n * k <= 2e9:
+        # and against the oracle's double products, independent of the library's plain kernels
+        bits = x.cpu().numpy().view(np.uint16)
+        g = oracle.product(wg, half_n, k, bits, m)
+        u = oracle.product(wu, half_n, k, bits, m)
+        ideal = g / (1.0 + np.exp(-g)) * u
+        have = got.cpu().numpy().astype(np.float64)
+        assert (np.abs(have - ideal) <= 2.0 ** -9 * np.abs(ideal) + 1e-4 * np.abs(ideal).max() + 1e-7).all()
 
 
 def test_fused_arguments(ctx):
