@@ -94,8 +94,9 @@ def test_gated_unit_equals_two_products_then_swiglu(ctx, oracle, half_n, k, m, o
         g = oracle.product(wg, half_n, k, bits, m)
         u = oracle.product(wu, half_n, k, bits, m)
         ideal = g / (1.0 + np.exp(-g)) * u
-        have = got.cpu().numpy().astype(np.float64)
-        assert (np.abs(have - ideal) <= 2.0 ** -9 * np.abs(ideal) + 1e-4 * np.abs(ideal).max() + 1e-7).all()
+        # the reference's measure (the general kernel multiplies with unrounded weights, the
+        # oracle with the half-rounded ones, as for the plain product)
+        assert oracle.diff(got.cpu().numpy(), ideal)[0] == 0
 
 
 def test_fused_arguments(ctx):
