@@ -422,3 +422,65 @@ def test_threaded_read_equals_plain_read(mine, tmp_path):
                 assert np.array_equal(f.read(t.offset + offset, count, threads=threads), want)
         with pytest.raises(GGUFError):
             f.read(t.offset + 1, f.data_bytes, threads=8)
+
+
+def random_structure(rnd):
+    """A random well-formed file: any value types, arrays of any element type, 0 to 12 tensors
+    of any listed type (and a few ids without a layout), any legal alignment."""
+    kinds = [gw.U8, gw.I8, gw.U16, gw.I16, gw.U32, gw.I32, gw.F32, gw.BOOL, gw.STRING, gw.U64, gw.I64, gw.F64]
+    ranges = {gw.U8: (0, 255), gw.I8: (-128, 127), gw.U16: (0, 65535), gw.I16: (-32768, 32767),
+              gw.U32: (0, 2 ** 32 - 1), gw.I32: (-2 ** 31, 2 ** 31 - 1), gw.U64: (0, 2 ** 64 - 1),
+              gw.I64: (-2 ** 63, 2 ** 63 - 1)}
+
+    def value(kind):
+        if kind in ranges:
+            low, high = ranges[kind]
+            return rnd.choice([low, high, 0, 1, rnd.randint(low, high)])
+        if kind in (gw.F32, gw.F64):
+            return rnd.choice([0.0, -1.5, 1e-30, 3.0e38 if kind == gw.F32 else 1e300, rnd.random()])
+        if kind == gw.BOOL:
+            return rnd.randint(0, 1)
+        return "".join(rnd.choice("abcxyz.é_0") for _ in range(rnd.randint(0, 12)))
+
+    meta, keys = [], set()
+    for _ in range(rnd.randint(0, 14)):
+        key = ".".join("".join(rnd.choice("abcdefgh") for _ in range(rnd.randint(1, 6)))
+                       for _ in range(rnd.randint(1, 3)))
+        if key in keys:
+            continue
+        keys.add(key)
+        if rnd.random() < 0.3:
+            element = rnd.choice(kinds)
+            meta.append((key, gw.ARRAY, (element, [value(element) for _ in range(rnd.randint(0, 6))])))
+        else:
+            kind = rnd.choice(kinds)
+            meta.append((key, kind, value(kind)))
+    alignment = rnd.choice([1, 2, 8, 32, 32, 64, 256, 65536])
+    tensors, names = [], set()
+    for _ in range(rnd.randint(0, 12)):
+        name = "t" + "".join(rnd.choice("abc.0123") for _ in range(rnd.randint(1, 20)))
+        if name in names:
+            continue
+        names.add(name)
+        kind = rnd.choice(sorted(gw.LAYOUT) + [4, 9, 30])
+        block = gw.LAYOUT.get(kind, (1, 0))[0]
+        dims = [block * rnd.randint(1, 3)] + [rnd.randint(1, 4) for _ in range(rnd.randint(0, 3))]
+        size = gw.tensor_bytes(kind, dims) if kind in gw.LAYOUT else rnd.randint(0, 64)
+        tensors.append({"name": name, "dims": dims, "type": kind,
+                        "data": bytes(rnd.getrandbits(8) for _ in range(size))})
+    blob, _ = gw.build(meta, tensors, alignment=alignment)
+    return blob, [m[0] for m in meta] + ["general.alignment"]
+
+
+def test_random_well_formed_structures(ref, mine, tmp_path):
+    rnd = random.Random(2024)
+    path = str(tmp_path / "random.gguf")
+    for _ in range(150):
+        blob, keys = random_structure(rnd)
+        open(path, "wb").write(blob)
+        rc_ref, r, rc_mine, m = open_both(ref, mine, path)
+        try:
+            assert rc_ref == 0 and rc_mine == 0
+            compare_open_files(ref, mine, r, m, keys)
+        finally:
+            close_both(ref, mine, r, m)
