@@ -17,6 +17,7 @@ struct aotx_q8_ctx {
     int overlap;
     unsigned int launches;
     q8::UmmaScratch scratch;
+    q8::NextWeights next; /* one-shot hint of aotx_q8_hint_next, taken by the next product */
 };
 
 namespace {
@@ -45,11 +46,6 @@ bool aligned(const void *p, uintptr_t to)
     return (reinterpret_cast<uintptr_t>(p) & (to - 1u)) == 0u;
 }
 
-size_t round_up(size_t v, size_t to)
-{
-    return (v + to - 1u) / to * to;
-}
-
 } // namespace
 
 extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
@@ -67,6 +63,8 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     ctx->last_cuda = 0;
     ctx->overlap = 1;
     ctx->launches = 0;
+    ctx->next.w = nullptr;
+    ctx->next.bytes = 0;
     cudaError_t err = cudaSetDevice(device);
     int sms = 0;
     if (err == cudaSuccess) {
@@ -140,6 +138,29 @@ extern "C" int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled)
     return AOTX_Q8_OK;
 }
 
+extern "C" int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, size_t bytes)
+{
+    if (ctx == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    ctx->next.w = bytes == 0u ? nullptr : w_next;
+    ctx->next.bytes = w_next == nullptr ? 0u : bytes;
+    return AOTX_Q8_OK;
+}
+
+namespace {
+
+/* The hint is for one product: whoever launches next takes it, whether its kernel uses it or not. */
+q8::NextWeights take_hint(aotx_q8_ctx *ctx)
+{
+    q8::NextWeights next = ctx->next;
+    ctx->next.w = nullptr;
+    ctx->next.bytes = 0;
+    return next;
+}
+
+} // namespace
+
 extern "C" int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx)
 {
     return ctx == nullptr ? 0 : ctx->last_cuda;
@@ -192,6 +213,8 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
+    /* the hint is for this call, whatever becomes of it */
+    const q8::NextWeights next = take_hint(ctx);
     if (!q8::block_type_known(type)) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -225,7 +248,7 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     cudaError_t err;
     if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
         err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m,
-                              m_dev, y, y_dtype, ctx->launches++, ctx->overlap != 0);
+                              m_dev, y, y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, 0u, &next);
     } else {
         err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
     }
@@ -239,11 +262,12 @@ extern "C" int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    if (type != AOTX_Q8_TYPE_Q8_0) {
-        return AOTX_Q8_ERR_TYPE;
-    }
     if (epilogue == AOTX_Q8_EPILOGUE_STORE) {
         return aotx_q8_matmul(ctx, stream, w, type, n, k, x, x_dtype, m, m_dev, y, y_dtype);
+    }
+    const q8::NextWeights next = take_hint(ctx);
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
     }
     if (epilogue != AOTX_Q8_EPILOGUE_ADD && epilogue != AOTX_Q8_EPILOGUE_SWIGLU) {
         return AOTX_Q8_ERR_ARGUMENT;
@@ -268,7 +292,7 @@ extern "C" int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *
     cudaError_t err;
     if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
         err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y,
-                              y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, (unsigned int)epilogue);
+                              y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, (unsigned int)epilogue, &next);
     } else {
         err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype,
                                    (unsigned int)epilogue);
@@ -309,6 +333,7 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
+    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -359,6 +384,7 @@ extern "C" int aotx_q8_moe_ffn_fused(aotx_q8_ctx *ctx, void *stream, const void 
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
+    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -423,6 +449,7 @@ extern "C" int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
+    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }

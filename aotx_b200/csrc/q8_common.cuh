@@ -195,6 +195,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
         : "memory");
 }
 
+// Ask L2 to fetch [addr, addr + bytes) from device memory; nothing waits for it.  Address and
+// size are multiples of 16.
+__device__ __forceinline__ void l2_prefetch_bulk(const void *addr, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(addr), "r"(bytes) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // Tensor memory and the fifth-generation tensor core.
 // ---------------------------------------------------------------------------------------

@@ -66,12 +66,19 @@ struct PeerOut {
     unsigned int ldy;
 };
 
+// The weights the product after this one will read (see UmmaArgs::next_w).
+struct NextWeights {
+    const void *w;
+    unsigned long long bytes;
+};
+
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap, const PeerOut *out = nullptr, unsigned int epilogue = 0u);
+                        bool overlap, const PeerOut *out = nullptr, unsigned int epilogue = 0u,
+                        const NextWeights *next = nullptr);
 
 // Grouped mode of the decode-regime kernel: tiles from a device table (see q8_tile.cuh).
 struct GroupTile;

@@ -73,6 +73,12 @@ struct UmmaArgs {
     // y holds (residual stream); or, with rows 2p and 2p+1 of w being the gate and up rows of
     // output column p, write silu(gate) * up to column p of a y that is n / 2 wide.
     unsigned int epilogue;
+    // The head of the weights that the product after this one will read (16-byte aligned, a
+    // multiple of 16 bytes), or null.  Every block asks L2 for its share of it once it has issued
+    // its own last weight copy, so that memory does not idle while this launch drains and the
+    // next one fills its pipeline.
+    const unsigned char *next_w;
+    unsigned long long next_bytes;
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null

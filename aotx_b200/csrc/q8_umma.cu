@@ -447,6 +447,19 @@ static EncodeTiledFn encode_tiled()
     return fn;
 }
 
+// How much of the next product's weights a launch asks L2 for: what the memory system moves
+// while one launch drains and the next fills (a few microseconds), well below the 126 MB of L2.
+static unsigned long long next_bytes_limit()
+{
+#ifdef Q8_EXPERIMENT
+    const char *env = getenv("Q8_NEXT_MB");
+    if (env != nullptr) {
+        return (unsigned long long)atoi(env) << 20;
+    }
+#endif
+    return 32ull << 20;
+}
+
 unsigned int umma_token_tile(unsigned int m)
 {
     if (m <= 16u) {
@@ -514,7 +527,7 @@ static cudaError_t launch_tile(cudaStream_t stream, const CUtensorMap &tw, const
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap, const PeerOut *out, unsigned int epilogue)
+                        bool overlap, const PeerOut *out, unsigned int epilogue, const NextWeights *next)
 {
     if (!umma_supports(w, n, k, x, m)) {
         return cudaErrorNotSupported;
@@ -579,6 +592,18 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.group_count = nullptr;
     args.row_map = nullptr;
     args.epilogue = epilogue;
+    args.next_w = nullptr;
+    args.next_bytes = 0ull;
+    if (next != nullptr && next->w != nullptr) {
+        // the head of the tensor, on 16-byte boundaries, at most kNextBytes of it
+        const uintptr_t from = (reinterpret_cast<uintptr_t>(next->w) + 15u) & ~(uintptr_t)15u;
+        const unsigned long long skipped = from - reinterpret_cast<uintptr_t>(next->w);
+        if (next->bytes > skipped + 16ull) {
+            unsigned long long bytes = (next->bytes - skipped) & ~15ull;
+            args.next_w = reinterpret_cast<const unsigned char *>(from);
+            args.next_bytes = bytes < next_bytes_limit() ? bytes : next_bytes_limit();
+        }
+    }
     args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
     args.peers = 0u;
     args.col0 = 0u;
@@ -680,6 +705,8 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     args.peers = 0u;
     args.col0 = 0u;
     args.epilogue = epilogue;
+    args.next_w = nullptr;
+    args.next_bytes = 0ull;
 #ifdef Q8_EXPERIMENT
     args.debug = 0u;
     args.trace = nullptr;

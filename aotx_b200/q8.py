@@ -15,7 +15,7 @@ F32, F16, BF16 = 0, 1, 2
 PATH_AUTO, PATH_GENERAL, PATH_TENSOR = 0, 1, 2
 EPILOGUE_STORE, EPILOGUE_ADD, EPILOGUE_SWIGLU = 0, 1, 2
 
-_ERRORS = {1: "bad argument", 2: "block type is not Q8_0", 3: "CUDA call failed",
+_ERRORS = {1: "bad argument", 2: "block type without a layout, or not served by this entry point", 3: "CUDA call failed",
            4: "shape unsupported by the forced kernel family", 5: "workspace missing or small",
            6: "a device-side wait ran out"}
 
@@ -155,6 +155,14 @@ class Q8Context:
             _dtype_code(x.dtype), m, m_dev.data_ptr() if m_dev is not None else None,
             y.data_ptr(), _dtype_code(y.dtype)))
         return y
+
+    def hint_next(self, w_next):
+        """Name the weights the product after the next one will read (a uint8 device tensor), so
+        that the next product warms L2 with their head while it drains.  One-shot."""
+        if w_next is None:
+            self._check(self.lib.aotx_q8_hint_next(self.handle, None, 0))
+        else:
+            self._check(self.lib.aotx_q8_hint_next(self.handle, w_next.data_ptr(), w_next.numel()))
 
     def matmul_fused(self, w, n, k, x, epilogue, m=None, m_dev=None, y=None, y_dtype=None, type=Q8_0):
         """The product with the next step of the layer in its store.  EPILOGUE_ADD: `y` is the

@@ -183,20 +183,29 @@ def run_ours(args, rank, world, local_rank):
         t["y"] = torch.zeros(shape, dtype=kind, device="cuda")
         t["y_host"] = torch.empty(shape, dtype=kind).pin_memory()
 
-    def product(t, c):
+    def following(i, c):
+        """The weights the product after tensors[i] of step c reads: steps run with copy c, c + 1, ..."""
+        if i + 1 < len(tensors):
+            return tensors[i + 1]["w"][c]
+        return tensors[0]["w"][(c + 1) % copies]
+
+    def product(i, c):
+        t = tensors[i]
+        if args.prefetch_next:
+            ctx.hint_next(following(i, c))
         if t["mode"]:
             ctx.matmul_fused(t["w"][c], t["n"], t["k"], t["x"], t["mode"], y=t["y"])
         else:
             ctx.matmul(t["w"][c], t["n"], t["k"], t["x"], y=t["y"])
 
     def step(c):
-        for t in tensors:
-            product(t, c)
+        for i in range(len(tensors)):
+            product(i, c)
 
     def step_e2e(c):
-        for t in tensors:
+        for i, t in enumerate(tensors):
             t["x"].copy_(t["x_host"], non_blocking=True)
-            product(t, c)
+            product(i, c)
             t["y_host"].copy_(t["y"], non_blocking=True)
 
     # One graph per weight copy: the step is launch-bound on the host otherwise.
@@ -272,9 +281,9 @@ def run_ours(args, rank, world, local_rank):
                             event.record(up_stream)
                             ready.append(event)
                     down_stream.wait_stream(main_stream)
-                    for t, event in zip(tensors, ready):
+                    for i, (t, event) in enumerate(zip(tensors, ready)):
                         main_stream.wait_event(event)
-                        product(t, c)
+                        product(i, c)
                         done = torch.cuda.Event()
                         done.record(main_stream)
                         with torch.cuda.stream(down_stream):
@@ -359,7 +368,8 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": args.workload, "rows": m, "x": x_name, "y": y_name,
                    "projections": {name: [k, n] for name, k, n in projections},
                    "weight_copies_rotated": copies, "l2": "weight copies rotate; total > 3x L2",
-                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True},
+                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True,
+                   "prefetch_next": bool(args.prefetch_next)},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode, "host_result_matches_device": check},
@@ -688,6 +698,8 @@ def main():
                         help="lm_head_colsplit: store the slices into the peers instead of an all-gather")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--prefetch-next", action="store_true",
+                        help="name the next projection's weights before each product (aotx_q8_hint_next)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
