@@ -64,7 +64,7 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     ctx->overlap = 1;
     ctx->launches = 0;
     ctx->next.w = nullptr;
-    ctx->next.bytes = 0;
+    ctx->next.n = ctx->next.k = ctx->next.m = 0;
     cudaError_t err = cudaSetDevice(device);
     int sms = 0;
     if (err == cudaSuccess) {
@@ -138,13 +138,16 @@ extern "C" int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled)
     return AOTX_Q8_OK;
 }
 
-extern "C" int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, size_t bytes)
+extern "C" int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, uint32_t n_next, uint32_t k_next,
+                                 uint32_t m_next)
 {
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    ctx->next.w = bytes == 0u ? nullptr : w_next;
-    ctx->next.bytes = w_next == nullptr ? 0u : bytes;
+    ctx->next.w = w_next;
+    ctx->next.n = n_next;
+    ctx->next.k = k_next;
+    ctx->next.m = m_next;
     return AOTX_Q8_OK;
 }
 
@@ -155,7 +158,6 @@ q8::NextWeights take_hint(aotx_q8_ctx *ctx)
 {
     q8::NextWeights next = ctx->next;
     ctx->next.w = nullptr;
-    ctx->next.bytes = 0;
     return next;
 }
 

@@ -66,10 +66,10 @@ struct PeerOut {
     unsigned int ldy;
 };
 
-// The weights the product after this one will read (see UmmaArgs::next_w).
+// The product that follows on the stream (see UmmaArgs::next_w): its weights and shape.
 struct NextWeights {
     const void *w;
-    unsigned long long bytes;
+    unsigned int n, k, m;
 };
 
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes

@@ -175,21 +175,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 u += (s1 - s0);
             }
             if (ok && args.next_w != nullptr) {
-                // This block's share of the head of the next product's weights, in pieces of
-                // 32 KB; the requests only warm L2 and nobody waits for them.
-                unsigned long long share = ((args.next_bytes / blocks) + 15ull) & ~15ull;
-                if (share == 0ull) {
-                    share = 16ull;
-                }
-                const unsigned long long begin = (unsigned long long)blockIdx.x * share;
-                unsigned long long end = begin + share;
-                if (end > args.next_bytes) {
-                    end = args.next_bytes;
-                }
-                for (unsigned long long at = begin; at < end; at += 32768ull) {
-                    const unsigned long long piece = end - at < 32768ull ? end - at : 32768ull;
-                    l2_prefetch_bulk(args.next_w + at, (uint32_t)piece);
-                }
+                prefetch_next_units(args);
             }
             // Let every copy this thread started land before the block ends.
             uint32_t local_abort = 0;

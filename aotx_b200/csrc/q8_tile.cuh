@@ -73,12 +73,17 @@ struct UmmaArgs {
     // y holds (residual stream); or, with rows 2p and 2p+1 of w being the gate and up rows of
     // output column p, write silu(gate) * up to column p of a y that is n / 2 wide.
     unsigned int epilogue;
-    // The head of the weights that the product after this one will read (16-byte aligned, a
-    // multiple of 16 bytes), or null.  Every block asks L2 for its share of it once it has issued
-    // its own last weight copy, so that memory does not idle while this launch drains and the
-    // next one fills its pipeline.
+    // The product that follows this one on the stream, or next_w == null: its weights, rows,
+    // bytes per row, segments per row and token tiles.  Once a block has issued its own last
+    // weight copy it asks L2 for the first `next_units` units that the same block index will
+    // read in that launch (the schedule is a function of these numbers and the grid), so that
+    // memory does not idle while this launch drains and the next one fills its pipeline.
     const unsigned char *next_w;
-    unsigned long long next_bytes;
+    unsigned long long next_stride;
+    unsigned int next_n;
+    unsigned int next_segs;
+    unsigned int next_tok_tiles;
+    unsigned int next_units;
 #ifdef Q8_EXPERIMENT
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null
@@ -114,6 +119,55 @@ __host__ __device__ __forceinline__ unsigned int last_holder(unsigned int b, uns
         }
     }
     return last_cc;
+}
+
+// The weight bytes that block `block` of a grid of `grid` reads first in the product that
+// follows on the stream (UmmaArgs::next_*): its first `next_units` units, each a run of 272
+// bytes in each of the 128 rows of a tile; runs of consecutive segments of one tile come as one
+// piece per row.  `emit(address, bytes)` is called once per piece.
+template <typename Emit>
+__host__ __device__ __forceinline__ void next_unit_pieces(const UmmaArgs &args, unsigned int block,
+                                                          unsigned int grid, Emit emit)
+{
+    const unsigned int row_tiles = (args.next_n + kRows - 1u) / kRows;
+    const unsigned long long units = (unsigned long long)row_tiles * args.next_tok_tiles * args.next_segs;
+    const unsigned int blocks = units < grid ? (unsigned int)units : grid;
+    if (block >= blocks) {
+        return;
+    }
+    unsigned long long u, u_end;
+    unit_range(block, blocks, units, &u, &u_end);
+    if (u_end > u + args.next_units) {
+        u_end = u + args.next_units;
+    }
+    while (u < u_end) {
+        const unsigned int tile = (unsigned int)(u / args.next_segs);
+        const unsigned int s0 = (unsigned int)(u % args.next_segs);
+        const unsigned long long left = u_end - u;
+        const unsigned int s1 = (args.next_segs - s0) < left ? args.next_segs : (unsigned int)(s0 + left);
+        const unsigned int row0 = (tile / args.next_tok_tiles) * kRows;
+        const unsigned int rows = args.next_n - row0 < kRows ? args.next_n - row0 : kRows;
+        const unsigned char *at = args.next_w + (unsigned long long)row0 * args.next_stride
+                                + (unsigned long long)s0 * kSegBytes;
+        const uint32_t bytes = (s1 - s0) * kSegBytes;
+        for (unsigned int r = 0; r < rows; ++r) {
+            emit(at + (unsigned long long)r * args.next_stride, bytes);
+        }
+        u += (s1 - s0);
+    }
+}
+
+struct L2PrefetchEmit {
+    __device__ __forceinline__ void operator()(const unsigned char *at, uint32_t bytes) const
+    {
+        l2_prefetch_bulk(at, bytes);
+    }
+};
+
+// Warm L2 with those pieces.  One thread; nothing waits for the requests.
+__device__ __forceinline__ void prefetch_next_units(const UmmaArgs &args)
+{
+    next_unit_pieces(args, blockIdx.x, gridDim.x, L2PrefetchEmit());
 }
 
 // Dequantise the two blocks of one MMA stage that this thread owns and store them as 8

@@ -593,15 +593,22 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     args.row_map = nullptr;
     args.epilogue = epilogue;
     args.next_w = nullptr;
-    args.next_bytes = 0ull;
-    if (next != nullptr && next->w != nullptr) {
-        // the head of the tensor, on 16-byte boundaries, at most kNextBytes of it
-        const uintptr_t from = (reinterpret_cast<uintptr_t>(next->w) + 15u) & ~(uintptr_t)15u;
-        const unsigned long long skipped = from - reinterpret_cast<uintptr_t>(next->w);
-        if (next->bytes > skipped + 16ull) {
-            unsigned long long bytes = (next->bytes - skipped) & ~15ull;
-            args.next_w = reinterpret_cast<const unsigned char *>(from);
-            args.next_bytes = bytes < next_bytes_limit() ? bytes : next_bytes_limit();
+    args.next_stride = 0ull;
+    args.next_n = args.next_segs = args.next_tok_tiles = args.next_units = 0u;
+    if (next != nullptr && next->w != nullptr && next->n != 0u && next->m != 0u && next->k != 0u
+        && (next->k % kSegK) == 0u && (reinterpret_cast<uintptr_t>(next->w) & 15u) == 0u) {
+        // the following product runs on this kernel too: same schedule arithmetic as below
+        const unsigned int next_tile = umma_token_tile(next->m);
+        args.next_w = static_cast<const unsigned char *>(next->w);
+        args.next_stride = row_bytes(next->k);
+        args.next_n = next->n;
+        args.next_segs = next->k / kSegK;
+        args.next_tok_tiles = (next->m + next_tile - 1u) / next_tile;
+        // what the memory system moves while one launch drains and the next fills, per block
+        const unsigned long long per_block = next_bytes_limit() / (sm_count == 0u ? 1u : sm_count);
+        args.next_units = (unsigned int)(per_block / kRawStageBytes);
+        if (args.next_units == 0u) {
+            args.next_units = 1u;
         }
     }
     args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
@@ -706,7 +713,8 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     args.col0 = 0u;
     args.epilogue = epilogue;
     args.next_w = nullptr;
-    args.next_bytes = 0ull;
+    args.next_stride = 0ull;
+    args.next_n = args.next_segs = args.next_tok_tiles = args.next_units = 0u;
 #ifdef Q8_EXPERIMENT
     args.debug = 0u;
     args.trace = nullptr;

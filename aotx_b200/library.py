@@ -65,7 +65,7 @@ def load_library():
     lib.aotx_q8_matmul_static.argtypes = [vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32]
     lib.aotx_q8_matmul_peers.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), u32,
                                          u32, u32, i32]
-    lib.aotx_q8_hint_next.argtypes = [vp, vp, C.c_size_t]
+    lib.aotx_q8_hint_next.argtypes = [vp, vp, u32, u32, u32]
     lib.aotx_q8_matmul_fused.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32, i32]
     lib.aotx_q8_moe_ffn_fused.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
                                           u32, vp, i32, vp, C.c_size_t]

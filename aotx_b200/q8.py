@@ -156,13 +156,13 @@ class Q8Context:
             y.data_ptr(), _dtype_code(y.dtype)))
         return y
 
-    def hint_next(self, w_next):
-        """Name the weights the product after the next one will read (a uint8 device tensor), so
-        that the next product warms L2 with their head while it drains.  One-shot."""
+    def hint_next(self, w_next, n=0, k=0, m=0):
+        """Name the product that follows the next one (weights `w_next[n][k]`, batch `m`), so that
+        the next product warms L2 with what that one reads first.  One-shot; None clears it."""
         if w_next is None:
-            self._check(self.lib.aotx_q8_hint_next(self.handle, None, 0))
+            self._check(self.lib.aotx_q8_hint_next(self.handle, None, 0, 0, 0))
         else:
-            self._check(self.lib.aotx_q8_hint_next(self.handle, w_next.data_ptr(), w_next.numel()))
+            self._check(self.lib.aotx_q8_hint_next(self.handle, w_next.data_ptr(), n, k, m))
 
     def matmul_fused(self, w, n, k, x, epilogue, m=None, m_dev=None, y=None, y_dtype=None, type=Q8_0):
         """The product with the next step of the layer in its store.  EPILOGUE_ADD: `y` is the

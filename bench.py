@@ -184,15 +184,17 @@ def run_ours(args, rank, world, local_rank):
         t["y_host"] = torch.empty(shape, dtype=kind).pin_memory()
 
     def following(i, c):
-        """The weights the product after tensors[i] of step c reads: steps run with copy c, c + 1, ..."""
+        """The product after tensors[i] of step c: steps run with copy c, c + 1, ..."""
         if i + 1 < len(tensors):
-            return tensors[i + 1]["w"][c]
-        return tensors[0]["w"][(c + 1) % copies]
+            t = tensors[i + 1]
+            return t["w"][c], t["n"], t["k"], m
+        t = tensors[0]
+        return t["w"][(c + 1) % copies], t["n"], t["k"], m
 
     def product(i, c):
         t = tensors[i]
         if args.prefetch_next:
-            ctx.hint_next(following(i, c))
+            ctx.hint_next(*following(i, c))
         if t["mode"]:
             ctx.matmul_fused(t["w"][c], t["n"], t["k"], t["x"], t["mode"], y=t["y"])
         else:
