@@ -102,6 +102,15 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
     unsigned long long u_begin, u_end;
     unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
+#ifdef Q8_EXPERIMENT
+    if ((args.debug & 16u) != 0u && warp == kWeightWarp && lane == 0u && args.group_tiles == nullptr
+        && args.w != nullptr) {
+        // experiment: memory starts moving for this block before its barriers and tensor
+        // memory are set up
+        first_unit_pieces(args.w, (unsigned long long)(args.k / 32u) * 34u, args.n, segs, tok_tiles,
+                          S::raw_stages, blockIdx.x, gridDim.x, L2PrefetchEmit());
+    }
+#endif
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {

@@ -85,6 +85,7 @@ struct UmmaArgs {
     unsigned int next_tok_tiles;
     unsigned int next_units;
 #ifdef Q8_EXPERIMENT
+    const unsigned char *w; // the weights as a plain pointer (debug & 16: a block warms L2 with its own first units)
     unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
     unsigned long long *trace; // [launch][block][4] timestamps, or null
 #endif
@@ -126,35 +127,44 @@ __host__ __device__ __forceinline__ unsigned int last_holder(unsigned int b, uns
 // bytes in each of the 128 rows of a tile; runs of consecutive segments of one tile come as one
 // piece per row.  `emit(address, bytes)` is called once per piece.
 template <typename Emit>
-__host__ __device__ __forceinline__ void next_unit_pieces(const UmmaArgs &args, unsigned int block,
-                                                          unsigned int grid, Emit emit)
+__host__ __device__ __forceinline__ void first_unit_pieces(const unsigned char *w, unsigned long long stride,
+                                                           unsigned int n, unsigned int segs,
+                                                           unsigned int tok_tiles, unsigned int limit,
+                                                           unsigned int block, unsigned int grid, Emit emit)
 {
-    const unsigned int row_tiles = (args.next_n + kRows - 1u) / kRows;
-    const unsigned long long units = (unsigned long long)row_tiles * args.next_tok_tiles * args.next_segs;
+    const unsigned int row_tiles = (n + kRows - 1u) / kRows;
+    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
     const unsigned int blocks = units < grid ? (unsigned int)units : grid;
     if (block >= blocks) {
         return;
     }
     unsigned long long u, u_end;
     unit_range(block, blocks, units, &u, &u_end);
-    if (u_end > u + args.next_units) {
-        u_end = u + args.next_units;
+    if (u_end > u + limit) {
+        u_end = u + limit;
     }
     while (u < u_end) {
-        const unsigned int tile = (unsigned int)(u / args.next_segs);
-        const unsigned int s0 = (unsigned int)(u % args.next_segs);
+        const unsigned int tile = (unsigned int)(u / segs);
+        const unsigned int s0 = (unsigned int)(u % segs);
         const unsigned long long left = u_end - u;
-        const unsigned int s1 = (args.next_segs - s0) < left ? args.next_segs : (unsigned int)(s0 + left);
-        const unsigned int row0 = (tile / args.next_tok_tiles) * kRows;
-        const unsigned int rows = args.next_n - row0 < kRows ? args.next_n - row0 : kRows;
-        const unsigned char *at = args.next_w + (unsigned long long)row0 * args.next_stride
-                                + (unsigned long long)s0 * kSegBytes;
+        const unsigned int s1 = (segs - s0) < left ? segs : (unsigned int)(s0 + left);
+        const unsigned int row0 = (tile / tok_tiles) * kRows;
+        const unsigned int rows = n - row0 < kRows ? n - row0 : kRows;
+        const unsigned char *at = w + (unsigned long long)row0 * stride + (unsigned long long)s0 * kSegBytes;
         const uint32_t bytes = (s1 - s0) * kSegBytes;
         for (unsigned int r = 0; r < rows; ++r) {
-            emit(at + (unsigned long long)r * args.next_stride, bytes);
+            emit(at + (unsigned long long)r * stride, bytes);
         }
         u += (s1 - s0);
     }
+}
+
+template <typename Emit>
+__host__ __device__ __forceinline__ void next_unit_pieces(const UmmaArgs &args, unsigned int block,
+                                                          unsigned int grid, Emit emit)
+{
+    first_unit_pieces(args.next_w, args.next_stride, args.next_n, args.next_segs, args.next_tok_tiles,
+                      args.next_units, block, grid, emit);
 }
 
 struct L2PrefetchEmit {

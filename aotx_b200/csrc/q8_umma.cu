@@ -629,6 +629,7 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     {
         const char *env = getenv("Q8_EXPERIMENT");
         args.debug = env != nullptr ? (unsigned int)atoi(env) : 0u;
+        args.w = static_cast<const unsigned char *>(w);
         if (getenv("Q8_TRACE") != nullptr) {
             if (g_trace_base == nullptr) {
                 cudaMalloc((void **)&g_trace_base, 256ull * 160ull * 8ull * 8ull);
@@ -718,6 +719,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
 #ifdef Q8_EXPERIMENT
     args.debug = 0u;
     args.trace = nullptr;
+    args.w = nullptr;
 #endif
     return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
 }
