@@ -459,9 +459,18 @@ def run_sharded(args, rank, world, local_rank):
         if world == 1:
             ws = ctx.moe_workspace(tokens, used, hidden, ffn)
             out = torch.empty((tokens, hidden), dtype=torch.float32, device="cuda")
+            if args.moe_fused:
+                # gate and up of every expert as one tensor with the rows interleaved
+                both = [torch.from_numpy(aotx_b200.interleave_rows(g.cpu().numpy(), u.cpu().numpy(), hidden,
+                                                                   groups=experts)).cuda()
+                        for g, u, _ in sets]
 
-            def step(c):
-                ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
+                def step(c):
+                    ctx.moe_ffn_fused(both[c], sets[c][2], experts, hidden, ffn, x_loc, prob, ids, out=out,
+                                      workspace=ws)
+            else:
+                def step(c):
+                    ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
         else:
             eps = [expert_parallel_on_gpu(ctx, *sets[c], experts, used, hidden, ffn, world, rank)
                    for c in range(copies)]
@@ -472,8 +481,9 @@ def run_sharded(args, rank, world, local_rank):
         hit = int((torch.bincount(ids_all.reshape(-1).long(), minlength=experts) > 0).sum())
         slice_bytes = 2 * ffn * (hidden // 32) * 34 + hidden * (ffn // 32) * 34
         step_bytes = hit * slice_bytes + tokens * hidden * 2 + tokens * hidden * 4
-        launches = 8
-        config = {"workload": args.workload, "tokens": tokens, "experts": experts, "used": used,
+        launches = 5 if (args.moe_fused and world == 1) else 8
+        config = {"workload": args.workload, "interleaved_gate_up": bool(args.moe_fused and world == 1),
+                  "tokens": tokens, "experts": experts, "used": used,
                   "hidden": hidden, "ffn": ffn, "experts_hit": hit, "x": "float16", "y": "float32",
                   "router": "selections made once outside the timed region",
                   "parallelism": "expert parallel x%d + all-to-all" % world if world > 1 else "single"}
@@ -700,6 +710,8 @@ def main():
                         help="lm_head_colsplit: store the slices into the peers instead of an all-gather")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--moe-fused", action="store_true",
+                        help="moe_qwen3_30b_a3b on one GPU: interleaved gate+up tensor, gated unit in the store")
     parser.add_argument("--prefetch-next", action="store_true",
                         help="name the next projection's weights before each product (aotx_q8_hint_next)")
     args = parser.parse_args()
