@@ -127,3 +127,17 @@ def test_row_bytes_and_unknown_types(decoder):
     out = np.ones(32, np.float32)
     decoder.lib.blocks_decode_run(99, np.zeros(64, np.uint8).ctypes.data, 0, out.ctypes.data)
     assert (out == 0).all()
+
+
+def test_reference_q4_0_fixtures(decoder):
+    """The reference's own Q4_0 cases (tests/matrix_test.cu:347-428), from
+    tests/golden/reference_q4_0.npz: its 96 x 256 tensor dequantises to its expected halves bit
+    for bit, and the double product over the decoded 80 x 128 tensor is its expected product."""
+    data = np.load(os.path.join(ROOT, "tests", "golden", "reference_q4_0.npz"))
+    got = decoder.rows(2, data["dequant_w"], 96, 256, half=True)
+    assert np.array_equal(got, data["dequant_want"])
+    weights = half_to_double(decoder.rows(2, data["product_w"], 80, 128, half=True))
+    for m in (1, 64):
+        x = data["product_x_m%d" % m].view(np.float16).astype(np.float64).reshape(m, 128)
+        want = data["product_want_m%d" % m]
+        assert np.abs(x @ weights.T - want).max() <= 1e-9 * np.abs(want).max()

@@ -105,3 +105,24 @@ def test_types_without_a_layout_and_rows_that_are_not_whole_blocks(ctx):
         ctx.set_path(0)
     torch.cuda.synchronize()
     assert bool((y == GUARD).all())
+
+
+def test_reference_q4_0_fixtures_on_the_gpu(ctx, oracle):
+    """The reference's own Q4_0 cases (tests/matrix_test.cu:347-428, fixtures and expectations in
+    tests/golden/reference_q4_0.npz): dequantisation of rows 16.. at 1 and 64 rows bit for bit,
+    the 80 x 128 product at 1 and 64 rows of x within its measure."""
+    import os
+    torch = torch_mod()
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_q4_0.npz"))
+    w = dev_weights(data["dequant_w"])
+    for rows in (1, 64):
+        out = ctx.dequant(w, 256, 16, rows, type=2)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), data["dequant_want"][16:16 + rows])
+    w = dev_weights(data["product_w"])
+    for m in (1, 64):
+        x = dev(data["product_x_m%d" % m].view(np.float16).reshape(m, 128))
+        y = torch.zeros((m, 80), dtype=torch.float32, device="cuda")
+        ctx.matmul(w, 80, 128, x, y=y, type=2)
+        torch.cuda.synchronize()
+        assert oracle.diff(y.cpu().numpy(), data["product_want_m%d" % m])[0] == 0
