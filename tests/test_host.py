@@ -169,3 +169,25 @@ def test_sharding_helpers_match_the_benchmark_shapes():
         total += b1 - b0
     assert total == n * (k // 32) * 34
     assert shard_rows(128, 8, 7) == (112, 128)
+
+
+def test_bench_accounting():
+    """The byte and flop counts the benchmark divides by: every weight byte once plus
+    activations in and results out; the fused layer reads and writes the float residual stream
+    and writes one half per gate/up pair."""
+    import importlib
+    bench = importlib.import_module("bench")
+    m, projections, _, _ = bench.WORKLOADS["decode_m32_llama3_8b_layer"]
+    weights = sum(n * (k // 32) * 34 for _, k, n in projections)
+    assert weights == 231735296                       # the four projections of the 8B layer
+    plain = bench.algorithmic_bytes(m, projections, 2, 2)
+    assert plain == weights + sum(m * k * 2 + m * n * 2 for _, k, n in projections)
+    fused = bench.algorithmic_bytes(m, projections, 2, 2, fused=True)
+    by_name = {name: (k, n) for name, k, n in projections}
+    expect = weights + sum(m * k * 2 for _, k, _ in projections)
+    expect += m * by_name["qkv"][1] * 2
+    expect += 2 * m * by_name["o"][1] * 4 + 2 * m * by_name["down"][1] * 4
+    expect += m * (by_name["gate_up"][1] // 2) * 2
+    assert fused == expect
+    assert bench.flops(m, projections) == sum(2 * m * n * k for _, k, n in projections)
+    assert set(bench.FUSED) <= set(bench.WORKLOADS) and bench.TENSOR_BOUND <= set(bench.WORKLOADS)
