@@ -57,6 +57,11 @@ class Oracle:
         lib.q8o_within_bound.restype = C.c_int
         lib.q8o_within_bound.argtypes = [_f32p, _f64p, C.c_size_t, C.POINTER(C.c_double),
                                          C.POINTER(C.c_double)]
+        lib.q8o_block_row_bytes.restype = C.c_uint64
+        lib.q8o_block_row_bytes.argtypes = [C.c_uint32, C.c_uint32]
+        lib.q8o_block_weight.restype = C.c_double
+        lib.q8o_block_weight.argtypes = [C.c_uint32, C.c_void_p, C.c_uint32]
+        lib.q8o_block_rows.argtypes = [C.c_uint32, _u8p, C.c_uint32, C.c_uint32, C.c_uint32, _f64p]
         lib.q8o_route.argtypes = [_u16p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   _f64p, _u32p]
         lib.q8o_rank.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_uint32, _u32p]
@@ -108,6 +113,16 @@ class Oracle:
                                 np.ascontiguousarray(y, np.float32).reshape(-1), count, seed, tol,
                                 C.byref(worst))
         return bad, worst.value
+
+    def block_row_bytes(self, kind, k):
+        return int(self.lib.q8o_block_row_bytes(kind, k))
+
+    def block_rows(self, kind, w, k, first, rows):
+        """[rows][k] doubles: the value of every weight of rows [first, first + rows) of a tensor
+        of block type `kind` (blocks_oracle.c)."""
+        out = np.empty((rows, k), np.float64)
+        self.lib.q8o_block_rows(kind, np.ascontiguousarray(w, np.uint8).reshape(-1), k, first, rows, out)
+        return out
 
     def within_bound(self, got, want):
         err = C.c_double(0)

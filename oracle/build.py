@@ -1,6 +1,7 @@
 """Build recipes for the checker libraries.  TEST INFRASTRUCTURE ONLY.
 
-`build_oracle()` compiles the C restatement beside this file into `libq8_oracle.so`.
+`build_oracle()` compiles the C restatements beside this file (`q8_oracle.c`, `blocks_oracle.c`)
+into `libq8_oracle.so`.
 `build_ref()` compiles the reference's own sources, from where they lie in a reference tree,
 into `_ref/libaotx_ref.so`, `build_gguf_ref()` the reference's model-file reader into
 `_ref/libgguf_ref.so`; both need that tree and are skipped (return None) without it.
@@ -26,11 +27,11 @@ def _newer(target, sources):
 
 
 def build_oracle(force=False):
-    src = os.path.join(HERE, "q8_oracle.c")
-    if not force and _newer(ORACLE_SO, [src]):
+    sources = [os.path.join(HERE, "q8_oracle.c"), os.path.join(HERE, "blocks_oracle.c")]
+    if not force and _newer(ORACLE_SO, sources):
         return ORACLE_SO
     cmd = ["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-shared", "-std=c11",
-           "-ffp-contract=off", "-o", ORACLE_SO, src, "-lm"]
+           "-ffp-contract=off", "-o", ORACLE_SO, *sources, "-lm"]
     subprocess.run(cmd, check=True)
     return ORACLE_SO
 

@@ -141,3 +141,40 @@ def test_reference_q4_0_fixtures(decoder):
         x = data["product_x_m%d" % m].view(np.float16).astype(np.float64).reshape(m, 128)
         want = data["product_want_m%d" % m]
         assert np.abs(x @ weights.T - want).max() <= 1e-9 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("kind", [3, 6, 7, 10, 11, 12, 13, 14])
+def test_oracle_restatement_against_the_reference_reading(oracle, kref, kind):
+    """oracle/blocks_oracle.c, the CPU restatement the GPU tests check against, gives the
+    reference reading's doubles (same expressions in double: equal to the last bits)."""
+    rng = np.random.default_rng(200 + kind)
+    n, k = 4, 512
+    w = _blocks.random_rows(kind, n, k, rng, subnormal_share=0.3)
+    assert oracle.block_row_bytes(kind, k) == kref.kref_row_bytes(kind, k)
+    want = kref_rows(kref, kind, w, n, k)
+    got = oracle.block_rows(kind, w, k, 0, n)
+    assert (np.abs(got - want) <= np.abs(want) * 4e-16).all()
+    assert np.array_equal(oracle.block_rows(kind, w, k, 1, 2), got[1:3])
+
+
+def test_oracle_restatement_of_the_plain_types(oracle, decoder):
+    """Q8_0, Q4_0, F16, F32: value = d q (or the stored number); the host decoder's floats are
+    exactly these doubles."""
+    rng = np.random.default_rng(17)
+    for kind in (8, 2, 1, 0):
+        n, k = 3, 256
+        w = _blocks.random_rows(kind, n, k, rng)
+        want = oracle.block_rows(kind, w, k, 0, n)
+        got = decoder.rows(kind, w, n, k).astype(np.float64)
+        assert np.array_equal(got, want), kind
+    for kind, k in ((12, 128), (8, 48), (4, 32), (99, 32)):
+        assert oracle.block_row_bytes(kind, k) == 0
+
+
+def test_oracle_restatement_against_golden(oracle):
+    data = np.load(GOLDEN)
+    for kind in _blocks.PACKED:
+        w, want = data["w%d" % kind], data["want%d" % kind]
+        n, k = want.shape
+        got = oracle.block_rows(kind, w, k, 0, n)
+        assert (np.abs(got - want) <= np.abs(want) * 4e-16).all(), kind

@@ -1,8 +1,11 @@
 """Every block type of the model file through aotx_q8_dequant and aotx_q8_matmul on the GPU.
 
-The dequantised halves must equal, bit for bit, what the host build of the same decoder gives
-(which tests/test_blocks.py holds against the reference's host readings on the CPU); the
-product must match the double product over those weights within the reference's measure
+The checker is the oracle's restatement of the reference's host reading (oracle/blocks_oracle.c,
+pinned against the reference's own reading on the CPU by tests/test_blocks.py): the
+dequantised halves must lie within the reference's acceptance bound of its doubles
+(tests/matrix_kcases.h:160-190: relative error at most 2^-10 or one binary16 subnormal step),
+and must equal, bit for bit, what the host build of the decoder gives; the product must match
+the double product over the oracle's weights within the reference's measure
 (tests/matrix_test.cu:246-274, 1e-2) and the bound max|err| <= 1e-2 max|y| + 1e-3; rows past
 the batch keep their guard value; a type without a layout writes nothing
 (cuda/model/dequant.cu:24-25)."""
@@ -30,7 +33,7 @@ def decoder(tmp_path_factory):
 
 
 @pytest.mark.parametrize("kind", sorted(_blocks.TYPES))
-def test_dequant_of_every_type_is_bit_exact(ctx, decoder, kind):
+def test_dequant_of_every_type_is_bit_exact(ctx, oracle, decoder, kind):
     torch = torch_mod()
     rng = np.random.default_rng(300 + kind)
     n, k = 40, 512
@@ -40,6 +43,11 @@ def test_dequant_of_every_type_is_bit_exact(ctx, decoder, kind):
     ctx.dequant(dev_weights(w), k, first, rows, out=out[:rows], type=kind)
     torch.cuda.synchronize()
     got = out.cpu().numpy().view(np.uint16)
+    ideal = oracle.block_rows(kind, w, k, first, rows)
+    have = got[:rows].view(np.float16).astype(np.float64)
+    err = np.abs(have - ideal)
+    assert np.isfinite(have).all()
+    assert ((err <= np.abs(ideal) * 9.765625e-04) | (err <= 5.9604644775390625e-08)).all()
     want = decoder.rows(kind, w, n, k, half=True)[first:first + rows]
     assert np.array_equal(got[:rows], want)
     assert (got[rows:] == np.float16(GUARD).view(np.uint16)).all()
@@ -52,7 +60,7 @@ def test_product_of_every_type(ctx, oracle, decoder, kind, m, x_kind):
     rng = np.random.default_rng(400 + kind + m)
     n, k = 72, 768
     w = _blocks.random_rows(kind, n, k, rng)
-    weights = decoder.rows(kind, w, n, k).astype(np.float64)
+    weights = oracle.block_rows(kind, w, k, 0, n)
     x = torch.from_numpy(x_fp16(m, k, 500 + kind).astype(np.float32)).to(getattr(torch, x_kind))
     want = x.double().numpy() @ weights.T
     y = torch.full((m + 2, n), GUARD, dtype=torch.float32, device="cuda")
@@ -65,12 +73,12 @@ def test_product_of_every_type(ctx, oracle, decoder, kind, m, x_kind):
     assert (got[m:] == GUARD).all()
 
 
-def test_live_batch_and_half_results_on_a_k_type(ctx, decoder):
+def test_live_batch_and_half_results_on_a_k_type(ctx, oracle):
     torch = torch_mod()
     kind, n, k, m = 12, 64, 1024, 16
     rng = np.random.default_rng(9)
     w = _blocks.random_rows(kind, n, k, rng)
-    weights = decoder.rows(kind, w, n, k).astype(np.float64)
+    weights = oracle.block_rows(kind, w, k, 0, n)
     x = x_fp16(m, k, 10)
     live = torch.tensor([5], dtype=torch.int32, device="cuda")
     y = torch.full((m, n), GUARD, dtype=torch.bfloat16, device="cuda")
