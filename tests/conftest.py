@@ -9,8 +9,18 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+def pytest_addoption(parser):
+    parser.addoption("--fake-device", action="store_true",
+                     help="check the GPU tests themselves on a machine without a GPU: the context "
+                          "is replaced by a CPU stand-in built on the oracle (tests/_fake.py)")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    if config.getoption("--fake-device"):
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        import _fake
+        _fake.install()
 
 
 @pytest.fixture(scope="session")
