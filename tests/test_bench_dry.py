@@ -141,3 +141,15 @@ def test_sharded_workloads_run_on_one_rank(monkeypatch, capsys, workload, extra)
     assert line["value"] > 0 and "roofline" in line and "clocks" in line
     if workload.startswith("moe"):
         assert line["config"]["interleaved_gate_up"] == bool(extra)
+
+
+def test_smoke_entry_runs_on_the_stand_in(monkeypatch, capsys):
+    """__graft_entry__.smoke(): the same dry run (its checks are real: the stand-in's results
+    come from the oracle, so they pass; a mistake in the smoke's own code would not)."""
+    import aotx_b200
+    entry = importlib.import_module("__graft_entry__")
+    monkeypatch.setitem(sys.modules, "torch", DryTorch())
+    monkeypatch.setattr(aotx_b200, "Q8Context", _fake.FakeContext)
+    monkeypatch.setattr(real_torch.Tensor, "cuda", lambda self, *a, **k: self)
+    entry.smoke()
+    assert "smoke ok" in capsys.readouterr().out
