@@ -18,6 +18,10 @@
 
 #include "aotx_b200_seam.hpp"
 
+#ifdef SEAM_DRY_RUN
+#include "seam_dry.h" // host stand-ins for the device, see there
+#endif
+
 #define CHECK_CUDA(call)                                                                       \
     do {                                                                                       \
         cudaError_t err_ = (call);                                                             \

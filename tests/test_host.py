@@ -117,6 +117,27 @@ def test_cpp_seam_program_builds_and_fails_loudly_without_a_device(built, tmp_pa
     assert "aotx_q8_init" in run.stderr
 
 
+def test_cpp_seam_program_dry_run(tmp_path):
+    """The same program built with -DSEAM_DRY_RUN (tests/seam_dry.h: device memory is the heap,
+    the captured graph is the recorded call replayed, the product is a host loop) runs to
+    "pass": its fixtures, its host product, its measure, its guard rows and its loop over the
+    batch word are sound.  The kernels are not involved."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    exe = tmp_path / "seam_dry"
+    subprocess.run([nvcc, "-O2", "-std=c++17", "-DSEAM_DRY_RUN", "-diag-suppress", "550", "-gencode",
+                    "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"),
+                    "-I", os.path.join(ROOT, "tests"), "-o", str(exe),
+                    os.path.join(ROOT, "tests", "seam_check.cu")], check=True, timeout=900)
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout[-2000:]
+    lines = run.stdout.strip().splitlines()
+    assert lines[-1] == "pass" and len(lines) == 11
+
+
 def test_argument_checks_need_no_device(built):
     """Every entry point refuses bad arguments before it touches CUDA, so these calls are safe
     on a machine without a GPU: null context, wrong block type, depth not a multiple of 32, a
