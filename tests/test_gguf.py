@@ -484,3 +484,83 @@ def test_random_well_formed_structures(ref, mine, tmp_path):
             compare_open_files(ref, mine, r, m, keys)
         finally:
             close_both(ref, mine, r, m)
+
+
+def test_upload_logic_dry_run(tmp_path):
+    """aotx_b200/csrc/gguf_upload.cu built with tests/gguf_dry.h in front (the CUDA runtime calls
+    become host calls) and driven like the GPU test drives the real one: byte ranges and row
+    ranges through pieces smaller and larger than the range, the strided row copy that
+    interleaves two tensors, and the refusals.  Checks the loader's host logic, not a GPU."""
+    import shutil
+    import subprocess
+    import aotx_b200
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    path = str(tmp_path / "libgguf_dry.so")
+    csrc = os.path.join(ROOT, "aotx_b200", "csrc")
+    subprocess.run([nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-diag-suppress", "174",
+                    "-gencode", "arch=compute_100a,code=sm_100a", "-include",
+                    os.path.join(ROOT, "tests", "gguf_dry.h"), "-o", path,
+                    os.path.join(csrc, "gguf_table.cpp"), os.path.join(csrc, "gguf_upload.cu")],
+                   check=True, timeout=900)
+    lib = C.CDLL(path)
+    vp, u64 = C.c_void_p, C.c_uint64
+    lib.aotx_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.aotx_gguf_close.argtypes = [vp]
+    lib.aotx_gguf_find.argtypes = [vp, C.c_char_p, vp]
+    lib.aotx_gguf_loader_init.argtypes = [C.POINTER(vp), C.c_int, C.c_size_t]
+    lib.aotx_gguf_loader_destroy.argtypes = [vp]
+    lib.aotx_gguf_upload.argtypes = [vp, vp, u64, u64, vp, vp]
+    lib.aotx_gguf_upload_rows.argtypes = [vp, vp, u64, u64, u64, vp, u64, vp]
+    lib.aotx_gguf_data_bytes.argtypes = [vp]
+    lib.aotx_gguf_data_bytes.restype = u64
+
+    k, n, ffn, experts = 512, 300, 40, 3
+    stride = aotx_b200.row_bytes(k)
+    w = aotx_b200.synth_q8_0(n, k, 51)
+    gate = aotx_b200.synth_q8_0(experts * ffn, k, 52)
+    up = aotx_b200.synth_q8_0(experts * ffn, k, 53)
+    big = np.random.default_rng(54).integers(0, 256, 9 * (1 << 20) + 32, dtype=np.uint8)
+    blob, placed = gw.build([], [{"name": "w", "dims": [k, n], "type": 8, "data": w.tobytes()},
+                                 {"name": "g", "dims": [k, ffn, experts], "type": 8, "data": gate.tobytes()},
+                                 {"name": "u", "dims": [k, ffn, experts], "type": 8, "data": up.tobytes()},
+                                 {"name": "big", "dims": [big.size // 4], "type": 0, "data": big.tobytes()}])
+    offsets = {name: offset for name, offset, _ in placed}
+    file_path = str(tmp_path / "m.gguf")
+    open(file_path, "wb").write(blob)
+    handle = vp()
+    assert lib.aotx_gguf_open(file_path.encode(), C.byref(handle)) == 0
+    try:
+        for piece in (1000, 4096, 1 << 20, 0):
+            loader = vp()
+            assert lib.aotx_gguf_loader_init(C.byref(loader), 0, piece) == 0
+            try:
+                # byte ranges: whole tensor, a shard, an odd range, nothing
+                for offset, count in ((offsets["w"], w.size), (offsets["w"] + 7 * stride, 100 * stride),
+                                      (offsets["w"] + 3, 12345), (offsets["big"], big.size), (0, 0)):
+                    out = np.full(count + 8, 0xAB, np.uint8)
+                    assert lib.aotx_gguf_upload(loader, handle, offset, count, out.ctypes.data, None) == 0
+                    assert np.array_equal(out[:count], np.frombuffer(blob, np.uint8)[
+                        len(blob) - lib.aotx_gguf_data_bytes(handle) + offset:][:count])
+                    assert (out[count:] == 0xAB).all()
+                # interleaved rows of two tensors (a piece must hold at least one row)
+                both = np.full(2 * experts * ffn * stride + 16, 0xCD, np.uint8)
+                for which, name in enumerate(("g", "u")):
+                    code = lib.aotx_gguf_upload_rows(loader, handle, offsets[name], stride, experts * ffn,
+                                                     both.ctypes.data + which * stride, 2 * stride, None)
+                    assert code == (1 if 0 < piece < stride else 0)
+                if not 0 < piece < stride:
+                    assert np.array_equal(both[:-16], aotx_b200.interleave_rows(gate, up, k, groups=experts))
+                    assert (both[-16:] == 0xCD).all()
+                # refusals: past the end of the tensor bytes, pitch below the row
+                data = lib.aotx_gguf_data_bytes(handle)
+                scratch = np.zeros(64, np.uint8)
+                assert lib.aotx_gguf_upload(loader, handle, data, 1, scratch.ctypes.data, None) == 2
+                assert lib.aotx_gguf_upload_rows(loader, handle, 0, stride, 1, scratch.ctypes.data, stride - 1, None) == 1
+                assert lib.aotx_gguf_upload_rows(loader, handle, data - stride, stride, 2, scratch.ctypes.data,
+                                                 stride, None) == 2
+            finally:
+                lib.aotx_gguf_loader_destroy(loader)
+    finally:
+        lib.aotx_gguf_close(handle)
