@@ -2,8 +2,8 @@
 // Interface and the reference code it stands in for: include/aotx_gguf_b200.h.
 //
 // The file is mapped read-only and the header is parsed by a bounds-checked cursor over the
-// mapping; only what the path needs is kept (scalar and string metadata, the tensor table with
-// an index by name).  Tensor bytes are read with pread on the descriptor, so a read of a file
+// mapping; scalar and string metadata and the tensor table (with an index by name) are kept,
+// array values stay in the file until a getter asks for one.  Tensor bytes are read with pread on the descriptor, so a read of a file
 // that was cut short after open fails with a code instead of a fault on a mapped page.
 //
 // The structural checks are the ones the reference's reader makes (disk/modelfile/gguf.c,
@@ -14,7 +14,7 @@
 // up to 65536, tensors on the alignment and inside the tensor bytes, unique keys and names, and
 // a head (everything before the tensor bytes) of at most 256 MiB.  The reference also bounds
 // the memory its own parser allocates (512 MiB, mostly copies of string arrays); this reader
-// keeps no array elements and has no such bound.
+// copies an array only when it is asked for and has no such bound.
 #include "../../include/aotx_gguf_b200.h"
 
 #include <errno.h>
@@ -102,6 +102,16 @@ struct Meta {
     int64_t i = 0;
     double f = 0.0;
     std::string text;
+    // An array's elements stay in the file; `array_pos` is the file offset of the first one and
+    // `array_bytes` their span.  A getter reads and converts them the first time it is asked.
+    uint64_t array_pos = 0;
+    uint64_t array_bytes = 0;
+    mutable bool loaded = false;
+    mutable bool fits = false;            // every element fits the type the getter gives
+    mutable std::vector<int32_t> i32;
+    mutable std::vector<float> f32;
+    mutable std::vector<uint8_t> run;      // booleans, or the bytes of all strings
+    mutable std::vector<uint64_t> offsets; // count + 1 entries into `run`
 };
 
 } // namespace
@@ -241,6 +251,7 @@ public:
             fail("an array holds more elements than the limit");
             return;
         }
+        m.array_pos = pos_;
         if (m.element_type == kString) {
             if (m.count > (file_->file_bytes - pos_) / 8u || pos_ > kHeadLimit
                 || m.count > (kHeadLimit - pos_) / 8u) {
@@ -251,6 +262,7 @@ public:
                 uint64_t length = 0;
                 text(&length);
             }
+            m.array_bytes = pos_ - m.array_pos;
             return;
         }
         unsigned width = width_of(m.element_type);
@@ -259,6 +271,7 @@ public:
             return;
         }
         const unsigned char *at = take(m.count * width);
+        m.array_bytes = m.count * width;
         if (at != nullptr && m.element_type == kBool) {
             for (uint64_t i = 0; i < m.count; ++i) {
                 if (at[i] > 1u) {
@@ -659,6 +672,185 @@ extern "C" int aotx_gguf_array(const aotx_gguf *file, const char *key, uint32_t 
     if (count != nullptr) {
         *count = m->count;
     }
+    return 0;
+}
+
+namespace {
+
+bool read_at(const aotx_gguf *file, uint64_t from, uint64_t bytes, unsigned char *out)
+{
+    while (bytes > 0) {
+        ssize_t got = pread(file->fd, out, (size_t)bytes, (off_t)from);
+        if (got < 0 && errno == EINTR) {
+            continue;
+        }
+        if (got <= 0) {
+            return false;
+        }
+        out += got;
+        from += (uint64_t)got;
+        bytes -= (uint64_t)got;
+    }
+    return true;
+}
+
+uint64_t little(const unsigned char *at, unsigned width)
+{
+    uint64_t value = 0;
+    for (unsigned i = 0; i < width; ++i) {
+        value |= (uint64_t)at[i] << (8u * i);
+    }
+    return value;
+}
+
+// Bring the elements of an array value in from the file, once, in the form its getter gives.
+// The structure was checked at open, so the bytes parse.
+bool load_array(const aotx_gguf *file, const Meta &m)
+{
+    if (m.loaded) {
+        return true;
+    }
+    std::vector<unsigned char> raw((size_t)m.array_bytes);
+    if (!raw.empty() && !read_at(file, m.array_pos, m.array_bytes, raw.data())) {
+        return false;
+    }
+    if (m.element_type == kString) {
+        m.offsets.assign((size_t)m.count + 1, 0);
+        uint64_t at = 0;
+        for (uint64_t i = 0; i < m.count; ++i) {
+            const uint64_t length = little(raw.data() + at, 8);
+            at += 8;
+            m.run.insert(m.run.end(), raw.begin() + (ptrdiff_t)at, raw.begin() + (ptrdiff_t)(at + length));
+            at += length;
+            m.offsets[(size_t)i + 1] = m.run.size();
+        }
+        m.fits = true;
+    } else if (m.element_type == kI32 || m.element_type == kU32) {
+        m.i32.assign((size_t)m.count, 0);
+        m.fits = true;
+        for (uint64_t i = 0; i < m.count; ++i) {
+            const uint64_t bits = little(raw.data() + 4 * i, 4);
+            if (m.element_type == kU32 && bits > 0x7fffffffull) {
+                m.fits = false; // the getter gives int32; the reference withholds such an array too
+            }
+            m.i32[(size_t)i] = (int32_t)(uint32_t)bits;
+        }
+    } else if (m.element_type == kF32) {
+        m.f32.assign((size_t)m.count, 0.0f);
+        for (uint64_t i = 0; i < m.count; ++i) {
+            const uint32_t bits = (uint32_t)little(raw.data() + 4 * i, 4);
+            std::memcpy(&m.f32[(size_t)i], &bits, 4);
+        }
+        m.fits = true;
+    } else if (m.element_type == kBool) {
+        m.run.assign(raw.begin(), raw.end());
+        m.fits = true;
+    }
+    m.loaded = true;
+    return true;
+}
+
+const Meta *find_array(const aotx_gguf *file, const char *key, int *code)
+{
+    const Meta *m = find_meta(file, key);
+    if (m == nullptr) {
+        *code = 1;
+        return nullptr;
+    }
+    if (m->type != kArray) {
+        *code = 2;
+        return nullptr;
+    }
+    *code = 0;
+    return m;
+}
+
+// a pointer that is never null, also for an empty array
+template <typename T>
+const T *data_or_spot(const std::vector<T> &values)
+{
+    static const T spot = T();
+    return values.empty() ? &spot : values.data();
+}
+
+} // namespace
+
+extern "C" int aotx_gguf_i32s(const aotx_gguf *file, const char *key, const int32_t **values, uint64_t *count)
+{
+    int code = 0;
+    const Meta *m = values != nullptr ? find_array(file, key, &code) : nullptr;
+    if (values == nullptr) {
+        return 1;
+    }
+    if (m == nullptr) {
+        return code;
+    }
+    if ((m->element_type != kI32 && m->element_type != kU32) || !load_array(file, *m) || !m->fits) {
+        return 2;
+    }
+    *values = data_or_spot(m->i32);
+    if (count != nullptr) {
+        *count = m->count;
+    }
+    return 0;
+}
+
+extern "C" int aotx_gguf_f32s(const aotx_gguf *file, const char *key, const float **values, uint64_t *count)
+{
+    int code = 0;
+    const Meta *m = values != nullptr ? find_array(file, key, &code) : nullptr;
+    if (values == nullptr) {
+        return 1;
+    }
+    if (m == nullptr) {
+        return code;
+    }
+    if (m->element_type != kF32 || !load_array(file, *m)) {
+        return 2;
+    }
+    *values = data_or_spot(m->f32);
+    if (count != nullptr) {
+        *count = m->count;
+    }
+    return 0;
+}
+
+extern "C" int aotx_gguf_bools(const aotx_gguf *file, const char *key, const uint8_t **values, uint64_t *count)
+{
+    int code = 0;
+    const Meta *m = values != nullptr ? find_array(file, key, &code) : nullptr;
+    if (values == nullptr) {
+        return 1;
+    }
+    if (m == nullptr) {
+        return code;
+    }
+    if (m->element_type != kBool || !load_array(file, *m)) {
+        return 2;
+    }
+    *values = data_or_spot(m->run);
+    if (count != nullptr) {
+        *count = m->count;
+    }
+    return 0;
+}
+
+extern "C" int aotx_gguf_strings(const aotx_gguf *file, const char *key, aotx_gguf_string_array *array)
+{
+    int code = 0;
+    const Meta *m = array != nullptr ? find_array(file, key, &code) : nullptr;
+    if (array == nullptr) {
+        return 1;
+    }
+    if (m == nullptr) {
+        return code;
+    }
+    if (m->element_type != kString || !load_array(file, *m)) {
+        return 2;
+    }
+    array->count = m->count;
+    array->bytes = data_or_spot(m->run);
+    array->offsets = m->offsets.data();
     return 0;
 }
 

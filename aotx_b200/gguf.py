@@ -136,6 +136,38 @@ class GGUFFile:
             raise TypeError("%s holds another type" % key)
         return int(kind.value), int(count.value)
 
+    def _numbers(self, fn, key, dtype):
+        values, count = C.c_void_p(), C.c_uint64()
+        code = fn(self.handle, key.encode(), C.byref(values), C.byref(count))
+        if code == 1:
+            raise KeyError(key)
+        if code != 0:
+            raise TypeError("%s holds another type" % key)
+        raw = C.string_at(values.value, count.value * np.dtype(dtype).itemsize)
+        return np.frombuffer(raw, dtype=dtype).copy()
+
+    def i32s(self, key):
+        return self._numbers(self.lib.aotx_gguf_i32s, key, np.int32)
+
+    def f32s(self, key):
+        return self._numbers(self.lib.aotx_gguf_f32s, key, np.float32)
+
+    def bools(self, key):
+        return self._numbers(self.lib.aotx_gguf_bools, key, np.uint8).astype(bool)
+
+    def strings(self, key):
+        """The strings of an array value, as bytes objects."""
+        from .library import StringArray
+        array = StringArray()
+        code = self.lib.aotx_gguf_strings(self.handle, key.encode(), C.byref(array))
+        if code == 1:
+            raise KeyError(key)
+        if code != 0:
+            raise TypeError("%s holds another type" % key)
+        offsets = [array.offsets[i] for i in range(array.count + 1)]
+        run = C.string_at(array.bytes, offsets[-1])
+        return [run[offsets[i]:offsets[i + 1]] for i in range(array.count)]
+
     # -- bytes ----------------------------------------------------------------------------
     def read(self, offset, count, threads=1):
         out = np.empty(count, dtype=np.uint8)

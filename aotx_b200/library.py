@@ -19,7 +19,8 @@ GGUF_SYMBOLS = (
     "aotx_gguf_open", "aotx_gguf_close", "aotx_gguf_file_bytes", "aotx_gguf_header_bytes",
     "aotx_gguf_data_bytes", "aotx_gguf_alignment", "aotx_gguf_tensor_count", "aotx_gguf_tensor",
     "aotx_gguf_find", "aotx_gguf_u32", "aotx_gguf_u64", "aotx_gguf_f32", "aotx_gguf_string",
-    "aotx_gguf_array", "aotx_gguf_read", "aotx_gguf_read_threads", "aotx_gguf_row_bytes", "aotx_gguf_row_range",
+    "aotx_gguf_array", "aotx_gguf_i32s", "aotx_gguf_f32s", "aotx_gguf_bools", "aotx_gguf_strings",
+    "aotx_gguf_read", "aotx_gguf_read_threads", "aotx_gguf_row_bytes", "aotx_gguf_row_range",
     "aotx_gguf_loader_init", "aotx_gguf_loader_destroy", "aotx_gguf_loader_last_cuda_error",
     "aotx_gguf_upload", "aotx_gguf_upload_rows",
 )
@@ -29,6 +30,11 @@ class TensorInfo(C.Structure):
     """aotx_gguf_tensor_info of include/aotx_gguf_b200.h."""
     _fields_ = [("name", C.c_char * 128), ("dim_count", C.c_uint32), ("type", C.c_uint32),
                 ("dims", C.c_uint64 * 4), ("offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
+class StringArray(C.Structure):
+    """aotx_gguf_string_array of include/aotx_gguf_b200.h."""
+    _fields_ = [("count", C.c_uint64), ("bytes", C.c_void_p), ("offsets", C.POINTER(C.c_uint64))]
 
 
 class LibraryMissing(RuntimeError):
@@ -90,6 +96,10 @@ def load_library():
     lib.aotx_gguf_f32.argtypes = [vp, C.c_char_p, C.POINTER(C.c_float)]
     lib.aotx_gguf_string.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
     lib.aotx_gguf_array.argtypes = [vp, C.c_char_p, C.POINTER(u32), C.POINTER(u64)]
+    lib.aotx_gguf_i32s.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]
+    lib.aotx_gguf_f32s.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]
+    lib.aotx_gguf_bools.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]
+    lib.aotx_gguf_strings.argtypes = [vp, C.c_char_p, C.POINTER(StringArray)]
     lib.aotx_gguf_read.argtypes = [vp, u64, u64, vp]
     lib.aotx_gguf_read_threads.argtypes = [vp, u64, u64, vp, u32]
     lib.aotx_gguf_row_bytes.argtypes = [u32, u64]

@@ -74,13 +74,28 @@ int aotx_gguf_find(const aotx_gguf *file, const char *name, aotx_gguf_tensor_inf
 
 /* Scalar and string metadata by key (disk/modelfile/modelfile.h:138-143).  Any whole-number
  * type that is not negative reads as u64 / u32 (u32 refuses values above 2^32 - 1); F32 and
- * F64 read as f32.  Arrays are checked at open and can be sized here; their elements are not
- * kept (the path needs shapes and counts, not token tables). */
+ * F64 read as f32.  Arrays are checked at open and can be sized with aotx_gguf_array; their
+ * elements come through the getters further down. */
 int aotx_gguf_u32(const aotx_gguf *file, const char *key, uint32_t *value);
 int aotx_gguf_u64(const aotx_gguf *file, const char *key, uint64_t *value);
 int aotx_gguf_f32(const aotx_gguf *file, const char *key, float *value);
 int aotx_gguf_string(const aotx_gguf *file, const char *key, const char **value, size_t *length);
 int aotx_gguf_array(const aotx_gguf *file, const char *key, uint32_t *element_type, uint64_t *count);
+
+/* Array values by key (disk/modelfile/modelfile.h:144-151), read from the file the first time
+ * they are asked for and kept until close.  i32s gives arrays of I32 and of U32 whose elements
+ * all fit int32; f32s arrays of F32; bools arrays of BOOL; strings arrays of STRING as one byte
+ * run with count + 1 offsets (same layout as the reference's aotx_string_array,
+ * disk/modelfile/modelfile.h:108-114).  The pointers stay valid until aotx_gguf_close. */
+typedef struct aotx_gguf_string_array {
+    uint64_t count;
+    const uint8_t *bytes;    /* every string, one after the other, no separators */
+    const uint64_t *offsets; /* string i is [offsets[i], offsets[i + 1]) */
+} aotx_gguf_string_array;
+int aotx_gguf_i32s(const aotx_gguf *file, const char *key, const int32_t **values, uint64_t *count);
+int aotx_gguf_f32s(const aotx_gguf *file, const char *key, const float **values, uint64_t *count);
+int aotx_gguf_bools(const aotx_gguf *file, const char *key, const uint8_t **values, uint64_t *count);
+int aotx_gguf_strings(const aotx_gguf *file, const char *key, aotx_gguf_string_array *array);
 
 /* Read tensor bytes into host memory; offset from the start of the tensor bytes
  * (disk/modelfile/modelfile.h:159-162). */

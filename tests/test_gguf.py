@@ -29,6 +29,11 @@ class RefInfo(C.Structure):
                 ("dims", C.c_uint64 * 4), ("offset", C.c_uint64), ("bytes", C.c_uint64)]
 
 
+class RefStrings(C.Structure):
+    # aotx_string_array, disk/modelfile/modelfile.h:108-114
+    _fields_ = [("count", C.c_uint64), ("bytes", C.c_void_p), ("offsets", C.POINTER(C.c_uint64))]
+
+
 @pytest.fixture(scope="module")
 def ref():
     from oracle import build
@@ -50,6 +55,9 @@ def ref():
     lib.aotx_modelfile_f32.argtypes = [vp, C.c_char_p, C.POINTER(C.c_float)]
     lib.aotx_modelfile_string.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
     lib.aotx_modelfile_read.argtypes = [vp, u64, u64, vp]
+    for name in ("i32s", "f32s", "bools"):
+        getattr(lib, "aotx_modelfile_" + name).argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]
+    lib.aotx_modelfile_strings.argtypes = [vp, C.c_char_p, C.POINTER(RefStrings)]
     return lib
 
 
@@ -76,7 +84,7 @@ def close_both(ref, mine, r, m):
 
 
 def compare_open_files(ref, mine, r, m, keys):
-    from aotx_b200.library import TensorInfo
+    from aotx_b200.library import StringArray, TensorInfo
     assert mine.aotx_gguf_file_bytes(m) == ref.aotx_modelfile_file_bytes(r)
     assert mine.aotx_gguf_header_bytes(m) == ref.aotx_modelfile_header_bytes(r)
     assert mine.aotx_gguf_data_bytes(m) == ref.aotx_modelfile_data_bytes(r)
@@ -106,6 +114,21 @@ def compare_open_files(ref, mine, r, m, keys):
         assert rc == mine.aotx_gguf_string(m, k, C.byref(bp), C.byref(bl)), key
         if rc == 0:
             assert C.string_at(ap.value, al.value) == C.string_at(bp.value, bl.value)
+        for name, width in (("i32s", 4), ("f32s", 4), ("bools", 1)):
+            ap, bp, ac, bc = C.c_void_p(), C.c_void_p(), C.c_uint64(99), C.c_uint64(99)
+            rc = getattr(ref, "aotx_modelfile_" + name)(r, k, C.byref(ap), C.byref(ac))
+            assert rc == getattr(mine, "aotx_gguf_" + name)(m, k, C.byref(bp), C.byref(bc)), (key, name)
+            if rc == 0:
+                assert ac.value == bc.value
+                assert C.string_at(ap.value, ac.value * width) == C.string_at(bp.value, bc.value * width), (key, name)
+        sa, sb = RefStrings(), StringArray()
+        rc = ref.aotx_modelfile_strings(r, k, C.byref(sa))
+        assert rc == mine.aotx_gguf_strings(m, k, C.byref(sb)), key
+        if rc == 0:
+            assert sa.count == sb.count
+            assert [sa.offsets[i] for i in range(sa.count + 1)] == [sb.offsets[i] for i in range(sb.count + 1)]
+            total = sa.offsets[sa.count]
+            assert C.string_at(sa.bytes, total) == C.string_at(sb.bytes, total)
 
 
 def sample_file(rng, alignment=32):
@@ -380,6 +403,25 @@ def test_row_ranges_are_the_shards_of_a_column_split(mine, tmp_path):
         with pytest.raises(KeyError):
             f.find("absent")
         assert f.string("general.architecture") == b"llama"
+
+
+def test_array_values_through_the_python_mirror(mine, tmp_path):
+    from aotx_b200.gguf import GGUFFile
+    blob, _, _ = sample_file(np.random.default_rng(3))
+    path = str(tmp_path / "s.gguf")
+    open(path, "wb").write(blob)
+    with GGUFFile(path) as f:
+        assert f.strings("tokenizer.ggml.tokens") == [b"a", b"", b"hello", "世界".encode()]
+        assert f.i32s("tokenizer.ggml.token_type").tolist() == [1, 2, 3, -4]
+        assert f.f32s("tokenizer.ggml.scores").tolist() == [0.5, -1.25]
+        assert f.bools("tokenizer.flags").tolist() == [False, True, True]
+        assert f.array("tokenizer.wide") == (gw.U64, 2)
+        with pytest.raises(TypeError):
+            f.i32s("tokenizer.wide")          # 64-bit elements do not come as int32
+        with pytest.raises(TypeError):
+            f.strings("llama.block_count")
+        with pytest.raises(KeyError):
+            f.f32s("absent")
 
 
 def test_library_exports_every_declared_gguf_symbol(mine):
