@@ -13,20 +13,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#define Q8_BLOCK 32u
-#define Q8_BLOCK_BYTES 34u
-#define Q8_TYPE_Q8_0 8u /* cuda/model/model.cuh:31 */
+#include "q8_store.cuh"
+
 
 // Bits of the device status word that kernels raise instead of hanging.
 #define Q8_DEV_BARRIER_TIMEOUT 1u /* a wait on a shared-memory barrier ran out */
 #define Q8_DEV_FLAG_TIMEOUT 2u    /* a wait on another block's partial sum ran out */
 
 namespace q8 {
-
-__host__ __device__ inline unsigned long long row_bytes(unsigned int k)
-{
-    return (unsigned long long)(k / Q8_BLOCK) * Q8_BLOCK_BYTES;
-}
 
 // ---------------------------------------------------------------------------------------
 // Exact dequantisation of packed bytes.
@@ -373,27 +367,6 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int *p)
 __device__ __forceinline__ void st_release_gpu(unsigned int *p, uint32_t v)
 {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-template <typename T>
-__device__ __forceinline__ void store_out(T *y, size_t at, float v);
-
-template <>
-__device__ __forceinline__ void store_out<float>(float *y, size_t at, float v)
-{
-    y[at] = v;
-}
-
-template <>
-__device__ __forceinline__ void store_out<__half>(__half *y, size_t at, float v)
-{
-    y[at] = __float2half_rn(v);
-}
-
-template <>
-__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *y, size_t at, float v)
-{
-    y[at] = __float2bfloat16_rn(v);
 }
 
 } // namespace q8

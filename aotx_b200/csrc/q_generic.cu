@@ -4,8 +4,8 @@
 // go through the one decoder of q_blocks.cuh here, so that the entry points serve whatever type
 // a model file holds.  These kernels are written for coverage and exactness first: a lane
 // decodes a run of 32 weights into registers once and uses it for up to 8 rows of x.
-#include "q8_common.cuh"
 #include "q8_launch.h"
+#include "q8_store.cuh"
 #include "q_blocks.cuh"
 
 namespace q8 {
@@ -111,6 +111,7 @@ q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n
     }
 }
 
+#ifndef Q8_HOST_EMULATION /* the launchers use the <<< >>> syntax; the emulator calls the kernels itself */
 bool block_type_known(unsigned int type)
 {
     uint32_t weights = 0, bytes = 0;
@@ -172,5 +173,7 @@ cudaError_t launch_gemv_any(cudaStream_t stream, const void *w, unsigned int typ
 #undef QG_CASE
     return cudaErrorInvalidValue;
 }
+
+#endif
 
 } // namespace q8

@@ -1,0 +1,213 @@
+// A small host emulator for the kernels that run on the ordinary cores (no tensor memory, no
+// bulk copies): the kernel source is compiled as host code, a block runs as blockDim.x host
+// threads, and __shfl_*_sync / __syncwarp / __syncthreads are barriers between them, so the
+// kernels execute with the warp semantics they rely on.  It lets the tests run, without a GPU,
+//   q_dequant_any_kernel, q_gemv_any_kernel            (aotx_b200/csrc/q_generic.cu)
+//   q8_gemv_simt_kernel, q8_gemv_simt_fused_kernel     (aotx_b200/csrc/q8_simt_gemv.cuh)
+// on small shapes and compare them with the oracle.  It checks the kernels' index arithmetic and
+// data flow; it says nothing about the hardware.
+//
+// Built as a shared library by tests/test_simt_emu.py (nvcc, host code only).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <condition_variable>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+namespace emu {
+
+struct Index {
+    unsigned int x, y, z;
+};
+
+class Barrier {
+public:
+    explicit Barrier(unsigned int count) : count_(count), waiting_(0), generation_(0) {}
+    void wait()
+    {
+        std::unique_lock<std::mutex> lock(mutex_);
+        const unsigned int generation = generation_;
+        if (++waiting_ == count_) {
+            waiting_ = 0;
+            generation_ += 1;
+            wake_.notify_all();
+        } else {
+            wake_.wait(lock, [&] { return generation_ != generation; });
+        }
+    }
+
+private:
+    std::mutex mutex_;
+    std::condition_variable wake_;
+    unsigned int count_, waiting_, generation_;
+};
+
+struct Warp {
+    Barrier barrier{32};
+    uint32_t slot[32];
+};
+
+struct Block {
+    std::vector<Warp> warps;
+    Barrier *all;
+};
+
+thread_local Index thread_index = {0, 0, 0};
+thread_local Index block_index = {0, 0, 0};
+thread_local Block *block = nullptr;
+Index block_dim = {1, 1, 1};
+Index grid_dim = {1, 1, 1};
+
+// every lane of the warp calls these together (full mask), as the kernels under test do
+inline uint32_t exchange(uint32_t value, unsigned int from_lane_of_mine(unsigned int))
+{
+    Warp &warp = block->warps[thread_index.x / 32u];
+    const unsigned int lane = thread_index.x % 32u;
+    warp.slot[lane] = value;
+    warp.barrier.wait();
+    const unsigned int source = from_lane_of_mine(lane);
+    const uint32_t got = source < 32u ? warp.slot[source] : value;
+    warp.barrier.wait();
+    return got;
+}
+
+thread_local unsigned int shift = 0;
+
+inline float shfl_down(float value, unsigned int delta)
+{
+    shift = delta;
+    uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    bits = exchange(bits, [](unsigned int lane) { return lane + shift; });
+    std::memcpy(&value, &bits, 4);
+    return value;
+}
+
+inline float shfl_xor(float value, unsigned int mask)
+{
+    shift = mask;
+    uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    bits = exchange(bits, [](unsigned int lane) { return lane ^ shift; });
+    std::memcpy(&value, &bits, 4);
+    return value;
+}
+
+inline void sync_warp()
+{
+    block->warps[thread_index.x / 32u].barrier.wait();
+}
+
+inline void sync_block()
+{
+    block->all->wait();
+}
+
+inline float uint_as_float(uint32_t bits)
+{
+    float value;
+    std::memcpy(&value, &bits, 4);
+    return value;
+}
+
+// Run `body` as a grid of `grid` blocks of `threads` threads (a multiple of 32), block by block.
+inline void launch(unsigned int grid, unsigned int threads, const std::function<void()> &body)
+{
+    block_dim = {threads, 1, 1};
+    grid_dim = {grid, 1, 1};
+    for (unsigned int b = 0; b < grid; ++b) {
+        Block shared;
+        shared.warps = std::vector<Warp>(threads / 32u);
+        Barrier all(threads);
+        shared.all = &all;
+        std::vector<std::thread> lanes;
+        lanes.reserve(threads);
+        for (unsigned int t = 0; t < threads; ++t) {
+            lanes.emplace_back([&, t, b] {
+                thread_index = {t, 0, 0};
+                block_index = {b, 0, 0};
+                block = &shared;
+                body();
+            });
+        }
+        for (std::thread &lane : lanes) {
+            lane.join();
+        }
+    }
+}
+
+} // namespace emu
+
+// ---- the kernel sources as host code --------------------------------------------------------
+#undef __global__
+#define __global__
+#undef __device__
+#define __device__
+#undef __host__
+#define __host__
+#undef __forceinline__
+#define __forceinline__ inline
+#undef __launch_bounds__
+#define __launch_bounds__(...)
+#define threadIdx (emu::thread_index)
+#define blockIdx (emu::block_index)
+#define blockDim (emu::block_dim)
+#define gridDim (emu::grid_dim)
+#define __shfl_down_sync(mask, value, delta) emu::shfl_down((value), (delta))
+#define __shfl_xor_sync(mask, value, lanes) emu::shfl_xor((value), (lanes))
+#define __syncwarp() emu::sync_warp()
+#define __syncthreads() emu::sync_block()
+#define __uint_as_float(bits) emu::uint_as_float(bits)
+#define Q8_HOST_EMULATION 1
+
+#include "q8_simt_gemv.cuh"
+#include "q_generic.cu"
+
+// ---- entry points for the tests -------------------------------------------------------------
+extern "C" void emu_dequant_any(const unsigned char *w, uint32_t type, uint32_t k, uint32_t first_row, uint32_t rows,
+                                unsigned short *out, uint32_t grid)
+{
+    emu::launch(grid, 256, [=] {
+        q8::q_dequant_any_kernel(w, type, k, first_row, rows, reinterpret_cast<__half *>(out));
+    });
+}
+
+// x and y: binary16 in, float out (the reference's types)
+extern "C" void emu_gemv_any(const unsigned char *w, uint32_t type, uint32_t n, uint32_t k, const unsigned short *x,
+                             uint32_t m, const unsigned int *m_dev, float *y, uint32_t grid)
+{
+    emu::launch(grid, QG_WARPS * 32u, [=] {
+        q8::q_gemv_any_kernel<__half, float>(w, type, n, k, reinterpret_cast<const __half *>(x), m, m_dev, y);
+    });
+}
+
+extern "C" void emu_gemv_q8(const unsigned char *w, uint32_t n, uint32_t k, const unsigned short *x, uint32_t m,
+                            const unsigned int *m_dev, float *y, uint32_t grid)
+{
+    emu::launch(grid, Q8_SIMT_WARPS * 32u, [=] {
+        q8::q8_gemv_simt_kernel<__half, float>(w, n, k, reinterpret_cast<const __half *>(x), m, m_dev, y);
+    });
+}
+
+// epilogue 1: y float, added to; epilogue 2: y binary16 [m][n / 2]
+extern "C" void emu_gemv_q8_fused(const unsigned char *w, uint32_t n, uint32_t k, const unsigned short *x, uint32_t m,
+                                  const unsigned int *m_dev, void *y, uint32_t epilogue, uint32_t grid)
+{
+    if (epilogue == 1u) {
+        emu::launch(grid, Q8_SIMT_WARPS * 32u, [=] {
+            q8::q8_gemv_simt_fused_kernel<__half, float>(w, n, k, reinterpret_cast<const __half *>(x), m, m_dev,
+                                                         static_cast<float *>(y), epilogue);
+        });
+    } else {
+        emu::launch(grid, Q8_SIMT_WARPS * 32u, [=] {
+            q8::q8_gemv_simt_fused_kernel<__half, __half>(w, n, k, reinterpret_cast<const __half *>(x), m, m_dev,
+                                                          static_cast<__half *>(y), epilogue);
+        });
+    }
+}

@@ -1,0 +1,104 @@
+"""The kernels that run on the ordinary cores, executed on the host by tests/simt_emu.cu (the
+kernel source compiled as host code, a block as host threads, warp shuffles as barriers between
+them) and checked against the oracle: the any-shape Q8_0 product, its two fused stores, and the
+dequantisation and product kernels of the other block types.  This checks the kernels' index
+arithmetic and data flow - which rows, which columns, which lane stores - on a machine without
+a GPU; the GPU tests repeat the checks on the real thing."""
+import ctypes as C
+import os
+import shutil
+import subprocess
+
+import numpy as np
+import pytest
+
+import _blocks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def emu(tmp_path_factory):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    path = str(tmp_path_factory.mktemp("emu") / "libsimt_emu.so")
+    done = subprocess.run([nvcc, "-O1", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-gencode",
+                           "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "aotx_b200", "csrc"),
+                           "-o", path, os.path.join(ROOT, "tests", "simt_emu.cu")],
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-3000:]
+    lib = C.CDLL(path)
+    vp, u32 = C.c_void_p, C.c_uint32
+    lib.emu_dequant_any.argtypes = [vp, u32, u32, u32, u32, vp, u32]
+    lib.emu_gemv_any.argtypes = [vp, u32, u32, u32, vp, u32, vp, vp, u32]
+    lib.emu_gemv_q8.argtypes = [vp, u32, u32, vp, u32, vp, vp, u32]
+    lib.emu_gemv_q8_fused.argtypes = [vp, u32, u32, vp, u32, vp, vp, u32, u32]
+    return lib
+
+
+def inputs(m, k, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return rng.standard_normal((m, k)).astype(np.float16)
+
+
+@pytest.mark.parametrize("n,k,m,grid", [(20, 128, 3, 2), (9, 96, 11, 1), (17, 64, 8, 3)])
+def test_q8_product_kernel(emu, oracle, n, k, m, grid):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 5)
+    x = inputs(m, k, 6)
+    y = np.full((m + 1, n), -7.0, np.float32)
+    emu.emu_gemv_q8(w.ctypes.data, n, k, x.ctypes.data, m, None, y.ctypes.data, grid)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == -7.0).all()
+    # the live batch word
+    live = np.array([2], np.uint32)
+    y2 = np.full((m, n), -7.0, np.float32)
+    emu.emu_gemv_q8(w.ctypes.data, n, k, x.ctypes.data, m, live.ctypes.data, y2.ctypes.data, grid)
+    assert np.array_equal(y2[:2], y[:2]) and (y2[2:] == -7.0).all()
+
+
+@pytest.mark.parametrize("n,k,m,grid", [(20, 128, 3, 2), (12, 64, 10, 1)])
+def test_q8_product_with_the_fused_stores(emu, oracle, n, k, m, grid):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 7)
+    x = (inputs(m, k, 8).astype(np.float32) * 8).astype(np.float16)
+    plain = np.zeros((m, n), np.float32)
+    emu.emu_gemv_q8(w.ctypes.data, n, k, x.ctypes.data, m, None, plain.ctypes.data, grid)
+    # residual add: one float add of the same sum
+    rng = np.random.default_rng(9)
+    y0 = rng.standard_normal((m + 1, n)).astype(np.float32)
+    y = y0.copy()
+    emu.emu_gemv_q8_fused(w.ctypes.data, n, k, x.ctypes.data, m, None, y.ctypes.data, 1, grid)
+    assert np.array_equal(y[:m], y0[:m] + plain) and np.array_equal(y[m:], y0[m:])
+    # gated unit over row pairs: rows 2p, 2p + 1 -> column p
+    act = np.full((m + 1, n // 2), 9.0, np.float16)
+    emu.emu_gemv_q8_fused(w.ctypes.data, n, k, x.ctypes.data, m, None, act.ctypes.data, 2, grid)
+    gate, up = plain[:, 0::2], plain[:, 1::2]
+    want = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float32)
+    got = act[:m].astype(np.float32)
+    assert (np.abs(got - want) <= 2.0 ** -10 * np.abs(want) + 1e-6).all()
+    assert (act[m:] == np.float16(9.0)).all()
+    assert np.abs(want).max() > 0.1
+
+
+@pytest.mark.parametrize("kind", sorted(_blocks.TYPES))
+def test_other_block_types_dequant_and_product(emu, oracle, kind):
+    rng = np.random.default_rng(40 + kind)
+    n, k, m = 10, 512, 9
+    w = _blocks.random_rows(kind, n, k, rng)
+    first, rows = 3, 6
+    out = np.full((rows + 1, k), 0x7777, np.uint16)
+    emu.emu_dequant_any(w.ctypes.data, kind, k, first, rows, out.ctypes.data, 2)
+    ideal = oracle.block_rows(kind, w, k, first, rows)
+    have = out[:rows].view(np.float16).astype(np.float64)
+    err = np.abs(have - ideal)
+    assert ((err <= np.abs(ideal) * 9.765625e-04) | (err <= 5.9604644775390625e-08)).all()
+    assert (out[rows:] == 0x7777).all()
+    x = inputs(m, k, 50 + kind)
+    y = np.full((m + 1, n), -7.0, np.float32)
+    emu.emu_gemv_any(w.ctypes.data, kind, n, k, x.ctypes.data, m, None, y.ctypes.data, 2)
+    want = x.astype(np.float64) @ oracle.block_rows(kind, w, k, 0, n).T
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == -7.0).all()
