@@ -50,22 +50,42 @@ __device__ __forceinline__ float x_value<__nv_bfloat16>(const __nv_bfloat16 *x)
     return __bfloat162float(*x);
 }
 
-// One warp, one row of w, up to 8 rows of x: lanes take runs of 32 weights 32 apart, keep the
-// float value of a weight (no rounding to half, like the reference's memory-bound kernel,
-// cuda/model/matrix.cuh:493-670), and add their parts with a shuffle tree.
-template <typename XT, typename YT>
-__global__ void __launch_bounds__(QG_WARPS * 32u)
-q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n, uint32_t k,
-                  const XT *__restrict__ x, uint32_t m_max, const unsigned int *m_dev, YT *__restrict__ y)
+// eight activations from one 16-byte load
+template <typename XT>
+__device__ __forceinline__ void x_eight(const uint4 &packed, float *out);
+
+template <>
+__device__ __forceinline__ void x_eight<__half>(const uint4 &packed, float *out)
 {
-    uint32_t m = m_max;
-    if (m_dev != nullptr) {
-        const uint32_t live = *m_dev;
-        m = live < m_max ? live : m_max;
+    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 pair = __half22float2(*reinterpret_cast<const __half2 *>(&words[i]));
+        out[2 * i] = pair.x;
+        out[2 * i + 1] = pair.y;
     }
+}
+
+template <>
+__device__ __forceinline__ void x_eight<__nv_bfloat16>(const uint4 &packed, float *out)
+{
+    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(words[i] << 16);
+        out[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+    }
+}
+
+// The rows of one warp for one block type.  TYPE is a constant here, so the decoder's switch
+// folds to the one reader; the activations come as 16-byte loads when x allows it.
+template <uint32_t TYPE, typename XT, typename YT>
+__device__ __forceinline__ void gemv_rows(const unsigned char *__restrict__ w, uint32_t n, uint32_t k,
+                                          const XT *__restrict__ x, uint32_t m, YT *__restrict__ y, bool wide_x)
+{
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = threadIdx.x >> 5;
-    const unsigned long long stride = block_row_bytes(type, k);
+    const unsigned long long stride = block_row_bytes(TYPE, k);
     const uint32_t runs = k / 32u;
     for (uint32_t j = blockIdx.x * QG_WARPS + warp; j < n; j += gridDim.x * QG_WARPS) {
         const unsigned char *row = w + stride * j;
@@ -78,15 +98,28 @@ q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n
             }
             for (uint32_t run = lane; run < runs; run += 32u) {
                 float values[32];
-                decode_run(type, row, run, values);
+                decode_run(TYPE, row, run, values);
 #pragma unroll
                 for (uint32_t t = 0; t < QG_TAKE; ++t) {
                     if (t < take) {
                         const XT *xr = x + (size_t)(m0 + t) * k + (size_t)run * 32u;
                         float sum = acc[t];
+                        if (wide_x) {
+                            const uint4 *wide = reinterpret_cast<const uint4 *>(xr);
 #pragma unroll
-                        for (uint32_t i = 0; i < 32u; ++i) {
-                            sum = fmaf(values[i], x_value<XT>(xr + i), sum);
+                            for (uint32_t q = 0; q < 4u; ++q) {
+                                float eight[8];
+                                x_eight<XT>(wide[q], eight);
+#pragma unroll
+                                for (uint32_t i = 0; i < 8u; ++i) {
+                                    sum = fmaf(values[8u * q + i], eight[i], sum);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (uint32_t i = 0; i < 32u; ++i) {
+                                sum = fmaf(values[i], x_value<XT>(xr + i), sum);
+                            }
                         }
                         acc[t] = sum;
                     }
@@ -108,6 +141,38 @@ q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n
                 }
             }
         }
+    }
+}
+
+// One warp, one row of w, up to 8 rows of x: lanes take runs of 32 weights 32 apart, keep the
+// float value of a weight (no rounding to half, like the reference's memory-bound kernel,
+// cuda/model/matrix.cuh:493-670), and add their parts with a shuffle tree.
+template <typename XT, typename YT>
+__global__ void __launch_bounds__(QG_WARPS * 32u)
+q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n, uint32_t k,
+                  const XT *__restrict__ x, uint32_t m_max, const unsigned int *m_dev, YT *__restrict__ y,
+                  uint32_t wide_x)
+{
+    uint32_t m = m_max;
+    if (m_dev != nullptr) {
+        const uint32_t live = *m_dev;
+        m = live < m_max ? live : m_max;
+    }
+    const bool wide = wide_x != 0u;
+    switch (type) {
+    case kTypeF32: gemv_rows<kTypeF32, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeF16: gemv_rows<kTypeF16, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ4_0: gemv_rows<kTypeQ4_0, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ4_1: gemv_rows<kTypeQ4_1, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ5_0: gemv_rows<kTypeQ5_0, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ5_1: gemv_rows<kTypeQ5_1, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ8_0: gemv_rows<kTypeQ8_0, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ2_K: gemv_rows<kTypeQ2_K, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ3_K: gemv_rows<kTypeQ3_K, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ4_K: gemv_rows<kTypeQ4_K, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ5_K: gemv_rows<kTypeQ5_K, XT, YT>(w, n, k, x, m, y, wide); break;
+    case kTypeQ6_K: gemv_rows<kTypeQ6_K, XT, YT>(w, n, k, x, m, y, wide); break;
+    default: break; // a type without a layout writes nothing
     }
 }
 
@@ -144,9 +209,11 @@ static cudaError_t launch_gemv_any_typed(cudaStream_t stream, const void *w, uns
 {
     const unsigned int want = (n + QG_WARPS - 1u) / QG_WARPS;
     const unsigned int grid = want < 148u * 8u ? want : 148u * 8u;
+    // rows of x are k * 2 bytes, a multiple of 64: 16-byte loads need only an aligned base
+    const uint32_t wide_x = (reinterpret_cast<uintptr_t>(x) & 15u) == 0u ? 1u : 0u;
     q_gemv_any_kernel<XT, YT><<<grid, QG_WARPS * 32u, 0, stream>>>(
         static_cast<const unsigned char *>(w), type, n, k, static_cast<const XT *>(x), m, m_dev,
-        static_cast<YT *>(y));
+        static_cast<YT *>(y), wide_x);
     return cudaGetLastError();
 }
 

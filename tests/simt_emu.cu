@@ -180,10 +180,22 @@ extern "C" void emu_dequant_any(const unsigned char *w, uint32_t type, uint32_t 
 
 // x and y: binary16 in, float out (the reference's types)
 extern "C" void emu_gemv_any(const unsigned char *w, uint32_t type, uint32_t n, uint32_t k, const unsigned short *x,
-                             uint32_t m, const unsigned int *m_dev, float *y, uint32_t grid)
+                             uint32_t m, const unsigned int *m_dev, float *y, uint32_t wide_x, uint32_t grid)
 {
     emu::launch(grid, QG_WARPS * 32u, [=] {
-        q8::q_gemv_any_kernel<__half, float>(w, type, n, k, reinterpret_cast<const __half *>(x), m, m_dev, y);
+        q8::q_gemv_any_kernel<__half, float>(w, type, n, k, reinterpret_cast<const __half *>(x), m, m_dev, y,
+                                             wide_x);
+    });
+}
+
+// bfloat16 activations, bfloat16 results
+extern "C" void emu_gemv_any_bf16(const unsigned char *w, uint32_t type, uint32_t n, uint32_t k,
+                                  const unsigned short *x, uint32_t m, unsigned short *y, uint32_t wide_x,
+                                  uint32_t grid)
+{
+    emu::launch(grid, QG_WARPS * 32u, [=] {
+        q8::q_gemv_any_kernel<__nv_bfloat16, __nv_bfloat16>(w, type, n, k, reinterpret_cast<const __nv_bfloat16 *>(x),
+                                                            m, nullptr, reinterpret_cast<__nv_bfloat16 *>(y), wide_x);
     });
 }
 

@@ -31,7 +31,8 @@ def emu(tmp_path_factory):
     lib = C.CDLL(path)
     vp, u32 = C.c_void_p, C.c_uint32
     lib.emu_dequant_any.argtypes = [vp, u32, u32, u32, u32, vp, u32]
-    lib.emu_gemv_any.argtypes = [vp, u32, u32, u32, vp, u32, vp, vp, u32]
+    lib.emu_gemv_any.argtypes = [vp, u32, u32, u32, vp, u32, vp, vp, u32, u32]
+    lib.emu_gemv_any_bf16.argtypes = [vp, u32, u32, u32, vp, u32, vp, u32, u32]
     lib.emu_gemv_q8.argtypes = [vp, u32, u32, vp, u32, vp, vp, u32]
     lib.emu_gemv_q8_fused.argtypes = [vp, u32, u32, vp, u32, vp, vp, u32, u32]
     return lib
@@ -97,8 +98,21 @@ def test_other_block_types_dequant_and_product(emu, oracle, kind):
     assert ((err <= np.abs(ideal) * 9.765625e-04) | (err <= 5.9604644775390625e-08)).all()
     assert (out[rows:] == 0x7777).all()
     x = inputs(m, k, 50 + kind)
-    y = np.full((m + 1, n), -7.0, np.float32)
-    emu.emu_gemv_any(w.ctypes.data, kind, n, k, x.ctypes.data, m, None, y.ctypes.data, 2)
     want = x.astype(np.float64) @ oracle.block_rows(kind, w, k, 0, n).T
-    assert oracle.diff(y[:m], want)[0] == 0
-    assert (y[m:] == -7.0).all()
+    results = []
+    for wide_x in (1, 0):      # 16-byte loads of x, and the element-wise path for an unaligned x
+        y = np.full((m + 1, n), -7.0, np.float32)
+        emu.emu_gemv_any(w.ctypes.data, kind, n, k, x.ctypes.data, m, None, y.ctypes.data, wide_x, 2)
+        assert oracle.diff(y[:m], want)[0] == 0
+        assert (y[m:] == -7.0).all()
+        results.append(y)
+    assert np.array_equal(results[0], results[1])
+    # bfloat16 in and out
+    import torch
+    xb = torch.from_numpy(x.astype(np.float32)).to(torch.bfloat16)
+    bits = xb.view(torch.int16).numpy().view(np.uint16)
+    yb = np.zeros((m, n), np.uint16)
+    emu.emu_gemv_any_bf16(w.ctypes.data, kind, n, k, bits.ctypes.data, m, yb.ctypes.data, 1, 2)
+    got = torch.from_numpy(yb.view(np.int16)).view(torch.bfloat16).double().numpy()
+    want_b = xb.double().numpy() @ oracle.block_rows(kind, w, k, 0, n).T
+    assert np.abs(got - want_b).max() <= 1e-2 * np.abs(want_b).max() + 1e-3
