@@ -229,9 +229,7 @@ __device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_
             }
             const uint32_t kc = (uint32_t)(4 * jb + c);
             const uint32_t addr = row_base + ((kc ^ phase) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[0]), "r"(out[1]),
-                         "r"(out[2]), "r"(out[3])
-                         : "memory");
+            st_shared_v4(addr, out[0], out[1], out[2], out[3]);
         }
     }
 }
@@ -271,10 +269,8 @@ __device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
 {
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
-                     : "r"(raw_row + (uint32_t)(H * 128 + 16 * i))
-                     : "memory");
+        ld_shared_v4(raw_row + (uint32_t)(H * 128 + 16 * i), raw[4 * i], raw[4 * i + 1], raw[4 * i + 2],
+                     raw[4 * i + 3]);
     }
 }
 
