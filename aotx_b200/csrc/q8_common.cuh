@@ -89,13 +89,6 @@ __device__ __forceinline__ __half dequant_one(int q, __half d)
 // Shared-memory barriers.
 // ---------------------------------------------------------------------------------------
 
-
-
-
-
-
-
-
 // Every wait is bounded.  When the bound runs out the waiter raises `*abort_flag` (shared)
 // and the device status word, and the caller leaves its loop; the kernel then runs to its
 // end with a wrong result rather than holding the GPU.
@@ -136,23 +129,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // Bulk tensor copies (TMA), global -> shared, no multicast.
 // ---------------------------------------------------------------------------------------
 
-
-
 // ---------------------------------------------------------------------------------------
 // Tensor memory and the fifth-generation tensor core.
 // ---------------------------------------------------------------------------------------
-
-
-
-
-
-
-
-
-
-
-
-
 
 // Shared-memory operand descriptor, K-major rows of 128 bytes with the 128-byte swizzle:
 // rows 128 bytes apart, groups of 8 rows 1024 bytes apart, 16-byte chunk c of row r stored
@@ -181,10 +160,5 @@ __host__ __device__ inline uint32_t umma_idesc(unsigned int m, unsigned int n, u
     d |= (m >> 4) << 24;        // M, in units of 16
     return d;
 }
-
-
-
-
-
 
 } // namespace q8

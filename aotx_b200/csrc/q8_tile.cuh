@@ -507,6 +507,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     }
 }
 
+#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 // Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
 template <typename Kernel>
 inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask)
@@ -549,5 +550,6 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
 // Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.
 cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                  const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
+#endif
 
 } // namespace q8

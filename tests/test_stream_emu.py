@@ -1,0 +1,188 @@
+"""The decode-regime tensor-core kernel run whole on the host (tests/stream_emu.cu): the source of
+`q8_stream_kernel` (aotx_b200/csrc/q8_stream.cu) is compiled as host code, a block runs as its 480
+host threads, and every instruction behind inline PTX is a host stand-in (tests/q8_ptx_emu.cuh) -
+bulk tensor copies with the 128-byte swizzle, shared-memory barriers with arrival and byte counts,
+tensor memory as an array, the MMA in float.  The results are checked against the oracle, so
+this covers on a machine without a GPU what only the GPU tests covered before: the five warp
+roles and their rings, the byte arithmetic of the dequantisation into tensor memory, the operand
+layouts, the bfloat16 path, the unit schedule with tiles cut between blocks, the live batch word,
+the three store modes and the L2 requests for the following product.  The stand-ins encode what
+the instructions do as the kernel was verified against the hardware; the hardware itself is the
+GPU tests' matter."""
+import ctypes as C
+import os
+import shutil
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GUARD = np.float32(-7.0)
+ROWS, SEG_K, SEG_BYTES = 128, 256, 272
+
+
+@pytest.fixture(scope="module")
+def emu(tmp_path_factory):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    path = str(tmp_path_factory.mktemp("emu") / "libstream_emu.so")
+    done = subprocess.run([nvcc, "-O1", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-gencode",
+                           "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "aotx_b200", "csrc"),
+                           "-I", os.path.join(ROOT, "tests"), "-o", path,
+                           os.path.join(ROOT, "tests", "stream_emu.cu")],
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-3000:]
+    lib = C.CDLL(path)
+    vp, u32 = C.c_void_p, C.c_uint32
+    lib.stream_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, u32,
+                               vp]
+    lib.stream_emu.restype = C.c_uint
+
+    def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None):
+        m = x.shape[0]
+        requested = C.c_ulonglong(0)
+        nw, nn, nk, nm, units = following if following is not None else (None, 0, 0, 0, 0)
+        status = lib.stream_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, m,
+                                live.ctypes.data if live is not None else None, y.ctypes.data, y.shape[1], mode,
+                                grid, ntok, nw.ctypes.data if nw is not None else None, nn, nk, nm, units,
+                                C.byref(requested))
+        assert status == 0, hex(status)
+        return requested.value
+    return run
+
+
+def inputs(m, k, seed, scale=1.0):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return (rng.standard_normal((m, k)) * scale).astype(np.float16)
+
+
+# shapes chosen so that tiles are cut between blocks, the last row tile is ragged, the batch does
+# not fill its token tile, and (last three) there are several token tiles
+SHAPES = [(200, 512, 5, 3, 16), (300, 1024, 20, 5, 32), (260, 768, 50, 4, 64), (130, 256, 100, 6, 128),
+          (384, 2048, 33, 11, 16), (128, 256, 1, 1, 16), (1000, 512, 7, 9, 16), (300, 1024, 200, 7, 128),
+          (140, 512, 70, 5, 32)]
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok", SHAPES)
+def test_product_against_the_oracle(emu, oracle, n, k, m, grid, ntok):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, n + k)
+    x = inputs(m, k, m)
+    y = np.full((m + 2, n), GUARD, np.float32)
+    emu(w, n, k, x, y[:m], grid=grid, ntok=ntok)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == GUARD).all()
+
+
+def test_one_block_and_many_blocks_agree_to_rounding(emu, oracle):
+    import aotx_b200
+    n, k, m = 300, 1536, 12
+    w = aotx_b200.synth_q8_0(n, k, 3)
+    x = inputs(m, k, 4)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    for grid in (1, 2, 7, 18):          # 18 = one block per unit
+        y = np.zeros((m, n), np.float32)
+        emu(w, n, k, x, y, grid=grid, ntok=16)
+        assert oracle.diff(y, want)[0] == 0
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok", [(200, 512, 9, 3, 16), (260, 768, 50, 4, 64), (130, 512, 100, 5, 128)])
+def test_bfloat16_activations(emu, oracle, n, k, m, grid, ntok):
+    import aotx_b200
+    import torch
+    w = aotx_b200.synth_q8_0(n, k, 11)
+    xb = torch.from_numpy(inputs(m, k, 12).astype(np.float32)).to(torch.bfloat16)
+    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
+    y = np.full((m + 1, n), GUARD, np.float32)
+    emu(w, n, k, bits, y[:m], bf16=1, grid=grid, ntok=ntok)
+    # the kernel turns x into binary16 where it lies: exact for these magnitudes above 2^-14,
+    # the few smaller ones round to the half subnormals
+    x16 = xb.float().numpy().astype(np.float16)
+    want = oracle.product(w, n, k, x16.view(np.uint16), m)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == GUARD).all()
+
+
+def test_live_batch_word(emu, oracle):
+    import aotx_b200
+    n, k, m = 200, 512, 40
+    w = aotx_b200.synth_q8_0(n, k, 21)
+    x = inputs(m, k, 22)
+    full = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, full, grid=4, ntok=64)
+    for live in (0, 1, 17, 40, 99):
+        y = np.full((m, n), GUARD, np.float32)
+        emu(w, n, k, x, y, live=np.array([live], np.uint32), grid=4, ntok=64)
+        rows = min(live, m)
+        # fewer live rows: the same sums (a row's sum does not depend on the other rows)
+        assert np.array_equal(y[:rows], full[:rows])
+        assert (y[rows:] == GUARD).all()
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok", [(300, 1024, 20, 5, 32), (260, 768, 50, 4, 64), (200, 512, 5, 3, 16)])
+def test_add_into_a_float_y(emu, n, k, m, grid, ntok):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 31)
+    x = inputs(m, k, 32)
+    plain = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, plain, grid=grid, ntok=ntok)
+    y0 = np.random.default_rng(33).standard_normal((m + 1, n)).astype(np.float32)
+    y = y0.copy()
+    emu(w, n, k, x, y[:m], mode=1, grid=grid, ntok=ntok)
+    assert np.array_equal(y[:m], y0[:m] + plain)
+    assert np.array_equal(y[m:], y0[m:])
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok", [(300, 1024, 20, 5, 32), (256, 768, 50, 4, 64), (130, 512, 5, 3, 16)])
+def test_gated_unit_over_row_pairs(emu, n, k, m, grid, ntok):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 41)
+    x = inputs(m, k, 42, scale=4.0)
+    plain = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, plain, grid=grid, ntok=ntok)
+    act = np.full((m + 1, n // 2), GUARD, np.float32)
+    emu(w, n, k, x, act[:m], mode=2, grid=grid, ntok=ntok)
+    gate, up = plain[:, 0::2].astype(np.float64), plain[:, 1::2].astype(np.float64)
+    want = gate / (1.0 + np.exp(-gate)) * up
+    assert np.abs(act[:m] - want).max() <= 2e-6 * np.abs(want).max()
+    assert (act[m:] == GUARD).all()
+    assert np.abs(want).max() > 0.1
+
+
+def pieces_bytes(n, k, m, ntok, limit, grid):
+    """Bytes of the first `limit` units of every block of a launch of `grid` blocks over w[n][k]."""
+    segs = k // SEG_K
+    tok_tiles = -(-m // ntok)
+    units = -(-n // ROWS) * tok_tiles * segs
+    blocks = min(units, grid)
+    total = 0
+    for b in range(blocks):
+        u, end = b * units // blocks, (b + 1) * units // blocks
+        end = min(end, u + limit)
+        while u < end:
+            tile, s0 = divmod(u, segs)
+            s1 = min(segs, s0 + (end - u))
+            row0 = (tile // tok_tiles) * ROWS
+            total += min(ROWS, n - row0) * (s1 - s0) * SEG_BYTES
+            u += s1 - s0
+    return total
+
+
+@pytest.mark.parametrize("limit", [1, 2, 5])
+def test_requests_for_the_following_product(emu, oracle, limit):
+    import aotx_b200
+    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
+    w = aotx_b200.synth_q8_0(n, k, 51)
+    n2, k2 = 200, 768
+    w2 = aotx_b200.synth_q8_0(n2, k2, 52)
+    x = inputs(m, k, 53)
+    y = np.zeros((m, n), np.float32)
+    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, following=(w2, n2, k2, m, limit))
+    assert asked == pieces_bytes(n2, k2, m, ntok, limit, grid)
+    assert asked > 0
+    # and the product itself is what it is without the requests
+    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
+    assert emu(w, n, k, x, y, grid=grid, ntok=ntok) == 0
