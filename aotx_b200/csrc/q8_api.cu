@@ -178,7 +178,12 @@ extern "C" int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int cle
         err = cudaMemcpy(status, ctx->scratch.status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
     }
     if (err == cudaSuccess && clear) {
-        err = cudaMemset(ctx->scratch.status, 0, sizeof(uint32_t));
+        // A launch whose wait ran out may have left hand-over flags raised (a partial sum that
+        // was published and never taken); the next launch would misread them.  Nothing runs
+        // now, so the flags of both sets go back to zero together with the status word, which
+        // lies right behind them.
+        const size_t words = *status != 0u ? 2u * (size_t)ctx->scratch.blocks * 4u + 1u : 1u;
+        err = cudaMemset(ctx->scratch.status + 1 - words, 0, words * sizeof(uint32_t));
     }
     if (err != cudaSuccess) {
         return cuda_fail(ctx, err);

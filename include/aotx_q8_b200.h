@@ -106,7 +106,9 @@ int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, uint32_t n_next, uin
 int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx);
 
 /* Synchronise the device and read the status word that kernels raise instead of hanging;
- * 0 means every bounded wait completed.  `clear` != 0 zeroes it afterwards. */
+ * 0 means every bounded wait completed.  `clear` != 0 zeroes it afterwards, and after a wait
+ * that ran out also resets the hand-over state between blocks that such a launch can leave
+ * behind: after AOTX_Q8_ERR_DEVICE call this with `clear` != 0 before the next product. */
 int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int clear);
 
 /* Rows [first_row, first_row + rows) of w as binary16: out[r][j] = half(float(q) * float(d)),

@@ -6,9 +6,13 @@
 //                   so that 0 is never a valid address)
 //   tensor memory   128 lanes x 512 columns of 32-bit words
 //   mbarrier        arrivals, outstanding copy bytes and a phase count per barrier address
-//   bulk tensor copy (TMA)  done at once by the calling thread, then its bytes are credited
-//   tcgen05.mma     done at once by the calling thread, in float, from tensor / shared memory
-//   tcgen05.commit  arrives at once (everything issued before it has already run)
+//   bulk tensor copy (TMA)  copies the box, then credits its bytes to the barrier
+//   tcgen05.mma     in float, from tensor / shared memory
+//   tcgen05.commit  an arrival after everything issued before it
+// The copies and the tensor-core work run either at once in the calling thread or, in the
+// asynchronous mode, later and in order on a thread of their own per engine (with a random delay
+// before each operation), so that a kernel which reused a buffer before the operation reading or
+// writing it had finished would compute wrong numbers here as it would on the hardware.
 // The operand layouts follow what the kernels were written and verified against on the GPU:
 // K-major rows of 128 bytes with the 128-byte swizzle for shared-memory operands, lane = row and
 // two 16-bit values per column for a tensor-memory A operand, lane = row and one float per
@@ -20,11 +24,15 @@
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdint>
 #include <cstring>
+#include <deque>
+#include <functional>
 #include <map>
 #include <mutex>
+#include <random>
 #include <thread>
 
 namespace q8 {
@@ -85,6 +93,95 @@ inline float bf16_bits_to_float(uint16_t bits)
 }
 
 inline unsigned int lane_of_thread();
+
+// An engine that runs operations in the order they were issued, some time after the issue.
+class Engine {
+public:
+    void start(unsigned int seed, unsigned int max_delay_us)
+    {
+        stop_ = false;
+        rng_.seed(seed);
+        max_delay_us_ = max_delay_us;
+        worker_ = std::thread([this] { run(); });
+    }
+    void push(std::function<void()> op)
+    {
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            queue_.push_back(std::move(op));
+        }
+        wake_.notify_one();
+    }
+    // Ends the thread after the queue has drained; returns how many operations were still
+    // waiting or running when the call came (a block must not end with work in flight).
+    size_t finish()
+    {
+        size_t in_flight;
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            in_flight = queue_.size() + (busy_ ? 1u : 0u);
+            stop_ = true;
+        }
+        wake_.notify_one();
+        worker_.join();
+        return in_flight;
+    }
+
+private:
+    void run()
+    {
+        for (;;) {
+            std::function<void()> op;
+            {
+                std::unique_lock<std::mutex> lock(mutex_);
+                wake_.wait(lock, [this] { return stop_ || !queue_.empty(); });
+                if (queue_.empty()) {
+                    return;
+                }
+                op = std::move(queue_.front());
+                queue_.pop_front();
+                busy_ = true;
+            }
+            if (max_delay_us_ != 0u) {
+                const unsigned int wait = rng_() % (max_delay_us_ + 1u);
+                if (wait != 0u) {
+                    std::this_thread::sleep_for(std::chrono::microseconds(wait));
+                }
+            }
+            op();
+            {
+                std::lock_guard<std::mutex> lock(mutex_);
+                busy_ = false;
+            }
+        }
+    }
+    std::mutex mutex_;
+    std::condition_variable wake_;
+    std::deque<std::function<void()>> queue_;
+    std::thread worker_;
+    std::minstd_rand rng_;
+    unsigned int max_delay_us_ = 0;
+    bool stop_ = false, busy_ = false;
+};
+
+inline Engine copy_engine, tensor_pipe;
+inline bool asynchronous = false;
+
+// Fault injection on the host: the copy with this number (counted over the launch, from 0) never
+// lands - its bytes are not credited - so the waits that depend on it must run out.
+inline long long lost_copy = -1;
+inline std::atomic<long long> copies_issued{0};
+// Columns of tensor memory the running block holds (it must hand them back before it ends).
+inline std::atomic<uint32_t> tmem_held{0};
+
+inline void issue(Engine &engine, std::function<void()> op)
+{
+    if (asynchronous) {
+        engine.push(std::move(op));
+    } else {
+        op();
+    }
+}
 
 } // namespace q8emu
 
@@ -186,9 +283,8 @@ inline uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 inline void fence_proxy_async_smem() {}
 inline void tma_prefetch_desc(const void *) {}
 
-inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1)
+inline void emu_tma_load_2d(uint32_t dst, const q8emu::TensorMap &map, uint32_t bar, int c0, int c1)
 {
-    const q8emu::TensorMap &map = *static_cast<const q8emu::TensorMap *>(tmap);
     const uint32_t row_bytes = map.box[0] * map.elem_bytes;
     for (uint32_t r = 0; r < map.box[1]; ++r) {
         const long long row = (long long)c1 + r;
@@ -213,6 +309,15 @@ inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, in
     q8emu::advance(b);
 }
 
+inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1)
+{
+    const q8emu::TensorMap map = *static_cast<const q8emu::TensorMap *>(tmap);
+    if (q8emu::copies_issued.fetch_add(1) == q8emu::lost_copy) {
+        return;
+    }
+    q8emu::issue(q8emu::copy_engine, [=] { emu_tma_load_2d(dst, map, bar, c0, c1); });
+}
+
 inline unsigned long long l2_requests = 0;
 
 inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
@@ -223,14 +328,22 @@ inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
     l2_requests += bytes;
 }
 
-inline void tmem_alloc(uint32_t smem_result, uint32_t)
+inline void tmem_alloc(uint32_t smem_result, uint32_t columns)
 {
     const uint32_t base = 0;
+    if (q8emu::lane_of_thread() == 0u) {
+        q8emu::tmem_held += columns;
+    }
     std::memcpy(q8emu::shared_at(smem_result), &base, 4);
 }
 
 inline void tmem_relinquish() {}
-inline void tmem_dealloc(uint32_t, uint32_t) {}
+inline void tmem_dealloc(uint32_t, uint32_t columns)
+{
+    if (q8emu::lane_of_thread() == 0u) {
+        q8emu::tmem_held -= columns;
+    }
+}
 inline void tc_fence_before_sync() {}
 inline void tc_fence_after_sync() {}
 
@@ -271,31 +384,35 @@ inline void emu_mma(uint32_t d_tmem, AValue a_value, uint64_t b_desc, uint32_t i
 
 inline void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
-    const uint32_t a_col = a_tmem & 0xFFFFu;
-    const bool a_bf16 = ((idesc >> 7) & 1u) != 0u;
-    emu_mma(d_tmem, [&](uint32_t row, uint32_t kk) {
-        const uint32_t word = q8emu::tensor_memory[row][a_col + kk / 2u];
-        const uint16_t bits = (uint16_t)(kk & 1u ? word >> 16 : word & 0xFFFFu);
-        return a_bf16 ? q8emu::bf16_bits_to_float(bits) : q8emu::half_bits_to_float(bits);
-    }, b_desc, idesc, accumulate);
+    q8emu::issue(q8emu::tensor_pipe, [=] {
+        const uint32_t a_col = a_tmem & 0xFFFFu;
+        const bool a_bf16 = ((idesc >> 7) & 1u) != 0u;
+        emu_mma(d_tmem, [&](uint32_t row, uint32_t kk) {
+            const uint32_t word = q8emu::tensor_memory[row][a_col + kk / 2u];
+            const uint16_t bits = (uint16_t)(kk & 1u ? word >> 16 : word & 0xFFFFu);
+            return a_bf16 ? q8emu::bf16_bits_to_float(bits) : q8emu::half_bits_to_float(bits);
+        }, b_desc, idesc, accumulate);
+    });
 }
 
 inline void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
-    const uint32_t a_start = (uint32_t)(a_desc & 0x3FFFu) << 4;
-    const bool a_bf16 = ((idesc >> 7) & 1u) != 0u;
-    emu_mma(d_tmem, [&](uint32_t row, uint32_t kk) {
-        uint32_t addr = a_start + (row >> 3) * 1024u + (row & 7u) * 128u + kk * 2u;
-        addr ^= ((addr >> 7) & 7u) << 4;
-        uint16_t bits;
-        std::memcpy(&bits, q8emu::shared_at(addr), 2);
-        return a_bf16 ? q8emu::bf16_bits_to_float(bits) : q8emu::half_bits_to_float(bits);
-    }, b_desc, idesc, accumulate);
+    q8emu::issue(q8emu::tensor_pipe, [=] {
+        const uint32_t a_start = (uint32_t)(a_desc & 0x3FFFu) << 4;
+        const bool a_bf16 = ((idesc >> 7) & 1u) != 0u;
+        emu_mma(d_tmem, [&](uint32_t row, uint32_t kk) {
+            uint32_t addr = a_start + (row >> 3) * 1024u + (row & 7u) * 128u + kk * 2u;
+            addr ^= ((addr >> 7) & 7u) << 4;
+            uint16_t bits;
+            std::memcpy(&bits, q8emu::shared_at(addr), 2);
+            return a_bf16 ? q8emu::bf16_bits_to_float(bits) : q8emu::half_bits_to_float(bits);
+        }, b_desc, idesc, accumulate);
+    });
 }
 
 inline void umma_commit(uint32_t bar)
 {
-    mbar_arrive(bar);
+    q8emu::issue(q8emu::tensor_pipe, [=] { mbar_arrive(bar); });
 }
 
 // thread t of the warp reads / writes lane (base lane + t)

@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdint>
 #include <cstring>
@@ -58,6 +59,7 @@ thread_local Index block_index = {0, 0, 0};
 thread_local Warp *warp = nullptr;
 Barrier *block_barrier = nullptr;
 Index grid_dim = {1, 1, 1};
+unsigned int max_delay_us = 0;
 
 inline float shfl_xor(float value, unsigned int mask)
 {
@@ -84,6 +86,17 @@ inline uint32_t float_as_uint(float value)
     uint32_t bits;
     std::memcpy(&bits, &value, 4);
     return bits;
+}
+
+long long cycles_per_us = 400;
+
+// The kernels bound their waits by the SM clock (about two seconds' worth of cycles); here the
+// same bound runs out after about ten seconds (cycles_per_us = 400), so that a kernel that has stopped making progress
+// ends with its status bits raised, as on the hardware, instead of holding the test.
+inline long long clock_now()
+{
+    const auto now = std::chrono::steady_clock::now().time_since_epoch();
+    return (long long)std::chrono::duration_cast<std::chrono::nanoseconds>(now).count() / 1000ll * cycles_per_us;
 }
 
 inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
@@ -115,7 +128,7 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define __syncthreads() emu::block_barrier->wait()
 #define __uint_as_float(bits) emu::uint_as_float(bits)
 #define __float_as_uint(value) emu::float_as_uint(value)
-#define clock64() 0ll
+#define clock64() emu::clock_now()
 #define atomicOr(word, bits) emu::atomic_or((word), (bits))
 #define __ldcg(p) (*(p))
 #define __stcg(p, v) (*(p) = (v))
@@ -195,6 +208,10 @@ static unsigned int run(const unsigned char *w, uint32_t n, uint32_t k, const vo
         emu::Barrier all(kThreads);
         emu::block_barrier = &all;
         std::vector<emu::Warp> warps(kThreads / 32u);
+        if (q8emu::asynchronous) {
+            q8emu::copy_engine.start(17u * b + 1u, emu::max_delay_us);
+            q8emu::tensor_pipe.start(31u * b + 2u, emu::max_delay_us);
+        }
         std::vector<std::thread> threads;
         threads.reserve(kThreads);
         for (unsigned int t = 0; t < kThreads; ++t) {
@@ -207,6 +224,12 @@ static unsigned int run(const unsigned char *w, uint32_t n, uint32_t k, const vo
         }
         for (std::thread &thread : threads) {
             thread.join();
+        }
+        if (q8emu::asynchronous && q8emu::copy_engine.finish() + q8emu::tensor_pipe.finish() != 0u) {
+            status |= 0x200u; // the block ended with a copy or tensor-core work in flight
+        }
+        if (q8emu::tmem_held.exchange(0u) != 0u) {
+            status |= 0x400u; // the block ended holding tensor memory
         }
     }
     for (unsigned int flag : flags) {
@@ -235,8 +258,11 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
                                    uint32_t m, const unsigned int *m_dev, float *y, uint32_t ldy, uint32_t epilogue,
                                    uint32_t grid, uint32_t ntok, const unsigned char *next_w, uint32_t next_n,
                                    uint32_t next_k, uint32_t next_m, uint32_t next_units,
-                                   unsigned long long *l2_bytes)
+                                   unsigned long long *l2_bytes, int asynchronous, uint32_t max_delay_us)
 {
+    q8emu::asynchronous = asynchronous != 0;
+    emu::max_delay_us = max_delay_us;
+    q8emu::copies_issued = 0;
     const Next next = {next_w, next_n, next_k, next_m, next_units};
     q8::l2_requests = 0;
     const unsigned int status = stream_emu_tile(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, ntok, next);
@@ -244,4 +270,12 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
         *l2_bytes = q8::l2_requests;
     }
     return status;
+}
+
+// Fault injection for the bounded waits: copy number `lost_copy` of the next launches never lands
+// (-1: none), and the wait bound is `seconds` long.
+extern "C" void stream_emu_faults(long long lost_copy, double seconds)
+{
+    q8emu::lost_copy = lost_copy;
+    emu::cycles_per_us = (long long)(4000.0 / seconds);
 }

@@ -6,9 +6,13 @@ tensor memory as an array, the MMA in float.  The results are checked against th
 this covers on a machine without a GPU what only the GPU tests covered before: the five warp
 roles and their rings, the byte arithmetic of the dequantisation into tensor memory, the operand
 layouts, the bfloat16 path, the unit schedule with tiles cut between blocks, the live batch word,
-the three store modes and the L2 requests for the following product.  The stand-ins encode what
-the instructions do as the kernel was verified against the hardware; the hardware itself is the
-GPU tests' matter."""
+the three store modes and the L2 requests for the following product.  In the asynchronous mode
+the copies and the tensor-core work complete later, in order, on threads of their own with random
+delays, so a buffer reused too early would give wrong numbers; and a copy that never lands (made
+on the host) checks that every wait is bounded: the block raises its status bit, lets its other
+copies land, hands its tensor memory back and ends.  The stand-ins encode what the instructions
+do as the kernel was verified against the hardware; the hardware itself is the GPU tests'
+matter."""
 import ctypes as C
 import os
 import shutil
@@ -37,19 +41,25 @@ def emu(tmp_path_factory):
     lib = C.CDLL(path)
     vp, u32 = C.c_void_p, C.c_uint32
     lib.stream_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, u32,
-                               vp]
+                               vp, C.c_int, u32]
     lib.stream_emu.restype = C.c_uint
+    lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
 
-    def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None):
+    def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
+            expect=0):
+        """delay_us: None runs copies and MMAs at once in the issuing thread, a number runs them
+        later on engine threads with random delays up to that many microseconds."""
         m = x.shape[0]
         requested = C.c_ulonglong(0)
         nw, nn, nk, nm, units = following if following is not None else (None, 0, 0, 0, 0)
+        lib.stream_emu_faults(lost_copy, 10.0 if lost_copy < 0 else 0.5)
         status = lib.stream_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, m,
                                 live.ctypes.data if live is not None else None, y.ctypes.data, y.shape[1], mode,
                                 grid, ntok, nw.ctypes.data if nw is not None else None, nn, nk, nm, units,
-                                C.byref(requested))
-        assert status == 0, hex(status)
-        return requested.value
+                                C.byref(requested), 0 if delay_us is None else 1, delay_us or 0)
+        if expect is not None:
+            assert status == expect, hex(status)
+        return requested.value if expect == 0 else status
     return run
 
 
@@ -75,6 +85,42 @@ def test_product_against_the_oracle(emu, oracle, n, k, m, grid, ntok):
     want = oracle.product(w, n, k, x.view(np.uint16), m)
     assert oracle.diff(y[:m], want)[0] == 0
     assert (y[m:] == GUARD).all()
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok,delay", [(200, 512, 5, 3, 16, 0), (300, 1024, 20, 5, 32, 200),
+                                                   (260, 768, 50, 4, 64, 100), (130, 256, 100, 6, 128, 100),
+                                                   (384, 2048, 33, 11, 16, 50), (300, 1024, 200, 7, 128, 30)])
+def test_copies_and_tensor_core_work_that_complete_later(emu, oracle, n, k, m, grid, ntok, delay):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, n + k)
+    x = inputs(m, k, m)
+    now = np.full((m, n), GUARD, np.float32)
+    emu(w, n, k, x, now, grid=grid, ntok=ntok)
+    later = np.full((m + 1, n), GUARD, np.float32)
+    emu(w, n, k, x, later[:m], grid=grid, ntok=ntok, delay_us=delay)
+    assert np.array_equal(later[:m], now)           # when an operation completes changes no bit
+    assert (later[m:] == GUARD).all()
+    assert oracle.diff(now, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
+
+
+@pytest.mark.parametrize("lost,delay", [(0, None), (1, 50), (7, None), (12, 50), (30, None)])
+def test_a_copy_that_never_lands_ends_the_block_with_a_status(emu, lost, delay):
+    """Copies alternate between the weight and the x thread, so the lost one is of either kind.
+    Status bit 1: a barrier wait ran out; bit 2: the owner of a cut tile gave up on a partial sum
+    (its holder had stopped); 0x100: a hand-over flag stayed raised, which the library's status
+    call resets.  Never 0x200 (work in flight at the end) nor 0x400 (tensor memory kept)."""
+    import aotx_b200
+    n, k, m, grid, ntok = 300, 2048, 20, 5, 32
+    w = aotx_b200.synth_q8_0(n, k, 5)
+    x = inputs(m, k, 6)
+    y = np.full((m + 1, n), GUARD, np.float32)
+    status = emu(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay, lost_copy=lost, expect=None)
+    assert status & 1
+    assert status & ~0x103 == 0, hex(status)
+    assert (y[m:] == GUARD).all()
+    # the same launch without the fault is whole again
+    good = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, good, grid=grid, ntok=ntok, delay_us=delay)
 
 
 def test_one_block_and_many_blocks_agree_to_rounding(emu, oracle):
