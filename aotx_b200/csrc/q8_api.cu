@@ -372,8 +372,8 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
                                      w_up, w_down, experts, hidden, ffn, x_f16, ids, tokens, tokens_dev, used,
                                      base, ws);
     } else {
-        err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, tokens, tokens_dev,
-                                           used, base + ws.act, proj);
+        err = q8::launch_expert_pairs_simt(s, w_gate, w_up, w_down, hidden, ffn, x_f16, ids, experts, tokens,
+                                           tokens_dev, used, base + ws.act, proj);
     }
     if (err == cudaSuccess) {
         err = q8::launch_expert_sum(s, proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out,

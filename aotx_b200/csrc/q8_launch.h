@@ -37,9 +37,9 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
 
 cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
                                      const void *w_down, unsigned int hidden, unsigned int ffn,
-                                     const void *x, const unsigned int *ids, unsigned int tokens,
-                                     const unsigned int *tokens_dev, unsigned int used, void *act,
-                                     float *proj);
+                                     const void *x, const unsigned int *ids, unsigned int experts,
+                                     unsigned int tokens, const unsigned int *tokens_dev, unsigned int used,
+                                     void *act, float *proj);
 
 cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
                               const unsigned int *ids, unsigned int tokens,

@@ -44,6 +44,7 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
     __shared__ unsigned int cursor[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int feed_base[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int down_base[Q8_GROUP_MAX_EXPERTS];
+    __shared__ unsigned int placed;
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
         unsigned int live = *tokens_dev;
@@ -81,6 +82,7 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
         }
         counts[0] = feed;
         counts[1] = down;
+        placed = at;
     }
     __syncthreads();
     for (unsigned int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -89,6 +91,10 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
             unsigned int at = offset[e] + atomicAdd(&cursor[e], 1u);
             sorted_pair[at] = p;
         }
+    }
+    // the places that pairs left out would have taken name no pair (the gather skips them)
+    for (unsigned int at = placed + threadIdx.x; at < pairs; at += blockDim.x) {
+        sorted_pair[at] = 0xFFFFFFFFu;
     }
     for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
         unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
@@ -132,7 +138,11 @@ __global__ void q8_gather_rows_kernel(const uint4 *__restrict__ x, const unsigne
     }
     const unsigned int pairs = tokens * used;
     for (unsigned int i = blockIdx.x; i < pairs; i += gridDim.x) {
-        const unsigned int t = sorted_pair[i] / used;
+        const unsigned int p = sorted_pair[i];
+        if (p >= pairs) {
+            continue; // no pair here: a selection outside the expert table was left out
+        }
+        const unsigned int t = p / used;
         for (unsigned int c = threadIdx.x; c < row_chunks; c += blockDim.x) {
             out[(size_t)i * row_chunks + c] = x[(size_t)t * row_chunks + c];
         }
@@ -203,6 +213,7 @@ MoeWorkspace moe_workspace_layout(unsigned int tokens, unsigned int used, unsign
     return ws;
 }
 
+#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                                unsigned int *launches, bool overlap, const void *w_gate, const void *w_up,
                                const void *w_down, unsigned int experts, unsigned int hidden,
@@ -303,5 +314,6 @@ cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scr
                                tile_tokens, tiles_down, counts + 1, ws.max_down, sorted_pair, proj, hidden,
                                0, (*launches)++, overlap);
 }
+#endif
 
 } // namespace q8

@@ -170,7 +170,7 @@ q8_route_kernel(const __half *__restrict__ x, const float *__restrict__ router, 
 __global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
 q8_expert_feed_kernel(const unsigned char *__restrict__ w_gate, const unsigned char *__restrict__ w_up,
                       unsigned int hidden, unsigned int ffn, const __half *__restrict__ x,
-                      const unsigned int *__restrict__ ids, unsigned int tokens_max,
+                      const unsigned int *__restrict__ ids, unsigned int experts, unsigned int tokens_max,
                       const unsigned int *tokens_dev, unsigned int used, __half *__restrict__ act)
 {
     unsigned int tokens = tokens_max;
@@ -188,6 +188,9 @@ q8_expert_feed_kernel(const unsigned char *__restrict__ w_gate, const unsigned c
     for (unsigned int pair = blockIdx.y; pair < tokens * used; pair += gridDim.y) {
         unsigned int t = pair / used;
         unsigned int expert = ids[pair];
+        if (expert >= experts) {
+            continue; // a selection outside the expert table: left out, as in the grouped path
+        }
         const unsigned char *gate_row = w_gate + ((unsigned long long)expert * ffn + f) * stride;
         const unsigned char *up_row = w_up + ((unsigned long long)expert * ffn + f) * stride;
         float gate[Q8_SIMT_TAKE];
@@ -205,8 +208,8 @@ q8_expert_feed_kernel(const unsigned char *__restrict__ w_gate, const unsigned c
 __global__ void __launch_bounds__(Q8_SIMT_WARPS * 32u)
 q8_expert_down_kernel(const unsigned char *__restrict__ w_down, unsigned int hidden, unsigned int ffn,
                       const __half *__restrict__ act, const unsigned int *__restrict__ ids,
-                      unsigned int tokens_max, const unsigned int *tokens_dev, unsigned int used,
-                      float *__restrict__ proj)
+                      unsigned int experts, unsigned int tokens_max, const unsigned int *tokens_dev,
+                      unsigned int used, float *__restrict__ proj)
 {
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
@@ -222,6 +225,9 @@ q8_expert_down_kernel(const unsigned char *__restrict__ w_down, unsigned int hid
     }
     for (unsigned int pair = blockIdx.y; pair < tokens * used; pair += gridDim.y) {
         unsigned int expert = ids[pair];
+        if (expert >= experts) {
+            continue;
+        }
         const unsigned char *row = w_down + ((unsigned long long)expert * hidden + d) * stride;
         float sum[Q8_SIMT_TAKE];
         simt_row<__half>(row, ffn, act + (size_t)pair * ffn, ffn, 1u, sum);
@@ -249,8 +255,13 @@ __global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float
             float sum = 0.0f;
             for (unsigned int r = 0; r < used; ++r) {
                 unsigned int expert = ids[(size_t)t * used + r];
-                float p = prob[(size_t)t * experts + expert];
-                float value = __fmul_rn(proj[((size_t)t * used + r) * hidden + d], p);
+                // a selection outside the expert table has no probability and no projection
+                // (the product kernels leave it out): it adds nothing
+                float value = 0.0f;
+                if (expert < experts) {
+                    float p = prob[(size_t)t * experts + expert];
+                    value = __fmul_rn(proj[((size_t)t * used + r) * hidden + d], p);
+                }
                 sum = (r == 0u) ? value : __fadd_rn(sum, value);
             }
             store_out<YT>(out, (size_t)t * hidden + d, sum);
@@ -354,9 +365,9 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
 
 cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
                                      const void *w_down, unsigned int hidden, unsigned int ffn,
-                                     const void *x, const unsigned int *ids, unsigned int tokens,
-                                     const unsigned int *tokens_dev, unsigned int used, void *act,
-                                     float *proj)
+                                     const void *x, const unsigned int *ids, unsigned int experts,
+                                     unsigned int tokens, const unsigned int *tokens_dev, unsigned int used,
+                                     void *act, float *proj)
 {
     unsigned int pairs = tokens * used;
     if (pairs == 0u) {
@@ -367,14 +378,14 @@ cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, co
     dim3 down((hidden + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, wave);
     q8_expert_feed_kernel<<<feed, Q8_SIMT_WARPS * 32u, 0, stream>>>(
         static_cast<const unsigned char *>(w_gate), static_cast<const unsigned char *>(w_up), hidden,
-        ffn, static_cast<const __half *>(x), ids, tokens, tokens_dev, used, static_cast<__half *>(act));
+        ffn, static_cast<const __half *>(x), ids, experts, tokens, tokens_dev, used, static_cast<__half *>(act));
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
         return err;
     }
     q8_expert_down_kernel<<<down, Q8_SIMT_WARPS * 32u, 0, stream>>>(
         static_cast<const unsigned char *>(w_down), hidden, ffn, static_cast<const __half *>(act), ids,
-        tokens, tokens_dev, used, proj);
+        experts, tokens, tokens_dev, used, proj);
     return cudaGetLastError();
 }
 

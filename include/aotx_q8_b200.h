@@ -177,7 +177,11 @@ size_t aotx_q8_moe_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidd
  * [experts][ffn][hidden], Wd is [experts][hidden][ffn], all Q8_0.  Replaces the loop of
  * aotx_model_capture_experts (cuda/model/experts_host.cu:99-111): aotx_model_expert_matrix
  * (cuda/model/expert_matrix.cu:8-63), aotx_model_swiglu (cuda/model/norm.cu:92-105) and
- * aotx_model_expert_add (cuda/model/experts.cu:77-98). */
+ * aotx_model_expert_add (cuda/model/experts.cu:77-98).
+ * A selection ids[t][r] >= experts names no expert: it is left out of the products and adds
+ * nothing to out[t] (the reference's selections come from its own router and are always in the
+ * table; here they come from the caller, and no value of them may make a kernel read outside
+ * the tensors). */
 int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up,
                     const void *w_down, uint32_t type, uint32_t experts, uint32_t hidden,
                     uint32_t ffn, const void *x_f16, const float *prob, const uint32_t *ids,

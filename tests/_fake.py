@@ -167,8 +167,15 @@ class FakeContext:
 
     def _moe(self, wg, wu, wd, experts, hidden, ffn, x, prob, ids, tokens, out, out_dtype):
         tokens = x.shape[0] if tokens is None else tokens
-        want = self.oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, _bits16(x[:tokens]),
-                                   prob.numpy()[:tokens], ids.numpy().view(np.uint32)[:tokens])
+        prob = prob.numpy()[:tokens].copy()
+        ids = ids.numpy().view(np.uint32)[:tokens].copy()
+        # a selection outside the expert table adds nothing: stand in an expert the token did
+        # not select, with probability zero
+        for t, r in zip(*np.nonzero(ids >= experts)):
+            spare = min(set(range(experts)) - set(int(e) for e in ids[t] if e < experts))
+            ids[t, r] = spare
+            prob[t, spare] = 0.0
+        want = self.oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, _bits16(x[:tokens]), prob, ids)
         if out is None:
             out = real_torch.empty((tokens, hidden), dtype=out_dtype or real_torch.float32)
         out[:tokens] = real_torch.from_numpy(np.asarray(want, np.float32)).to(out.dtype)

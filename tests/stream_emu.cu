@@ -59,6 +59,7 @@ thread_local Index block_index = {0, 0, 0};
 thread_local Warp *warp = nullptr;
 Barrier *block_barrier = nullptr;
 Index grid_dim = {1, 1, 1};
+Index block_dim = {1, 1, 1};
 unsigned int max_delay_us = 0;
 
 inline float shfl_xor(float value, unsigned int mask)
@@ -99,6 +100,11 @@ inline long long clock_now()
     return (long long)std::chrono::duration_cast<std::chrono::nanoseconds>(now).count() / 1000ll * cycles_per_us;
 }
 
+inline unsigned int atomic_add(unsigned int *word, unsigned int value)
+{
+    return reinterpret_cast<std::atomic<unsigned int> *>(word)->fetch_add(value);
+}
+
 inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 {
     return reinterpret_cast<std::atomic<unsigned int> *>(word)->fetch_or(bits);
@@ -133,6 +139,8 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define __ldcg(p) (*(p))
 #define __stcg(p, v) (*(p) = (v))
 #define __threadfence() std::atomic_thread_fence(std::memory_order_seq_cst)
+#define blockDim (emu::block_dim)
+#define atomicAdd(word, value) emu::atomic_add((word), (value))
 #define Q8_HOST_EMULATION 1
 
 #include "q8_ptx_emu.cuh"
@@ -150,80 +158,45 @@ inline unsigned int lane_of_thread()
 
 #include "q8_stream.cu"
 
+// the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
+// so one static copy stands for it
+#undef __shared__
+#define __shared__ static
+#include "q8_moe.cu"
+
 using namespace q8;
 
-// the product that follows on the stream, whose first units each block asks the L2 for
-struct Next {
-    const unsigned char *w;
-    uint32_t n, k, m, units_per_block;
-};
-
-template <int NTOK, typename YT>
-static unsigned int run(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16, uint32_t m,
-                        const unsigned int *m_dev, void *y, uint32_t ldy, uint32_t epilogue, uint32_t grid,
-                        const Next &next)
+// Run `body` as a grid of blocks of `threads` threads, one block at a time, the last block first
+// (the owner of a cut tile waits only for blocks after its own, so that order never blocks).
+template <typename Body>
+static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
 {
-    static_assert(sizeof(q8emu::TensorMap) <= sizeof(CUtensorMap), "the stand-in fits the real type");
-    CUtensorMap tw, tx;
-    q8emu::TensorMap map_w = {w, {(uint64_t)(k / 32u) * 34u / 4u, n}, (uint64_t)(k / 32u) * 34u, {kSegWords, kRows}, 4u, 0u};
-    q8emu::TensorMap map_x = {static_cast<const unsigned char *>(x), {k, m}, (uint64_t)k * 2u, {kSubK, (uint32_t)NTOK}, 2u, 1u};
-    std::memcpy(&tw, &map_w, sizeof map_w);
-    std::memcpy(&tx, &map_x, sizeof map_x);
-
-    const unsigned long long units = (unsigned long long)((n + kRows - 1u) / kRows) * ((m + NTOK - 1u) / NTOK) * (k / kSegK);
-    if (units < grid) {
-        grid = (unsigned int)units;
-    }
-    std::vector<float> partial((size_t)grid * kRows * NTOK, 0.0f);
-    std::vector<unsigned int> flags((size_t)grid * 4u, 0u);
     unsigned int status = 0;
-    UmmaArgs args;
-    std::memset(&args, 0, sizeof args);
-    args.n = n;
-    args.k = k;
-    args.m_max = m;
-    args.m_dev = m_dev;
-    args.y = y;
-    args.partial = partial.data();
-    args.flags = flags.data();
-    args.status = &status;
-    args.tile_floats = (unsigned long long)kRows * NTOK;
-    args.b_bf16 = x_bf16 ? 1u : 0u;
-    args.ldy = ldy;
-    args.epilogue = epilogue;
-    if (next.w != nullptr) {
-        args.next_w = next.w;
-        args.next_stride = (unsigned long long)(next.k / 32u) * 34u;
-        args.next_n = next.n;
-        args.next_segs = next.k / kSegK;
-        args.next_tok_tiles = (next.m + NTOK - 1u) / NTOK;
-        args.next_units = next.units_per_block;
-    }
     emu::grid_dim = {grid, 1, 1};
-
+    emu::block_dim = {threads, 1, 1};
     for (unsigned int b = grid; b-- > 0u;) {
         std::memset(q8emu::tensor_memory, 0xEE, sizeof q8emu::tensor_memory);
         std::memset(q8::smem_raw_, 0xDD, q8::kEmuSharedBytes);
         q8emu::barriers.clear();
-        emu::Barrier all(kThreads);
+        emu::Barrier all(threads);
         emu::block_barrier = &all;
-        std::vector<emu::Warp> warps(kThreads / 32u);
+        std::vector<emu::Warp> warps(threads / 32u);
         if (q8emu::asynchronous) {
             q8emu::copy_engine.start(17u * b + 1u, emu::max_delay_us);
             q8emu::tensor_pipe.start(31u * b + 2u, emu::max_delay_us);
         }
-        std::vector<std::thread> threads;
-        threads.reserve(kThreads);
-        for (unsigned int t = 0; t < kThreads; ++t) {
-            threads.emplace_back([&, t, b] {
+        std::vector<std::thread> lanes;
+        lanes.reserve(threads);
+        for (unsigned int t = 0; t < threads; ++t) {
+            lanes.emplace_back([&, t, b] {
                 emu::thread_index = {t, 0, 0};
                 emu::block_index = {b, 0, 0};
                 emu::warp = &warps[t / 32u];
-                q8_stream_kernel<NTOK, YT>(tw, tx, args);
+                body();
             });
         }
-        for (std::thread &thread : threads) {
-            thread.join();
+        for (std::thread &lane : lanes) {
+            lane.join();
         }
         if (q8emu::asynchronous && q8emu::copy_engine.finish() + q8emu::tensor_pipe.finish() != 0u) {
             status |= 0x200u; // the block ended with a copy or tensor-core work in flight
@@ -232,6 +205,36 @@ static unsigned int run(const unsigned char *w, uint32_t n, uint32_t k, const vo
             status |= 0x400u; // the block ended holding tensor memory
         }
     }
+    return status;
+}
+
+// The two tensor maps as the host launch code encodes them (launch_umma, launch_umma_grouped).
+static void make_maps(const unsigned char *w, uint32_t w_rows, uint32_t k, const void *x, uint32_t x_rows,
+                      uint32_t ntok, CUtensorMap *tw, CUtensorMap *tx)
+{
+    static_assert(sizeof(q8emu::TensorMap) <= sizeof(CUtensorMap), "the stand-in fits the real type");
+    const uint64_t row_b = (uint64_t)(k / 32u) * 34u;
+    q8emu::TensorMap map_w = {w, {row_b / 4u, w_rows}, row_b, {kSegWords, kRows}, 4u, 0u};
+    q8emu::TensorMap map_x = {static_cast<const unsigned char *>(x), {k, x_rows}, (uint64_t)k * 2u, {kSubK, ntok}, 2u, 1u};
+    std::memset(tw, 0, sizeof *tw);
+    std::memset(tx, 0, sizeof *tx);
+    std::memcpy(tw, &map_w, sizeof map_w);
+    std::memcpy(tx, &map_x, sizeof map_x);
+}
+
+// One launch of the kernel with scratch slots and flags of its own.
+template <int NTOK, typename YT>
+static unsigned int run_stream(const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args, unsigned int grid)
+{
+    std::vector<float> partial((size_t)grid * kRows * NTOK, 0.0f);
+    std::vector<unsigned int> flags((size_t)grid * 4u, 0u);
+    unsigned int status = 0;
+    args.partial = partial.data();
+    args.flags = flags.data();
+    args.status = &status;
+    args.tile_floats = (unsigned long long)kRows * NTOK;
+    const unsigned int ended = run_grid(grid, kThreads, [&] { q8_stream_kernel<NTOK, YT>(tw, tx, args); });
+    status |= ended;
     for (unsigned int flag : flags) {
         if (flag != 0u) {
             status |= 0x100u; // a flag left raised would be misread by the next launch
@@ -240,35 +243,142 @@ static unsigned int run(const unsigned char *w, uint32_t n, uint32_t k, const vo
     return status;
 }
 
-static unsigned int stream_emu_tile(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
-                                    uint32_t m, const unsigned int *m_dev, float *y, uint32_t ldy, uint32_t epilogue,
-                                    uint32_t grid, uint32_t ntok, const Next &next)
+template <typename YT>
+static unsigned int run_stream_tile(uint32_t ntok, const CUtensorMap &tw, const CUtensorMap &tx, const UmmaArgs &args,
+                                    unsigned int grid)
 {
     switch (ntok) {
-    case 16: return run<16, float>(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, next);
-    case 32: return run<32, float>(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, next);
-    case 64: return run<64, float>(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, next);
-    case 128: return run<128, float>(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, next);
+    case 16: return run_stream<16, YT>(tw, tx, args, grid);
+    case 32: return run_stream<32, YT>(tw, tx, args, grid);
+    case 64: return run_stream<64, YT>(tw, tx, args, grid);
+    case 128: return run_stream<128, YT>(tw, tx, args, grid);
     default: return 0xFFFFu;
     }
 }
 
-// x: binary16 or bfloat16 [m][k]; y: float [m][ldy] (epilogue 0, 1) or [m][n / 2] (epilogue 2)
+static void set_mode(int asynchronous, uint32_t max_delay_us)
+{
+    q8emu::asynchronous = asynchronous != 0;
+    emu::max_delay_us = max_delay_us;
+    q8emu::copies_issued = 0;
+}
+
+// One product, arguments as launch_umma fills them.  x: binary16 or bfloat16 [m][k]; y: float
+// [m][ldy] (epilogue 0, 1) or [m][n / 2] (epilogue 2).  next_*: the product that follows on the
+// stream, whose first units each block asks the L2 for; *l2_bytes receives the bytes asked for.
 extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
                                    uint32_t m, const unsigned int *m_dev, float *y, uint32_t ldy, uint32_t epilogue,
                                    uint32_t grid, uint32_t ntok, const unsigned char *next_w, uint32_t next_n,
                                    uint32_t next_k, uint32_t next_m, uint32_t next_units,
                                    unsigned long long *l2_bytes, int asynchronous, uint32_t max_delay_us)
 {
-    q8emu::asynchronous = asynchronous != 0;
-    emu::max_delay_us = max_delay_us;
-    q8emu::copies_issued = 0;
-    const Next next = {next_w, next_n, next_k, next_m, next_units};
+    set_mode(asynchronous, max_delay_us);
     q8::l2_requests = 0;
-    const unsigned int status = stream_emu_tile(w, n, k, x, x_bf16, m, m_dev, y, ldy, epilogue, grid, ntok, next);
+    CUtensorMap tw, tx;
+    make_maps(w, n, k, x, m, ntok, &tw, &tx);
+    const unsigned long long units = (unsigned long long)((n + kRows - 1u) / kRows) * ((m + ntok - 1u) / ntok) * (k / kSegK);
+    if (units < grid) {
+        grid = (unsigned int)units;
+    }
+    UmmaArgs args;
+    std::memset(&args, 0, sizeof args);
+    args.n = n;
+    args.k = k;
+    args.m_max = m;
+    args.m_dev = m_dev;
+    args.y = y;
+    args.b_bf16 = x_bf16 ? 1u : 0u;
+    args.ldy = ldy;
+    args.epilogue = epilogue;
+    if (next_w != nullptr) {
+        args.next_w = next_w;
+        args.next_stride = (unsigned long long)(next_k / 32u) * 34u;
+        args.next_n = next_n;
+        args.next_segs = next_k / kSegK;
+        args.next_tok_tiles = (next_m + ntok - 1u) / ntok;
+        args.next_units = next_units;
+    }
+    const unsigned int status = run_stream_tile<float>(ntok, tw, tx, args, grid);
     if (l2_bytes != nullptr) {
         *l2_bytes = q8::l2_requests;
     }
+    return status;
+}
+
+// Grouped mode, arguments as launch_umma_grouped fills them.
+template <typename YT>
+static unsigned int run_grouped(const unsigned char *w_stacked, uint32_t total_rows, uint32_t k, const void *x_sorted,
+                                uint32_t x_rows, uint32_t ntok, const GroupTile *tiles, const unsigned int *count,
+                                uint32_t max_tiles, const unsigned int *row_map, void *y, uint32_t ldy,
+                                uint32_t epilogue, uint32_t grid)
+{
+    if (max_tiles == 0u || x_rows == 0u) {
+        return 0u;
+    }
+    CUtensorMap tw, tx;
+    make_maps(w_stacked, total_rows, k, x_sorted, x_rows, ntok, &tw, &tx);
+    const unsigned long long units = (unsigned long long)max_tiles * (k / kSegK);
+    if (units < grid) {
+        grid = (unsigned int)units;
+    }
+    UmmaArgs args;
+    std::memset(&args, 0, sizeof args);
+    args.n = total_rows;
+    args.k = k;
+    args.m_max = x_rows;
+    args.y = y;
+    args.group_tiles = tiles;
+    args.group_count = count;
+    args.row_map = row_map;
+    args.ldy = ldy;
+    args.epilogue = epilogue;
+    return run_stream_tile<YT>(ntok, tw, tx, args, grid);
+}
+
+// The routed-expert step as launch_moe_grouped (w_gate_up null) and launch_moe_grouped_fused
+// (w_gate_up set: gate and up rows interleaved) run it: table build, row gather, grouped products,
+// the gated unit.  x: binary16 [tokens][hidden]; ids [tokens][used].  Out: proj float
+// [tokens * used][hidden] (row = token * used + rank), act binary16 [tokens * used][ffn] in the
+// sorted order, sorted_pair [tokens * used].
+extern "C" unsigned int stream_emu_moe(const unsigned char *w_gate, const unsigned char *w_up,
+                                       const unsigned char *w_gate_up, const unsigned char *w_down, uint32_t experts,
+                                       uint32_t hidden, uint32_t ffn, const void *x, const unsigned int *ids,
+                                       uint32_t tokens, const unsigned int *tokens_dev, uint32_t used,
+                                       uint32_t tile_tokens, uint32_t grid, float *proj, unsigned short *act,
+                                       unsigned int *sorted_pair, int asynchronous, uint32_t max_delay_us)
+{
+    set_mode(asynchronous, max_delay_us);
+    const bool fused = w_gate_up != nullptr;
+    const uint32_t pairs = tokens * used;
+    const MoeWorkspace ws = moe_workspace_layout(tokens, used, hidden, ffn, experts);
+    std::vector<GroupTile> tiles_feed(ws.max_feed), tiles_down(ws.max_down);
+    std::vector<unsigned short> x_sorted((size_t)pairs * hidden, 0);
+    unsigned int counts[2] = {0u, 0u};
+    unsigned int status = 0;
+    status |= run_grid(1u, Q8_GROUP_THREADS, [&] {
+        q8_group_build_kernel(ids, tokens, tokens_dev, used, experts, fused ? 2u * ffn : ffn, hidden, sorted_pair,
+                              tiles_feed.data(), tiles_down.data(), counts, tile_tokens);
+    });
+    status |= run_grid(pairs < 3u ? pairs : 3u, 128u, [&] {
+        q8_gather_rows_kernel(static_cast<const uint4 *>(x), sorted_pair, tokens, tokens_dev, used, hidden / 8u,
+                              reinterpret_cast<uint4 *>(x_sorted.data()));
+    });
+    if (fused) {
+        status |= run_grouped<__half>(w_gate_up, experts * 2u * ffn, hidden, x_sorted.data(), pairs, tile_tokens,
+                                      tiles_feed.data(), counts + 0, ws.max_feed, nullptr, act, ffn, kEpilogueSwiglu,
+                                      grid);
+    } else {
+        std::vector<float> gate((size_t)pairs * ffn, 0.0f), up((size_t)pairs * ffn, 0.0f);
+        status |= run_grouped<float>(w_gate, experts * ffn, hidden, x_sorted.data(), pairs, tile_tokens,
+                                     tiles_feed.data(), counts + 0, ws.max_feed, nullptr, gate.data(), ffn, 0u, grid);
+        status |= run_grouped<float>(w_up, experts * ffn, hidden, x_sorted.data(), pairs, tile_tokens,
+                                     tiles_feed.data(), counts + 0, ws.max_feed, nullptr, up.data(), ffn, 0u, grid);
+        status |= run_grid(2u, 256u, [&] {
+            q8_swiglu_kernel(gate.data(), up.data(), tokens, tokens_dev, used, ffn, reinterpret_cast<__half *>(act));
+        });
+    }
+    status |= run_grouped<float>(w_down, experts * hidden, ffn, act, pairs, tile_tokens, tiles_down.data(),
+                                 counts + 1, ws.max_down, sorted_pair, proj, hidden, 0u, grid);
     return status;
 }
 

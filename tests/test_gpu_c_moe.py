@@ -101,6 +101,39 @@ def test_moe_ffn_matches_oracle(ctx, oracle, tokens, experts, used, hidden, ffn)
     assert (got[tokens:] == GUARD).all()
 
 
+def test_selection_outside_the_expert_table_adds_nothing(ctx, oracle):
+    """The selections come from the caller: one that names no expert is left out of the products
+    (no kernel indexes a tensor with it) and adds nothing to its token's sum, on the grouped
+    tensor-core path and on the per-pair path.  The reference has no such case: its selections
+    come from its own router (cuda/model/experts.cu:10-75)."""
+    import aotx_b200
+    torch = torch_mod()
+    tokens, experts, used, hidden, ffn = 24, 6, 2, 256, 256
+    wg, wu, wd, x, router = _moe_case(oracle, tokens, experts, used, hidden, ffn, 77)
+    xd = dev(x)
+    prob, ids = ctx.moe_route(xd, dev(router), used)
+    p = prob.cpu().numpy()
+    i = ids.cpu().numpy().view(np.uint32)
+    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), p, i)
+    first = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), p, np.ascontiguousarray(i[:, :1]))
+    want[3] = first[3]
+    bad = i.copy()
+    bad[3, 1] = 0xFFFFFFFF
+    bad_dev = dev(bad.view(np.int32))
+    dwg, dwu, dwd = dev_weights(wg), dev_weights(wu), dev_weights(wd)
+    for path in (0, aotx_b200.PATH_GENERAL):
+        ctx.set_path(path)
+        try:
+            out = ctx.moe_ffn(dwg, dwu, dwd, experts, hidden, ffn, xd, prob, bad_dev)
+        finally:
+            ctx.set_path(0)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
+        assert ok, (path, err, bound)
+    assert ctx.device_status() == 0
+
+
 def test_ordered_sum_bit_exact(ctx, oracle):
     """The rank-ordered weighted sum equals the oracle bit for bit, rows past the batch stay
     untouched (tests/expert_test.cu:164-195)."""

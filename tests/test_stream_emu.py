@@ -44,6 +44,9 @@ def emu(tmp_path_factory):
                                vp, C.c_int, u32]
     lib.stream_emu.restype = C.c_uint
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
+    lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
+                                   C.c_int, u32]
+    lib.stream_emu_moe.restype = C.c_uint
 
     def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
             expect=0):
@@ -60,6 +63,21 @@ def emu(tmp_path_factory):
         if expect is not None:
             assert status == expect, hex(status)
         return requested.value if expect == 0 else status
+
+    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None):
+        """The routed-expert step; returns proj [tokens][used][hidden], act and the sorted pairs."""
+        tokens, used = ids.shape
+        proj = np.full((tokens * used, hidden), GUARD, np.float32)
+        act = np.zeros((tokens * used, ffn), np.uint16)
+        pair = np.full(tokens * used, 0xFFFFFFFF, np.uint32)
+        ptr = lambda a: a.ctypes.data if a is not None else None
+        lib.stream_emu_faults(-1, 10.0)
+        status = lib.stream_emu_moe(ptr(wg), ptr(wu), ptr(both), ptr(wd), experts, hidden, ffn, x.ctypes.data,
+                                    ids.ctypes.data, tokens, ptr(live), used, tile, grid, proj.ctypes.data,
+                                    act.ctypes.data, pair.ctypes.data, 0 if delay_us is None else 1, delay_us or 0)
+        assert status == 0, hex(status)
+        return proj.reshape(tokens, used, hidden), act, pair
+    run.moe = moe
     return run
 
 
@@ -232,3 +250,79 @@ def test_requests_for_the_following_product(emu, oracle, limit):
     # and the product itself is what it is without the requests
     assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
     assert emu(w, n, k, x, y, grid=grid, ntok=ntok) == 0
+
+
+def moe_case(oracle, tokens, experts, used, hidden, ffn, seed):
+    import aotx_b200
+    wg = aotx_b200.synth_q8_0(experts * ffn, hidden, seed)
+    wu = aotx_b200.synth_q8_0(experts * ffn, hidden, seed + 1)
+    wd = aotx_b200.synth_q8_0(experts * hidden, ffn, seed + 2)
+    rng = np.random.Generator(np.random.PCG64(seed + 3))
+    x = rng.standard_normal((tokens, hidden)).astype(np.float16)
+    router = rng.standard_normal((experts, hidden)).astype(np.float32) / np.float32(np.sqrt(hidden))
+    prob, ids = oracle.route(x.view(np.uint16), router, used)
+    return wg, wu, wd, x, prob.astype(np.float32), ids
+
+
+@pytest.mark.parametrize("tokens,experts,used,hidden,ffn,tile,grid", [(1, 5, 3, 512, 256, 64, 4),
+                                                                      (33, 6, 2, 256, 256, 16, 5),
+                                                                      (40, 3, 2, 512, 256, 32, 7),
+                                                                      (90, 2, 1, 256, 512, 64, 3)])
+def test_routed_experts_as_grouped_products(emu, oracle, tokens, experts, used, hidden, ffn, tile, grid):
+    """Table build, row gather, the grouped mode of the tensor-core kernel over the table (with
+    experts that got no token, token tiles that are not full and - last case - an expert with
+    more than one token tile), the gated unit and the scatter through the row map; then the
+    oracle's rank-ordered sum over the emulated projections against the oracle's whole step."""
+    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 60 + tokens)
+    proj, act, pair = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=tile, grid=grid)
+    assert sorted(pair.tolist()) == list(range(tokens * used))
+    assert (proj != GUARD).all()
+    got = oracle.ordered_sum(np.ascontiguousarray(proj.transpose(1, 0, 2)), prob, ids)
+    want, want_act = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids, want_act=True)
+    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
+    assert ok, (err, bound)
+    # the activations, pair by pair (the kernel keeps them in the sorted order)
+    ours = act.view(np.float16).astype(np.float32)
+    theirs = want_act.view(np.float16).astype(np.float32)           # [used][tokens][ffn]
+    for at, p in enumerate(pair.tolist()):
+        t, r = divmod(p, used)
+        assert np.abs(ours[at] - theirs[r, t]).max() <= 2e-3 * np.abs(theirs[r, t]).max() + 1e-6
+
+
+@pytest.mark.parametrize("tokens,experts,used,hidden,ffn,tile,grid,delay", [(33, 6, 2, 256, 256, 16, 5, None),
+                                                                            (70, 3, 2, 512, 256, 64, 7, 50)])
+def test_routed_experts_with_interleaved_gate_up(emu, oracle, tokens, experts, used, hidden, ffn, tile, grid, delay):
+    import aotx_b200
+    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 80 + tokens)
+    both = aotx_b200.interleave_rows(wg, wu, hidden, groups=experts)
+    plain, act0, pair0 = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=tile, grid=grid)
+    fused, act1, pair1 = emu.moe(None, None, both, wd, experts, hidden, ffn, x, ids, tile=tile, grid=grid,
+                                 delay_us=delay)
+    order0, order1 = np.argsort(pair0), np.argsort(pair1)
+    a0 = act0.view(np.float16).astype(np.float32)[order0]
+    a1 = act1.view(np.float16).astype(np.float32)[order1]
+    # the same sums cut at other points of the depth, then one rounding to half
+    assert np.abs(a1 - a0).max() <= 2e-3 * np.abs(a0).max()
+    assert np.abs(fused - plain).max() <= 1e-2 * np.abs(plain).max() + 1e-6
+    got = oracle.ordered_sum(np.ascontiguousarray(fused.transpose(1, 0, 2)), prob, ids)
+    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
+    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
+    assert ok, (err, bound)
+
+
+def test_routed_experts_live_batch_and_selections_outside_the_table(emu, oracle):
+    tokens, experts, used, hidden, ffn = 12, 4, 2, 256, 256
+    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 99)
+    whole, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=16, grid=4)
+    # fewer live tokens: their rows are the same, the others are not written
+    part, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, live=np.array([5], np.uint32), tile=16,
+                         grid=4)
+    assert np.array_equal(part[:5], whole[:5]) and (part[5:] == GUARD).all()
+    # a selection outside the expert table is left out; its projection row is never written
+    bad = ids.copy()
+    bad[3, 1] = experts + 7
+    proj, _, pair = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, bad, tile=16, grid=4)
+    assert (proj[3, 1] == GUARD).all()
+    proj[3, 1] = whole[3, 1]
+    assert np.array_equal(proj, whole)
+    assert sorted(pair.tolist())[:-1] == [p for p in range(tokens * used) if p != 3 * used + 1]
