@@ -8,9 +8,12 @@
 // weights of that kernel (cuda/model/gemm.cuh:108-113), bit for bit (bfloat16 when x is
 // bfloat16).  It is NOT DISPATCHED at present: repeated launches on the same inputs differed in
 // a fraction of a percent of the outputs, so batches above 128 rows run as token tiles of 128
-// on the kernel of q8_stream.cu (umma_token_tile below).  The kernel stays in the library so
-// that the fault can be found; only a build with -DQ8_EXPERIMENT and Q8_WIDE_TILE set in the
-// environment reaches it.  (-DQ8_EXPERIMENT also compiles time stamps and switches that leave
+// on the kernel of q8_stream.cu (umma_token_tile below).  Run whole on the host by the tests
+// (every PTX instruction a stand-in, copies and MMAs completing later) the kernel gives correct
+// and repeatable results, so its rings and schedule are sound; what is left is how the hardware
+// orders the converters' shared-memory stores against the tensor core's reads.  The kernel stays
+// in the library so that the fault can be found; only a build with -DQ8_EXPERIMENT and
+// Q8_WIDE_TILE set in the environment reaches it.  (-DQ8_EXPERIMENT also compiles time stamps and switches that leave
 // out one stage of the pipeline at a time; the product library is built without it.)
 //
 // Shape of the work.  The weight rows are the M side of the MMA: a tile is 128 rows of w by
@@ -425,6 +428,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
 }
 
+#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 // ---------------------------------------------------------------------------------------
 // Host side.
 // ---------------------------------------------------------------------------------------
@@ -723,6 +727,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
 #endif
     return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
 }
+#endif
 
 } // namespace q8
 

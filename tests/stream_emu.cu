@@ -157,6 +157,7 @@ inline unsigned int lane_of_thread()
 } // namespace q8emu
 
 #include "q8_stream.cu"
+#include "q8_umma.cu"
 
 // the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
 // so one static copy stands for it
@@ -303,6 +304,56 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
         *l2_bytes = q8::l2_requests;
     }
     return status;
+}
+
+// One product on the prefill-regime kernel (operands from shared memory, whole waves of tiles
+// dealt round-robin and the last partial wave cut into units), arguments as launch_umma fills
+// them for it.  y: float [m][n].
+template <int NTOK>
+static unsigned int run_umma(const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args, unsigned int grid)
+{
+    std::vector<float> partial((size_t)grid * kRows * NTOK, 0.0f);
+    std::vector<unsigned int> flags((size_t)grid * 4u, 0u);
+    unsigned int status = 0;
+    args.partial = partial.data();
+    args.flags = flags.data();
+    args.status = &status;
+    args.tile_floats = (unsigned long long)kRows * NTOK;
+    status |= run_grid(grid, kThreads, [&] { q8_umma_kernel<NTOK, float>(tw, tx, args); });
+    for (unsigned int flag : flags) {
+        if (flag != 0u) {
+            status |= 0x100u;
+        }
+    }
+    return status;
+}
+
+extern "C" unsigned int umma_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
+                                 uint32_t m, const unsigned int *m_dev, float *y, uint32_t epilogue, uint32_t grid,
+                                 uint32_t ntok, int asynchronous, uint32_t max_delay_us)
+{
+    set_mode(asynchronous, max_delay_us);
+    CUtensorMap tw, tx;
+    make_maps(w, n, k, x, m, ntok, &tw, &tx);
+    const unsigned long long units = (unsigned long long)((n + kRows - 1u) / kRows) * ((m + ntok - 1u) / ntok) * (k / kSegK);
+    if (units < grid) {
+        grid = (unsigned int)units;
+    }
+    UmmaArgs args;
+    std::memset(&args, 0, sizeof args);
+    args.n = n;
+    args.k = k;
+    args.m_max = m;
+    args.m_dev = m_dev;
+    args.y = y;
+    args.b_bf16 = x_bf16 ? 1u : 0u;
+    args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
+    args.epilogue = epilogue;
+    switch (ntok) {
+    case 64: return run_umma<64>(tw, tx, args, grid);
+    case 256: return run_umma<256>(tw, tx, args, grid);
+    default: return 0xFFFFu;
+    }
 }
 
 // Grouped mode, arguments as launch_umma_grouped fills them.

@@ -47,6 +47,8 @@ def emu(tmp_path_factory):
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
+    lib.umma_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, C.c_int, u32]
+    lib.umma_emu.restype = C.c_uint
 
     def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
             expect=0):
@@ -77,7 +79,15 @@ def emu(tmp_path_factory):
                                     act.ctypes.data, pair.ctypes.data, 0 if delay_us is None else 1, delay_us or 0)
         assert status == 0, hex(status)
         return proj.reshape(tokens, used, hidden), act, pair
+
+    def wide(w, n, k, x, y, bf16=0, mode=0, grid=3, ntok=256, delay_us=None):
+        """The prefill-regime kernel (operands from shared memory)."""
+        lib.stream_emu_faults(-1, 10.0)
+        status = lib.umma_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, x.shape[0], None, y.ctypes.data, mode, grid,
+                              ntok, 0 if delay_us is None else 1, delay_us or 0)
+        assert status == 0, hex(status)
     run.moe = moe
+    run.wide = wide
     return run
 
 
@@ -326,3 +336,42 @@ def test_routed_experts_live_batch_and_selections_outside_the_table(emu, oracle)
     proj[3, 1] = whole[3, 1]
     assert np.array_equal(proj, whole)
     assert sorted(pair.tolist())[:-1] == [p for p in range(tokens * used) if p != 3 * used + 1]
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok,delay", [(300, 1024, 300, 5, 256, None), (520, 1024, 300, 3, 256, 0),
+                                                   (520, 1024, 300, 3, 256, 50), (300, 512, 70, 4, 64, 50)])
+def test_prefill_regime_kernel(emu, oracle, n, k, m, grid, ntok, delay):
+    """The kernel with both operands in shared memory and token tiles of 256 rows
+    (aotx_b200/csrc/q8_umma.cu), which the library does not dispatch because repeated launches on
+    the GPU differed in a few outputs.  Run whole on the host - whole waves of tiles dealt
+    round-robin, the partial wave cut into units, three operand stages shared between the two
+    converter halves, operations completing later - its results equal the oracle's and repeat bit
+    for bit, so its rings and schedule are sound and the fault lies in what the stand-ins do not
+    model (how the hardware orders the converters' shared-memory stores against the tensor
+    core's reads)."""
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 7)
+    x = inputs(m, k, 8)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    runs = []
+    for _ in range(2):
+        y = np.full((m + 1, n), GUARD, np.float32)
+        emu.wide(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay)
+        assert oracle.diff(y[:m], want)[0] == 0
+        assert (y[m:] == GUARD).all()
+        runs.append(y)
+    assert np.array_equal(runs[0], runs[1])
+
+
+def test_prefill_regime_kernel_bfloat16(emu, oracle):
+    import aotx_b200
+    import torch
+    n, k, m = 260, 768, 270
+    w = aotx_b200.synth_q8_0(n, k, 9)
+    xb = torch.from_numpy(inputs(m, k, 10).astype(np.float32)).to(torch.bfloat16)
+    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
+    y = np.zeros((m, n), np.float32)
+    emu.wide(w, n, k, bits, y, bf16=1, grid=4, delay_us=20)
+    # weights rounded to bfloat16 here (one MMA takes both operands in one format)
+    want = oracle.product(w, n, k, bits, m, bf16=True)
+    assert oracle.diff(y, want)[0] == 0
