@@ -234,9 +234,10 @@ __device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_
     }
 }
 
-// The same two blocks as 32 packed words (64 halves in order of k), written to this thread's
-// lane of tensor memory: column c of the stage holds weights 2c and 2c+1 of the stage.
-template <int H, int JJ>
+// The same two blocks as 32 packed words (64 16-bit values in order of k: binary16, or
+// bfloat16 with BF), written to this thread's lane of tensor memory: column c of the stage holds
+// weights 2c and 2c+1 of the stage.
+template <int H, int JJ, bool BF = false>
 __device__ __forceinline__ void convert_stage_tmem(const uint32_t (&raw)[36], uint32_t taddr)
 {
     uint32_t out[32];
@@ -250,14 +251,16 @@ __device__ __forceinline__ void convert_stage_tmem(const uint32_t (&raw)[36], ui
         __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
 #pragma unroll
         for (int p = 0; p < 16; ++p) {
-            if (odd) {
-                const int word = wi + 1 + p / 2;
-                uint32_t flipped = raw[word] ^ 0x80808080u;
-                out[16 * jb + p] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+            // odd: the payload starts at the next word boundary; else in the high half of the
+            // scale's word
+            const int word = odd ? wi + 1 + p / 2 : wi + (p + 1) / 2;
+            const bool high = odd ? (p % 2) != 0 : ((p + 1) % 2) != 0;
+            const uint32_t flipped = raw[word] ^ 0x80808080u;
+            if constexpr (BF) {
+                const float d = __low2float(d2);
+                out[16 * jb + p] = high ? dequant_pair_bf16<1>(flipped, d) : dequant_pair_bf16<0>(flipped, d);
             } else {
-                const int word = wi + (p + 1) / 2;
-                uint32_t flipped = raw[word] ^ 0x80808080u;
-                out[16 * jb + p] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
+                out[16 * jb + p] = high ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
             }
         }
     }
@@ -550,6 +553,10 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
 // Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.
 cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                  const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
+
+// Host launcher of the second prefill-regime kernel (q8_wide.cu), token tiles of 256.
+cudaError_t launch_wide_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                               const UmmaArgs &args, unsigned int grid, int y_dtype);
 #endif
 
 } // namespace q8

@@ -650,6 +650,16 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     if (ntok <= 128u) {
         return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
     }
+#ifdef Q8_EXPERIMENT
+    {
+        // Q8_WIDE_TILE=2: the 256-row kernel with the weights in tensor memory (q8_wide.cu);
+        // any other value: the one with both operands in shared memory (above)
+        const char *env = getenv("Q8_WIDE_TILE");
+        if (env != nullptr && atoi(env) == 2) {
+            return launch_wide_kernel(stream, tw, tx, args, grid, y_dtype);
+        }
+    }
+#endif
     return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
 }
 

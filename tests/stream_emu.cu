@@ -158,6 +158,7 @@ inline unsigned int lane_of_thread()
 
 #include "q8_stream.cu"
 #include "q8_umma.cu"
+#include "q8_wide.cu"
 
 // the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
 // so one static copy stands for it
@@ -306,11 +307,13 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
     return status;
 }
 
-// One product on the prefill-regime kernel (operands from shared memory, whole waves of tiles
-// dealt round-robin and the last partial wave cut into units), arguments as launch_umma fills
-// them for it.  y: float [m][n].
-template <int NTOK>
-static unsigned int run_umma(const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args, unsigned int grid)
+// One product on a prefill-regime kernel (whole waves of tiles dealt round-robin and the last
+// partial wave cut into units), arguments as launch_umma fills them for it.  y: float [m][n].
+// form 0: both operands from shared memory (q8_umma.cu; ntok 64 or 256); form 1: the weights in
+// tensor memory (q8_wide.cu; ntok 256).
+template <int NTOK, typename Kernel>
+static unsigned int run_prefill(Kernel kernel, const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args,
+                                unsigned int grid)
 {
     std::vector<float> partial((size_t)grid * kRows * NTOK, 0.0f);
     std::vector<unsigned int> flags((size_t)grid * 4u, 0u);
@@ -319,7 +322,7 @@ static unsigned int run_umma(const CUtensorMap &tw, const CUtensorMap &tx, UmmaA
     args.flags = flags.data();
     args.status = &status;
     args.tile_floats = (unsigned long long)kRows * NTOK;
-    status |= run_grid(grid, kThreads, [&] { q8_umma_kernel<NTOK, float>(tw, tx, args); });
+    status |= run_grid(grid, kThreads, [&] { kernel(tw, tx, args); });
     for (unsigned int flag : flags) {
         if (flag != 0u) {
             status |= 0x100u;
@@ -330,7 +333,7 @@ static unsigned int run_umma(const CUtensorMap &tw, const CUtensorMap &tx, UmmaA
 
 extern "C" unsigned int umma_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
                                  uint32_t m, const unsigned int *m_dev, float *y, uint32_t epilogue, uint32_t grid,
-                                 uint32_t ntok, int asynchronous, uint32_t max_delay_us)
+                                 uint32_t ntok, int asynchronous, uint32_t max_delay_us, uint32_t form)
 {
     set_mode(asynchronous, max_delay_us);
     CUtensorMap tw, tx;
@@ -349,11 +352,16 @@ extern "C" unsigned int umma_emu(const unsigned char *w, uint32_t n, uint32_t k,
     args.b_bf16 = x_bf16 ? 1u : 0u;
     args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
     args.epilogue = epilogue;
-    switch (ntok) {
-    case 64: return run_umma<64>(tw, tx, args, grid);
-    case 256: return run_umma<256>(tw, tx, args, grid);
-    default: return 0xFFFFu;
+    if (form == 1u && ntok == 256u) {
+        return run_prefill<256>(q8_wide_kernel<float>, tw, tx, args, grid);
     }
+    if (form == 0u && ntok == 64u) {
+        return run_prefill<64>(q8_umma_kernel<64, float>, tw, tx, args, grid);
+    }
+    if (form == 0u && ntok == 256u) {
+        return run_prefill<256>(q8_umma_kernel<256, float>, tw, tx, args, grid);
+    }
+    return 0xFFFFu;
 }
 
 // Grouped mode, arguments as launch_umma_grouped fills them.

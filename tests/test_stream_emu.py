@@ -47,7 +47,7 @@ def emu(tmp_path_factory):
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
-    lib.umma_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, C.c_int, u32]
+    lib.umma_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, C.c_int, u32, u32]
     lib.umma_emu.restype = C.c_uint
 
     def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
@@ -80,11 +80,13 @@ def emu(tmp_path_factory):
         assert status == 0, hex(status)
         return proj.reshape(tokens, used, hidden), act, pair
 
-    def wide(w, n, k, x, y, bf16=0, mode=0, grid=3, ntok=256, delay_us=None):
-        """The prefill-regime kernel (operands from shared memory)."""
+    def wide(w, n, k, x, y, bf16=0, mode=0, grid=3, ntok=256, delay_us=None, form=0, live=None):
+        """A prefill-regime kernel: form 0 operands from shared memory, form 1 weights in tensor
+        memory."""
         lib.stream_emu_faults(-1, 10.0)
-        status = lib.umma_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, x.shape[0], None, y.ctypes.data, mode, grid,
-                              ntok, 0 if delay_us is None else 1, delay_us or 0)
+        status = lib.umma_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, x.shape[0],
+                              live.ctypes.data if live is not None else None, y.ctypes.data, mode, grid,
+                              ntok, 0 if delay_us is None else 1, delay_us or 0, form)
         assert status == 0, hex(status)
     run.moe = moe
     run.wide = wide
@@ -375,3 +377,48 @@ def test_prefill_regime_kernel_bfloat16(emu, oracle):
     # weights rounded to bfloat16 here (one MMA takes both operands in one format)
     want = oracle.product(w, n, k, bits, m, bf16=True)
     assert oracle.diff(y, want)[0] == 0
+
+
+@pytest.mark.parametrize("n,k,m,grid,delay", [(300, 1024, 300, 5, None), (520, 1024, 300, 3, 50),
+                                              (520, 2048, 520, 4, 20), (128, 256, 257, 2, 0)])
+def test_prefill_kernel_with_weights_in_tensor_memory(emu, oracle, n, k, m, grid, delay):
+    """The second 256-row kernel (aotx_b200/csrc/q8_wide.cu; not dispatched by the product build):
+    one accumulator, two segments of weights in tensor memory, x in boxes of 64 columns through a
+    ring of its own, whole waves of tiles and a partial wave cut into units."""
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 17)
+    x = inputs(m, k, 18)
+    y = np.full((m + 1, n), GUARD, np.float32)
+    emu.wide(w, n, k, x, y[:m], grid=grid, delay_us=delay, form=1)
+    assert oracle.diff(y[:m], oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
+    assert (y[m:] == GUARD).all()
+    # the live batch word and the add store
+    live = m - 70
+    part = np.full((m, n), GUARD, np.float32)
+    emu.wide(w, n, k, x, part, grid=grid, delay_us=delay, form=1, live=np.array([live], np.uint32))
+    assert (part[live:] == GUARD).all()
+    if -(-live // 256) == -(-m // 256):
+        assert np.array_equal(part[:live], y[:live])       # same tiles, same cuts, same sums
+    else:
+        assert np.abs(part[:live] - y[:live]).max() <= 1e-5 * np.abs(y[:m]).max()
+    y0 = np.random.default_rng(19).standard_normal((m, n)).astype(np.float32)
+    added = y0.copy()
+    emu.wide(w, n, k, x, added, mode=1, grid=grid, delay_us=delay, form=1)
+    assert np.array_equal(added, y0 + y[:m])
+
+
+def test_prefill_kernel_with_weights_in_tensor_memory_bfloat16(emu, oracle):
+    import aotx_b200
+    import torch
+    n, k, m = 260, 768, 270
+    w = aotx_b200.synth_q8_0(n, k, 9)
+    xb = torch.from_numpy(inputs(m, k, 10).astype(np.float32)).to(torch.bfloat16)
+    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
+    y = np.zeros((m, n), np.float32)
+    emu.wide(w, n, k, bits, y, bf16=1, grid=4, delay_us=20, form=1)
+    want = oracle.product(w, n, k, bits, m, bf16=True)
+    assert oracle.diff(y, want)[0] == 0
+    # bit for bit the sums of the first form, which rounds the weights to bfloat16 the same way
+    first = np.zeros((m, n), np.float32)
+    emu.wide(w, n, k, bits, first, bf16=1, grid=4, form=0)
+    assert np.array_equal(first, y)
