@@ -74,7 +74,12 @@ q8_route_kernel(const __half *__restrict__ x, const float *__restrict__ router, 
                 const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                 unsigned int used, float *__restrict__ prob, unsigned int *__restrict__ ids)
 {
-    extern __shared__ float route_x[]; // the group's activations as float: [Q8_ROUTE_TOKENS][hidden]
+    // the group's activations as float: [Q8_ROUTE_TOKENS][hidden]
+#ifdef Q8_HOST_EMULATION
+    float *route_x = emulated_dynamic_shared;
+#else
+    extern __shared__ float route_x[];
+#endif
     __shared__ float probability[Q8_ROUTE_TOKENS][Q8_ROUTE_THREADS];
     __shared__ float reduce[Q8_ROUTE_THREADS];
     unsigned int tokens = tokens_max;
@@ -238,8 +243,10 @@ q8_expert_down_kernel(const unsigned char *__restrict__ w_down, unsigned int hid
 }
 
 // out[t][d] = the ordered sum over ranks: rank 0 gives fmul(proj, p); each later rank adds
-// fmul(proj, p) with a separate rounding of the product and of the sum.
-template <typename YT>
+// fmul(proj, p) with a separate rounding of the product and of the sum.  A thread carries
+// WIDTH neighbouring columns (WIDTH = 4: one 16-byte load of proj per rank); every column's
+// chain of roundings is the one written above whatever the width.
+template <typename YT, unsigned int WIDTH>
 __global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float *__restrict__ prob,
                                      const unsigned int *__restrict__ ids, unsigned int tokens_max,
                                      const unsigned int *tokens_dev, unsigned int hidden,
@@ -251,24 +258,51 @@ __global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float
         tokens = live < tokens_max ? live : tokens_max;
     }
     for (unsigned int t = blockIdx.x; t < tokens; t += gridDim.x) {
-        for (unsigned int d = threadIdx.x; d < hidden; d += blockDim.x) {
-            float sum = 0.0f;
+        for (unsigned int d = threadIdx.x * WIDTH; d < hidden; d += blockDim.x * WIDTH) {
+            float sum[WIDTH];
+#pragma unroll
+            for (unsigned int i = 0; i < WIDTH; ++i) {
+                sum[i] = 0.0f;
+            }
             for (unsigned int r = 0; r < used; ++r) {
                 unsigned int expert = ids[(size_t)t * used + r];
                 // a selection outside the expert table has no probability and no projection
                 // (the product kernels leave it out): it adds nothing
-                float value = 0.0f;
+                float value[WIDTH];
+#pragma unroll
+                for (unsigned int i = 0; i < WIDTH; ++i) {
+                    value[i] = 0.0f;
+                }
                 if (expert < experts) {
                     float p = prob[(size_t)t * experts + expert];
-                    value = __fmul_rn(proj[((size_t)t * used + r) * hidden + d], p);
+                    const float *from = proj + ((size_t)t * used + r) * hidden + d;
+                    if (WIDTH == 4u) {
+                        float4 four = *reinterpret_cast<const float4 *>(from);
+                        value[0] = __fmul_rn(four.x, p);
+                        value[1 % WIDTH] = __fmul_rn(four.y, p);
+                        value[2 % WIDTH] = __fmul_rn(four.z, p);
+                        value[3 % WIDTH] = __fmul_rn(four.w, p);
+                    } else {
+#pragma unroll
+                        for (unsigned int i = 0; i < WIDTH; ++i) {
+                            value[i] = __fmul_rn(from[i], p);
+                        }
+                    }
                 }
-                sum = (r == 0u) ? value : __fadd_rn(sum, value);
+#pragma unroll
+                for (unsigned int i = 0; i < WIDTH; ++i) {
+                    sum[i] = (r == 0u) ? value[i] : __fadd_rn(sum[i], value[i]);
+                }
             }
-            store_out<YT>(out, (size_t)t * hidden + d, sum);
+#pragma unroll
+            for (unsigned int i = 0; i < WIDTH; ++i) {
+                store_out<YT>(out, (size_t)t * hidden + d + i, sum[i]);
+            }
         }
     }
 }
 
+#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 // ---------------------------------------------------------------------------------------
 // Launchers.
 // ---------------------------------------------------------------------------------------
@@ -389,6 +423,21 @@ cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, co
     return cudaGetLastError();
 }
 
+template <typename YT>
+static void expert_sum_launch(bool wide, unsigned int grid, cudaStream_t stream, const float *proj,
+                              const float *prob, const unsigned int *ids, unsigned int tokens,
+                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                              unsigned int used, void *out)
+{
+    if (wide) {
+        q8_expert_sum_kernel<YT, 4u><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden, experts,
+                                                               used, static_cast<YT *>(out));
+    } else {
+        q8_expert_sum_kernel<YT, 1u><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden, experts,
+                                                               used, static_cast<YT *>(out));
+    }
+}
+
 cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
                               const unsigned int *ids, unsigned int tokens,
                               const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
@@ -398,19 +447,22 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
         return cudaSuccess;
     }
     unsigned int grid = tokens < 148u * 8u ? tokens : 148u * 8u;
+    // 16-byte loads of proj need rows of a multiple of four floats on a 16-byte boundary
+    const bool wide = (hidden % 4u) == 0u && (reinterpret_cast<uintptr_t>(proj) & 15u) == 0u;
     if (out_dtype == 0) {
-        q8_expert_sum_kernel<float><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden,
-                                                              experts, used, static_cast<float *>(out));
+        expert_sum_launch<float>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts, used,
+                                 out);
     } else if (out_dtype == 1) {
-        q8_expert_sum_kernel<__half><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden,
-                                                               experts, used, static_cast<__half *>(out));
+        expert_sum_launch<__half>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts, used,
+                                  out);
     } else if (out_dtype == 2) {
-        q8_expert_sum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-            proj, prob, ids, tokens, tokens_dev, hidden, experts, used, static_cast<__nv_bfloat16 *>(out));
+        expert_sum_launch<__nv_bfloat16>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts,
+                                         used, out);
     } else {
         return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
 }
+#endif
 
 } // namespace q8

@@ -4,6 +4,8 @@
 // kernels execute with the warp semantics they rely on.  It lets the tests run, without a GPU,
 //   q_dequant_any_kernel, q_gemv_any_kernel            (aotx_b200/csrc/q_generic.cu)
 //   q8_gemv_simt_kernel, q8_gemv_simt_fused_kernel     (aotx_b200/csrc/q8_simt_gemv.cuh)
+//   q8_dequant_kernel, q8_route_kernel, q8_expert_feed_kernel, q8_expert_down_kernel,
+//   q8_expert_sum_kernel                               (aotx_b200/csrc/q8_simt.cu)
 // on small shapes and compare them with the oracle.  It checks the kernels' index arithmetic and
 // data flow; it says nothing about the hardware.
 //
@@ -116,6 +118,19 @@ inline float uint_as_float(uint32_t bits)
     return value;
 }
 
+// one rounding each, never contracted into a fused multiply-add
+inline float fmul_rn(float a, float b)
+{
+    volatile float product = a * b;
+    return product;
+}
+
+inline float fadd_rn(float a, float b)
+{
+    volatile float sum = a + b;
+    return sum;
+}
+
 // Run `body` as a grid of `grid` blocks of `threads` threads (a multiple of 32), block by block.
 inline void launch(unsigned int grid, unsigned int threads, const std::function<void()> &body)
 {
@@ -142,6 +157,34 @@ inline void launch(unsigned int grid, unsigned int threads, const std::function<
     }
 }
 
+// the same with a grid of grid.x * grid.y blocks
+inline void launch2(Index grid, unsigned int threads, const std::function<void()> &body)
+{
+    block_dim = {threads, 1, 1};
+    grid_dim = grid;
+    for (unsigned int by = 0; by < grid.y; ++by) {
+        for (unsigned int bx = 0; bx < grid.x; ++bx) {
+            Block shared;
+            shared.warps = std::vector<Warp>(threads / 32u);
+            Barrier all(threads);
+            shared.all = &all;
+            std::vector<std::thread> lanes;
+            lanes.reserve(threads);
+            for (unsigned int t = 0; t < threads; ++t) {
+                lanes.emplace_back([&, t, bx, by] {
+                    thread_index = {t, 0, 0};
+                    block_index = {bx, by, 0};
+                    block = &shared;
+                    body();
+                });
+            }
+            for (std::thread &lane : lanes) {
+                lane.join();
+            }
+        }
+    }
+}
+
 } // namespace emu
 
 // ---- the kernel sources as host code --------------------------------------------------------
@@ -164,9 +207,33 @@ inline void launch(unsigned int grid, unsigned int threads, const std::function<
 #define __syncwarp() emu::sync_warp()
 #define __syncthreads() emu::sync_block()
 #define __uint_as_float(bits) emu::uint_as_float(bits)
+#define __int_as_float(bits) emu::uint_as_float((uint32_t)(bits))
+#define __fmul_rn(a, b) emu::fmul_rn((a), (b))
+#define __fadd_rn(a, b) emu::fadd_rn((a), (b))
+#define clock64() 0ll                           /* only the tensor-core kernels wait; none runs here */
+#define atomicOr(word, bits) (*(word) |= (bits))
 #define Q8_HOST_EMULATION 1
 
-#include "q8_simt_gemv.cuh"
+// the stand-ins for the few PTX instructions these kernels reach (byte permute for the exact
+// dequantisation); the rest of that header serves the tensor-core kernels' emulation
+#include "q8_ptx_emu.cuh"
+
+namespace q8 {
+alignas(1024) unsigned char smem_raw_[kEmuSharedBytes];
+static float emulated_dynamic_shared[4 * 16384]; // the router kernel's dynamic shared memory
+} // namespace q8
+
+namespace q8emu {
+inline unsigned int lane_of_thread()
+{
+    return emu::thread_index.x % 32u;
+}
+} // namespace q8emu
+
+// static shared arrays: one block runs at a time, so one static copy stands for the block's
+#undef __shared__
+#define __shared__ static
+#include "q8_simt.cu"
 #include "q_generic.cu"
 
 // ---- entry points for the tests -------------------------------------------------------------
@@ -220,6 +287,56 @@ extern "C" void emu_gemv_q8_fused(const unsigned char *w, uint32_t n, uint32_t k
         emu::launch(grid, Q8_SIMT_WARPS * 32u, [=] {
             q8::q8_gemv_simt_fused_kernel<__half, __half>(w, n, k, reinterpret_cast<const __half *>(x), m, m_dev,
                                                           static_cast<__half *>(y), epilogue);
+        });
+    }
+}
+
+extern "C" void emu_dequant_q8(const unsigned char *w, unsigned long long blocks, unsigned short *out, int wide,
+                               uint32_t grid)
+{
+    emu::launch(grid, 256, [=] { q8::q8_dequant_kernel(w, blocks, reinterpret_cast<__half *>(out), wide); });
+}
+
+extern "C" void emu_route(const unsigned short *x, const float *router, uint32_t tokens, const unsigned int *tokens_dev,
+                          uint32_t hidden, uint32_t experts, uint32_t used, float *prob, unsigned int *ids,
+                          uint32_t grid)
+{
+    emu::launch(grid, Q8_ROUTE_THREADS, [=] {
+        q8::q8_route_kernel(reinterpret_cast<const __half *>(x), router, tokens, tokens_dev, hidden, experts, used,
+                            prob, ids);
+    });
+}
+
+// the per-pair expert products: act binary16 [tokens * used][ffn], proj float [tokens * used][hidden]
+extern "C" void emu_expert_pairs(const unsigned char *w_gate, const unsigned char *w_up, const unsigned char *w_down,
+                                 uint32_t hidden, uint32_t ffn, const unsigned short *x, const unsigned int *ids,
+                                 uint32_t experts, uint32_t tokens, const unsigned int *tokens_dev, uint32_t used,
+                                 unsigned short *act, float *proj, uint32_t pair_blocks)
+{
+    emu::Index feed = {(ffn + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, pair_blocks, 1};
+    emu::Index down = {(hidden + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, pair_blocks, 1};
+    emu::launch2(feed, Q8_SIMT_WARPS * 32u, [=] {
+        q8::q8_expert_feed_kernel(w_gate, w_up, hidden, ffn, reinterpret_cast<const __half *>(x), ids, experts, tokens,
+                                  tokens_dev, used, reinterpret_cast<__half *>(act));
+    });
+    emu::launch2(down, Q8_SIMT_WARPS * 32u, [=] {
+        q8::q8_expert_down_kernel(w_down, hidden, ffn, reinterpret_cast<const __half *>(act), ids, experts, tokens,
+                                  tokens_dev, used, proj);
+    });
+}
+
+// width 4: 16-byte loads of proj; width 1: any hidden, any alignment
+extern "C" void emu_expert_sum(const float *proj, const float *prob, const unsigned int *ids, uint32_t tokens,
+                               const unsigned int *tokens_dev, uint32_t hidden, uint32_t experts, uint32_t used,
+                               float *out, uint32_t width, uint32_t grid)
+{
+    if (width == 4u) {
+        emu::launch(grid, 256, [=] {
+            q8::q8_expert_sum_kernel<float, 4u>(proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
+        });
+    } else {
+        emu::launch(grid, 256, [=] {
+            q8::q8_expert_sum_kernel<float, 1u>(proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
         });
     }
 }
