@@ -66,7 +66,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     unsigned long long t_start = 0;
     if (args.trace != nullptr && threadIdx.x == 0) {
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
@@ -102,7 +102,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
     unsigned long long u_begin, u_end;
     unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
     if ((args.debug & 16u) != 0u && warp == kWeightWarp && lane == 0u && args.group_tiles == nullptr
         && args.w != nullptr) {
         // experiment: memory starts moving for this block before its barriers and tensor
@@ -144,7 +144,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -171,7 +171,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         ok = false;
                         break;
                     }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                     if (args.debug & 1u) {
                         mbar_arrive(raw_full + 8u * st);
                         continue;
@@ -213,7 +213,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         ok = false;
                         break;
                     }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                     if (args.debug & 8u) {
                         mbar_arrive(x_full + 8u * st);
                         continue;
@@ -239,7 +239,12 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0u) {
             // bfloat16 activations were turned into binary16 in shared memory by the converters
-            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
+            uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
+#ifdef Q8_SWITCHES
+            if ((args.debug & 32u) != 0u && args.b_bf16 != 0u) {
+                idesc = umma_idesc(kRows, (uint32_t)NTOK, 1u, 1u); // both operands stay bfloat16
+            }
+#endif
             uint32_t g = 0;
             uint32_t tc = 0;
             bool ok = true;
@@ -265,7 +270,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         break;
                     }
                     tc_fence_after_sync();
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                     if (args.debug & 4u) {
                         umma_commit(seg_empty + 8u * st);
                         continue;
@@ -318,7 +323,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
                 uint32_t raw[36];
                 const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                 if (args.debug & 2u) {
 #pragma unroll
                     for (int i = 0; i < 36; ++i) {
@@ -341,12 +346,23 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     ok = false;
                     break;
                 }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                 if (!(args.debug & 2u))
 #endif
                 {
                     const uint32_t taddr = lane_base + st * S::a_seg_columns;
                     tc_fence_after_sync();
+#ifdef Q8_SWITCHES
+                    if ((args.debug & 32u) != 0u && args.b_bf16 != 0u) {
+                        if (half_id == 0u) {
+                            convert_stage_tmem<0, 0, true>(raw, taddr);
+                            convert_stage_tmem<0, 1, true>(raw, taddr + kSubK / 2u);
+                        } else {
+                            convert_stage_tmem<1, 0, true>(raw, taddr);
+                            convert_stage_tmem<1, 1, true>(raw, taddr + kSubK / 2u);
+                        }
+                    } else
+#endif
                     if (half_id == 0u) {
                         convert_stage_tmem<0, 0>(raw, taddr);
                         convert_stage_tmem<0, 1>(raw, taddr + kSubK / 2u);
@@ -357,7 +373,11 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     tmem_st_wait();
                     tc_fence_before_sync();
                 }
-                if (args.b_bf16 != 0u) {
+                bool rewrite_x = args.b_bf16 != 0u;
+#ifdef Q8_SWITCHES
+                rewrite_x = rewrite_x && (args.debug & 32u) == 0u;
+#endif
+                if (rewrite_x) {
                     // One MMA takes both operands in one format: turn this segment's x tile into
                     // binary16 where it lies (the swizzle moves whole 16-byte chunks, so the
                     // conversion is chunk by chunk whatever the layout).
@@ -404,7 +424,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -415,7 +435,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, S::tmem_columns);
     }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && threadIdx.x == 14 * 32) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -9,6 +9,17 @@
 #include "q8_common.cuh"
 #include "q8_launch.h"
 
+// -DQ8_EXPERIMENT (never the product build) compiles switches that leave out or change one stage
+// of a kernel at a time (UmmaArgs::debug) and time stamps (UmmaArgs::trace).  The tests' host
+// emulation compiles the switches too (not the time stamps), so that a variant can be checked
+// on the host before it first runs on a GPU.
+#if defined(Q8_EXPERIMENT) || defined(Q8_HOST_EMULATION)
+#define Q8_SWITCHES 1
+#endif
+#if defined(Q8_EXPERIMENT) && !defined(Q8_HOST_EMULATION)
+#define Q8_TRACE 1
+#endif
+
 namespace q8 {
 
 constexpr uint32_t kRows = 128;                          // rows of w per tile (MMA M)
@@ -84,9 +95,11 @@ struct UmmaArgs {
     unsigned int next_segs;
     unsigned int next_tok_tiles;
     unsigned int next_units;
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
     const unsigned char *w; // the weights as a plain pointer (debug & 16: a block warms L2 with its own first units)
-    unsigned int debug; // 1: no weight copies, 2: no conversion, 4: no MMA
+    // 1: no weight copies, 2: no conversion, 4: no MMA, 8: no x copies, 16: see `w`,
+    // 32: bfloat16 activations get bfloat16 weights in tensor memory (x is not rewritten)
+    unsigned int debug;
     unsigned long long *trace; // [launch][block][4] timestamps, or null
 #endif
 };
@@ -363,7 +376,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     const unsigned long long tile_end = ((unsigned long long)cut_tile + 1ull) * segs;
     float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
 
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && wq == 0u && lane == 0u) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -392,7 +405,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
         __syncwarp();
     }
 
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && wq == 0u && lane == 0u) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -478,7 +491,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             }
         }
     }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_TRACE
     if (args.trace != nullptr && wq == 0u && lane == 0u) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

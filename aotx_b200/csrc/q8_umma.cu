@@ -190,7 +190,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         ok = false;
                         break;
                     }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                     if (args.debug & 1u) {
                         mbar_arrive(raw_full + 8u * st);
                         continue;
@@ -228,7 +228,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             ok = false;
                             break;
                         }
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                         if (args.debug & 8u) {
                             mbar_arrive(x_full + 8u * st);
                             continue;
@@ -280,7 +280,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         }
                         tc_fence_after_sync();
                         const uint64_t b_desc = umma_desc_sw128(x_base + xst * S::x_stage_bytes);
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                         if (args.debug & 4u) {
                             umma_commit(mma_empty + 8u * st);
                             umma_commit(x_empty + 8u * xst);
@@ -329,7 +329,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 }
                 uint32_t raw[36];
                 const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                 if (args.debug & 2u) {
 #pragma unroll
                     for (int i = 0; i < 36; ++i) {
@@ -354,7 +354,7 @@ q8_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         break;
                     }
                     tc_fence_after_sync();
-#ifdef Q8_EXPERIMENT
+#ifdef Q8_SWITCHES
                     if (args.debug & 2u) {
                         mbar_arrive(a_full + 8u * st);
                         continue;

@@ -258,6 +258,14 @@ static unsigned int run_stream_tile(uint32_t ntok, const CUtensorMap &tw, const 
     }
 }
 
+// the switches of an experiment build (UmmaArgs::debug) for the launches that follow
+static unsigned int switches = 0;
+
+extern "C" void stream_emu_switches(unsigned int debug)
+{
+    switches = debug;
+}
+
 static void set_mode(int asynchronous, uint32_t max_delay_us)
 {
     q8emu::asynchronous = asynchronous != 0;
@@ -292,6 +300,8 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
     args.b_bf16 = x_bf16 ? 1u : 0u;
     args.ldy = ldy;
     args.epilogue = epilogue;
+    args.debug = switches;
+    args.w = w;
     if (next_w != nullptr) {
         args.next_w = next_w;
         args.next_stride = (unsigned long long)(next_k / 32u) * 34u;

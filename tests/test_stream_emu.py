@@ -44,6 +44,7 @@ def emu(tmp_path_factory):
                                vp, C.c_int, u32]
     lib.stream_emu.restype = C.c_uint
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
+    lib.stream_emu_switches.argtypes = [C.c_uint]
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
@@ -51,17 +52,19 @@ def emu(tmp_path_factory):
     lib.umma_emu.restype = C.c_uint
 
     def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
-            expect=0):
+            expect=0, switches=0):
         """delay_us: None runs copies and MMAs at once in the issuing thread, a number runs them
         later on engine threads with random delays up to that many microseconds."""
         m = x.shape[0]
         requested = C.c_ulonglong(0)
         nw, nn, nk, nm, units = following if following is not None else (None, 0, 0, 0, 0)
         lib.stream_emu_faults(lost_copy, 10.0 if lost_copy < 0 else 0.5)
+        lib.stream_emu_switches(switches)
         status = lib.stream_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, m,
                                 live.ctypes.data if live is not None else None, y.ctypes.data, y.shape[1], mode,
                                 grid, ntok, nw.ctypes.data if nw is not None else None, nn, nk, nm, units,
                                 C.byref(requested), 0 if delay_us is None else 1, delay_us or 0)
+        lib.stream_emu_switches(0)
         if expect is not None:
             assert status == expect, hex(status)
         return requested.value if expect == 0 else status
@@ -422,3 +425,46 @@ def test_prefill_kernel_with_weights_in_tensor_memory_bfloat16(emu, oracle):
     first = np.zeros((m, n), np.float32)
     emu.wide(w, n, k, bits, first, bf16=1, grid=4, form=0)
     assert np.array_equal(first, y)
+
+
+@pytest.mark.parametrize("n,k,m,grid,ntok", [(200, 512, 9, 3, 16), (300, 1024, 30, 5, 32), (260, 768, 50, 4, 64),
+                                             (130, 512, 100, 5, 128)])
+def test_switch_bfloat16_weights_in_tensor_memory(emu, oracle, n, k, m, grid, ntok):
+    """Switch 32 of an experiment build: with bfloat16 activations the weights go to tensor memory
+    as bfloat16 (one rounding of the exact q * d) and both MMA operands are bfloat16, so the x
+    tile is never rewritten in shared memory.  Against the oracle's product over
+    bfloat16-rounded weights."""
+    import aotx_b200
+    import torch
+    w = aotx_b200.synth_q8_0(n, k, 11)
+    xb = torch.from_numpy(inputs(m, k, 12).astype(np.float32)).to(torch.bfloat16)
+    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
+    y = np.full((m + 1, n), GUARD, np.float32)
+    emu(w, n, k, bits, y[:m], bf16=1, grid=grid, ntok=ntok, switches=32, delay_us=20)
+    want = oracle.product(w, n, k, bits, m, bf16=True)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == GUARD).all()
+    # and within the product tolerance of the form that ships (binary16 weights, x converted)
+    ships = np.zeros((m, n), np.float32)
+    emu(w, n, k, bits, ships, bf16=1, grid=grid, ntok=ntok)
+    assert np.abs(ships - y[:m]).max() <= 1e-2 * np.abs(ships).max() + 1e-3
+    # binary16 activations are not touched by the switch
+    x16 = inputs(m, k, 13)
+    a = np.zeros((m, n), np.float32)
+    b = np.zeros((m, n), np.float32)
+    emu(w, n, k, x16, a, grid=grid, ntok=ntok)
+    emu(w, n, k, x16, b, grid=grid, ntok=ntok, switches=32)
+    assert np.array_equal(a, b)
+
+
+def test_switch_block_warms_l2_with_its_own_first_units(emu, oracle):
+    """Switch 16: before its barriers and tensor memory are set up, a block asks L2 for the
+    first units it will copy.  The bytes asked for are those of its first raw stages."""
+    import aotx_b200
+    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
+    w = aotx_b200.synth_q8_0(n, k, 51)
+    x = inputs(m, k, 53)
+    y = np.zeros((m, n), np.float32)
+    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, switches=16)
+    assert asked == pieces_bytes(n, k, m, ntok, 5, grid)       # five raw stages at this tile width
+    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
