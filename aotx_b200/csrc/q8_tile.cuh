@@ -567,6 +567,11 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
 cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                  const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
 
+// Host launcher of the two-blocks-per-SM form of the decode-regime kernel (q8_duo.cu), token
+// tiles 16 and 32; `grid` may be up to twice the number of SMs.
+cudaError_t launch_duo_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                              const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
+
 // Host launcher of the second prefill-regime kernel (q8_wide.cu), token tiles of 256.
 cudaError_t launch_wide_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                const UmmaArgs &args, unsigned int grid, int y_dtype);

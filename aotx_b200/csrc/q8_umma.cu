@@ -647,6 +647,16 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     }
 #endif
 
+#ifdef Q8_EXPERIMENT
+    if (ntok <= 32u && getenv("Q8_DUO") != nullptr) {
+        // the two-blocks-per-SM form of the decode-regime kernel (q8_duo.cu)
+        unsigned int duo_grid = 2u * sm_count < scratch.blocks ? 2u * sm_count : scratch.blocks;
+        if (units < duo_grid) {
+            duo_grid = (unsigned int)units;
+        }
+        return launch_duo_kernel(stream, tw, tx, args, duo_grid, ntok, y_dtype);
+    }
+#endif
     if (ntok <= 128u) {
         return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
     }

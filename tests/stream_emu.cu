@@ -159,6 +159,7 @@ inline unsigned int lane_of_thread()
 #include "q8_stream.cu"
 #include "q8_umma.cu"
 #include "q8_wide.cu"
+#include "q8_duo.cu"
 
 // the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
 // so one static copy stands for it
@@ -224,6 +225,22 @@ static void make_maps(const unsigned char *w, uint32_t w_rows, uint32_t k, const
     std::memcpy(tx, &map_x, sizeof map_x);
 }
 
+// the switches of an experiment build (UmmaArgs::debug) for the launches that follow
+static unsigned int switches = 0;
+// which decode-regime kernel the launches that follow run: 0 the one that ships (q8_stream.cu),
+// 1 the two-blocks-per-SM form (q8_duo.cu; token tiles of 16 and 32)
+static unsigned int decode_form = 0;
+
+extern "C" void stream_emu_form(unsigned int form)
+{
+    decode_form = form;
+}
+
+extern "C" void stream_emu_switches(unsigned int debug)
+{
+    switches = debug;
+}
+
 // One launch of the kernel with scratch slots and flags of its own.
 template <int NTOK, typename YT>
 static unsigned int run_stream(const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args, unsigned int grid)
@@ -235,7 +252,12 @@ static unsigned int run_stream(const CUtensorMap &tw, const CUtensorMap &tx, Umm
     args.flags = flags.data();
     args.status = &status;
     args.tile_floats = (unsigned long long)kRows * NTOK;
-    const unsigned int ended = run_grid(grid, kThreads, [&] { q8_stream_kernel<NTOK, YT>(tw, tx, args); });
+    unsigned int ended = 0xFFFFu;
+    if (decode_form == 0u) {
+        ended = run_grid(grid, kThreads, [&] { q8_stream_kernel<NTOK, YT>(tw, tx, args); });
+    } else if constexpr (NTOK <= 32) {
+        ended = run_grid(grid, kDuoThreads, [&] { q8_duo_kernel<NTOK, YT>(tw, tx, args); });
+    }
     status |= ended;
     for (unsigned int flag : flags) {
         if (flag != 0u) {
@@ -256,14 +278,6 @@ static unsigned int run_stream_tile(uint32_t ntok, const CUtensorMap &tw, const 
     case 128: return run_stream<128, YT>(tw, tx, args, grid);
     default: return 0xFFFFu;
     }
-}
-
-// the switches of an experiment build (UmmaArgs::debug) for the launches that follow
-static unsigned int switches = 0;
-
-extern "C" void stream_emu_switches(unsigned int debug)
-{
-    switches = debug;
 }
 
 static void set_mode(int asynchronous, uint32_t max_delay_us)

@@ -45,6 +45,7 @@ def emu(tmp_path_factory):
     lib.stream_emu.restype = C.c_uint
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
     lib.stream_emu_switches.argtypes = [C.c_uint]
+    lib.stream_emu_form.argtypes = [C.c_uint]
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
@@ -52,7 +53,7 @@ def emu(tmp_path_factory):
     lib.umma_emu.restype = C.c_uint
 
     def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
-            expect=0, switches=0):
+            expect=0, switches=0, form=0):
         """delay_us: None runs copies and MMAs at once in the issuing thread, a number runs them
         later on engine threads with random delays up to that many microseconds."""
         m = x.shape[0]
@@ -60,11 +61,13 @@ def emu(tmp_path_factory):
         nw, nn, nk, nm, units = following if following is not None else (None, 0, 0, 0, 0)
         lib.stream_emu_faults(lost_copy, 10.0 if lost_copy < 0 else 0.5)
         lib.stream_emu_switches(switches)
+        lib.stream_emu_form(form)
         status = lib.stream_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, m,
                                 live.ctypes.data if live is not None else None, y.ctypes.data, y.shape[1], mode,
                                 grid, ntok, nw.ctypes.data if nw is not None else None, nn, nk, nm, units,
                                 C.byref(requested), 0 if delay_us is None else 1, delay_us or 0)
         lib.stream_emu_switches(0)
+        lib.stream_emu_form(0)
         if expect is not None:
             assert status == expect, hex(status)
         return requested.value if expect == 0 else status
@@ -468,3 +471,78 @@ def test_switch_block_warms_l2_with_its_own_first_units(emu, oracle):
     asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, switches=16)
     assert asked == pieces_bytes(n, k, m, ntok, 5, grid)       # five raw stages at this tile width
     assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
+
+
+# ---- the two-blocks-per-SM form of the decode-regime kernel (aotx_b200/csrc/q8_duo.cu; form=1) ----
+
+@pytest.mark.parametrize("n,k,m,grid,ntok,delay", [(200, 512, 5, 3, 16, None), (300, 1024, 20, 5, 32, 100),
+                                                   (384, 2048, 33, 11, 16, 30), (128, 256, 1, 1, 16, None),
+                                                   (1000, 512, 7, 9, 16, 0), (140, 512, 70, 5, 32, 20),
+                                                   (300, 1536, 12, 18, 16, None)])
+def test_duo_product_against_the_oracle(emu, oracle, n, k, m, grid, ntok, delay):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, n + k)
+    x = inputs(m, k, m)
+    y = np.full((m + 2, n), GUARD, np.float32)
+    emu(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay, form=1)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == GUARD).all()
+    # the same tiles, units and order of sums as the kernel that ships: the same bits
+    ships = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, ships, grid=grid, ntok=ntok)
+    assert np.array_equal(ships, y[:m])
+
+
+def test_duo_bfloat16_live_batch_and_fused_stores(emu, oracle):
+    import aotx_b200
+    import torch
+    n, k, m, grid, ntok = 300, 1024, 20, 5, 32
+    w = aotx_b200.synth_q8_0(n, k, 31)
+    xb = torch.from_numpy(inputs(m, k, 32).astype(np.float32)).to(torch.bfloat16)
+    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
+    y = np.full((m + 1, n), GUARD, np.float32)
+    emu(w, n, k, bits, y[:m], bf16=1, grid=grid, ntok=ntok, form=1, delay_us=30)
+    assert oracle.diff(y[:m], oracle.product(w, n, k, bits, m, bf16=True))[0] == 0
+    assert (y[m:] == GUARD).all()
+    x = inputs(m, k, 33, scale=4.0)
+    plain = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, plain, grid=grid, ntok=ntok, form=1)
+    for live in (0, 7, 20):
+        part = np.full((m, n), GUARD, np.float32)
+        emu(w, n, k, x, part, live=np.array([live], np.uint32), grid=grid, ntok=ntok, form=1)
+        assert np.array_equal(part[:live], plain[:live]) and (part[live:] == GUARD).all()
+    y0 = np.random.default_rng(34).standard_normal((m, n)).astype(np.float32)
+    added = y0.copy()
+    emu(w, n, k, x, added, mode=1, grid=grid, ntok=ntok, form=1)
+    assert np.array_equal(added, y0 + plain)
+    act = np.full((m + 1, n // 2), GUARD, np.float32)
+    emu(w, n, k, x, act[:m], mode=2, grid=grid, ntok=ntok, form=1)
+    gate, up = plain[:, 0::2].astype(np.float64), plain[:, 1::2].astype(np.float64)
+    want = gate / (1.0 + np.exp(-gate)) * up
+    assert np.abs(act[:m] - want).max() <= 2e-6 * np.abs(want).max()
+    assert (act[m:] == GUARD).all()
+
+
+@pytest.mark.parametrize("lost,delay", [(0, None), (3, 50), (11, None)])
+def test_duo_a_copy_that_never_lands(emu, lost, delay):
+    import aotx_b200
+    n, k, m, grid, ntok = 300, 2048, 20, 5, 32
+    w = aotx_b200.synth_q8_0(n, k, 5)
+    x = inputs(m, k, 6)
+    y = np.full((m + 1, n), GUARD, np.float32)
+    status = emu(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay, lost_copy=lost, expect=None, form=1)
+    assert status & 1
+    assert status & ~0x103 == 0, hex(status)
+    assert (y[m:] == GUARD).all()
+
+
+def test_duo_requests_for_the_following_product(emu, oracle):
+    import aotx_b200
+    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
+    w = aotx_b200.synth_q8_0(n, k, 51)
+    w2 = aotx_b200.synth_q8_0(200, 768, 52)
+    x = inputs(m, k, 53)
+    y = np.zeros((m, n), np.float32)
+    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, following=(w2, 200, 768, m, 2), form=1)
+    assert asked == pieces_bytes(200, 768, m, ntok, 2, grid)
