@@ -102,7 +102,12 @@ q8_duo_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const uint32_t segs = args.k / kSegK;
     const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
     const uint32_t tok_tiles = (m + (uint32_t)NTOK - 1u) / (uint32_t)NTOK;
-    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
+    unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
+    if (args.group_tiles != nullptr) {
+        // the table was built by the kernel before this one on the stream
+        grid_dependency_wait();
+        units = (unsigned long long)(*args.group_count) * segs;
+    }
     // No more blocks than units take part, so that every block in the schedule has work.
     const unsigned int blocks = units < gridDim.x ? (unsigned int)units : gridDim.x;
     if (blockIdx.x >= blocks) {

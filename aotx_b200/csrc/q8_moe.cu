@@ -30,8 +30,10 @@ static unsigned int group_tokens()
 }
 
 // One block.  Counts the pairs of every expert, places each pair in its expert's run of
-// `sorted_pair` (order inside a run is not fixed and does not affect any result: every column
-// of a tile is computed on its own), and writes the two tile tables.
+// `sorted_pair` in ascending order of the pair index (a stable sort: the place of a pair, and
+// with it the token tile it lands in and the points where that tile's sums are cut between
+// blocks, is a function of the selections alone, so the results repeat bit for bit from run to
+// run), and writes the two tile tables.
 __global__ void __launch_bounds__(Q8_GROUP_THREADS)
 q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_max,
                       const unsigned int *tokens_dev, unsigned int used, unsigned int experts,
@@ -45,6 +47,10 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
     __shared__ unsigned int feed_base[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int down_base[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int placed;
+    // one round of the placement: the expert of every thread's pair, and per warp and expert
+    // first the number of its pairs in this round, then the place of the warp's first one
+    __shared__ unsigned int round_expert[Q8_GROUP_THREADS];
+    __shared__ unsigned int warp_place[Q8_GROUP_THREADS / 32u][Q8_GROUP_MAX_EXPERTS];
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
         unsigned int live = *tokens_dev;
@@ -53,6 +59,9 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
     const unsigned int pairs = tokens * used;
     const unsigned int feed_rows = (ffn + kRows - 1u) / kRows;
     const unsigned int down_rows = (hidden + kRows - 1u) / kRows;
+    const unsigned int warp = threadIdx.x >> 5;
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned int warps = blockDim.x >> 5;
     for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
         count[e] = 0u;
         cursor[e] = 0u;
@@ -85,12 +94,47 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
         placed = at;
     }
     __syncthreads();
-    for (unsigned int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        unsigned int e = ids[p];
-        if (e < experts) {
-            unsigned int at = offset[e] + atomicAdd(&cursor[e], 1u);
-            sorted_pair[at] = p;
+    // Placement, blockDim pairs per round, in order of the pair index: a pair's place is its
+    // expert's offset + the pairs of that expert in earlier rounds (cursor) + those in lower
+    // warps of this round + those in lower lanes of its own warp.
+    for (unsigned int first = 0u; first < pairs; first += blockDim.x) {
+        const unsigned int p = first + threadIdx.x;
+        unsigned int e = p < pairs ? ids[p] : 0xFFFFFFFFu;
+        if (e >= experts) {
+            e = 0xFFFFFFFFu;
         }
+        round_expert[threadIdx.x] = e;
+        for (unsigned int i = lane; i < experts; i += 32u) {
+            warp_place[warp][i] = 0u;
+        }
+        __syncthreads();
+        unsigned int below = 0u;
+        unsigned int same = 0u;
+        if (e != 0xFFFFFFFFu) {
+            for (unsigned int i = 0u; i < 32u; ++i) {
+                const unsigned int other = round_expert[warp * 32u + i];
+                same += other == e ? 1u : 0u;
+                below += (other == e && i < lane) ? 1u : 0u;
+            }
+            if (below == 0u) {
+                warp_place[warp][e] = same; // the first lane with this expert speaks for the warp
+            }
+        }
+        __syncthreads();
+        for (unsigned int i = threadIdx.x; i < experts; i += blockDim.x) {
+            unsigned int running = cursor[i];
+            for (unsigned int w = 0u; w < warps; ++w) {
+                const unsigned int here = warp_place[w][i];
+                warp_place[w][i] = running;
+                running += here;
+            }
+            cursor[i] = running;
+        }
+        __syncthreads();
+        if (e != 0xFFFFFFFFu) {
+            sorted_pair[offset[e] + warp_place[warp][e] + below] = p;
+        }
+        __syncthreads();
     }
     // the places that pairs left out would have taken name no pair (the gather skips them)
     for (unsigned int at = placed + threadIdx.x; at < pairs; at += blockDim.x) {

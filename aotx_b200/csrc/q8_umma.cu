@@ -745,6 +745,15 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     args.trace = nullptr;
     args.w = nullptr;
 #endif
+#ifdef Q8_EXPERIMENT
+    if (ntok <= 32u && getenv("Q8_DUO") != nullptr) {
+        unsigned int duo_grid = 2u * sm_count < scratch.blocks ? 2u * sm_count : scratch.blocks;
+        if (units < duo_grid) {
+            duo_grid = (unsigned int)units;
+        }
+        return launch_duo_kernel(stream, tw, tx, args, duo_grid, ntok, y_dtype);
+    }
+#endif
     return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
 }
 #endif

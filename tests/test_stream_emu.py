@@ -72,7 +72,7 @@ def emu(tmp_path_factory):
             assert status == expect, hex(status)
         return requested.value if expect == 0 else status
 
-    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None):
+    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None, form=0):
         """The routed-expert step; returns proj [tokens][used][hidden], act and the sorted pairs."""
         tokens, used = ids.shape
         proj = np.full((tokens * used, hidden), GUARD, np.float32)
@@ -80,9 +80,11 @@ def emu(tmp_path_factory):
         pair = np.full(tokens * used, 0xFFFFFFFF, np.uint32)
         ptr = lambda a: a.ctypes.data if a is not None else None
         lib.stream_emu_faults(-1, 10.0)
+        lib.stream_emu_form(form)
         status = lib.stream_emu_moe(ptr(wg), ptr(wu), ptr(both), ptr(wd), experts, hidden, ffn, x.ctypes.data,
                                     ids.ctypes.data, tokens, ptr(live), used, tile, grid, proj.ctypes.data,
                                     act.ctypes.data, pair.ctypes.data, 0 if delay_us is None else 1, delay_us or 0)
+        lib.stream_emu_form(0)
         assert status == 0, hex(status)
         return proj.reshape(tokens, used, hidden), act, pair
 
@@ -293,8 +295,11 @@ def test_routed_experts_as_grouped_products(emu, oracle, tokens, experts, used, 
     oracle's rank-ordered sum over the emulated projections against the oracle's whole step."""
     wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 60 + tokens)
     proj, act, pair = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=tile, grid=grid)
-    assert sorted(pair.tolist()) == list(range(tokens * used))
+    # a stable sort by expert: the place of a pair depends on the selections alone
+    assert pair.tolist() == np.argsort(ids.reshape(-1), kind="stable").tolist()
     assert (proj != GUARD).all()
+    again, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=tile, grid=grid, delay_us=10)
+    assert np.array_equal(again, proj)                     # run to run: the same bits
     got = oracle.ordered_sum(np.ascontiguousarray(proj.transpose(1, 0, 2)), prob, ids)
     want, want_act = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids, want_act=True)
     ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
@@ -546,3 +551,20 @@ def test_duo_requests_for_the_following_product(emu, oracle):
     y = np.zeros((m, n), np.float32)
     asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, following=(w2, 200, 768, m, 2), form=1)
     assert asked == pieces_bytes(200, 768, m, ntok, 2, grid)
+
+
+@pytest.mark.parametrize("tile,fused", [(16, False), (32, True)])
+def test_duo_routed_experts(emu, oracle, tile, fused):
+    import aotx_b200
+    tokens, experts, used, hidden, ffn = 40, 3, 2, 512, 256
+    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 120 + tile)
+    both = aotx_b200.interleave_rows(wg, wu, hidden, groups=experts) if fused else None
+    proj, act, pair = emu.moe(None if fused else wg, None if fused else wu, both, wd, experts, hidden, ffn, x, ids,
+                              tile=tile, grid=7, delay_us=20, form=1)
+    ships, _, _ = emu.moe(None if fused else wg, None if fused else wu, both, wd, experts, hidden, ffn, x, ids,
+                          tile=tile, grid=7)
+    assert np.array_equal(proj, ships)
+    got = oracle.ordered_sum(np.ascontiguousarray(proj.transpose(1, 0, 2)), prob, ids)
+    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
+    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
+    assert ok, (err, bound)
