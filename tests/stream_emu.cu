@@ -241,6 +241,20 @@ extern "C" void stream_emu_switches(unsigned int debug)
     switches = debug;
 }
 
+// column-split mode for the launches that follow (UmmaArgs::peers, y_peer, col0): the product's
+// n columns are columns [col0, col0 + n) of `count` buffers that are ldy wide; count 0: off
+static void *peer_buffer[8];
+static unsigned int peer_count = 0, peer_col0 = 0;
+
+extern "C" void stream_emu_peers(unsigned int count, void *const *buffers, unsigned int col0)
+{
+    peer_count = count;
+    peer_col0 = col0;
+    for (unsigned int i = 0; i < 8u; ++i) {
+        peer_buffer[i] = i < count ? buffers[i] : nullptr;
+    }
+}
+
 // One launch of the kernel with scratch slots and flags of its own.
 template <int NTOK, typename YT>
 static unsigned int run_stream(const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args, unsigned int grid)
@@ -316,6 +330,11 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
     args.epilogue = epilogue;
     args.debug = switches;
     args.w = w;
+    args.peers = peer_count;
+    args.col0 = peer_col0;
+    for (unsigned int i = 0; i < 8u; ++i) {
+        args.y_peer[i] = peer_buffer[i];
+    }
     if (next_w != nullptr) {
         args.next_w = next_w;
         args.next_stride = (unsigned long long)(next_k / 32u) * 34u;

@@ -46,6 +46,7 @@ def emu(tmp_path_factory):
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
     lib.stream_emu_switches.argtypes = [C.c_uint]
     lib.stream_emu_form.argtypes = [C.c_uint]
+    lib.stream_emu_peers.argtypes = [C.c_uint, vp, C.c_uint]
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
@@ -96,8 +97,15 @@ def emu(tmp_path_factory):
                               live.ctypes.data if live is not None else None, y.ctypes.data, mode, grid,
                               ntok, 0 if delay_us is None else 1, delay_us or 0, form)
         assert status == 0, hex(status)
+
+    def peers(buffers, col0):
+        """Column-split stores for the launches that follow: every tile goes to columns
+        [col0, col0 + n) of each of the buffers; peers([], 0) switches it off."""
+        table = (C.c_void_p * 8)(*[b.ctypes.data for b in buffers] + [None] * (8 - len(buffers)))
+        lib.stream_emu_peers(len(buffers), table, col0)
     run.moe = moe
     run.wide = wide
+    run.peers = peers
     return run
 
 
@@ -568,3 +576,29 @@ def test_duo_routed_experts(emu, oracle, tile, fused):
     want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
     ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
     assert ok, (err, bound)
+
+
+@pytest.mark.parametrize("form", [0, 1])
+def test_column_split_stores_into_every_peer(emu, oracle, form):
+    """The store side of the column-split product: rank r computes columns [col0, col0 + n) and
+    writes them into its own copy of the full y and into every peer's (ordinary stores through
+    peer-mapped addresses on the GPU; here two host buffers).  Columns outside the slice and rows
+    past the batch stay untouched in both."""
+    import aotx_b200
+    n, k, m, width, col0 = 300, 1024, 20, 900, 300
+    w = aotx_b200.synth_q8_0(n, k, 61)
+    x = inputs(m, k, 62)
+    mine = np.full((m + 1, width), GUARD, np.float32)
+    theirs = np.full((m + 1, width), GUARD, np.float32)
+    unused = np.full((m, width), GUARD, np.float32)     # y itself is not written; its width is the row stride
+    emu.peers([mine, theirs], col0)
+    try:
+        emu(w, n, k, x, unused, grid=5, ntok=32, form=form)
+    finally:
+        emu.peers([], 0)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    for y in (mine, theirs):
+        assert oracle.diff(y[:m, col0:col0 + n], want)[0] == 0
+        assert (y[:m, :col0] == GUARD).all() and (y[:m, col0 + n:] == GUARD).all() and (y[m:] == GUARD).all()
+    assert np.array_equal(mine, theirs)
+    assert (unused == GUARD).all()
