@@ -185,8 +185,22 @@ class ColumnSplitFused:
     y lives in symmetric memory (`torch.distributed._symmetric_memory`): every rank can store
     into every rank's copy.  The kernel of rank r writes its column slice of each tile into all
     copies (plain stores over NVLink, no multicast loads), and one device-side barrier orders
-    the ranks before anyone reads y.  A barrier also opens the step, so that no rank overwrites
-    a y that a peer is still reading from the step before."""
+    the ranks before anyone reads y.
+
+    There are two copies of y, used by alternate steps, and that is what makes one barrier per
+    step enough: a rank that writes the buffer of step s + 2 has passed the barrier of step
+    s + 1, which every rank reaches only after its own product of step s + 1, and that product
+    follows, on the rank's stream, whatever the rank read from the buffer of step s.  So no
+    store can land in a buffer that a peer still reads.  The result of a step is a view that
+    stays valid until the step after the next one.
+
+    A call that is captured into a CUDA graph uses, on every replay, the buffer it was captured
+    with, so the argument above does not cover it: such a call is opened by a barrier as well
+    (`opening_barrier=None` decides by whether the stream is capturing).  A caller whose graph
+    holds another barrier of the same ranks between two uses of one buffer - as a rotation over
+    two or more of these objects does - may pass `opening_barrier=False`: a rank leaves that
+    barrier only after every peer has reached it, and a peer reaches it only after what it read
+    from the buffer before."""
 
     def __init__(self, ctx, w_local, n, k, world, rank, m_max, y_dtype, group=None):
         import torch
@@ -197,13 +211,23 @@ class ColumnSplitFused:
         self.first, self.last = shard_rows(n, world, rank)
         self.y_dtype = y_dtype
         group = group if group is not None else dist.group.WORLD
-        self.y = symm.empty((m_max, n), dtype=y_dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.y = symm.empty((2, m_max, n), dtype=y_dtype, device=torch.device("cuda", torch.cuda.current_device()))
         self.handle = symm.rendezvous(self.y, group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-
-    def matmul(self, x, m):
+        half = m_max * n * self.y.element_size()
+        self.ptrs = [[int(p) + which * half for p in self.handle.buffer_ptrs] for which in (0, 1)]
+        self.step = 0
+        # nobody stores into a peer before every rank has its buffers
         self.handle.barrier(channel=0)
-        self.ctx.matmul_peers(self.w_local, self.last - self.first, self.k, x, m, self.ptrs, self.n,
+
+    def matmul(self, x, m, opening_barrier=None):
+        import torch
+        which = self.step & 1
+        self.step += 1
+        if opening_barrier is None:
+            opening_barrier = torch.cuda.is_current_stream_capturing()
+        if opening_barrier:
+            self.handle.barrier(channel=which ^ 1)
+        self.ctx.matmul_peers(self.w_local, self.last - self.first, self.k, x, m, self.ptrs[which], self.n,
                               self.first, self.y_dtype)
-        self.handle.barrier(channel=1)
-        return self.y[:m]
+        self.handle.barrier(channel=which)
+        return self.y[which, :m]

@@ -427,8 +427,11 @@ def run_sharded(args, rank, world, local_rank):
             from aotx_b200.sharded import ColumnSplitFused
             fused = [ColumnSplitFused(ctx, w, n, k, world, rank, m, torch.bfloat16) for w in shards]
 
+            # One barrier per step is enough here even inside a graph: the step rotates over
+            # `copies` >= 2 of these objects, so another barrier of the same ranks lies between
+            # two uses of one object's buffer.
             def step(c):
-                fused[c].matmul(x, m)
+                fused[c].matmul(x, m, opening_barrier=False if copies >= 2 else None)
         else:
             splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
             out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
