@@ -56,6 +56,11 @@ struct DuoShape {
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * x_depth + 2 * a_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    // two blocks and the 1 KB the system keeps per block within the 228 KB of an SM
+    static_assert(2u * (smem_bytes + 1024u) <= 228u * 1024u, "two blocks' shared memory on one SM");
+    static_assert(a_column0 >= 2u * NTOK && a_column0 + a_stages * a_stage_columns <= tmem_columns
+                      && 2u * tmem_columns <= 512u,
+                  "two accumulators, then the A pieces, in half of the tensor memory");
 };
 
 template <int NTOK, typename YT>

@@ -38,6 +38,9 @@ struct StreamShape {
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 3 * depth + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    static_assert(smem_bytes <= 227u * 1024u, "one block's shared memory");
+    static_assert(a_column0 >= 2u * NTOK && a_column0 + depth * a_seg_columns <= tmem_columns,
+                  "two accumulators, then the A segments, within the allocation");
 };
 
 template <int NTOK, typename YT>

@@ -62,6 +62,8 @@ struct Shape {
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * mma_stages + 2 * x_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    static_assert(smem_bytes <= 227u * 1024u, "one block's shared memory");
+    static_assert(tmem_columns <= 512u, "two accumulators within the tensor memory");
 };
 
 template <int NTOK, typename YT>

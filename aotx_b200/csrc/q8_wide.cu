@@ -46,6 +46,9 @@ struct WideShape {
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * x_stages + 2 * a_stages + 2 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    static_assert(smem_bytes <= 227u * 1024u, "one block's shared memory");
+    static_assert(a_column0 >= ntok && a_column0 + a_stages * a_seg_columns <= tmem_columns,
+                  "the accumulator, then the A segments, within the allocation");
 };
 
 template <typename YT>

@@ -484,6 +484,21 @@ extern "C" unsigned int stream_emu_moe(const unsigned char *w_gate, const unsign
     return status;
 }
 
+// The table build alone: sorted pairs, the two tile tables (five words per entry) and their
+// entry counts.
+extern "C" void stream_emu_group_build(const unsigned int *ids, uint32_t tokens, const unsigned int *tokens_dev,
+                                       uint32_t used, uint32_t experts, uint32_t ffn, uint32_t hidden,
+                                       uint32_t tile_tokens, unsigned int *sorted_pair, unsigned int *tiles_feed,
+                                       unsigned int *tiles_down, unsigned int *counts)
+{
+    set_mode(0, 0);
+    run_grid(1u, Q8_GROUP_THREADS, [&] {
+        q8_group_build_kernel(ids, tokens, tokens_dev, used, experts, ffn, hidden, sorted_pair,
+                              reinterpret_cast<GroupTile *>(tiles_feed), reinterpret_cast<GroupTile *>(tiles_down),
+                              counts, tile_tokens);
+    });
+}
+
 // Fault injection for the bounded waits: copy number `lost_copy` of the next launches never lands
 // (-1: none), and the wait bound is `seconds` long.
 extern "C" void stream_emu_faults(long long lost_copy, double seconds)

@@ -47,6 +47,7 @@ def emu(tmp_path_factory):
     lib.stream_emu_switches.argtypes = [C.c_uint]
     lib.stream_emu_form.argtypes = [C.c_uint]
     lib.stream_emu_peers.argtypes = [C.c_uint, vp, C.c_uint]
+    lib.stream_emu_group_build.argtypes = [vp, u32, vp, u32, u32, u32, u32, u32, vp, vp, vp, vp]
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
@@ -106,6 +107,7 @@ def emu(tmp_path_factory):
     run.moe = moe
     run.wide = wide
     run.peers = peers
+    run.lib = lib
     return run
 
 
@@ -602,3 +604,38 @@ def test_column_split_stores_into_every_peer(emu, oracle, form):
         assert (y[:m, :col0] == GUARD).all() and (y[:m, col0 + n:] == GUARD).all() and (y[m:] == GUARD).all()
     assert np.array_equal(mine, theirs)
     assert (unused == GUARD).all()
+
+
+@pytest.mark.parametrize("tokens,used,experts,tile", [(512, 8, 128, 64), (700, 3, 5, 16), (1, 8, 128, 64), (300, 4, 256, 32)])
+def test_table_build_is_a_stable_sort_with_exact_tables(emu, tokens, used, experts, tile):
+    """The table build on its own at sizes of several placement rounds (1024 pairs each): pairs
+    sorted by expert in ascending pair order, selections outside the table left out, and the two
+    tables equal to the ones written down here from the counts."""
+    rng = np.random.default_rng(tokens + experts)
+    ids = np.stack([rng.permutation(experts)[:used] for _ in range(tokens)]).astype(np.uint32)
+    ids[rng.integers(tokens), rng.integers(used)] = experts + 1          # names no expert
+    ffn, hidden = 768, 2048
+    pairs = tokens * used
+    pair = np.full(pairs, 0x55555555, np.uint32)
+    room = (pairs // 16 + experts) * 16
+    feed = np.zeros((room, 5), np.uint32)
+    down = np.zeros((room, 5), np.uint32)
+    counts = np.zeros(2, np.uint32)
+    emu.lib.stream_emu_group_build(ids.ctypes.data, tokens, None, used, experts, ffn, hidden, tile, pair.ctypes.data,
+                                   feed.ctypes.data, down.ctypes.data, counts.ctypes.data)
+    flat = ids.reshape(-1)
+    valid = np.nonzero(flat < experts)[0]
+    order = valid[np.argsort(flat[valid], kind="stable")]
+    assert pair[:len(order)].tolist() == order.tolist()
+    assert (pair[len(order):] == 0xFFFFFFFF).all()
+    want_feed, want_down, at = [], [], 0
+    for e in range(experts):
+        count = int((flat == e).sum())
+        for tt in range(-(-count // tile)):
+            tok0, limit = at + tt * tile, min(at + count, at + (tt + 1) * tile)
+            want_feed += [(e * ffn + r * 128, r * 128, ffn, tok0, limit) for r in range(ffn // 128)]
+            want_down += [(e * hidden + r * 128, r * 128, hidden, tok0, limit) for r in range(hidden // 128)]
+        at += count
+    assert counts.tolist() == [len(want_feed), len(want_down)]
+    assert feed[:len(want_feed)].tolist() == [list(t) for t in want_feed]
+    assert down[:len(want_down)].tolist() == [list(t) for t in want_down]
