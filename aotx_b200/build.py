@@ -30,13 +30,44 @@ def _stale(target, deps):
 def _compile(src):
     obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
     deps = [os.path.join(CSRC, src)] + [os.path.join(CSRC, h) for h in HEADERS]
-    if not _stale(obj, deps):
+    log = obj + ".ptxas.log"   # what ptxas -v said for this object: registers, spills, shared memory
+    if not _stale(obj, deps) and os.path.exists(log):
         return obj, ""
     cmd = ["nvcc", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
     done = subprocess.run(cmd, capture_output=True, text=True)
     if done.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s" % (src, done.stderr))
+    with open(log, "w") as f:
+        f.write(done.stderr)
     return obj, done.stderr
+
+
+def resource_usage():
+    """{kernel name (mangled): {"registers": r, "spill_stores": s, "spill_loads": l, "stack": b}}
+    from the ptxas reports kept beside the objects (build() first)."""
+    import re
+    usage = {}
+    for src in SOURCES:
+        log = os.path.join(OBJ, os.path.splitext(src)[0] + ".o.ptxas.log")
+        if not os.path.exists(log):
+            continue
+        name = None
+        for line in open(log):
+            found = re.search(r"Compiling entry function '([^']+)'", line)
+            if found:
+                name = found.group(1)
+                usage[name] = {}
+                continue
+            if name is None:
+                continue
+            found = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if found:
+                usage[name].update(stack=int(found.group(1)), spill_stores=int(found.group(2)),
+                                   spill_loads=int(found.group(3)))
+            found = re.search(r"Used (\d+) registers", line)
+            if found:
+                usage[name]["registers"] = int(found.group(1))
+    return usage
 
 
 def build(verbose=False):
