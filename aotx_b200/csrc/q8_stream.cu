@@ -24,10 +24,21 @@
 
 namespace q8 {
 
+// Stage counts of the 64-row token tile (the routed-expert products and batches of 33 to 64
+// rows), open to -D for experiments: fewer x / A stages leave room for more raw segments in
+// flight.  The static checks below hold the budget.
+#ifndef Q8_DEPTH_64
+#define Q8_DEPTH_64 3
+#endif
+#ifndef Q8_RAW_64
+#define Q8_RAW_64 3
+#endif
+
 template <int NTOK>
 struct StreamShape {
-    static constexpr uint32_t depth = NTOK <= 64 ? 3 : 2;            // A (TMEM) and x (shared) segment stages
-    static constexpr uint32_t raw_stages = NTOK <= 32 ? 5 : (NTOK == 64 ? 3 : 2);
+    // A (TMEM) and x (shared) segment stages
+    static constexpr uint32_t depth = NTOK <= 32 ? 3 : (NTOK == 64 ? Q8_DEPTH_64 : 2);
+    static constexpr uint32_t raw_stages = NTOK <= 32 ? 5 : (NTOK == 64 ? Q8_RAW_64 : 2);
     static constexpr uint32_t x_sub_bytes = NTOK * kSubK * 2;        // one [NTOK x 64] swizzled box
     static constexpr uint32_t x_seg_bytes = kSubs * x_sub_bytes;     // four boxes = 256 weights deep
     static constexpr uint32_t a_column0 = NTOK <= 64 ? 128 : 256;    // after the two accumulators
