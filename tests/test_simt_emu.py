@@ -195,7 +195,7 @@ def test_rank_ordered_sum_bit_for_bit(emu, oracle, hidden, width):
 
 def test_per_pair_expert_products(emu, oracle):
     import aotx_b200
-    tokens, experts, used, hidden, ffn = 5, 4, 2, 64, 96
+    tokens, experts, used, hidden, ffn = 5, 4, 2, 64, 32
     wg = aotx_b200.synth_q8_0(experts * ffn, hidden, 1)
     wu = aotx_b200.synth_q8_0(experts * ffn, hidden, 2)
     wd = aotx_b200.synth_q8_0(experts * hidden, ffn, 3)
