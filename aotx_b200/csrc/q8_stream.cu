@@ -214,6 +214,17 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             uint32_t g = 0;
             grid_dependency_wait();
             bool ok = true;
+#ifdef Q8_SWITCHES
+            // switch 64: when a row of x is exactly as many segments deep as the ring has stages,
+            // stage j always holds the same segment of x, and consecutive tiles over the same rows
+            // of x (the row tiles of one expert's token tile in the grouped down product) find
+            // it there: the copy is left out and the stage is handed over as it is
+            uint32_t held[S::depth];
+            for (uint32_t i = 0; i < S::depth; ++i) {
+                held[i] = 0xFFFFFFFFu;
+            }
+            const bool reuse = (args.debug & 64u) != 0u && segs == S::depth && args.b_bf16 == 0u;
+#endif
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
                 const uint32_t s0 = (uint32_t)(u % segs);
@@ -231,6 +242,20 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     if (args.debug & 8u) {
                         mbar_arrive(x_full + 8u * st);
                         continue;
+                    }
+                    if (reuse) {
+                        bool same = false;
+#pragma unroll
+                        for (uint32_t i = 0; i < S::depth; ++i) {
+                            if (i == st) {
+                                same = held[i] == tok0;
+                                held[i] = tok0;
+                            }
+                        }
+                        if (same) {
+                            mbar_arrive(x_full + 8u * st);
+                            continue;
+                        }
                     }
 #endif
                     mbar_expect_tx(x_full + 8u * st, S::x_seg_bytes);

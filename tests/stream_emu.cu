@@ -434,6 +434,7 @@ static unsigned int run_grouped(const unsigned char *w_stacked, uint32_t total_r
     args.row_map = row_map;
     args.ldy = ldy;
     args.epilogue = epilogue;
+    args.debug = switches;
     return run_stream_tile<YT>(ntok, tw, tx, args, grid);
 }
 
@@ -497,6 +498,12 @@ extern "C" void stream_emu_group_build(const unsigned int *ids, uint32_t tokens,
                               reinterpret_cast<GroupTile *>(tiles_feed), reinterpret_cast<GroupTile *>(tiles_down),
                               counts, tile_tokens);
     });
+}
+
+// Bulk tensor copies issued since the last entry point was called.
+extern "C" long long stream_emu_copies()
+{
+    return q8emu::copies_issued.load();
 }
 
 // Fault injection for the bounded waits: copy number `lost_copy` of the next launches never lands

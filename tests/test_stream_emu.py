@@ -46,6 +46,7 @@ def emu(tmp_path_factory):
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
     lib.stream_emu_switches.argtypes = [C.c_uint]
     lib.stream_emu_form.argtypes = [C.c_uint]
+    lib.stream_emu_copies.restype = C.c_longlong
     lib.stream_emu_peers.argtypes = [C.c_uint, vp, C.c_uint]
     lib.stream_emu_group_build.argtypes = [vp, u32, vp, u32, u32, u32, u32, u32, vp, vp, vp, vp]
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
@@ -74,7 +75,8 @@ def emu(tmp_path_factory):
             assert status == expect, hex(status)
         return requested.value if expect == 0 else status
 
-    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None, form=0):
+    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None, form=0,
+            switches=0):
         """The routed-expert step; returns proj [tokens][used][hidden], act and the sorted pairs."""
         tokens, used = ids.shape
         proj = np.full((tokens * used, hidden), GUARD, np.float32)
@@ -83,10 +85,13 @@ def emu(tmp_path_factory):
         ptr = lambda a: a.ctypes.data if a is not None else None
         lib.stream_emu_faults(-1, 10.0)
         lib.stream_emu_form(form)
+        lib.stream_emu_switches(switches)
         status = lib.stream_emu_moe(ptr(wg), ptr(wu), ptr(both), ptr(wd), experts, hidden, ffn, x.ctypes.data,
                                     ids.ctypes.data, tokens, ptr(live), used, tile, grid, proj.ctypes.data,
                                     act.ctypes.data, pair.ctypes.data, 0 if delay_us is None else 1, delay_us or 0)
         lib.stream_emu_form(0)
+        lib.stream_emu_switches(0)
+        run.copies = lib.stream_emu_copies()
         assert status == 0, hex(status)
         return proj.reshape(tokens, used, hidden), act, pair
 
@@ -639,3 +644,23 @@ def test_table_build_is_a_stable_sort_with_exact_tables(emu, tokens, used, exper
     assert counts.tolist() == [len(want_feed), len(want_down)]
     assert feed[:len(want_feed)].tolist() == [list(t) for t in want_feed]
     assert down[:len(want_down)].tolist() == [list(t) for t in want_down]
+
+
+def test_switch_x_tile_kept_across_row_tiles(emu, oracle):
+    """Switch 64 of an experiment build: in the grouped down product of a layer whose expert
+    width is three segments (768), the three x stages hold a token tile's whole rows, and the
+    row tiles that follow over the same token tile take them as they are.  Same bits, fewer
+    copies."""
+    tokens, experts, used, hidden, ffn = 40, 3, 2, 256, 768
+    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 140)
+    plain, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=64, grid=3)
+    copies_plain = emu.copies
+    kept, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=64, grid=3, switches=64, delay_us=20)
+    assert np.array_equal(kept, plain)
+    # down: 3 experts x 2 row tiles x 3 segments x 4 boxes of x; with the switch each block copies a
+    # token tile's segments once
+    assert emu.copies < copies_plain
+    got = oracle.ordered_sum(np.ascontiguousarray(kept.transpose(1, 0, 2)), prob, ids)
+    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
+    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
+    assert ok, (err, bound)
