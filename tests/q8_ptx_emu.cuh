@@ -330,7 +330,9 @@ inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
 
 inline void tmem_alloc(uint32_t smem_result, uint32_t columns)
 {
-    const uint32_t base = 0;
+    // the allocation sits at the top of the 512 columns, so a kernel that takes fewer than all of
+    // them gets a base that is not zero (as a second block on the SM would) and must add it
+    const uint32_t base = 512u - columns;
     if (q8emu::lane_of_thread() == 0u) {
         q8emu::tmem_held += columns;
     }
