@@ -93,6 +93,10 @@ inline float bf16_bits_to_float(uint16_t bits)
 }
 
 inline unsigned int lane_of_thread();
+inline unsigned int warp_of_thread();
+// Accesses that the hardware does not define: a warp reading or writing tensor-memory lanes
+// outside its own quarter (warp w of a block reaches lanes 32 (w mod 4) .. + 31 only).
+inline std::atomic<unsigned int> lane_violations{0};
 
 // An engine that runs operations in the order they were issued, some time after the issue.
 class Engine {
@@ -421,6 +425,9 @@ inline void umma_commit(uint32_t bar)
 inline void emu_tmem_access(uint32_t taddr, uint32_t *v, const uint32_t *from, unsigned int count)
 {
     const unsigned int lane = ((taddr >> 16) & 0xFFFFu) + q8emu::lane_of_thread();
+    if (((taddr >> 16) & 0xFFFFu) != 32u * (q8emu::warp_of_thread() & 3u)) {
+        q8emu::lane_violations += 1u;
+    }
     const unsigned int column = taddr & 0xFFFFu;
     for (unsigned int i = 0; i < count; ++i) {
         if (from != nullptr) {

@@ -228,6 +228,11 @@ inline unsigned int lane_of_thread()
 {
     return emu::thread_index.x % 32u;
 }
+
+inline unsigned int warp_of_thread()
+{
+    return emu::thread_index.x / 32u;
+}
 } // namespace q8emu
 
 // static shared arrays: one block runs at a time, so one static copy stands for the block's

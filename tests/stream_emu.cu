@@ -154,6 +154,11 @@ inline unsigned int lane_of_thread()
 {
     return emu::thread_index.x % 32u;
 }
+
+inline unsigned int warp_of_thread()
+{
+    return emu::thread_index.x / 32u;
+}
 } // namespace q8emu
 
 #include "q8_stream.cu"
@@ -206,6 +211,9 @@ static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
         }
         if (q8emu::tmem_held.exchange(0u) != 0u) {
             status |= 0x400u; // the block ended holding tensor memory
+        }
+        if (q8emu::lane_violations.exchange(0u) != 0u) {
+            status |= 0x800u; // a warp touched tensor-memory lanes outside its quarter
         }
     }
     return status;
