@@ -94,9 +94,13 @@ inline float bf16_bits_to_float(uint16_t bits)
 
 inline unsigned int lane_of_thread();
 inline unsigned int warp_of_thread();
-// Accesses that the hardware does not define: a warp reading or writing tensor-memory lanes
-// outside its own quarter (warp w of a block reaches lanes 32 (w mod 4) .. + 31 only).
+// Uses that the hardware does not define or faults on, counted: a warp reading or writing
+// tensor-memory lanes outside its own quarter (warp w of a block reaches lanes 32 (w mod 4) .. + 31
+// only) or columns outside the block's allocation; a bulk tensor copy whose inner coordinate is
+// not a multiple of 16 bytes or whose destination is not on a 128-byte (1024 with the swizzle)
+// boundary; an L2 request that is not 16-byte aligned and sized.
 inline std::atomic<unsigned int> lane_violations{0};
+inline std::atomic<uint32_t> tmem_first_column{0};
 
 // An engine that runs operations in the order they were issued, some time after the issue.
 class Engine {
@@ -316,6 +320,10 @@ inline void emu_tma_load_2d(uint32_t dst, const q8emu::TensorMap &map, uint32_t 
 inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1)
 {
     const q8emu::TensorMap map = *static_cast<const q8emu::TensorMap *>(tmap);
+    if (((long long)c0 * (long long)map.elem_bytes) % 16 != 0 || dst % (map.swizzle128 ? 1024u : 128u) != 0u
+        || c1 < 0) {
+        q8emu::lane_violations += 1u;
+    }
     if (q8emu::copies_issued.fetch_add(1) == q8emu::lost_copy) {
         return;
     }
@@ -327,7 +335,9 @@ inline unsigned long long l2_requests = 0;
 inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
 {
     // nothing to warm; the ranges are checked by the caller's test through the count
-    (void)addr;
+    if ((reinterpret_cast<uintptr_t>(addr) & 15u) != 0u || (bytes & 15u) != 0u || bytes == 0u) {
+        q8emu::lane_violations += 1u;
+    }
     std::lock_guard<std::mutex> lock(q8emu::barrier_mutex);
     l2_requests += bytes;
 }
@@ -339,6 +349,7 @@ inline void tmem_alloc(uint32_t smem_result, uint32_t columns)
     const uint32_t base = 512u - columns;
     if (q8emu::lane_of_thread() == 0u) {
         q8emu::tmem_held += columns;
+        q8emu::tmem_first_column = base;
     }
     std::memcpy(q8emu::shared_at(smem_result), &base, 4);
 }
@@ -360,6 +371,9 @@ inline void emu_mma(uint32_t d_tmem, AValue a_value, uint64_t b_desc, uint32_t i
     const uint32_t n = ((idesc >> 17) & 0x3Fu) << 3;
     const bool b_bf16 = ((idesc >> 10) & 1u) != 0u;
     const uint32_t d_col = d_tmem & 0xFFFFu;
+    if (d_col < q8emu::tmem_first_column.load() || d_col + n > 512u) {
+        q8emu::lane_violations += 1u;
+    }
     const uint32_t b_start = (uint32_t)(b_desc & 0x3FFFu) << 4;
     for (uint32_t row = 0; row < 128u; ++row) {
         float a[16];
@@ -425,10 +439,11 @@ inline void umma_commit(uint32_t bar)
 inline void emu_tmem_access(uint32_t taddr, uint32_t *v, const uint32_t *from, unsigned int count)
 {
     const unsigned int lane = ((taddr >> 16) & 0xFFFFu) + q8emu::lane_of_thread();
-    if (((taddr >> 16) & 0xFFFFu) != 32u * (q8emu::warp_of_thread() & 3u)) {
+    const unsigned int column = taddr & 0xFFFFu;
+    if (((taddr >> 16) & 0xFFFFu) != 32u * (q8emu::warp_of_thread() & 3u)
+        || column < q8emu::tmem_first_column.load() || column + count > 512u) {
         q8emu::lane_violations += 1u;
     }
-    const unsigned int column = taddr & 0xFFFFu;
     for (unsigned int i = 0; i < count; ++i) {
         if (from != nullptr) {
             q8emu::tensor_memory[lane][column + i] = from[i];

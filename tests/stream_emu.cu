@@ -213,7 +213,7 @@ static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
             status |= 0x400u; // the block ended holding tensor memory
         }
         if (q8emu::lane_violations.exchange(0u) != 0u) {
-            status |= 0x800u; // a warp touched tensor-memory lanes outside its quarter
+            status |= 0x800u; // a use the hardware does not define (lanes, columns, copy alignment)
         }
     }
     return status;

@@ -10,7 +10,11 @@ the three store modes and the L2 requests for the following product.  In the asy
 the copies and the tensor-core work complete later, in order, on threads of their own with random
 delays, so a buffer reused too early would give wrong numbers; and a copy that never lands (made
 on the host) checks that every wait is bounded: the block raises its status bit, lets its other
-copies land, hands its tensor memory back and ends.  The stand-ins encode what the instructions
+copies land, hands its tensor memory back and ends.  The stand-ins also count uses that the
+hardware does not define or faults on (tensor-memory lanes outside a warp's quarter, columns
+outside the allocation, a bulk tensor copy whose inner coordinate is not a multiple of 16 bytes
+or whose destination is off its boundary, an unaligned L2 request); any of them fails the launch
+here (status 0x800).  The stand-ins encode what the instructions
 do as the kernel was verified against the hardware; the hardware itself is the GPU tests'
 matter."""
 import ctypes as C
