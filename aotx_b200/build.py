@@ -70,6 +70,34 @@ def resource_usage():
     return usage
 
 
+EXPERIMENT_LIB = os.path.join(HERE, "libaotx_q8_b200_experiment.so")
+
+
+def build_experiment(defines=()):
+    """The library with -DQ8_EXPERIMENT (plus `defines`, e.g. "Q8_RAW_64=4"): the switches and
+    time stamps that the product build leaves out, and the way to the kernels the product build
+    does not dispatch (see the headers of q8_wide.cu, q8_duo.cu and q8_umma.cu for the
+    environment variables).  Loaded instead of the product library when AOTX_Q8_LIBRARY names it
+    (aotx_b200/library.py).  Always rebuilt: the defines are not tracked."""
+    out = os.path.join(OBJ, "experiment")
+    os.makedirs(out, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")] + ["-DQ8_EXPERIMENT"] + ["-D" + d for d in defines]
+
+    def one(src):
+        obj = os.path.join(out, os.path.splitext(src)[0] + ".o")
+        done = subprocess.run(["nvcc", *flags, "-c", os.path.join(CSRC, src), "-o", obj], capture_output=True,
+                              text=True)
+        if done.returncode != 0:
+            raise RuntimeError("nvcc failed for %s:\n%s" % (src, done.stderr))
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        objs = list(pool.map(one, SOURCES))
+    subprocess.run(["nvcc", "-shared", "-o", EXPERIMENT_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+                   check=True)
+    return EXPERIMENT_LIB
+
+
 def build(verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
@@ -88,4 +116,7 @@ def build(verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv))
+    if "--experiment" in sys.argv:
+        print(build_experiment([a[2:] for a in sys.argv if a.startswith("-D")]))
+    else:
+        print(build(verbose="-v" in sys.argv))

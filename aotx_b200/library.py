@@ -5,6 +5,13 @@ import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libaotx_q8_b200.so")
+# AOTX_Q8_LIBRARY=experiment loads the build of `python -m aotx_b200.build --experiment` instead
+# (development only: switches, time stamps, kernels the product build does not dispatch); any
+# other value is taken as the path of a library with the same interface.
+if os.environ.get("AOTX_Q8_LIBRARY") == "experiment":
+    LIB_PATH = os.path.join(HERE, "libaotx_q8_b200_experiment.so")
+elif os.environ.get("AOTX_Q8_LIBRARY"):
+    LIB_PATH = os.path.abspath(os.environ["AOTX_Q8_LIBRARY"])
 
 # every symbol include/aotx_q8_b200.h declares
 SYMBOLS = (

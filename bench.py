@@ -63,6 +63,15 @@ def measured_peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+def mark_library(line):
+    """A line measured on anything but the product library says so (AOTX_Q8_LIBRARY names a
+    development build, with the switches set in the environment): not a product number."""
+    if os.environ.get("AOTX_Q8_LIBRARY"):
+        line["config"]["library"] = os.environ["AOTX_Q8_LIBRARY"]
+        line["config"]["switches"] = {k: v for k, v in os.environ.items() if k.startswith("Q8_")}
+    return line
+
+
 def algorithmic_bytes(m, projections, x_bytes, y_bytes, fused=False):
     total = 0
     for name, k, n in projections:
@@ -386,7 +395,7 @@ def run_ours(args, rank, world, local_rank):
         except Exception as error:  # the second baseline must never break the benchmark line
             line["reference_gpu"] = {"unavailable": str(error)[:120]}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(mark_library(line)))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
@@ -548,7 +557,7 @@ def run_sharded(args, rank, world, local_rank):
         "gpu_launches": launches * args.steps, "clocks": sampler.summary(), "device_status": status,
     }
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(mark_library(line)), flush=True)
     # Graphs that hold captured collectives must go before the process group does; tearing the
     # group down first left every rank waiting at exit.
     graphs = None
