@@ -15,7 +15,7 @@
 // there has left.
 //
 // What a block is here: 352 threads (warps 0-3 epilogue, 4-7 converters, 8 raw weight copies,
-// 9 x copies, 10 MMA issue), at most 93 registers, about 101 KB of shared memory (two raw
+// 9 x copies, 10 MMA issue), 80 registers and no spills, about 101 KB of shared memory (two raw
 // segments of 34 KB in flight, two x segments), 256 columns of tensor memory (two accumulators
 // of NTOK columns, three A pieces of 64 columns).  A converter thread still owns one row of the
 // weight tile, but takes the two halves of a 256-weight segment one after the other, and the
@@ -379,8 +379,9 @@ q8_duo_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 break;
             }
             tc_fence_after_sync();
-            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, tile, s0, s1, segs,
-                                     tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
+            // one block's partial sums in flight at a time: 80 registers hold that without spills
+            epilogue_piece<NTOK, YT, false>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, tile, s0, s1,
+                                            segs, tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }
     }

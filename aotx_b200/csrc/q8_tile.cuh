@@ -350,7 +350,10 @@ __device__ __forceinline__ TilePlace tile_place(const UmmaArgs &args, uint32_t t
     return place;
 }
 
-template <int NTOK, typename YT>
+// PAIRS: the owner of a cut tile keeps the partial sums of two blocks in flight at a time (the
+// kernels with 128 registers a thread); without it one block's at a time, the same additions
+// in the same order.
+template <int NTOK, typename YT, bool PAIRS = true>
 __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t taddr_acc, uint32_t wq,
                                                uint32_t lane, uint32_t tile, uint32_t cut_tile, uint32_t s0,
                                                uint32_t s1,
@@ -428,10 +431,10 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             }
         } else {
             // Add the partial sums in block order, two blocks' loads in flight at a time.
-            for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; cc += 2u) {
+            for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; cc += PAIRS ? 2u : 1u) {
                 const float *slot0 = args.partial + (unsigned long long)cc * args.tile_floats
                                    + (unsigned long long)c0 * kRows + lane_row;
-                const bool two = cc + 1u <= last_cc;
+                const bool two = PAIRS && cc + 1u <= last_cc;
                 const float *slot1 = two ? slot0 + args.tile_floats : slot0;
                 float a0[kChunk];
                 float a1[kChunk];

@@ -13,7 +13,7 @@ HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_bui
 # any-shape fallbacks (shapes the tensor-core kernels do not take) and kernels no shipped path reaches
 SMALL_SPILLS = {"q8_gemv_simt_kernel": 32, "q8_gemv_simt_fused_kernel": 64, "q_gemv_any_kernel": 16,
                 "q8_expert_feed_kernel": 64, "q8_expert_down_kernel": 64,
-                "q8_wide_kernel": 16, "q8_duo_kernel": 128, "q8_umma_kernel": 0}
+                "q8_wide_kernel": 16, "q8_duo_kernel": 0, "q8_umma_kernel": 0}
 
 
 @pytest.fixture(scope="module")
