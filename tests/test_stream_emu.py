@@ -668,3 +668,21 @@ def test_switch_x_tile_kept_across_row_tiles(emu, oracle):
     want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
     ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
     assert ok, (err, bound)
+
+
+def test_benchmark_projection_at_full_size_and_grid(emu, oracle):
+    """The O projection of the benchmark's decode step as it is launched: 4096 x 4096 weights, 32
+    rows of binary16 x, 148 blocks (512 units, every block with a cut tile at both
+    ends of its range), on both decode-regime kernels."""
+    import aotx_b200
+    n, k, m = 4096, 4096, 32
+    w = aotx_b200.synth_q8_0(n, k, 77)
+    x = inputs(m, k, 78)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    y = np.full((m + 1, n), GUARD, np.float32)
+    emu(w, n, k, x, y[:m], grid=148, ntok=32)
+    assert oracle.diff(y[:m], want)[0] == 0
+    assert (y[m:] == GUARD).all()
+    two = np.zeros((m, n), np.float32)
+    emu(w, n, k, x, two, grid=296, ntok=32, form=1)
+    assert oracle.diff(two, want)[0] == 0
