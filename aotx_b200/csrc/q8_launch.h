@@ -4,7 +4,35 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#ifdef Q8_HOST_EMULATION
+#include <functional>
+#endif
+
 namespace q8 {
+
+// Every kernel of the library is launched through this one function (or, for the tensor-core
+// kernels with their launch attributes, through launch_tile_kernel in q8_tile.cuh).  In the
+// tests' host emulation (-DQ8_HOST_EMULATION: the kernels compiled as host code) the same call
+// runs the grid's blocks as host threads, so the host side of the library - argument checks,
+// tensor maps, grids, workspaces - is the code that ships in both.
+#ifdef Q8_HOST_EMULATION
+void emulate_grid(dim3 grid, unsigned int threads, const std::function<void()> &block_body);
+#endif
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, unsigned int threads, size_t shared_bytes,
+                                 cudaStream_t stream, Args... args)
+{
+#ifdef Q8_HOST_EMULATION
+    (void)shared_bytes;
+    (void)stream;
+    emulate_grid(grid, threads, [&] { kernel(args...); });
+    return cudaSuccess;
+#else
+    kernel<<<grid, threads, shared_bytes, stream>>>(args...);
+    return cudaGetLastError();
+#endif
+}
 
 // y dtype codes as in the public header: 0 float, 1 half, 2 bfloat16.
 

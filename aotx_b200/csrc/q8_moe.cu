@@ -277,16 +277,15 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
     __half *act = reinterpret_cast<__half *>(workspace + ws.act);
     float *proj = reinterpret_cast<float *>(workspace + ws.proj);
 
-    q8_group_build_kernel<<<1, Q8_GROUP_THREADS, 0, stream>>>(ids, tokens, tokens_dev, used, experts, ffn, hidden,
-                                                              sorted_pair, tiles_feed, tiles_down, counts, tile_tokens);
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = launch_kernel(q8_group_build_kernel, 1, Q8_GROUP_THREADS, 0, stream, ids, tokens, tokens_dev,
+                                    used, experts, ffn, hidden, sorted_pair, tiles_feed, tiles_down, counts,
+                                    tile_tokens);
     if (err != cudaSuccess) {
         return err;
     }
     const unsigned int wave = pairs < 148u * 16u ? pairs : 148u * 16u;
-    q8_gather_rows_kernel<<<wave, 128, 0, stream>>>(static_cast<const uint4 *>(x), sorted_pair, tokens, tokens_dev,
-                                                    used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
-    err = cudaGetLastError();
+    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, static_cast<const uint4 *>(x), sorted_pair, tokens,
+                        tokens_dev, used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
     if (err != cudaSuccess) {
         return err;
     }
@@ -302,8 +301,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
     if (err != cudaSuccess) {
         return err;
     }
-    q8_swiglu_kernel<<<148 * 8, 256, 0, stream>>>(gate, up, tokens, tokens_dev, used, ffn, act);
-    err = cudaGetLastError();
+    err = launch_kernel(q8_swiglu_kernel, 148 * 8, 256, 0, stream, gate, up, tokens, tokens_dev, used, ffn, act);
     if (err != cudaSuccess) {
         return err;
     }
@@ -334,17 +332,15 @@ cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scr
     float *proj = reinterpret_cast<float *>(workspace + ws.proj);
 
     // the feed table is built over the 2 * ffn interleaved rows of every expert
-    q8_group_build_kernel<<<1, Q8_GROUP_THREADS, 0, stream>>>(ids, tokens, tokens_dev, used, experts, 2u * ffn,
-                                                              hidden, sorted_pair, tiles_feed, tiles_down, counts,
-                                                              tile_tokens);
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = launch_kernel(q8_group_build_kernel, 1, Q8_GROUP_THREADS, 0, stream, ids, tokens, tokens_dev,
+                                    used, experts, 2u * ffn, hidden, sorted_pair, tiles_feed, tiles_down, counts,
+                                    tile_tokens);
     if (err != cudaSuccess) {
         return err;
     }
     const unsigned int wave = pairs < 148u * 16u ? pairs : 148u * 16u;
-    q8_gather_rows_kernel<<<wave, 128, 0, stream>>>(static_cast<const uint4 *>(x), sorted_pair, tokens, tokens_dev,
-                                                    used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
-    err = cudaGetLastError();
+    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, static_cast<const uint4 *>(x), sorted_pair, tokens,
+                        tokens_dev, used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
     if (err != cudaSuccess) {
         return err;
     }

@@ -318,8 +318,7 @@ cudaError_t launch_dequant(cudaStream_t stream, const void *w, unsigned int k, u
     unsigned long long want = (threads + 255ull) / 256ull;
     unsigned int grid = (unsigned int)(want < 148ull * 16ull ? want : 148ull * 16ull);
     int wide = (reinterpret_cast<uintptr_t>(out) & 15u) == 0u;
-    q8_dequant_kernel<<<grid, 256, 0, stream>>>(base, blocks, static_cast<__half *>(out), wide);
-    return cudaGetLastError();
+    return launch_kernel(q8_dequant_kernel, grid, 256, 0, stream, base, blocks, static_cast<__half *>(out), wide);
 }
 
 template <typename XT, typename YT>
@@ -330,15 +329,13 @@ static cudaError_t launch_gemv_simt_typed(cudaStream_t stream, const void *w, un
     unsigned int want = (n + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS;
     unsigned int grid = want < 148u * 8u ? want : 148u * 8u;
     if (epilogue == kEpilogueStore) {
-        q8_gemv_simt_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
-            static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
-            static_cast<YT *>(y));
-    } else {
-        q8_gemv_simt_fused_kernel<XT, YT><<<grid, Q8_SIMT_WARPS * 32u, 0, stream>>>(
-            static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
-            static_cast<YT *>(y), epilogue);
+        return launch_kernel(q8_gemv_simt_kernel<XT, YT>, grid, Q8_SIMT_WARPS * 32u, 0, stream,
+                             static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
+                             static_cast<YT *>(y));
     }
-    return cudaGetLastError();
+    return launch_kernel(q8_gemv_simt_fused_kernel<XT, YT>, grid, Q8_SIMT_WARPS * 32u, 0, stream,
+                         static_cast<const unsigned char *>(w), n, k, static_cast<const XT *>(x), m, m_dev,
+                         static_cast<YT *>(y), epilogue);
 }
 
 cudaError_t launch_gemv_simt(cudaStream_t stream, const void *w, unsigned int n, unsigned int k,
@@ -391,10 +388,8 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
         }
         configured = true;
     }
-    q8_route_kernel<<<grid, Q8_ROUTE_THREADS, smem, stream>>>(static_cast<const __half *>(x), router,
-                                                           tokens, tokens_dev, hidden, experts, used,
-                                                           prob, ids);
-    return cudaGetLastError();
+    return launch_kernel(q8_route_kernel, grid, Q8_ROUTE_THREADS, smem, stream, static_cast<const __half *>(x), router,
+                         tokens, tokens_dev, hidden, experts, used, prob, ids);
 }
 
 cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
@@ -410,32 +405,31 @@ cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, co
     unsigned int wave = pairs < 4096u ? pairs : 4096u;
     dim3 feed((ffn + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, wave);
     dim3 down((hidden + Q8_SIMT_WARPS - 1u) / Q8_SIMT_WARPS, wave);
-    q8_expert_feed_kernel<<<feed, Q8_SIMT_WARPS * 32u, 0, stream>>>(
-        static_cast<const unsigned char *>(w_gate), static_cast<const unsigned char *>(w_up), hidden,
-        ffn, static_cast<const __half *>(x), ids, experts, tokens, tokens_dev, used, static_cast<__half *>(act));
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = launch_kernel(q8_expert_feed_kernel, feed, Q8_SIMT_WARPS * 32u, 0, stream,
+                                    static_cast<const unsigned char *>(w_gate),
+                                    static_cast<const unsigned char *>(w_up), hidden, ffn,
+                                    static_cast<const __half *>(x), ids, experts, tokens, tokens_dev, used,
+                                    static_cast<__half *>(act));
     if (err != cudaSuccess) {
         return err;
     }
-    q8_expert_down_kernel<<<down, Q8_SIMT_WARPS * 32u, 0, stream>>>(
-        static_cast<const unsigned char *>(w_down), hidden, ffn, static_cast<const __half *>(act), ids,
-        experts, tokens, tokens_dev, used, proj);
-    return cudaGetLastError();
+    return launch_kernel(q8_expert_down_kernel, down, Q8_SIMT_WARPS * 32u, 0, stream,
+                         static_cast<const unsigned char *>(w_down), hidden, ffn, static_cast<const __half *>(act),
+                         ids, experts, tokens, tokens_dev, used, proj);
 }
 
 template <typename YT>
-static void expert_sum_launch(bool wide, unsigned int grid, cudaStream_t stream, const float *proj,
-                              const float *prob, const unsigned int *ids, unsigned int tokens,
-                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
-                              unsigned int used, void *out)
+static cudaError_t expert_sum_launch(bool wide, unsigned int grid, cudaStream_t stream, const float *proj,
+                                     const float *prob, const unsigned int *ids, unsigned int tokens,
+                                     const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                                     unsigned int used, void *out)
 {
     if (wide) {
-        q8_expert_sum_kernel<YT, 4u><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden, experts,
-                                                               used, static_cast<YT *>(out));
-    } else {
-        q8_expert_sum_kernel<YT, 1u><<<grid, 256, 0, stream>>>(proj, prob, ids, tokens, tokens_dev, hidden, experts,
-                                                               used, static_cast<YT *>(out));
+        return launch_kernel(q8_expert_sum_kernel<YT, 4u>, grid, 256, 0, stream, proj, prob, ids, tokens, tokens_dev,
+                             hidden, experts, used, static_cast<YT *>(out));
     }
+    return launch_kernel(q8_expert_sum_kernel<YT, 1u>, grid, 256, 0, stream, proj, prob, ids, tokens, tokens_dev,
+                         hidden, experts, used, static_cast<YT *>(out));
 }
 
 cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
@@ -450,18 +444,18 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
     // 16-byte loads of proj need rows of a multiple of four floats on a 16-byte boundary
     const bool wide = (hidden % 4u) == 0u && (reinterpret_cast<uintptr_t>(proj) & 15u) == 0u;
     if (out_dtype == 0) {
-        expert_sum_launch<float>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts, used,
-                                 out);
-    } else if (out_dtype == 1) {
-        expert_sum_launch<__half>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts, used,
-                                  out);
-    } else if (out_dtype == 2) {
-        expert_sum_launch<__nv_bfloat16>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts,
-                                         used, out);
-    } else {
-        return cudaErrorInvalidValue;
+        return expert_sum_launch<float>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts,
+                                        used, out);
     }
-    return cudaGetLastError();
+    if (out_dtype == 1) {
+        return expert_sum_launch<__half>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts,
+                                         used, out);
+    }
+    if (out_dtype == 2) {
+        return expert_sum_launch<__nv_bfloat16>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden,
+                                                experts, used, out);
+    }
+    return cudaErrorInvalidValue;
 }
 #endif
 

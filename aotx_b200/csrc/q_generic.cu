@@ -197,9 +197,8 @@ cudaError_t launch_dequant_any(cudaStream_t stream, const void *w, unsigned int 
     const unsigned long long total = (unsigned long long)rows * (k / 32u);
     unsigned long long want = (total + 255ull) / 256ull;
     const unsigned int grid = want < 148ull * 16ull ? (unsigned int)want : 148u * 16u;
-    q_dequant_any_kernel<<<grid, 256, 0, stream>>>(static_cast<const unsigned char *>(w), type, k, first_row, rows,
-                                                   static_cast<__half *>(out));
-    return cudaGetLastError();
+    return launch_kernel(q_dequant_any_kernel, grid, 256, 0, stream, static_cast<const unsigned char *>(w), type, k,
+                         first_row, rows, static_cast<__half *>(out));
 }
 
 template <typename XT, typename YT>
@@ -211,10 +210,9 @@ static cudaError_t launch_gemv_any_typed(cudaStream_t stream, const void *w, uns
     const unsigned int grid = want < 148u * 8u ? want : 148u * 8u;
     // rows of x are k * 2 bytes, a multiple of 64: 16-byte loads need only an aligned base
     const uint32_t wide_x = (reinterpret_cast<uintptr_t>(x) & 15u) == 0u ? 1u : 0u;
-    q_gemv_any_kernel<XT, YT><<<grid, QG_WARPS * 32u, 0, stream>>>(
-        static_cast<const unsigned char *>(w), type, n, k, static_cast<const XT *>(x), m, m_dev,
-        static_cast<YT *>(y), wide_x);
-    return cudaGetLastError();
+    return launch_kernel(q_gemv_any_kernel<XT, YT>, grid, QG_WARPS * 32u, 0, stream,
+                         static_cast<const unsigned char *>(w), type, n, k, static_cast<const XT *>(x), m, m_dev,
+                         static_cast<YT *>(y), wide_x);
 }
 
 cudaError_t launch_gemv_any(cudaStream_t stream, const void *w, unsigned int type, unsigned int n,
