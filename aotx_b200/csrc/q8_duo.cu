@@ -394,37 +394,18 @@ q8_duo_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
 }
 
-#ifndef Q8_HOST_EMULATION
 template <int NTOK, typename YT>
 static cudaError_t launch_duo_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                     const UmmaArgs &args, unsigned int grid)
 {
     using S = DuoShape<NTOK>;
     static unsigned long long configured = 0ull;
-    const unsigned long long before = configured;
-    cudaError_t err = allow_shared_memory(q8_duo_kernel<NTOK, YT>, S::smem_bytes, &configured);
+    cudaError_t err = allow_shared_memory(q8_duo_kernel<NTOK, YT>, S::smem_bytes, &configured, true);
     if (err != cudaSuccess) {
         return err;
     }
-    if (configured != before) {
-        // all of the configurable memory of an SM as shared memory, so that two blocks fit
-        err = cudaFuncSetAttribute(q8_duo_kernel<NTOK, YT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                   cudaSharedmemCarveoutMaxShared);
-        if (err != cudaSuccess) {
-            return err;
-        }
-    }
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(grid, 1, 1);
-    config.blockDim = dim3(kDuoThreads, 1, 1);
-    config.dynamicSmemBytes = S::smem_bytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = args.overlap != 0u ? 1 : 0;
-    return cudaLaunchKernelEx(&config, q8_duo_kernel<NTOK, YT>, tw, tx, args);
+    return launch_tile_kernel(q8_duo_kernel<NTOK, YT>, grid, S::smem_bytes, stream, args.overlap != 0u, tw, tx,
+                              args, kDuoThreads);
 }
 
 template <int NTOK>
@@ -455,6 +436,5 @@ cudaError_t launch_duo_kernel(cudaStream_t stream, const CUtensorMap &tw, const 
         return cudaErrorInvalidValue;
     }
 }
-#endif
 
 } // namespace q8

@@ -257,7 +257,6 @@ MoeWorkspace moe_workspace_layout(unsigned int tokens, unsigned int used, unsign
     return ws;
 }
 
-#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                                unsigned int *launches, bool overlap, const void *w_gate, const void *w_up,
                                const void *w_down, unsigned int experts, unsigned int hidden,
@@ -354,6 +353,5 @@ cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scr
                                tile_tokens, tiles_down, counts + 1, ws.max_down, sorted_pair, proj, hidden,
                                0, (*launches)++, overlap);
 }
-#endif
 
 } // namespace q8

@@ -302,7 +302,6 @@ __global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float
     }
 }
 
-#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 // ---------------------------------------------------------------------------------------
 // Launchers.
 // ---------------------------------------------------------------------------------------
@@ -457,6 +456,5 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
     }
     return cudaErrorInvalidValue;
 }
-#endif
 
 } // namespace q8

@@ -483,7 +483,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #endif
 }
 
-#ifndef Q8_HOST_EMULATION
 template <int NTOK, typename YT>
 static cudaError_t launch_stream_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                        const UmmaArgs &args, unsigned int grid)
@@ -530,7 +529,5 @@ cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, con
         return cudaErrorInvalidValue;
     }
 }
-
-#endif
 
 } // namespace q8

@@ -526,11 +526,20 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     }
 }
 
-#ifndef Q8_HOST_EMULATION /* host launch code: the tests' emulation runs the kernels itself */
 // Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
+// `two_per_sm`: also ask for all of the SM's configurable memory as shared memory, so that two
+// blocks of the kernel fit on one SM.
 template <typename Kernel>
-inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask)
+inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask,
+                                       bool two_per_sm = false)
 {
+#ifdef Q8_HOST_EMULATION
+    (void)kernel;
+    (void)bytes;
+    (void)done_mask;
+    (void)two_per_sm;
+    return cudaSuccess;
+#else
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) {
@@ -539,23 +548,36 @@ inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsign
     const unsigned long long bit = 1ull << (device & 63);
     if ((*done_mask & bit) == 0ull) {
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err == cudaSuccess && two_per_sm) {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                       cudaSharedmemCarveoutMaxShared);
+        }
         if (err != cudaSuccess) {
             return err;
         }
         *done_mask |= bit;
     }
     return cudaSuccess;
+#endif
 }
 
-// Launch with or without the programmatic-dependent-launch attribute.
+// Launch with or without the programmatic-dependent-launch attribute.  In the tests' host
+// emulation the blocks run as host threads instead (emulate_grid, q8_launch.h).
 template <typename Kernel>
 inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned int smem_bytes,
                                       cudaStream_t stream, bool overlap, const CUtensorMap &tw,
-                                      const CUtensorMap &tx, const UmmaArgs &args)
+                                      const CUtensorMap &tx, const UmmaArgs &args, unsigned int threads = kThreads)
 {
+#ifdef Q8_HOST_EMULATION
+    (void)smem_bytes;
+    (void)stream;
+    (void)overlap;
+    emulate_grid(dim3(grid, 1, 1), threads, [&] { kernel(tw, tx, args); });
+    return cudaSuccess;
+#else
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(grid, 1, 1);
-    config.blockDim = dim3(kThreads, 1, 1);
+    config.blockDim = dim3(threads, 1, 1);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
@@ -564,6 +586,7 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
     config.attrs = attribute;
     config.numAttrs = overlap ? 1 : 0;
     return cudaLaunchKernelEx(&config, kernel, tw, tx, args);
+#endif
 }
 
 // Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.
@@ -578,6 +601,5 @@ cudaError_t launch_duo_kernel(cudaStream_t stream, const CUtensorMap &tw, const 
 // Host launcher of the second prefill-regime kernel (q8_wide.cu), token tiles of 256.
 cudaError_t launch_wide_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                const UmmaArgs &args, unsigned int grid, int y_dtype);
-#endif
 
 } // namespace q8

@@ -365,7 +365,6 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
 }
 
-#ifndef Q8_HOST_EMULATION
 template <typename YT>
 static cudaError_t launch_wide_typed(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                      const UmmaArgs &args, unsigned int grid)
@@ -393,6 +392,5 @@ cudaError_t launch_wide_kernel(cudaStream_t stream, const CUtensorMap &tw, const
         return cudaErrorInvalidValue;
     }
 }
-#endif
 
 } // namespace q8

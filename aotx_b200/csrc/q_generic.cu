@@ -176,7 +176,6 @@ q_gemv_any_kernel(const unsigned char *__restrict__ w, uint32_t type, uint32_t n
     }
 }
 
-#ifndef Q8_HOST_EMULATION /* the launchers use the <<< >>> syntax; the emulator calls the kernels itself */
 bool block_type_known(unsigned int type)
 {
     uint32_t weights = 0, bytes = 0;
@@ -239,6 +238,5 @@ cudaError_t launch_gemv_any(cudaStream_t stream, const void *w, unsigned int typ
     return cudaErrorInvalidValue;
 }
 
-#endif
 
 } // namespace q8

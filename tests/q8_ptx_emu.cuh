@@ -79,6 +79,37 @@ struct TensorMap {
     uint32_t swizzle128;   // rows of the box are 128 bytes and stored with the 128-byte swizzle
 };
 
+// cuTensorMapEncodeTiled for two dimensions: the description goes into the 128 bytes of the map.
+// Refuses what the driver refuses: a base or a row stride off a 16-byte boundary, a box whose
+// rows are not a multiple of 16 bytes, a box side above 256, rows of a swizzled box that are not
+// 128 bytes.
+inline CUresult encode_tiled(CUtensorMap *map, CUtensorMapDataType type, cuuint32_t rank, void *base,
+                             const cuuint64_t *dims, const cuuint64_t *strides, const cuuint32_t *box,
+                             const cuuint32_t *element_strides, CUtensorMapInterleave, CUtensorMapSwizzle swizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill)
+{
+    static_assert(sizeof(TensorMap) <= sizeof(CUtensorMap), "the stand-in fits the real type");
+    uint32_t bytes = 0;
+    if (type == CU_TENSOR_MAP_DATA_TYPE_UINT32) {
+        bytes = 4;
+    } else if (type == CU_TENSOR_MAP_DATA_TYPE_FLOAT16 || type == CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
+        bytes = 2;
+    }
+    const bool swizzled = swizzle == CU_TENSOR_MAP_SWIZZLE_128B;
+    if (map == nullptr || rank != 2u || bytes == 0u || (reinterpret_cast<uintptr_t>(base) & 15u) != 0u
+        || (strides[0] & 15u) != 0u || ((uint64_t)box[0] * bytes) % 16u != 0u || box[0] > 256u || box[1] > 256u
+        || box[0] == 0u || box[1] == 0u || element_strides[0] != 1u || element_strides[1] != 1u
+        || (swizzle != CU_TENSOR_MAP_SWIZZLE_NONE && !swizzled) || (swizzled && box[0] * bytes != 128u)
+        || dims[0] == 0u || dims[1] == 0u) {
+        return CUDA_ERROR_INVALID_VALUE;
+    }
+    TensorMap described = {static_cast<const unsigned char *>(base), {dims[0], dims[1]}, strides[0], {box[0], box[1]},
+                           bytes, swizzled ? 1u : 0u};
+    std::memset(map, 0, sizeof *map);
+    std::memcpy(map, &described, sizeof described);
+    return CUDA_SUCCESS;
+}
+
 inline float half_bits_to_float(uint16_t bits)
 {
     return __half2float(__ushort_as_half(bits));

@@ -241,6 +241,14 @@ inline unsigned int warp_of_thread()
 #include "q8_simt.cu"
 #include "q_generic.cu"
 
+// what the library's own launch code runs a grid through in this build (q8_launch.h)
+namespace q8 {
+void emulate_grid(dim3 grid, unsigned int threads, const std::function<void()> &block_body)
+{
+    emu::launch2({grid.x, grid.y, 1}, threads, block_body);
+}
+} // namespace q8
+
 // ---- entry points for the tests -------------------------------------------------------------
 extern "C" void emu_dequant_any(const unsigned char *w, uint32_t type, uint32_t k, uint32_t first_row, uint32_t rows,
                                 unsigned short *out, uint32_t grid)

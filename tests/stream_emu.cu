@@ -177,10 +177,11 @@ using namespace q8;
 // Run `body` as a grid of blocks of `threads` threads, one block at a time, the last block first
 // (the owner of a cut tile waits only for blocks after its own, so that order never blocks).
 template <typename Body>
-static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
+static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body, unsigned int grid_x = 0)
 {
     unsigned int status = 0;
-    emu::grid_dim = {grid, 1, 1};
+    grid_x = grid_x == 0u ? grid : grid_x;          // a two-dimensional grid: grid_x blocks per row
+    emu::grid_dim = {grid_x, grid / grid_x, 1};
     emu::block_dim = {threads, 1, 1};
     for (unsigned int b = grid; b-- > 0u;) {
         std::memset(q8emu::tensor_memory, 0xEE, sizeof q8emu::tensor_memory);
@@ -198,7 +199,7 @@ static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
         for (unsigned int t = 0; t < threads; ++t) {
             lanes.emplace_back([&, t, b] {
                 emu::thread_index = {t, 0, 0};
-                emu::block_index = {b, 0, 0};
+                emu::block_index = {b % grid_x, b / grid_x, 0};
                 emu::warp = &warps[t / 32u];
                 body();
             });
@@ -218,6 +219,17 @@ static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body)
     }
     return status;
 }
+
+// What the library's own launch code runs a grid through in this build (q8_launch.h).  Status
+// bits of the runs since the last entry point was called collect in `emulated_status`.
+static unsigned int emulated_status = 0;
+
+namespace q8 {
+void emulate_grid(dim3 grid, unsigned int threads, const std::function<void()> &block_body)
+{
+    emulated_status |= run_grid(grid.x * grid.y, threads, block_body, grid.x);
+}
+} // namespace q8
 
 // The two tensor maps as the host launch code encodes them (launch_umma, launch_umma_grouped).
 static void make_maps(const unsigned char *w, uint32_t w_rows, uint32_t k, const void *x, uint32_t x_rows,
