@@ -60,6 +60,14 @@ def load_library():
             "%s is not built; run `python -m aotx_b200.build` (needs nvcc). "
             "This package has no CPU or PyTorch fallback." % LIB_PATH)
     lib = C.CDLL(LIB_PATH)
+    declare_q8(lib)
+    declare_gguf(lib)
+    _lib = lib
+    return lib
+
+
+def declare_q8(lib):
+    """Argument and result types of every entry point of include/aotx_q8_b200.h."""
     vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int
     lib.aotx_q8_init.argtypes = [C.POINTER(vp), i32]
     lib.aotx_q8_destroy.argtypes = [vp]
@@ -86,6 +94,11 @@ def load_library():
         fn = getattr(lib, name)
         if name != "aotx_q8_moe_workspace_bytes":
             fn.restype = i32
+
+
+def declare_gguf(lib):
+    """Argument and result types of every entry point of include/aotx_gguf_b200.h."""
+    vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int
     u64, info = C.c_uint64, C.POINTER(TensorInfo)
     lib.aotx_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
     lib.aotx_gguf_close.argtypes = [vp]
@@ -117,5 +130,3 @@ def load_library():
     lib.aotx_gguf_loader_last_cuda_error.argtypes = [vp]
     lib.aotx_gguf_upload.argtypes = [vp, vp, u64, u64, vp, vp]
     lib.aotx_gguf_upload_rows.argtypes = [vp, vp, u64, u64, u64, vp, u64, vp]
-    _lib = lib
-    return lib
