@@ -585,7 +585,7 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
         return cudaErrorInvalidValue;
     }
 
-    UmmaArgs args;
+    UmmaArgs args = {};
     args.n = n;
     args.k = k;
     args.m_max = m;
@@ -722,7 +722,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
     if (units < grid) {
         grid = (unsigned int)units;
     }
-    UmmaArgs args;
+    UmmaArgs args = {};
     args.n = total_rows;
     args.k = k;
     args.m_max = x_rows;

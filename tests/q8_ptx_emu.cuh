@@ -131,6 +131,9 @@ inline unsigned int warp_of_thread();
 // not a multiple of 16 bytes or whose destination is not on a 128-byte (1024 with the swizzle)
 // boundary; an L2 request that is not 16-byte aligned and sized.
 inline std::atomic<unsigned int> lane_violations{0};
+// which kinds were seen: 1 lanes, 2 columns of a load or store, 4 a bulk tensor copy, 8 an L2
+// request, 16 columns of an MMA's accumulator
+inline std::atomic<unsigned int> violation_kinds{0};
 inline std::atomic<uint32_t> tmem_first_column{0};
 
 // An engine that runs operations in the order they were issued, some time after the issue.
@@ -354,6 +357,7 @@ inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, in
     if (((long long)c0 * (long long)map.elem_bytes) % 16 != 0 || dst % (map.swizzle128 ? 1024u : 128u) != 0u
         || c1 < 0) {
         q8emu::lane_violations += 1u;
+        q8emu::violation_kinds |= 4u;
     }
     if (q8emu::copies_issued.fetch_add(1) == q8emu::lost_copy) {
         return;
@@ -368,6 +372,7 @@ inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
     // nothing to warm; the ranges are checked by the caller's test through the count
     if ((reinterpret_cast<uintptr_t>(addr) & 15u) != 0u || (bytes & 15u) != 0u || bytes == 0u) {
         q8emu::lane_violations += 1u;
+        q8emu::violation_kinds |= 8u;
     }
     std::lock_guard<std::mutex> lock(q8emu::barrier_mutex);
     l2_requests += bytes;
@@ -404,6 +409,7 @@ inline void emu_mma(uint32_t d_tmem, AValue a_value, uint64_t b_desc, uint32_t i
     const uint32_t d_col = d_tmem & 0xFFFFu;
     if (d_col < q8emu::tmem_first_column.load() || d_col + n > 512u) {
         q8emu::lane_violations += 1u;
+        q8emu::violation_kinds |= 16u;
     }
     const uint32_t b_start = (uint32_t)(b_desc & 0x3FFFu) << 4;
     for (uint32_t row = 0; row < 128u; ++row) {
@@ -471,9 +477,13 @@ inline void emu_tmem_access(uint32_t taddr, uint32_t *v, const uint32_t *from, u
 {
     const unsigned int lane = ((taddr >> 16) & 0xFFFFu) + q8emu::lane_of_thread();
     const unsigned int column = taddr & 0xFFFFu;
-    if (((taddr >> 16) & 0xFFFFu) != 32u * (q8emu::warp_of_thread() & 3u)
-        || column < q8emu::tmem_first_column.load() || column + count > 512u) {
+    if (((taddr >> 16) & 0xFFFFu) != 32u * (q8emu::warp_of_thread() & 3u)) {
         q8emu::lane_violations += 1u;
+        q8emu::violation_kinds |= 1u;
+    }
+    if (column < q8emu::tmem_first_column.load() || column + count > 512u) {
+        q8emu::lane_violations += 1u;
+        q8emu::violation_kinds |= 2u;
     }
     for (unsigned int i = 0; i < count; ++i) {
         if (from != nullptr) {

@@ -214,7 +214,8 @@ static unsigned int run_grid(unsigned int grid, unsigned int threads, Body body,
             status |= 0x400u; // the block ended holding tensor memory
         }
         if (q8emu::lane_violations.exchange(0u) != 0u) {
-            status |= 0x800u; // a use the hardware does not define (lanes, columns, copy alignment)
+            // a use the hardware does not define; which kinds, in bits 16 and up
+            status |= 0x800u | (q8emu::violation_kinds.exchange(0u) << 16);
         }
     }
     return status;

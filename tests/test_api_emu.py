@@ -168,3 +168,106 @@ def test_return_codes_and_nothing_written(api):
     finally:
         assert api.lib.aotx_q8_set_path(api.ctx, 0) == OK
     assert api.lib.aotx_q8_set_path(api.ctx, 9) == ERR_ARGUMENT
+
+
+@pytest.mark.parametrize("n,k,m", [(300, 1024, 20), (20, 96, 5)])
+def test_fused_stores_on_both_kernel_families(api, n, k, m):
+    import aotx_b200
+    w = aotx_b200.synth_q8_0(n, k, 31)
+    x = inputs(m, k, 32, scale=4.0)
+    plain = np.zeros((m, n), np.float32)
+    api.matmul(w, n, k, x, plain)
+    y0 = np.random.default_rng(33).standard_normal((m + 1, n)).astype(np.float32)
+    y = y0.copy()
+    api.matmul(w, n, k, x, y, m=m, epilogue=1)
+    assert np.array_equal(y[:m], y0[:m] + plain) and np.array_equal(y[m:], y0[m:])
+    act = np.full((m + 1, n // 2), 9.0, np.float16)
+    api.matmul(w, n, k, x, act, m=m, y_dtype=F16, epilogue=2)
+    gate, up = plain[:, 0::2].astype(np.float64), plain[:, 1::2].astype(np.float64)
+    want = gate / (1.0 + np.exp(-gate)) * up
+    got = act[:m].astype(np.float64)
+    assert (np.abs(got - want) <= 2.0 ** -10 * np.abs(want) + 1e-6).all()
+    assert (act[m:] == np.float16(9.0)).all() and np.abs(want).max() > 0.1
+
+
+def pieces_bytes(n, k, m, limit, grid):
+    """Bytes of the first `limit` units of every block of the launch that follows (its token tile
+    from its batch as the library picks it)."""
+    ntok = 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
+    segs, tok_tiles = k // 256, -(-m // ntok)
+    units = -(-n // 128) * tok_tiles * segs
+    blocks = min(units, grid)
+    total = 0
+    for b in range(blocks):
+        u, end = b * units // blocks, (b + 1) * units // blocks
+        end = min(end, u + limit)
+        while u < end:
+            tile, s0 = divmod(u, segs)
+            s1 = min(segs, s0 + (end - u))
+            total += min(128, n - (tile // tok_tiles) * 128) * (s1 - s0) * 272
+            u += s1 - s0
+    return total
+
+
+def test_hint_for_the_following_product(api, oracle):
+    """aotx_q8_hint_next: the next product's launch asks L2 for the first units of the product
+    named in the hint, block by block as that launch will read them; the hint is used once, any
+    product consumes it, and a hint the tensor-core kernel cannot follow is dropped."""
+    import aotx_b200
+    n, k, m = 700, 1024, 20
+    w = aotx_b200.synth_q8_0(n, k, 51)
+    n2, k2 = 900, 768
+    w2 = aotx_b200.synth_q8_0(n2, k2, 52)
+    x = inputs(m, k, 53)
+    y = np.zeros((m, n), np.float32)
+    api.lib.api_emu_l2_bytes()
+    assert api.lib.aotx_q8_hint_next(api.ctx, w2.ctypes.data, n2, k2, m) == OK
+    api.matmul(w, n, k, x, y)
+    asked = api.lib.api_emu_l2_bytes()
+    # 32 MiB over six emulated SMs is more than every block's whole share: all of w2 once
+    assert asked == pieces_bytes(n2, k2, m, 10 ** 9, 6) == n2 * (k2 // 32) * 34
+    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
+    api.matmul(w, n, k, x, y)
+    assert api.lib.api_emu_l2_bytes() == 0                      # used once
+    # consumed by a product of another kind (the any-shape kernel asks for nothing)
+    assert api.lib.aotx_q8_hint_next(api.ctx, w2.ctypes.data, n2, k2, m) == OK
+    w96 = aotx_b200.synth_q8_0(20, 96, 1)
+    api.matmul(w96, 20, 96, inputs(5, 96, 2), np.zeros((5, 20), np.float32))
+    api.matmul(w, n, k, x, y)
+    assert api.lib.api_emu_l2_bytes() == 0
+    # a following product the tensor-core kernel does not take: no requests
+    assert api.lib.aotx_q8_hint_next(api.ctx, w96.ctypes.data, 20, 96, 5) == OK
+    api.matmul(w, n, k, x, y)
+    assert api.lib.api_emu_l2_bytes() == 0
+    assert api.lib.aotx_q8_hint_next(None, w2.ctypes.data, n2, k2, m) == ERR_ARGUMENT
+
+
+def test_dequantisation_of_every_block_type(api, oracle):
+    import aotx_b200
+    from oracle.binding import row_bytes
+    rows, k, first = 33, 512, 5
+    w = aotx_b200.synth_q8_0(rows + first + 1, k, 70)
+    out = np.full((rows + 1, k), 0x7777, np.uint16)
+    assert api.lib.aotx_q8_dequant(api.ctx, None, w.ctypes.data, Q8_0, k, first, rows, out.ctypes.data) == OK
+    api.clean()
+    want = np.asarray(oracle.dequant(w, k, first, rows)).view(np.uint16).reshape(rows, k)
+    assert np.array_equal(out[:rows], want) and (out[rows:] == 0x7777).all()
+    rng = np.random.default_rng(71)
+    for kind in sorted(_blocks.TYPES):
+        n = 10
+        blocks = _blocks.random_rows(kind, n, k, rng)
+        out = np.full((7, k), 0x7777, np.uint16)
+        assert api.lib.aotx_q8_dequant(api.ctx, None, blocks.ctypes.data, kind, k, 3, 6, out.ctypes.data) == OK
+        api.clean()
+        ideal = oracle.block_rows(kind, blocks, k, 3, 6)
+        have = out[:6].view(np.float16).astype(np.float64)
+        err = np.abs(have - ideal)
+        assert ((err <= np.abs(ideal) * 9.765625e-04) | (err <= 5.9604644775390625e-08)).all(), kind
+        assert (out[6:] == 0x7777).all()
+        # and the product over that type
+        x = inputs(9, k, 72 + kind)
+        y = np.full((10, n), GUARD, np.float32)
+        api.matmul(blocks, n, k, x, y, kind=kind, m=9)
+        want = x.astype(np.float64) @ oracle.block_rows(kind, blocks, k, 0, n).T
+        assert oracle.diff(y[:9], want)[0] == 0 and (y[9:] == GUARD).all(), kind
+    assert api.lib.aotx_q8_dequant(api.ctx, None, w.ctypes.data, 9, k, 0, 1, out.ctypes.data) == ERR_TYPE
