@@ -34,6 +34,41 @@ inline cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, unsigned 
 #endif
 }
 
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
+// `two_per_sm`: also ask for all of the SM's configurable memory as shared memory, so that two
+// blocks of the kernel fit on one SM.
+template <typename Kernel>
+inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask,
+                                       bool two_per_sm = false)
+{
+#ifdef Q8_HOST_EMULATION
+    (void)kernel;
+    (void)bytes;
+    (void)done_mask;
+    (void)two_per_sm;
+    return cudaSuccess;
+#else
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        return err;
+    }
+    const unsigned long long bit = 1ull << (device & 63);
+    if ((*done_mask & bit) == 0ull) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err == cudaSuccess && two_per_sm) {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                       cudaSharedmemCarveoutMaxShared);
+        }
+        if (err != cudaSuccess) {
+            return err;
+        }
+        *done_mask |= bit;
+    }
+    return cudaSuccess;
+#endif
+}
+
 // y dtype codes as in the public header: 0 float, 1 half, 2 bfloat16.
 
 // What a product does with a finished sum (the epilogue codes of the public header).

@@ -378,14 +378,10 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
     if (smem > 160u * 1024u) {
         return cudaErrorInvalidValue;
     }
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(q8_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               160 * 1024);
-        if (err != cudaSuccess) {
-            return err;
-        }
-        configured = true;
+    static unsigned long long configured = 0ull;
+    cudaError_t err = allow_shared_memory(q8_route_kernel, 160u * 1024u, &configured);
+    if (err != cudaSuccess) {
+        return err;
     }
     return launch_kernel(q8_route_kernel, grid, Q8_ROUTE_THREADS, smem, stream, static_cast<const __half *>(x), router,
                          tokens, tokens_dev, hidden, experts, used, prob, ids);

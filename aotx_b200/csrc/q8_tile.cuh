@@ -526,41 +526,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     }
 }
 
-// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
-// `two_per_sm`: also ask for all of the SM's configurable memory as shared memory, so that two
-// blocks of the kernel fit on one SM.
-template <typename Kernel>
-inline cudaError_t allow_shared_memory(Kernel kernel, unsigned int bytes, unsigned long long *done_mask,
-                                       bool two_per_sm = false)
-{
-#ifdef Q8_HOST_EMULATION
-    (void)kernel;
-    (void)bytes;
-    (void)done_mask;
-    (void)two_per_sm;
-    return cudaSuccess;
-#else
-    int device = 0;
-    cudaError_t err = cudaGetDevice(&device);
-    if (err != cudaSuccess) {
-        return err;
-    }
-    const unsigned long long bit = 1ull << (device & 63);
-    if ((*done_mask & bit) == 0ull) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (err == cudaSuccess && two_per_sm) {
-            err = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                       cudaSharedmemCarveoutMaxShared);
-        }
-        if (err != cudaSuccess) {
-            return err;
-        }
-        *done_mask |= bit;
-    }
-    return cudaSuccess;
-#endif
-}
-
 // Launch with or without the programmatic-dependent-launch attribute.  In the tests' host
 // emulation the blocks run as host threads instead (emulate_grid, q8_launch.h).
 template <typename Kernel>

@@ -271,3 +271,113 @@ def test_dequantisation_of_every_block_type(api, oracle):
         want = x.astype(np.float64) @ oracle.block_rows(kind, blocks, k, 0, n).T
         assert oracle.diff(y[:9], want)[0] == 0 and (y[9:] == GUARD).all(), kind
     assert api.lib.aotx_q8_dequant(api.ctx, None, w.ctypes.data, 9, k, 0, 1, out.ctypes.data) == ERR_TYPE
+
+
+def moe_case(tokens, experts, used, hidden, ffn, seed):
+    import aotx_b200
+    wg = aotx_b200.synth_q8_0(experts * ffn, hidden, seed)
+    wu = aotx_b200.synth_q8_0(experts * ffn, hidden, seed + 1)
+    wd = aotx_b200.synth_q8_0(experts * hidden, ffn, seed + 2)
+    rng = np.random.Generator(np.random.PCG64(seed + 3))
+    x = rng.standard_normal((tokens, hidden)).astype(np.float16)
+    router = (rng.standard_normal((experts, hidden)) / np.sqrt(hidden)).astype(np.float32)
+    return wg, wu, wd, x, router
+
+
+@pytest.mark.parametrize("tokens,experts,used,hidden,ffn", [(40, 5, 2, 256, 256), (5, 4, 2, 96, 64)])
+def test_routed_expert_step_through_the_abi(api, oracle, tokens, experts, used, hidden, ffn):
+    """Router, then the feed-forward step on the grouped tensor-core path (first shape) or on the
+    per-pair kernels (second shape, which the grouped products do not take), the interleaved
+    form, and the ordered sum alone."""
+    import aotx_b200
+    wg, wu, wd, x, router = moe_case(tokens, experts, used, hidden, ffn, 200 + tokens)
+    prob = np.full((tokens + 1, experts), GUARD, np.float32)
+    ids = np.full((tokens + 1, used), 0xFFFFFFFF, np.uint32)
+    assert api.lib.aotx_q8_moe_route(api.ctx, None, x.ctypes.data, router.ctypes.data, tokens, None, hidden, experts,
+                                     used, prob.ctypes.data, ids.ctypes.data) == OK
+    api.clean()
+    want_p, want_i = oracle.route(x.view(np.uint16), router, used)
+    assert np.abs(prob[:tokens] - want_p).max() < 2e-6 and np.array_equal(ids[:tokens], want_i)
+    assert (prob[tokens:] == GUARD).all() and (ids[tokens:] == 0xFFFFFFFF).all()
+    prob, ids = np.ascontiguousarray(prob[:tokens]), np.ascontiguousarray(ids[:tokens])
+    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
+    space = api.workspace(tokens, used, hidden, ffn)
+
+    def ffn_call(expect=OK, space=space, size=None):
+        out = np.full((tokens + 1, hidden), GUARD, np.float32)
+        code = api.lib.aotx_q8_moe_ffn(api.ctx, None, wg.ctypes.data, wu.ctypes.data, wd.ctypes.data, Q8_0, experts,
+                                       hidden, ffn, x.ctypes.data, prob.ctypes.data, ids.ctypes.data, tokens, None,
+                                       used, out.ctypes.data, F32, api.ptr(space),
+                                       space.size if size is None else size)
+        assert code == expect, code
+        api.clean()
+        return out
+
+    out = ffn_call()
+    ok, err, bound = oracle.within_bound(out[:tokens], want.astype(np.float64))
+    assert ok, (err, bound)
+    assert (out[tokens:] == GUARD).all()
+    # workspace checks
+    ffn_call(expect=ERR_WORKSPACE, size=space.size - 1)
+    ffn_call(expect=ERR_WORKSPACE, space=None, size=0)
+    if hidden % 256 == 0 and ffn % 256 == 0:
+        both = aotx_b200.interleave_rows(wg, wu, hidden, groups=experts)
+        out = np.full((tokens + 1, hidden), GUARD, np.float32)
+        assert api.lib.aotx_q8_moe_ffn_fused(api.ctx, None, both.ctypes.data, wd.ctypes.data, Q8_0, experts, hidden,
+                                             ffn, x.ctypes.data, prob.ctypes.data, ids.ctypes.data, tokens, None,
+                                             used, out.ctypes.data, F32, space.ctypes.data, space.size) == OK
+        api.clean()
+        ok, err, bound = oracle.within_bound(out[:tokens], want.astype(np.float64))
+        assert ok, (err, bound)
+        assert (out[tokens:] == GUARD).all()
+    else:
+        both = np.zeros(16, np.uint8)
+        out = np.zeros((tokens, hidden), np.float32)
+        assert api.lib.aotx_q8_moe_ffn_fused(api.ctx, None, both.ctypes.data, wd.ctypes.data, Q8_0, experts, hidden,
+                                             ffn, x.ctypes.data, prob.ctypes.data, ids.ctypes.data, tokens, None,
+                                             used, out.ctypes.data, F32, space.ctypes.data,
+                                             space.size) == ERR_UNSUPPORTED
+    # the ordered sum alone, bit for bit
+    rng = np.random.default_rng(5)
+    proj = rng.standard_normal((tokens, used, hidden)).astype(np.float32)
+    out = np.zeros((tokens, hidden), np.float32)
+    assert api.lib.aotx_q8_moe_combine(api.ctx, None, proj.ctypes.data, prob.ctypes.data, ids.ctypes.data, tokens,
+                                       None, hidden, experts, used, out.ctypes.data, F32) == OK
+    api.clean()
+    exact = oracle.ordered_sum(np.ascontiguousarray(proj.transpose(1, 0, 2)), prob, ids)
+    assert np.array_equal(out.view(np.uint32), exact.view(np.uint32))
+
+
+def test_entry_point_without_a_context(api, oracle):
+    import aotx_b200
+    n, k, m = 300, 1024, 20
+    w = aotx_b200.synth_q8_0(n, k, 61)
+    x = inputs(m, k, 62)
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    for _ in range(2):
+        y = np.full((m + 1, n), GUARD, np.float32)
+        assert api.lib.aotx_q8_matmul_static(None, w.ctypes.data, Q8_0, n, k, x.ctypes.data, F16, m, None,
+                                             y.ctypes.data, F32) == OK
+        assert api.lib.api_emu_status() == 0
+        assert oracle.diff(y[:m], want)[0] == 0 and (y[m:] == GUARD).all()
+    big = inputs(65, k, 63)
+    y = np.zeros((65, n), np.float32)
+    assert api.lib.aotx_q8_matmul_static(None, w.ctypes.data, Q8_0, n, k, big.ctypes.data, F16, 65, None,
+                                         y.ctypes.data, F32) != OK            # more rows than its scratch holds
+
+
+def test_column_split_entry_point(api, oracle):
+    import aotx_b200
+    n, k, m, width, col0 = 300, 1024, 20, 900, 300
+    w = aotx_b200.synth_q8_0(n, k, 71)
+    x = inputs(m, k, 72)
+    mine = np.full((m + 1, width), GUARD, np.float32)
+    theirs = np.full((m + 1, width), GUARD, np.float32)
+    table = (C.c_void_p * 2)(mine.ctypes.data, theirs.ctypes.data)
+    assert api.lib.aotx_q8_matmul_peers(api.ctx, None, w.ctypes.data, Q8_0, n, k, x.ctypes.data, F16, m, None, table,
+                                        2, width, col0, F32) == OK
+    api.clean()
+    want = oracle.product(w, n, k, x.view(np.uint16), m)
+    for y in (mine, theirs):
+        assert oracle.diff(y[:m, col0:col0 + n], want)[0] == 0
+        assert (y[:m, :col0] == GUARD).all() and (y[:m, col0 + n:] == GUARD).all() and (y[m:] == GUARD).all()
