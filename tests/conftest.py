@@ -13,6 +13,9 @@ def pytest_addoption(parser):
     parser.addoption("--fake-device", action="store_true",
                      help="check the GPU tests themselves on a machine without a GPU: the context "
                           "is replaced by a CPU stand-in built on the oracle (tests/_fake.py)")
+    parser.addoption("--emulated-device", action="store_true",
+                     help="run the GPU tests without a GPU against the library's own code, compiled "
+                          "as host code around stand-ins for the hardware (tests/_emulated.py); slow")
 
 
 def pytest_configure(config):
@@ -21,6 +24,10 @@ def pytest_configure(config):
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
         import _fake
         _fake.install()
+    if config.getoption("--emulated-device"):
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        import _emulated
+        _emulated.install()
 
 
 @pytest.fixture(scope="session")
