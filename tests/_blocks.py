@@ -52,7 +52,7 @@ class HostDecoder:
         nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
         path = os.path.join(str(build_dir), "libblocks_host.so")
         done = subprocess.run(
-            [nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-gencode",
+            [nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC,-fno-strict-aliasing", "-gencode",
              "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "aotx_b200", "csrc"), "-o", path,
              os.path.join(ROOT, "tests", "blocks_host.cu")], capture_output=True, text=True, timeout=900)
         assert done.returncode == 0, done.stderr[-2000:]

@@ -31,7 +31,7 @@ def emulated_library():
     from aotx_b200 import library
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     path = os.path.join(tempfile.mkdtemp(prefix="aotx_emulated_"), "libapi_emu.so")
-    done = subprocess.run([nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-gencode",
+    done = subprocess.run([nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC,-fno-strict-aliasing", "-gencode",
                            "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "aotx_b200", "csrc"),
                            "-I", os.path.join(ROOT, "tests"), "-o", path, os.path.join(ROOT, "tests", "api_emu.cu")],
                           capture_output=True, text=True, timeout=1800)

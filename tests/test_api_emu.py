@@ -72,7 +72,7 @@ def api(tmp_path_factory):
     if not os.path.exists(nvcc):
         pytest.skip("no nvcc")
     path = str(tmp_path_factory.mktemp("emu") / "libapi_emu.so")
-    done = subprocess.run([nvcc, "-O1", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-gencode",
+    done = subprocess.run([nvcc, "-O1", "-std=c++17", "-shared", "-Xcompiler", "-fPIC,-fno-strict-aliasing", "-gencode",
                            "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "aotx_b200", "csrc"),
                            "-I", os.path.join(ROOT, "tests"), "-o", path, os.path.join(ROOT, "tests", "api_emu.cu")],
                           capture_output=True, text=True, timeout=1200)

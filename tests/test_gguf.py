@@ -541,7 +541,7 @@ def test_upload_logic_dry_run(tmp_path):
         pytest.skip("no nvcc")
     path = str(tmp_path / "libgguf_dry.so")
     csrc = os.path.join(ROOT, "aotx_b200", "csrc")
-    subprocess.run([nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-diag-suppress", "174",
+    subprocess.run([nvcc, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC,-fno-strict-aliasing", "-diag-suppress", "174",
                     "-gencode", "arch=compute_100a,code=sm_100a", "-include",
                     os.path.join(ROOT, "tests", "gguf_dry.h"), "-o", path,
                     os.path.join(csrc, "gguf_table.cpp"), os.path.join(csrc, "gguf_upload.cu")],
