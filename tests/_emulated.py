@@ -77,6 +77,7 @@ def install():
     fake = _fake.FakeTorch()
     aotx_b200.Q8Context = EmulatedContext
     q8.Q8Context = EmulatedContext
+    aotx_b200.load_library = emulated_library      # tests that call the C ABI directly
     aotx_b200.gguf.GGUFLoader = _fake.FakeLoader
     _util.torch_mod = lambda: fake
     _util.dev = lambda array, device="cpu": real_torch.from_numpy(np.ascontiguousarray(array))

@@ -19,6 +19,12 @@ class FakeCuda:
     def is_available():
         return True
 
+    @staticmethod
+    def current_stream(*args, **kwargs):
+        class Stream:
+            cuda_stream = 0
+        return Stream()
+
 
 class FakeTorch:
     """torch with the device arguments taken out."""
