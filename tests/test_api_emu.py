@@ -284,7 +284,7 @@ def moe_case(tokens, experts, used, hidden, ffn, seed):
     return wg, wu, wd, x, router
 
 
-@pytest.mark.parametrize("tokens,experts,used,hidden,ffn", [(40, 5, 2, 256, 256), (5, 4, 2, 96, 64)])
+@pytest.mark.parametrize("tokens,experts,used,hidden,ffn", [(24, 5, 2, 256, 256), (5, 4, 2, 96, 64)])
 def test_routed_expert_step_through_the_abi(api, oracle, tokens, experts, used, hidden, ffn):
     """Router, then the feed-forward step on the grouped tensor-core path (first shape) or on the
     per-pair kernels (second shape, which the grouped products do not take), the interleaved
