@@ -85,10 +85,7 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
         return AOTX_Q8_ERR_UNSUPPORTED;
     }
     ctx->sm_count = (unsigned int)sms;
-    ctx->scratch.blocks = ctx->sm_count;
-#ifdef Q8_EXPERIMENT
-    ctx->scratch.blocks = 2u * ctx->sm_count; /* the two-blocks-per-SM kernel (q8_duo.cu) */
-#endif
+    ctx->scratch.blocks = 2u * ctx->sm_count; /* the decode kernel runs two blocks per SM */
     ctx->scratch.tile_floats = 128ull * kMaxTokenTile;
     size_t partial_bytes = 2u * (size_t)ctx->scratch.blocks * ctx->scratch.tile_floats * sizeof(float);
     size_t flag_bytes = 2u * (size_t)ctx->scratch.blocks * 4u * sizeof(unsigned int);

@@ -95,6 +95,9 @@ struct UmmaArgs {
     unsigned int next_segs;
     unsigned int next_tok_tiles;
     unsigned int next_units;
+    // Decode kernel (q8_decode.cu): nonzero when the launch is one cluster of blocks per weight
+    // row tile, each block taking one run of the tile's segments; zero for the unit schedule.
+    unsigned int split;
 #ifdef Q8_SWITCHES
     const unsigned char *w; // the weights as a plain pointer (debug & 16: a block warms L2 with its own first units)
     // 1: no weight copies, 2: no conversion, 4: no MMA, 8: no x copies, 16: see `w`,
@@ -350,6 +353,54 @@ __device__ __forceinline__ TilePlace tile_place(const UmmaArgs &args, uint32_t t
     return place;
 }
 
+// What the owner of a tile does with `COUNT` finished sums of one row of w (one column j of y),
+// for the rows first_row .. first_row + COUNT - 1 of x: store them, add them to the float y
+// holds, or - with rows 2p and 2p+1 of w the gate and up rows of output column p - store
+// silu(gate) * up in column p.  Every lane of the warp calls this together (the gated unit
+// exchanges values between neighbouring lanes).  `lane_row` is the row within the tile.
+template <uint32_t COUNT, typename YT>
+__device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                            uint32_t j, uint32_t first_row, uint32_t (&v)[COUNT])
+{
+    YT *y = static_cast<YT *>(args.y);
+    const bool swiglu = args.epilogue == kEpilogueSwiglu;
+    if (swiglu) {
+        // Gate and up sums of one output column sit in neighbouring lanes.  The arithmetic is
+        // that of the separate kernel (cuda/model/norm.cu:92-105).
+#pragma unroll
+        for (uint32_t i = 0; i < COUNT; ++i) {
+            const float mine = __uint_as_float(v[i]);
+            const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1u);
+            const float unit = mine / (1.0f + expf(-mine));
+            v[i] = __float_as_uint(unit * other);
+        }
+    }
+    const bool writes = j < place.j_limit && (!swiglu || (lane_row & 1u) == 0u);
+    const uint32_t col = swiglu ? ((args.col0 + j) >> 1) : (args.col0 + j);
+    if (writes) {
+        const uint32_t copies = args.peers == 0u ? 1u : args.peers;
+        for (uint32_t peer = 0; peer < copies; ++peer) {
+            YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
+#pragma unroll
+            for (uint32_t i = 0; i < COUNT; ++i) {
+                const uint32_t row_x = first_row + i;
+                if (row_x < place.i_limit) {
+                    const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
+                    const size_t at = (size_t)row_y * args.ldy + col;
+                    if (args.epilogue == kEpilogueAdd) {
+                        // y is the float residual stream: one rounded add, as the separate
+                        // kernel does it (cuda/model/norm.cu:78-89)
+                        float *sum = reinterpret_cast<float *>(out) + at;
+                        *sum = *sum + __uint_as_float(v[i]);
+                    } else {
+                        store_out<YT>(out, at, __uint_as_float(v[i]));
+                    }
+                }
+            }
+        }
+    }
+}
+
 // PAIRS: the owner of a cut tile keeps the partial sums of two blocks in flight at a time (the
 // kernels with 128 registers a thread); without it one block's at a time, the same additions
 // in the same order.
@@ -363,7 +414,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                                                uint32_t acc_empty_bar)
 {
     constexpr uint32_t kChunk = NTOK < 32 ? 16 : 32;
-    YT *y = static_cast<YT *>(args.y);
     const TilePlace place = tile_place<NTOK>(args, tile, tok_tiles, m);
     const uint32_t lane_row = wq * 32u + lane;
     const uint32_t j = place.j0 + lane_row;              // row of w = column of y
@@ -455,43 +505,7 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                     v[i] = __float_as_uint(sum);
                 }
             }
-            const bool swiglu = args.epilogue == kEpilogueSwiglu;
-            if (swiglu) {
-                // Gate and up sums of one output column sit in neighbouring lanes (every lane of
-                // the warp is here: the branch conditions above are the same for the whole warp).
-                // The arithmetic is that of the separate kernel (cuda/model/norm.cu:92-105).
-#pragma unroll
-                for (uint32_t i = 0; i < kChunk; ++i) {
-                    const float mine = __uint_as_float(v[i]);
-                    const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1u);
-                    const float unit = mine / (1.0f + expf(-mine));
-                    v[i] = __float_as_uint(unit * other);
-                }
-            }
-            const bool writes = j < place.j_limit && (!swiglu || (lane_row & 1u) == 0u);
-            const uint32_t col = swiglu ? ((args.col0 + j) >> 1) : (args.col0 + j);
-            if (writes) {
-                const uint32_t copies = args.peers == 0u ? 1u : args.peers;
-                for (uint32_t peer = 0; peer < copies; ++peer) {
-                    YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
-#pragma unroll
-                    for (uint32_t i = 0; i < kChunk; ++i) {
-                        const uint32_t row_x = i0 + c0 + i;
-                        if (row_x < place.i_limit) {
-                            const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
-                            const size_t at = (size_t)row_y * args.ldy + col;
-                            if (args.epilogue == kEpilogueAdd) {
-                                // y is the float residual stream: one rounded add, as the
-                                // separate kernel does it (cuda/model/norm.cu:78-89)
-                                float *sum = reinterpret_cast<float *>(out) + at;
-                                *sum = *sum + __uint_as_float(v[i]);
-                            } else {
-                                store_out<YT>(out, at, __uint_as_float(v[i]));
-                            }
-                        }
-                    }
-                }
-            }
+            store_chunk<kChunk, YT>(args, place, lane_row, j, i0 + c0, v);
         }
     }
 #ifdef Q8_TRACE
@@ -531,12 +545,14 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
 template <typename Kernel>
 inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned int smem_bytes,
                                       cudaStream_t stream, bool overlap, const CUtensorMap &tw,
-                                      const CUtensorMap &tx, const UmmaArgs &args, unsigned int threads = kThreads)
+                                      const CUtensorMap &tx, const UmmaArgs &args, unsigned int threads = kThreads,
+                                      unsigned int cluster = 0u)
 {
 #ifdef Q8_HOST_EMULATION
     (void)smem_bytes;
     (void)stream;
     (void)overlap;
+    (void)cluster;
     emulate_grid(dim3(grid, 1, 1), threads, [&] { kernel(tw, tx, args); });
     return cudaSuccess;
 #else
@@ -545,11 +561,23 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
     config.blockDim = dim3(threads, 1, 1);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attribute[2];
+    unsigned int count = 0;
+    if (overlap) {
+        attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    if (cluster > 1u) {
+        // `cluster` consecutive blocks run together and reach each other's shared memory
+        attribute[count].id = cudaLaunchAttributeClusterDimension;
+        attribute[count].val.clusterDim.x = cluster;
+        attribute[count].val.clusterDim.y = 1;
+        attribute[count].val.clusterDim.z = 1;
+        ++count;
+    }
     config.attrs = attribute;
-    config.numAttrs = overlap ? 1 : 0;
+    config.numAttrs = count;
     return cudaLaunchKernelEx(&config, kernel, tw, tx, args);
 #endif
 }
@@ -557,6 +585,14 @@ inline cudaError_t launch_tile_kernel(Kernel kernel, unsigned int grid, unsigned
 // Host launcher of the decode-regime kernel (q8_stream.cu), token tiles 16..128.
 cudaError_t launch_stream_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                  const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
+
+// Host launcher of the decode kernel for batches of up to 32 rows (q8_decode.cu) and the choice
+// of its grid: a cluster of `*cluster` blocks per weight row tile, or (0) the unit schedule.
+unsigned int decode_grid(unsigned int row_tiles, unsigned int segs, unsigned int sm_count,
+                         unsigned int scratch_blocks, unsigned int *cluster);
+cudaError_t launch_decode_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
+                                 const UmmaArgs &args, unsigned int grid, unsigned int cluster, unsigned int ntok,
+                                 int y_dtype);
 
 // Host launcher of the two-blocks-per-SM form of the decode-regime kernel (q8_duo.cu), token
 // tiles 16 and 32; `grid` may be up to twice the number of SMs.

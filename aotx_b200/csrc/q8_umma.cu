@@ -479,15 +479,11 @@ unsigned int umma_token_tile(unsigned int m)
     if (m <= 64u) {
         return 64u;
     }
-    // Batches above 128 rows run as several token tiles of 128 on the decode-regime kernel.
-    // The 256-row kernel below is not dispatched: repeated launches of it on the same inputs
-    // differed in a fraction of a percent of the outputs (whole rows of a weight tile), which
-    // points at a race in its shared-memory rings that is not found yet.
-#ifdef Q8_EXPERIMENT
-    if (m > 128u && getenv("Q8_WIDE_TILE") != nullptr) {
+    // Batches above 128 rows run on the 256-row kernel with the weights in tensor memory
+    // (q8_wide.cu), one token tile of 256 rows at a time.
+    if (m > 128u) {
         return 256u;
     }
-#endif
     return 128u;
 }
 
@@ -661,20 +657,24 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
         return launch_duo_kernel(stream, tw, tx, args, duo_grid, ntok, y_dtype);
     }
 #endif
+    if (ntok <= 32u) {
+        // one token tile: the decode kernel, two blocks per SM (q8_decode.cu)
+        unsigned int cluster = 0u;
+        const unsigned int decode_blocks = decode_grid((unsigned int)row_tiles, k / kSegK, sm_count,
+                                                       scratch.blocks, &cluster);
+        args.split = cluster;
+        return launch_decode_kernel(stream, tw, tx, args, decode_blocks, cluster, ntok, y_dtype);
+    }
     if (ntok <= 128u) {
         return launch_stream_kernel(stream, tw, tx, args, grid, ntok, y_dtype);
     }
 #ifdef Q8_EXPERIMENT
-    {
-        // Q8_WIDE_TILE=2: the 256-row kernel with the weights in tensor memory (q8_wide.cu);
-        // any other value: the one with both operands in shared memory (above)
-        const char *env = getenv("Q8_WIDE_TILE");
-        if (env != nullptr && atoi(env) == 2) {
-            return launch_wide_kernel(stream, tw, tx, args, grid, y_dtype);
-        }
+    if (getenv("Q8_WIDE_TILE") != nullptr && atoi(getenv("Q8_WIDE_TILE")) == 1) {
+        // the first 256-row form, both operands in shared memory (above): not dispatched
+        return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
     }
 #endif
-    return launch_tile<256>(stream, tw, tx, args, grid, y_dtype);
+    return launch_wide_kernel(stream, tw, tx, args, grid, y_dtype);
 }
 
 cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,

@@ -264,3 +264,119 @@ class Reference:
     def same(self, w, n, k, first, rows, got):
         return self.lib.ref_same(np.ascontiguousarray(w), n, k, first, rows,
                                  np.ascontiguousarray(got, np.uint16).reshape(-1))
+
+
+class ReferenceExperts:
+    """The reference's routed-expert kernels run on a CUDA device (`_ref/libaotx_ref.so`:
+    cuda/model/experts.cu, expert_matrix.cu, norm.cu compiled unmodified; launchers in
+    ref_wrap.cu).  Device memory comes from torch.  The checker of the routed-expert oracle and
+    the second baseline of the benchmark's routed-expert workload; never on the product path."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.ref = Reference()
+        if not self.ref.available:
+            raise RuntimeError("the reference library is not built")
+        lib = self.ref.lib
+        self.lib = lib
+        P, U = C.c_void_p, C.c_uint32
+        lib.ref_gpu_moe_install.restype = C.c_int
+        lib.ref_gpu_moe_install.argtypes = [U, U, U, U, U, P, P, P, P, P, P, P, P, P]
+        lib.ref_gpu_moe_route.restype = C.c_int
+        lib.ref_gpu_moe_route.argtypes = [U, P]
+        lib.ref_gpu_moe_matrix.restype = C.c_int
+        lib.ref_gpu_moe_matrix.argtypes = [U, P, U, U, P, P, U, P]
+        lib.ref_gpu_moe_add.restype = C.c_int
+        lib.ref_gpu_moe_add.argtypes = [U, U, P]
+        lib.ref_gpu_moe_ffn.restype = C.c_int
+        lib.ref_gpu_moe_ffn.argtypes = [P, P, P, U, U, U, P, P, P, P, P, U, P]
+
+    def _dev(self, array):
+        return self.torch.from_numpy(np.ascontiguousarray(array)).cuda()
+
+    def _check(self, code, what):
+        if code != 0:
+            raise RuntimeError("%s: CUDA error %d" % (what, code))
+
+    def install(self, hidden, ffn, experts, used, tokens, router=None, x=None, prob=None, ids=None,
+                gate=None, up=None, act=None, proj=None, total=None):
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        self._check(self.lib.ref_gpu_moe_install(hidden, ffn, experts, used, tokens, ptr(router), ptr(x),
+                                                 ptr(prob), ptr(ids), ptr(gate), ptr(up), ptr(act),
+                                                 ptr(proj), ptr(total)), "install")
+
+    def route(self, x, router, used, grid=None):
+        torch = self.torch
+        tokens, hidden = x.shape
+        experts = router.shape[0]
+        xd, rd = self._dev(x.view(np.uint16).view(np.int16)), self._dev(router)
+        prob = torch.zeros(tokens, experts, dtype=torch.float32, device="cuda")
+        ids = torch.full((tokens, used), -1, dtype=torch.int32, device="cuda")
+        self.install(hidden, 0, experts, used, tokens, router=rd, x=xd, prob=prob, ids=ids)
+        self._check(self.lib.ref_gpu_moe_route(grid or tokens, None), "route")
+        torch.cuda.synchronize()
+        return prob.cpu().numpy(), ids.cpu().numpy().view(np.uint32)
+
+    def ordered_sum(self, proj, prob, ids):
+        """proj [used][tokens][hidden]; one add launch per rank as tests/expert_test.cu:164-187."""
+        torch = self.torch
+        used, tokens, hidden = proj.shape
+        experts = prob.shape[1]
+        pd = self._dev(prob)
+        idd = self._dev(ids.view(np.int32))
+        buf = torch.zeros(tokens, hidden, dtype=torch.float32, device="cuda")
+        total = torch.zeros(tokens, hidden, dtype=torch.float32, device="cuda")
+        self.install(hidden, 0, experts, used, tokens, prob=pd, ids=idd, proj=buf, total=total)
+        for rank in range(used):
+            buf.copy_(self._dev(proj[rank]))
+            self._check(self.lib.ref_gpu_moe_add(rank, 7, None), "add")
+        torch.cuda.synchronize()
+        return total.cpu().numpy()
+
+    def expert_matrix(self, w, n, k, x, ids, rank, experts):
+        torch = self.torch
+        tokens = x.shape[0]
+        used = ids.shape[1]
+        wd = self._dev(w)
+        xd = self._dev(x.view(np.uint16).view(np.int16))
+        idd = self._dev(ids.view(np.int32))
+        y = torch.zeros(tokens, n, dtype=torch.float32, device="cuda")
+        self.install(0, 0, experts, used, tokens, ids=idd)
+        self._check(self.lib.ref_gpu_moe_matrix(rank, wd.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(),
+                                                tokens + 2 if tokens == 1 else 7, None), "matrix")
+        torch.cuda.synchronize()
+        return y.cpu().numpy()
+
+    def ffn_buffers(self, wg, wu, wd, experts, hidden, ffn, x, router, used):
+        """Device tensors of a whole routed step, installed; returns a dict of them."""
+        torch = self.torch
+        tokens = x.shape[0]
+        f32 = dict(dtype=torch.float32, device="cuda")
+        b = {"wg": self._dev(wg), "wu": self._dev(wu), "wd": self._dev(wd),
+             "x": self._dev(x.view(np.uint16).view(np.int16)), "router": self._dev(router),
+             "prob": torch.zeros(tokens, experts, **f32),
+             "ids": torch.zeros(tokens, used, dtype=torch.int32, device="cuda"),
+             "gate": torch.zeros(tokens, ffn, **f32), "up": torch.zeros(tokens, ffn, **f32),
+             "act": torch.zeros(tokens, ffn, dtype=torch.float16, device="cuda"),
+             "proj": torch.zeros(tokens, hidden, **f32), "sum": torch.zeros(tokens, hidden, **f32)}
+        self.install(hidden, ffn, experts, used, tokens, router=b["router"], x=b["x"], prob=b["prob"],
+                     ids=b["ids"], gate=b["gate"], up=b["up"], act=b["act"], proj=b["proj"], total=b["sum"])
+        b["shape"] = (tokens, experts, used, hidden, ffn)
+        return b
+
+    def launch_step(self, b, stream=None):
+        """Route and the per-rank loop of cuda/model/experts_host.cu:96-111 on installed buffers."""
+        tokens, experts, used, hidden, ffn = b["shape"]
+        self._check(self.lib.ref_gpu_moe_route(tokens, stream), "route")
+        self._check(self.lib.ref_gpu_moe_ffn(b["wg"].data_ptr(), b["wu"].data_ptr(), b["wd"].data_ptr(),
+                                             hidden, ffn, used, b["x"].data_ptr(), b["gate"].data_ptr(),
+                                             b["up"].data_ptr(), b["act"].data_ptr(), b["proj"].data_ptr(),
+                                             tokens, stream), "expert loop")
+
+    def ffn(self, wg, wu, wd, experts, hidden, ffn, x, router, used):
+        b = self.ffn_buffers(wg, wu, wd, experts, hidden, ffn, x, router, used)
+        self.launch_step(b)
+        self.torch.cuda.synchronize()
+        return {"prob": b["prob"].cpu().numpy(), "ids": b["ids"].cpu().numpy().view(np.uint32),
+                "sum": b["sum"].cpu().numpy(), "act": b["act"].cpu().numpy().view(np.uint16)}

@@ -16,6 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libq8_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libaotx_ref.so")
+REF_MODULE = os.path.join(REF_DIR, "gemv_q8.cubin")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -37,19 +38,23 @@ def build_oracle(force=False):
 
 
 def reference_root():
-    root = os.environ.get("AOTX_REFERENCE_ROOT", "/root/reference")
+    """The reference tree: AOTX_REFERENCE_ROOT, else a directory `reference` beside this
+    repository.  None when neither holds the reference's matrix test."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    root = os.environ.get("AOTX_REFERENCE_ROOT", beside)
     probe = os.path.join(root, "tests", "matrix_test.cu")
     return root if os.path.exists(probe) else None
 
 
 def build_ref(force=False):
-    """Compile the reference's matrix kernels and host checks, unmodified, for sm_100a."""
+    """Compile the reference's matrix and routed-expert kernels and host checks, unmodified, for
+    sm_100a, and assemble its single-row PTX module (ptx/gemv_q8.ptx) into `_ref/gemv_q8.cubin`."""
     root = reference_root()
     if root is None or shutil.which("nvcc") is None:
         return REF_SO if os.path.exists(REF_SO) else None
     wrap = os.path.join(HERE, "ref_wrap.cu")
     stubs = os.path.join(HERE, "ref_stubs.c")
-    if not force and _newer(REF_SO, [wrap, stubs]):
+    if not force and _newer(REF_SO, [wrap, stubs]) and os.path.exists(REF_MODULE):
         return REF_SO
     os.makedirs(REF_DIR, exist_ok=True)
     stub_obj = os.path.join(REF_DIR, "ref_stubs.o")
@@ -61,8 +66,11 @@ def build_ref(force=False):
            '-DAOTX_PTX_DIR="%s"' % os.path.join(root, "ptx"),
            "-o", REF_SO, wrap,
            os.path.join(model, "gemv.cu"), os.path.join(model, "gemm.cu"),
-           os.path.join(model, "dequant.cu"), stub_obj]
+           os.path.join(model, "dequant.cu"), os.path.join(model, "experts.cu"),
+           os.path.join(model, "expert_matrix.cu"), os.path.join(model, "norm.cu"), stub_obj]
     subprocess.run(cmd, check=True)
+    subprocess.run(["ptxas", "-arch=sm_100a", "-o", REF_MODULE, os.path.join(root, "ptx", "gemv_q8.ptx")],
+                   check=True)
     return REF_SO
 
 

@@ -53,3 +53,46 @@ def check_product(oracle, w, n, k, x_bits, m, y, bf16=False, full_limit=6e9, spo
     bad, worst = oracle.spot(w, n, k, x_bits, m, y, count=spots, bf16=bf16)
     assert bad == 0, "spot check: %d of %d over 1e-2, worst %.3e" % (bad, spots, worst)
     return worst
+
+
+def device_synth_q8_0(n, k, seed):
+    """Seeded synthetic Q8_0 rows in the benchmark's distribution, generated on the device (the
+    large tensors of the sharded configurations take seconds there and minutes on the host).
+    Returns the device tensor (256-byte aligned) of n * (k / 32) * 34 bytes."""
+    torch = torch_mod()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    blocks = k // 32
+    t = torch.empty(n * blocks * 34 + 256, dtype=torch.uint8, device="cuda")
+    off = (-t.data_ptr()) % 256
+    out = t[off:off + n * blocks * 34].view(n, blocks, 34)
+    step = max(1, (1 << 28) // k)
+    for r0 in range(0, n, step):
+        r1 = min(n, r0 + step)
+        q = torch.randint(-127, 128, (r1 - r0, blocks, 32), dtype=torch.int8, device="cuda", generator=gen)
+        d = (torch.randn((r1 - r0, blocks), device="cuda", generator=gen).abs() * (0.02 / 127.0)).half()
+        out[r0:r1, :, 2:] = q.view(torch.uint8)
+        out[r0:r1, :, :2] = d.view(torch.uint8).view(r1 - r0, blocks, 2)
+    return out.view(-1)
+
+
+def check_columns(oracle, w_host, n, k, x_bits, m, y, bf16=True, columns=192, seed=77):
+    """Whole columns of a large product against the oracle: `columns` sampled weight rows, every
+    row of x.  Applies the reference's measure |err| / max(|want|, rms(want)) <= 1e-2
+    (tests/matrix_test.cu:246-274) and the bound max|err| <= 1e-2 * max|y_ref| + 1e-3.  This is
+    the check for products whose weights are rounded to bfloat16 (bfloat16 activations above
+    128 rows): the reference's sampled measure (tests/matrix_test.cu:279-312) has a floor for
+    small sums that assumes binary16 weights."""
+    from oracle.binding import row_bytes
+    rng = np.random.Generator(np.random.PCG64(seed))
+    picks = np.sort(rng.permutation(n)[:min(columns, n)])
+    stride = row_bytes(k)
+    piece = np.concatenate([w_host[j * stride:(j + 1) * stride] for j in picks])
+    want = oracle.product(piece, len(picks), k, x_bits, m, bf16=bf16)
+    got = np.ascontiguousarray(np.asarray(y, np.float32)[:, picks])
+    assert np.isfinite(got).all()
+    bad, worst = oracle.diff(got, want)
+    ok, err, bound = oracle.within_bound(got, want)
+    assert bad == 0, "reference measure: %d over 1e-2, worst %.3e" % (bad, worst)
+    assert ok, "max err %.3e over bound %.3e" % (err, bound)
+    return worst

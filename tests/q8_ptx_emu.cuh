@@ -525,4 +525,24 @@ inline void st_release_gpu(unsigned int *p, uint32_t v)
     reinterpret_cast<std::atomic<unsigned int> *>(p)->store(v, std::memory_order_release);
 }
 
+// Clusters are not modelled: the emulated blocks run one after another, so the library never
+// picks a cluster launch in this build, and a block is a cluster of its own.
+inline uint32_t cluster_ctarank() { return 0u; }
+inline uint32_t cluster_nctarank() { return 1u; }
+inline void cluster_arrive_release() {}
+inline void cluster_wait_acquire() {}
+inline uint32_t mapa_shared(uint32_t addr, uint32_t) { return addr; }
+
+inline void st_shared_cluster_f32(uint32_t addr, float v)
+{
+    std::memcpy(q8emu::shared_at(addr), &v, sizeof v);
+}
+
+inline float ld_shared_f32(uint32_t addr)
+{
+    float v;
+    std::memcpy(&v, q8emu::shared_at(addr), sizeof v);
+    return v;
+}
+
 } // namespace q8

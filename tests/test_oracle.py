@@ -1,6 +1,7 @@
 """The oracle restatement against the reference: golden fixtures (anywhere) and the
 reference's own host functions compiled from its sources (where that library was built)."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -197,3 +198,44 @@ def test_expert_matrix_slices(oracle):
             # the slice check keeps the product un-rounded; the product reference rounds the
             # weight to half first: they agree to the half rounding
             assert np.all(np.abs(y[t] - want[0]) <= 6e-4 * mag[t] + 1e-12)
+
+
+def test_routed_experts_against_reference_kernel_outputs(oracle):
+    """The routed-expert half of the oracle against what the reference's own kernels produced on
+    a GPU (tests/golden/reference_moe.npz, written by tests/golden/make_golden_moe.py from
+    cuda/model/experts.cu, expert_matrix.cu and norm.cu compiled unmodified), with the
+    reference's own tolerances (tests/expert_test.cu:131-150, 164-178, 309-319)."""
+    import _moe_cases as cases
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_moe.npz")
+    if not os.path.exists(path):
+        pytest.skip("golden file not written yet")
+    gold = dict(np.load(path))
+    for tokens, experts, used, precision in cases.ROUTE_CASES:
+        router, x = cases.route_fixture(tokens, experts, precision)
+        tag = "route_%d_%d_%d_%d" % (tokens, experts, used, precision)
+        prob, ids = oracle.route(x.view(np.uint16), router, used)
+        assert np.array_equal(ids, gold[tag + "_ids"])
+        assert np.abs(prob - gold[tag + "_prob"]).max() < 2e-6
+        assert np.array_equal(oracle.rank(gold[tag + "_prob"], used), gold[tag + "_ids"])
+        proj = cases.add_fixture(tokens, used)
+        got = oracle.ordered_sum(proj, gold[tag + "_prob"], gold[tag + "_ids"])
+        assert np.array_equal(got.view(np.uint32), gold[tag + "_sum"].view(np.uint32))
+    c = cases.SLICE_CASE
+    for tokens in (1, 64):
+        w, x, ids = cases.slice_fixture(tokens)
+        for rank in range(c["used"]):
+            want, mag = oracle.expert_matrix(w, c["n"], c["k"], x.view(np.uint16), ids, rank)
+            assert (np.abs(gold["slice_%d" % tokens][rank] - want) <= 2e-6 * mag + 2e-5).all()
+    for name in cases.FFN_CASES:
+        (tokens, experts, used, hidden, ffn), wg, wu, wd, x, router = cases.ffn_fixture(name)
+        prob, ids = gold["ffn_%s_prob" % name], gold["ffn_%s_ids" % name]
+        want_p, want_i = oracle.route(x.view(np.uint16), router, used)
+        assert np.array_equal(ids, want_i)
+        assert np.abs(prob - want_p).max() < 2e-6
+        keep = np.arange(tokens) if name == "small" else gold["ffn_full_tokens"][:4]
+        want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, np.ascontiguousarray(x[keep]).view(np.uint16),
+                              np.ascontiguousarray(prob[keep]), np.ascontiguousarray(ids[keep]))
+        ref_sum = gold["ffn_small_sum"] if name == "small" else gold["ffn_full_sum"][:4]
+        ok, err, bound = oracle.within_bound(ref_sum, want.astype(np.float64))
+        assert ok, (name, err, bound)
+        assert oracle.diff(ref_sum, want.astype(np.float64))[0] == 0
