@@ -64,6 +64,14 @@ __device__ __forceinline__ uint32_t dequant_pair_bf16(uint32_t flipped, float d)
     return cvt_bf16x2_rn(q.y * d, q.x * d);
 }
 
+// Two bfloat16 values in one word become two binary16 values (same rule as below).
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w)
+{
+    const float lo = __uint_as_float(w << 16);
+    const float hi = __uint_as_float(w & 0xFFFF0000u);
+    return cvt_f16x2_rn_sat(hi, lo);
+}
+
 // Eight bfloat16 values in shared memory become eight binary16 values in place.  Every
 // bfloat16 of magnitude between 2^-14 and 65504 converts exactly; larger ones saturate to the
 // largest half, smaller ones round to the half subnormals.
@@ -94,16 +102,20 @@ __device__ __forceinline__ __half dequant_one(int q, __half d)
 // end with a wrong result rather than holding the GPU.
 #define Q8_WAIT_CYCLES 4000000000ll /* about two seconds of SM clock */
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          unsigned int *status)
+// Out of line on purpose: a kernel has dozens of waits, and a short launch fetches its code cold
+// at its start and again at its end, so the call sites have to stay small.
+static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                              unsigned int *status)
 {
     // The common case: the phase completes within a few thousand polls; no clock is read.
+#pragma unroll 1
     for (uint32_t spin = 0; spin < 4096u; ++spin) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
     }
     const long long begin = clock64();
+#pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) {
             return true;
@@ -124,6 +136,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+
+// The same wait for the hot loops (the converters, which hold a row of raw bytes in registers
+// across it): the polls are inline, so that no call - and with it no save and restore of the
+// live registers through local memory - lies on the path that is taken every time.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                              unsigned int *status)
+{
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < 64u; ++spin) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return mbar_wait(bar, parity, abort_flag, status);
+}
 
 // ---------------------------------------------------------------------------------------
 // Bulk tensor copies (TMA), global -> shared, no multicast.

@@ -19,15 +19,24 @@
 //     the owner fetches and adds them while its own last MMAs still run.
 //
 // Inside a block (11 warps): warp 8 issues bulk tensor copies of raw weight segments
-// [128 rows x 272 B] into a two-deep ring; warps 4-7 are converters, thread = row: nine 16-byte
-// shared loads per half segment, exact dequantisation in registers, tcgen05.st of 64 packed
-// words into the thread's lane of tensor memory; warp 10 issues tcgen05.mma 128 x NTOK x 16 with
-// A from tensor memory and B = the x tile in shared memory (128-byte swizzle); warp 9 copies x
-// tiles and turns a bfloat16 x tile into binary16 where it lies (one MMA takes both operands
-// in one format; exact for magnitudes in [2^-14, 65504], saturating above); warps 0-3 read the
-// accumulator and store.  The schedule never depends on the live batch (one token tile), so the
-// batch word is read only by the storing warps, after the launches before this one finished.
-// Every wait on a barrier or flag is bounded and raises a status bit when it runs out.
+// [128 rows x 272 B] into a two-deep ring; warps 0-7 are converters, thread = row, warps 4-7 for
+// the first half of every 256-weight segment and warps 0-3 for the second: nine 16-byte shared
+// loads, exact dequantisation in registers, tcgen05.st of 64 packed words into the thread's lane
+// of tensor memory; warp 10 issues tcgen05.mma 128 x NTOK x 16 with A from tensor memory and
+// B = the x tile in shared memory (128-byte swizzle), and first turns a bfloat16 x tile into
+// binary16 where it lies (one MMA takes both operands in one format; exact for magnitudes in
+// [2^-14, 65504], saturating above); warp 9 copies x tiles.  Warps 0-3 also read a finished
+// accumulator and store: between two segments they look whether the MMAs of the piece before
+// have completed, so the conversion never waits for a store.  The schedule never depends on the
+// live batch (one token tile), so the batch word is read only when storing, after the launches
+// before this one finished.  Every wait on a barrier or flag is bounded and raises a status bit
+// when it runs out.
+//
+// A short launch fetches its code cold, at its start and again at its end, so the code is kept
+// small: the accumulator is read and stored in chunks of 8 columns inside ordinary loops, the
+// store with every option (add, gated unit, several output buffers, row map) is one out-of-line
+// function beside a short inline path for the plain store, and the slow part of a wait is out of
+// line too.
 //
 // Reference kernels replaced: ptx/gemv_q8.ptx:18-223, cuda/model/gemv.cuh:33-145 (and the
 // three-node switch of cuda/model/graph_host.cu:31-39 for these batches).
@@ -61,7 +70,7 @@ struct DecodeShape {
     static constexpr uint32_t x_offset = 0;
     static constexpr uint32_t raw_offset = x_offset + x_depth * x_seg_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
-    static constexpr uint32_t bar_count = 2 * raw_stages + 3 * x_depth + 2 * a_stages + 4 + 1;
+    static constexpr uint32_t bar_count = 2 * raw_stages + 2 * x_depth + 2 * a_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
     // what a block receives from the other blocks of its cluster lies over the x ring, which is
     // idle by then: per sending block its share of the token columns, 128 floats each
@@ -74,16 +83,142 @@ struct DecodeShape {
                   "two accumulators, then the A pieces, in half of the tensor memory");
 };
 
-// The accumulator of one piece into registers: NTOK columns of this thread's lane.
-template <int NTOK>
-__device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[NTOK])
-{
-    if (NTOK == 32) {
-        tmem_ld_32x32(taddr, v);
-    } else {
-        tmem_ld_32x16(taddr, v);
+#ifdef Q8_TRACE
+#define Q8_STAMP(slot, cond)                                                         \
+    if (args.trace != nullptr && (cond)) {                                           \
+        unsigned long long t_;                                                       \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
+        args.trace[blockIdx.x * 8u + (slot)] = t_;                                   \
     }
-    tmem_ld_wait();
+#else
+#define Q8_STAMP(slot, cond)
+#endif
+
+// The store with every option, once per kernel instance (see store_chunk in q8_tile.cuh).
+template <typename YT>
+static __device__ __noinline__ void store_eight_any(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                                    uint32_t j, uint32_t first_row, uint32_t (&v)[8])
+{
+    store_chunk<8u, YT>(args, place, lane_row, j, first_row, v);
+}
+
+// Eight finished sums of column j of y, rows first_row .. first_row + 7 of x.
+template <typename YT>
+__device__ __forceinline__ void store_eight(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                            uint32_t j, uint32_t first_row, uint32_t (&v)[8])
+{
+    if (args.epilogue == kEpilogueStore && args.peers == 0u && args.row_map == nullptr) {
+        if (j < place.j_limit) {
+            YT *y = static_cast<YT *>(args.y);
+#pragma unroll
+            for (uint32_t i = 0; i < 8u; ++i) {
+                if (first_row + i < place.i_limit) {
+                    store_out<YT>(y, (size_t)(first_row + i) * args.ldy + j, __uint_as_float(v[i]));
+                }
+            }
+        }
+        return;
+    }
+    store_eight_any<YT>(args, place, lane_row, j, first_row, v);
+}
+
+template <typename YT>
+static __device__ __noinline__ void store_one_any(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                                  uint32_t j, uint32_t row, float value)
+{
+    uint32_t one[1] = {__float_as_uint(value)};
+    store_chunk<1u, YT>(args, place, lane_row, j, row, one);
+}
+
+template <typename YT>
+__device__ __forceinline__ void store_one(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                          uint32_t j, uint32_t row, float value)
+{
+    if (args.epilogue == kEpilogueStore && args.peers == 0u && args.row_map == nullptr) {
+        if (j < place.j_limit && row < place.i_limit) {
+            store_out<YT>(static_cast<YT *>(args.y), (size_t)row * args.ldy + j, value);
+        }
+        return;
+    }
+    store_one_any<YT>(args, place, lane_row, j, row, value);
+}
+
+// The units of block b of `blocks`, `units` in all (32-bit arithmetic: the first `units mod
+// blocks` blocks take one unit more), and the block that holds unit `u`.
+__host__ __device__ __forceinline__ void decode_range(uint32_t b, uint32_t blocks, uint32_t units,
+                                                      uint32_t *begin, uint32_t *end)
+{
+    const uint32_t q = units / blocks;
+    const uint32_t rem = units - q * blocks;
+    *begin = b * q + (b < rem ? b : rem);
+    *end = *begin + q + (b < rem ? 1u : 0u);
+}
+
+__host__ __device__ __forceinline__ uint32_t decode_holder(uint32_t u, uint32_t blocks, uint32_t units)
+{
+    const uint32_t q = units / blocks;
+    const uint32_t rem = units - q * blocks;
+    const uint32_t cut = rem * (q + 1u);
+    return u < cut ? u / (q + 1u) : rem + (u - cut) / q;
+}
+
+// Barriers and buffers of a block, as shared-space addresses.
+struct DecodeRings {
+    uint32_t x_base, raw_base;
+    uint32_t raw_full, raw_empty, x_land, x_empty, a_full, a_empty, acc_full, acc_empty;
+};
+
+// One unit (a 256-weight segment of the block's 128 rows), half H of it: this thread's row from
+// the raw ring into registers, exact dequantisation, 64 packed words into the thread's lane of
+// the A stage.  The four warps of a half hand the stage over together.  The hand-over of a
+// stage is deferred to the next call (`pending` holds its barrier, 0 for none): the stores into
+// tensor memory then complete while the next raw row is being fetched, instead of holding up
+// the warp after every half segment.  convert_flush hands over the last one.
+__device__ __forceinline__ void convert_flush(uint32_t &pending, uint32_t lane)
+{
+    if (pending != 0u) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0u) {
+            mbar_arrive(pending);
+        }
+        pending = 0u;
+    }
+}
+
+template <int NTOK, int H>
+__device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, uint32_t row, uint32_t lane,
+                                             uint32_t lane_base, uint32_t &pending,
+                                             volatile uint32_t *abort_flag, unsigned int *status)
+{
+    using S = DecodeShape<NTOK>;
+    const uint32_t rst = g % S::raw_stages;
+    const uint32_t rph = (g / S::raw_stages) & 1u;
+    if (!mbar_wait_hot(r.raw_full + 8u * rst, rph, abort_flag, status)) {
+        return false;
+    }
+    uint32_t raw[36];
+    load_raw<H>(r.raw_base + rst * kRawStageBytes + row * kSegBytes, raw);
+    // the stage before this one is complete by now: hand it to the MMA thread
+    convert_flush(pending, lane);
+    // this half is in registers: as far as this warp goes, the raw segment may be overwritten
+    __syncwarp();
+    if (lane == 0u) {
+        mbar_arrive(r.raw_empty + 8u * rst);
+    }
+    const uint32_t hh = 2u * g + (uint32_t)H;
+    const uint32_t st = hh % S::a_stages;
+    const uint32_t ph = (hh / S::a_stages) & 1u;
+    if (!mbar_wait_hot(r.a_empty + 8u * st, ph ^ 1u, abort_flag, status)) {
+        return false;
+    }
+    const uint32_t taddr = lane_base + st * S::a_stage_columns;
+    tc_fence_after_sync();
+    convert_stage_tmem<H, 0, false>(raw, taddr);
+    convert_stage_tmem<H, 1, false>(raw, taddr + kSubK / 2u);
+    pending = r.a_full + 8u * st;
+    return true;
 }
 
 template <int NTOK, typename YT>
@@ -94,19 +229,19 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     using S = DecodeShape<NTOK>;
     extern __shared__ unsigned char smem_raw_[];
     const uint32_t smem0 = (smem_u32(smem_raw_) + 1023u) & ~1023u;
-    const uint32_t x_base = smem0 + S::x_offset;
-    const uint32_t raw_base = smem0 + S::raw_offset;
+    DecodeRings r;
+    r.x_base = smem0 + S::x_offset;
+    r.raw_base = smem0 + S::raw_offset;
     const uint32_t bar_base = smem0 + S::bar_offset;
-    const uint32_t raw_full = bar_base;
-    const uint32_t raw_empty = raw_full + 8u * S::raw_stages;
-    const uint32_t x_land = raw_empty + 8u * S::raw_stages;  // the copy of an x segment is complete
-    const uint32_t x_full = x_land + 8u * S::x_depth;        // ... and it is binary16
-    const uint32_t x_empty = x_full + 8u * S::x_depth;
-    const uint32_t a_full = x_empty + 8u * S::x_depth;
-    const uint32_t a_empty = a_full + 8u * S::a_stages;
-    const uint32_t acc_full = a_empty + 8u * S::a_stages;
-    const uint32_t acc_empty = acc_full + 16u;
-    const uint32_t drain_bar = acc_empty + 16u;
+    r.raw_full = bar_base;
+    r.raw_empty = r.raw_full + 8u * S::raw_stages;
+    r.x_land = r.raw_empty + 8u * S::raw_stages;  // the copy of an x segment is complete
+    r.x_empty = r.x_land + 8u * S::x_depth;
+    r.a_full = r.x_empty + 8u * S::x_depth;
+    r.a_empty = r.a_full + 8u * S::a_stages;
+    r.acc_full = r.a_empty + 8u * S::a_stages;
+    r.acc_empty = r.acc_full + 16u;
+    const uint32_t drain_bar = r.acc_empty + 16u;
     const uint32_t tmem_slot = drain_bar + 8u;
     unsigned char *generic0 = smem_raw_ + (smem0 - smem_u32(smem_raw_));
     volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(generic0 + (tmem_slot - smem0));
@@ -114,6 +249,7 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
+    Q8_STAMP(0u, threadIdx.x == 0u)
 
     // The next kernel on the stream may start its blocks beside this one's.  Work that only
     // reads the weights runs ahead of the kernels before this one; everything that reads x or
@@ -122,45 +258,46 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t segs = args.k / kSegK;
     const uint32_t row_tiles = (args.n + kRows - 1u) / kRows;
-    const unsigned long long units = (unsigned long long)row_tiles * segs;
+    const uint32_t units = row_tiles * segs; // the host refuses products with 2^31 units or more
     const bool split = args.split != 0u;
     uint32_t crank = 0u;
     uint32_t csize = 1u;
-    unsigned int blocks = gridDim.x;
-    unsigned long long u_begin, u_end;
+    uint32_t blocks = gridDim.x;
+    uint32_t u_begin, u_end;
     if (split) {
         // one tile per cluster, one run of its segments per block
         csize = cluster_nctarank();
         crank = cluster_ctarank();
-        const unsigned long long tile = blockIdx.x / csize;
-        u_begin = tile * segs + (unsigned long long)crank * segs / csize;
-        u_end = tile * segs + (unsigned long long)(crank + 1u) * segs / csize;
+        const uint32_t tile = blockIdx.x / csize;
+        u_begin = tile * segs + crank * segs / csize;
+        u_end = tile * segs + (crank + 1u) * segs / csize;
     } else {
         // No more blocks than units take part, so that every block in the schedule has work.
-        blocks = units < gridDim.x ? (unsigned int)units : gridDim.x;
+        blocks = units < gridDim.x ? units : gridDim.x;
         if (blockIdx.x >= blocks) {
             return;
         }
-        unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
+        decode_range(blockIdx.x, blocks, units, &u_begin, &u_end);
     }
+    const uint32_t tile_begin = u_begin / segs;      // the tile and segment of the first unit
+    const uint32_t seg_begin = u_begin - tile_begin * segs;
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
-            mbar_init(raw_full + 8u * i, 1u);
-            mbar_init(raw_empty + 8u * i, kDecConvertWarps);
+            mbar_init(r.raw_full + 8u * i, 1u);
+            mbar_init(r.raw_empty + 8u * i, 2u * kDecConvertWarps);
         }
         for (uint32_t i = 0; i < S::x_depth; ++i) {
-            mbar_init(x_land + 8u * i, 1u);
-            mbar_init(x_full + 8u * i, 1u);
-            mbar_init(x_empty + 8u * i, 1u);
+            mbar_init(r.x_land + 8u * i, 1u);
+            mbar_init(r.x_empty + 8u * i, 1u);
         }
         for (uint32_t i = 0; i < S::a_stages; ++i) {
-            mbar_init(a_full + 8u * i, kDecConvertWarps);
-            mbar_init(a_empty + 8u * i, 1u);
+            mbar_init(r.a_full + 8u * i, kDecConvertWarps);
+            mbar_init(r.a_empty + 8u * i, 1u);
         }
         for (uint32_t i = 0; i < 2u; ++i) {
-            mbar_init(acc_full + 8u * i, 1u);
-            mbar_init(acc_empty + 8u * i, kEpilogueWarps);
+            mbar_init(r.acc_full + 8u * i, 1u);
+            mbar_init(r.acc_empty + 8u * i, kEpilogueWarps);
         }
         mbar_init(drain_bar, 1u);
         *abort_flag = 0u;
@@ -180,95 +317,60 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    // an x segment is ready for the MMA when its copy landed (binary16) or was turned (bfloat16)
-    const uint32_t x_ready = args.b_bf16 != 0u ? x_full : x_land;
+    Q8_STAMP(1u, threadIdx.x == 0u)
 
-    // In a cluster launch the block's single piece stays in these registers of the storing warps
-    // until the exchange at the end of the kernel.
-    uint32_t vals[NTOK];
     unsigned int m_live = 0u;
 
     if (warp == kDecWeightWarp) {
         // ---------------------------------------------------------------- raw weight copies
         if (lane == 0u) {
             uint32_t g = 0;
-            bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end;) {
-                const uint32_t tile = (uint32_t)(u / segs);
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t w_row = tile * kRows;
-                for (uint32_t s = s0; s < s1; ++s, ++g) {
-                    const uint32_t st = g % S::raw_stages;
-                    const uint32_t ph = (g / S::raw_stages) & 1u;
-                    if (!mbar_wait(raw_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(raw_full + 8u * st, kRawStageBytes);
-                    tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
-                                (int)(s * kSegWords), (int)w_row);
+            uint32_t tile = tile_begin;
+            uint32_t s = seg_begin;
+            for (uint32_t u = u_begin; u < u_end; ++u, ++g) {
+                const uint32_t st = g % S::raw_stages;
+                const uint32_t ph = (g / S::raw_stages) & 1u;
+                if (!mbar_wait(r.raw_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
+                    break;
                 }
-                u += (s1 - s0);
+                mbar_expect_tx(r.raw_full + 8u * st, kRawStageBytes);
+                tma_load_2d(r.raw_base + st * kRawStageBytes, &tmap_w, r.raw_full + 8u * st,
+                            (int)(s * kSegWords), (int)(tile * kRows));
+                if (++s == segs) {
+                    s = 0u;
+                    ++tile;
+                }
             }
             // Let every copy this thread started land before the block ends.
             uint32_t local_abort = 0;
             const uint32_t first = g > S::raw_stages ? g - S::raw_stages : 0u;
             for (uint32_t i = first; i < g; ++i) {
-                mbar_wait(raw_full + 8u * (i % S::raw_stages), (i / S::raw_stages) & 1u, &local_abort,
+                mbar_wait(r.raw_full + 8u * (i % S::raw_stages), (i / S::raw_stages) & 1u, &local_abort,
                           nullptr);
             }
         }
     } else if (warp == kDecInputWarp) {
         // ---------------------------------------------------------------- x copies
-        // Lane 0 keeps the copies of two segments in flight; for bfloat16 activations the whole
-        // warp then turns each landed segment into binary16 where it lies (the swizzle moves
-        // whole 16-byte chunks, so the conversion is chunk by chunk whatever the layout).
-        const uint32_t total = (uint32_t)(u_end - u_begin);
-        const uint32_t first_seg = (uint32_t)(u_begin % segs);
+        const uint32_t total = u_end - u_begin;
+        uint32_t next_seg = seg_begin;
         uint32_t issued = 0;
-        bool ok = true;
-        grid_dependency_wait();
-        for (uint32_t g = 0; ok && g < total; ++g) {
-            if (lane == 0u) {
-                while (ok && issued < total && issued < g + S::x_depth) {
-                    const uint32_t st = issued % S::x_depth;
-                    const uint32_t ph = (issued / S::x_depth) & 1u;
-                    if (!mbar_wait(x_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t s = (first_seg + issued) % segs;
-                    mbar_expect_tx(x_land + 8u * st, S::x_seg_bytes);
-#pragma unroll
-                    for (uint32_t j = 0; j < kSubs; ++j) {
-                        tma_load_2d(x_base + st * S::x_seg_bytes + j * S::x_sub_bytes, &tmap_x, x_land + 8u * st,
-                                    (int)(s * kSegK + j * kSubK), 0);
-                    }
-                    ++issued;
-                }
-            }
-            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
-            if (!ok) {
-                break;
-            }
-            if (args.b_bf16 != 0u) {
-                const uint32_t st = g % S::x_depth;
-                const uint32_t ph = (g / S::x_depth) & 1u;
-                if (!mbar_wait(x_land + 8u * st, ph, abort_flag, args.status)) {
-                    ok = false;
+        if (lane == 0u) {
+            grid_dependency_wait();
+            Q8_STAMP(2u, true)                     // the launches before this one have finished
+            for (; issued < total; ++issued) {
+                const uint32_t st = issued % S::x_depth;
+                const uint32_t ph = (issued / S::x_depth) & 1u;
+                if (!mbar_wait(r.x_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
                     break;
                 }
-                const uint32_t x_seg = x_base + st * S::x_seg_bytes;
-#pragma unroll 4
-                for (uint32_t c = lane; c < S::x_seg_bytes / 16u; c += 32u) {
-                    bf16_chunk_to_f16_inplace(x_seg + 16u * c);
+                mbar_expect_tx(r.x_land + 8u * st, S::x_seg_bytes);
+#pragma unroll
+                for (uint32_t j = 0; j < kSubs; ++j) {
+                    tma_load_2d(r.x_base + st * S::x_seg_bytes + j * S::x_sub_bytes, &tmap_x, r.x_land + 8u * st,
+                                (int)(next_seg * kSegK + j * kSubK), 0);
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0u) {
-                    mbar_arrive(x_full + 8u * st);
+                if (++next_seg == segs) {
+                    next_seg = 0u;
                 }
             }
         }
@@ -277,41 +379,67 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             uint32_t local_abort = 0;
             const uint32_t first = issued > S::x_depth ? issued - S::x_depth : 0u;
             for (uint32_t i = first; i < issued; ++i) {
-                mbar_wait(x_land + 8u * (i % S::x_depth), (i / S::x_depth) & 1u, &local_abort, nullptr);
+                mbar_wait(r.x_land + 8u * (i % S::x_depth), (i / S::x_depth) & 1u, &local_abort, nullptr);
             }
         }
     } else if (warp == kDecMmaWarp) {
         // ---------------------------------------------------------------- MMA issue
-        if (lane == 0u) {
-            const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
-            uint32_t g = 0;
-            uint32_t tc = 0;
-            bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t buf = tc & 1u;
-                const uint32_t aph = (tc >> 1) & 1u;
-                if (!mbar_wait(acc_empty + 8u * buf, aph ^ 1u, abort_flag, args.status)) {
+        // Lane 0 issues the MMAs.  For bfloat16 activations the whole warp first turns the x
+        // segment into binary16 where it lies (the swizzle moves whole 16-byte chunks, so the
+        // conversion is chunk by chunk whatever the layout); the MMAs it issued for the segment
+        // before run on the tensor core meanwhile.
+        const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
+        uint32_t g = 0;
+        uint32_t tc = 0;
+        uint32_t s0 = seg_begin;
+        bool ok = true;
+        for (uint32_t u = u_begin; ok && u < u_end; ++tc) {
+            const uint32_t left = u_end - u;
+            const uint32_t s1 = (segs - s0) < left ? segs : s0 + left;
+            const uint32_t buf = tc & 1u;
+            const uint32_t aph = (tc >> 1) & 1u;
+            const uint32_t d_tmem = tmem_base + buf * (uint32_t)NTOK;
+            uint32_t accumulate = 0u;
+            for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
+                const uint32_t xst = g % S::x_depth;
+                const uint32_t xph = (g / S::x_depth) & 1u;
+                if (!mbar_wait(r.x_land + 8u * xst, xph, abort_flag, args.status)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * (uint32_t)NTOK;
-                uint32_t accumulate = 0u;
-                for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
-                    const uint32_t xst = g % S::x_depth;
-                    const uint32_t xph = (g / S::x_depth) & 1u;
-                    if (!mbar_wait(x_ready + 8u * xst, xph, abort_flag, args.status)) {
-                        ok = false;
-                        break;
+                if (args.b_bf16 != 0u) {
+                    // eight chunks of 16 bytes per lane at a time: the loads go out together, so
+                    // their latency is paid once per batch and not once per chunk
+                    const uint32_t x_seg = r.x_base + xst * S::x_seg_bytes + 16u * lane;
+#pragma unroll 1
+                    for (uint32_t c0 = 0; c0 < S::x_seg_bytes / 16u; c0 += 256u) {
+                        uint32_t w[8][4];
+#pragma unroll
+                        for (uint32_t i = 0; i < 8u; ++i) {
+                            ld_shared_v4(x_seg + 16u * (c0 + 32u * i), w[i][0], w[i][1], w[i][2], w[i][3]);
+                        }
+#pragma unroll
+                        for (uint32_t i = 0; i < 8u; ++i) {
+#pragma unroll
+                            for (uint32_t e = 0; e < 4u; ++e) {
+                                w[i][e] = bf16x2_to_f16x2(w[i][e]);
+                            }
+                            st_shared_v4(x_seg + 16u * (c0 + 32u * i), w[i][0], w[i][1], w[i][2], w[i][3]);
+                        }
                     }
-                    for (uint32_t half = 0; half < 2u; ++half) {
+                    fence_proxy_async_smem();
+                }
+                __syncwarp();
+                if (lane == 0u) {
+                    if (s == s0 && !mbar_wait(r.acc_empty + 8u * buf, aph ^ 1u, abort_flag, args.status)) {
+                        ok = false;
+                    }
+#pragma unroll 1
+                    for (uint32_t half = 0; ok && half < 2u; ++half) {
                         const uint32_t hh = 2u * g + half;
                         const uint32_t st = hh % S::a_stages;
                         const uint32_t ph = (hh / S::a_stages) & 1u;
-                        if (!mbar_wait(a_full + 8u * st, ph, abort_flag, args.status)) {
+                        if (!mbar_wait(r.a_full + 8u * st, ph, abort_flag, args.status)) {
                             ok = false;
                             break;
                         }
@@ -321,7 +449,7 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         for (uint32_t jl = 0; jl < 2u; ++jl) {
                             const uint32_t j = 2u * half + jl;
                             const uint64_t b_desc =
-                                umma_desc_sw128(x_base + xst * S::x_seg_bytes + j * S::x_sub_bytes);
+                                umma_desc_sw128(r.x_base + xst * S::x_seg_bytes + j * S::x_sub_bytes);
 #pragma unroll
                             for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
                                 // 16 values: 8 columns of A, 32 bytes along the swizzled row of x
@@ -330,282 +458,271 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                 accumulate = 1u;
                             }
                         }
-                        umma_commit(a_empty + 8u * st);
+                        umma_commit(r.a_empty + 8u * st);
                     }
                     if (ok) {
-                        umma_commit(x_empty + 8u * xst);
+                        umma_commit(r.x_empty + 8u * xst);
                     }
                 }
-                if (ok) {
-                    umma_commit(acc_full + 8u * buf);
+                // a wait that ran out raised the block's abort flag: every lane leaves together
+                __syncwarp();
+                if (*abort_flag != 0u) {
+                    ok = false;
                 }
-                u += (s1 - s0);
             }
-            if (!ok) {
-                // Outstanding MMAs must finish before the tensor memory goes back.
-                uint32_t local_abort = 0;
-                umma_commit(drain_bar);
-                mbar_wait(drain_bar, 0u, &local_abort, nullptr);
+            if (ok && lane == 0u) {
+                umma_commit(r.acc_full + 8u * buf);
             }
+            u += (s1 - s0);
+            s0 = 0u;
+        }
+        if (!ok && lane == 0u) {
+            // Outstanding MMAs must finish before the tensor memory goes back.
+            uint32_t local_abort = 0;
+            umma_commit(drain_bar);
+            mbar_wait(drain_bar, 0u, &local_abort, nullptr);
         }
     } else if (warp >= kDecConvertWarp0) {
-        // ---------------------------------------------------------------- dequantise
+        // ---------------------------------------------------------------- dequantise, first halves
         const uint32_t cw = warp - kDecConvertWarp0;
         const uint32_t row = cw * 32u + lane;
         // this warp owns TMEM lanes [32 cw, +32): its rows of the tile
         const uint32_t lane_base = tmem_base + ((cw * 32u) << 16) + S::a_column0;
         uint32_t g = 0;
-        bool ok = true;
-        for (unsigned long long u = u_begin; ok && u < u_end; ++u, ++g) {
-            const uint32_t rst = g % S::raw_stages;
-            const uint32_t rph = (g / S::raw_stages) & 1u;
-            if (!mbar_wait(raw_full + 8u * rst, rph, abort_flag, args.status)) {
-                ok = false;
+        uint32_t pending = 0u;
+        for (uint32_t u = u_begin; u < u_end; ++u, ++g) {
+            if (!convert_unit<NTOK, 0>(r, g, row, lane, lane_base, pending, abort_flag, args.status)) {
                 break;
             }
-            const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
-#pragma unroll
-            for (uint32_t half = 0; half < 2u; ++half) {
-                uint32_t raw[36];
-                if (half == 0u) {
-                    load_raw<0>(raw_row, raw);
-                } else {
-                    load_raw<1>(raw_row, raw);
-                    // the second half is in registers: the raw segment may be overwritten
-                    __syncwarp();
-                    if (lane == 0u) {
-                        mbar_arrive(raw_empty + 8u * rst);
-                    }
-                }
-                const uint32_t hh = 2u * g + half;
-                const uint32_t st = hh % S::a_stages;
-                const uint32_t ph = (hh / S::a_stages) & 1u;
-                if (!mbar_wait(a_empty + 8u * st, ph ^ 1u, abort_flag, args.status)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t taddr = lane_base + st * S::a_stage_columns;
-                tc_fence_after_sync();
-                if (half == 0u) {
-                    convert_stage_tmem<0, 0, false>(raw, taddr);
-                    convert_stage_tmem<0, 1, false>(raw, taddr + kSubK / 2u);
-                } else {
-                    convert_stage_tmem<1, 0, false>(raw, taddr);
-                    convert_stage_tmem<1, 1, false>(raw, taddr + kSubK / 2u);
-                }
-                tmem_st_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0u) {
-                    mbar_arrive(a_full + 8u * st);
-                }
-            }
         }
+        convert_flush(pending, lane);
+        Q8_STAMP(3u, cw == 0u && lane == 0u)       // conversion of the block's units done
     } else {
-        // ---------------------------------------------------------------- read sums, store
+        // ------------------------------------------- dequantise, second halves; read sums, store
         const uint32_t wq = warp;
         const uint32_t lane_row = wq * 32u + lane;
         const uint32_t lane_taddr = tmem_base + ((wq * 32u) << 16);
-        grid_dependency_wait();
-        m_live = args.m_max;
-        if (args.m_dev != nullptr) {
-            const unsigned int live = *args.m_dev;
-            m_live = live < m_live ? live : m_live;
-        }
-        if (split) {
-            if (mbar_wait(acc_full, 0u, abort_flag, args.status)) {
-                tc_fence_after_sync();
-                load_accumulator<NTOK>(lane_taddr, vals);
-            } else {
-#pragma unroll
-                for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
-                    vals[i] = 0u;
-                }
+        const uint32_t lane_base = lane_taddr + S::a_column0;
+        // conversion runs ahead of the MMAs; `done` is the first unit of the piece to store next
+        uint32_t u = u_begin;
+        uint32_t done = u_begin;
+        uint32_t tile = tile_begin;   // of the piece to store next
+        uint32_t s0 = seg_begin;
+        uint32_t g = 0;
+        uint32_t tc = 0;
+        uint32_t pending = 0u;
+        bool waited = false;
+        bool ok = true;
+        while (ok) {
+            const bool more = u < u_end;
+            if (!more) {
+                convert_flush(pending, lane);
             }
-            tc_fence_before_sync();
-        } else {
-            uint32_t tc = 0;
-            bool ok = true;
-            for (unsigned long long u = u_begin; ok && u < u_end; ++tc) {
-                const uint32_t tile = (uint32_t)(u / segs);
-                const uint32_t s0 = (uint32_t)(u % segs);
-                const unsigned long long left = u_end - u;
-                const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
+            if (done < u_end && !split) {
                 const uint32_t buf = tc & 1u;
                 const uint32_t aph = (tc >> 1) & 1u;
-                const bool owner = s0 == 0u;
-                const bool whole = owner && s1 == segs;
-                TilePlace place;
-                place.w_row = place.j0 = tile * kRows;
-                place.j_limit = args.n;
-                place.i0 = 0u;
-                place.i_limit = m_live;
-                const uint32_t j = place.j0 + lane_row;
-                unsigned int last_cc = blockIdx.x;
-                float others[NTOK];
-                if (owner && !whole) {
-                    // The other holders of this tile are the blocks right after this one; they
-                    // met it at the start of their ranges.  Fetch and add their partial sums, in
-                    // block order, while this block's own MMAs of the tile still run.
-                    last_cc = last_holder(blockIdx.x, blocks, units, ((unsigned long long)tile + 1ull) * segs);
-                    for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
-                        const unsigned int cc = base + lane;
-                        if (cc <= last_cc) {
-                            const unsigned int *flag = args.flags + 4u * cc + wq;
-                            const long long begin = clock64();
-                            while (ld_acquire_gpu(flag) == 0u) {
-                                if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
-                                    atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
-                                    break;
+                // between two segments only look; with nothing left to convert, wait
+                const bool ready = more ? mbar_test_wait(r.acc_full + 8u * buf, aph) != 0u
+                                        : mbar_wait(r.acc_full + 8u * buf, aph, abort_flag, args.status);
+                if (!ready && !more) {
+                    break;
+                }
+                if (ready) {
+                    if (!waited) {
+                        grid_dependency_wait();
+                        m_live = args.m_max;
+                        if (args.m_dev != nullptr) {
+                            const unsigned int live = *args.m_dev;
+                            m_live = live < m_live ? live : m_live;
+                        }
+                        waited = true;
+                    }
+                    const uint32_t left = u_end - done;
+                    const uint32_t s1 = (segs - s0) < left ? segs : s0 + left;
+                    const bool owner = s0 == 0u;
+                    const bool whole = owner && s1 == segs;
+                    TilePlace place;
+                    place.w_row = place.j0 = tile * kRows;
+                    place.j_limit = args.n;
+                    place.i0 = 0u;
+                    place.i_limit = m_live;
+                    const uint32_t j = place.j0 + lane_row;
+                    unsigned int last_cc = blockIdx.x;
+                    if (owner && !whole) {
+                        // The other holders of this tile are the blocks right after this one; they
+                        // met it at the start of their ranges and have published their partial sums.
+                        last_cc = decode_holder((tile + 1u) * segs - 1u, blocks, units);
+                        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+                            const unsigned int cc = base + lane;
+                            if (cc <= last_cc) {
+                                const unsigned int *flag = args.flags + 4u * cc + wq;
+                                const long long begin = clock64();
+                                while (ld_acquire_gpu(flag) == 0u) {
+                                    if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
+                                        atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
+                                        break;
+                                    }
                                 }
                             }
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
-                    for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; ++cc) {
-                        const float *slot = args.partial + (unsigned long long)cc * args.tile_floats + lane_row;
+                    tc_fence_after_sync();
+                    float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats + lane_row;
+#pragma unroll 1
+                    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
+                        uint32_t v[8];
+                        tmem_ld_32x8(lane_taddr + buf * (uint32_t)NTOK + c0, v);
+                        tmem_ld_wait();
+                        if (!owner) {
 #pragma unroll
-                        for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 16u) {
-                            float a[16];
-#pragma unroll
-                            for (uint32_t i = 0; i < 16u; ++i) {
-                                a[i] = __ldcg(slot + (unsigned long long)(c0 + i) * kRows);
+                            for (uint32_t i = 0; i < 8u; ++i) {
+                                __stcg(own_slot + (unsigned long long)(c0 + i) * kRows, __uint_as_float(v[i]));
                             }
+                        } else {
+                            // add the other blocks' partial sums in block order
+#pragma unroll 1
+                            for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; ++cc) {
+                                const float *slot = args.partial + (unsigned long long)cc * args.tile_floats
+                                                  + (unsigned long long)c0 * kRows + lane_row;
+                                float a[8];
 #pragma unroll
-                            for (uint32_t i = 0; i < 16u; ++i) {
-                                others[c0 + i] = cc == blockIdx.x + 1u ? a[i] : others[c0 + i] + a[i];
+                                for (uint32_t i = 0; i < 8u; ++i) {
+                                    a[i] = __ldcg(slot + (unsigned long long)i * kRows);
+                                }
+#pragma unroll
+                                for (uint32_t i = 0; i < 8u; ++i) {
+                                    v[i] = __float_as_uint(__uint_as_float(v[i]) + a[i]);
+                                }
                             }
+                            store_eight<YT>(args, place, lane_row, j, c0, v);
                         }
                     }
-                }
-                if (!mbar_wait(acc_full + 8u * buf, aph, abort_flag, args.status)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats + lane_row;
-#pragma unroll
-                for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 16u) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(lane_taddr + buf * (uint32_t)NTOK + c0, v);
-                    tmem_ld_wait();
-                    if (!owner) {
-#pragma unroll
-                        for (uint32_t i = 0; i < 16u; ++i) {
-                            __stcg(own_slot + (unsigned long long)(c0 + i) * kRows, __uint_as_float(v[i]));
-                        }
-                    } else {
-                        if (!whole) {
-#pragma unroll
-                            for (uint32_t i = 0; i < 16u; ++i) {
-                                v[i] = __float_as_uint(__uint_as_float(v[i]) + others[c0 + i]);
-                            }
-                        }
-                        store_chunk<16u, YT>(args, place, lane_row, j, c0, v);
-                    }
-                }
-                // The accumulator buffer is free again.
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0u) {
-                    mbar_arrive(acc_empty + 8u * buf);
-                }
-                if (!owner) {
-                    // Publish this warp's quarter of the partial tile; every lane makes its own
-                    // stores visible first.
-                    __threadfence();
+                    // The accumulator buffer is free again.
+                    tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0u) {
-                        st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
+                        mbar_arrive(r.acc_empty + 8u * buf);
                     }
-                } else if (!whole) {
-                    // Hand the consumed slots back for the next launch that uses this set (ordered
-                    // by the end of the kernel).
-                    for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
-                        const unsigned int cc = base + lane;
-                        if (cc <= last_cc) {
-                            *reinterpret_cast<volatile unsigned int *>(args.flags + 4u * cc + wq) = 0u;
+                    if (!owner) {
+                        // Publish this warp's quarter of the partial tile; every lane makes its own
+                        // stores visible first.
+                        __threadfence();
+                        __syncwarp();
+                        if (lane == 0u) {
+                            st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
+                        }
+                    } else if (!whole) {
+                        // Hand the consumed slots back for the next launch that uses this set
+                        // (ordered by the end of the kernel).
+                        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+                            const unsigned int cc = base + lane;
+                            if (cc <= last_cc) {
+                                *reinterpret_cast<volatile unsigned int *>(args.flags + 4u * cc + wq) = 0u;
+                            }
                         }
                     }
+                    done += (s1 - s0);
+                    s0 = 0u;
+                    ++tile;
+                    ++tc;
+                    continue;
                 }
-                u += (s1 - s0);
             }
+            if (!more) {
+                break;
+            }
+            ok = convert_unit<NTOK, 1>(r, g, lane_row, lane, lane_base, pending, abort_flag, args.status);
+            ++u;
+            ++g;
+        }
+        convert_flush(pending, lane);
+        if (split) {
+            // the block's one piece: wait for its MMAs, the exchange below reads the accumulator
+            grid_dependency_wait();
+            m_live = args.m_max;
+            if (args.m_dev != nullptr) {
+                const unsigned int live = *args.m_dev;
+                m_live = live < m_live ? live : m_live;
+            }
+            mbar_wait(r.acc_full, 0u, abort_flag, args.status);
+            tc_fence_after_sync();
+            Q8_STAMP(5u, wq == 0u && lane == 0u)
         }
     }
 
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == kDecMmaWarp) {
-        tc_fence_after_sync();
-        tmem_dealloc(tmem_base, S::tmem_columns);
-    }
     if (!split) {
+        tc_fence_before_sync();
+        __syncthreads();
+        if (warp == kDecMmaWarp) {
+            tc_fence_after_sync();
+            tmem_dealloc(tmem_base, S::tmem_columns);
+        }
+        Q8_STAMP(7u, threadIdx.x == 0u)
         return;
     }
 
     // ------------------------------------------------------------ sum of a cluster's pieces
-    // Token column i of the tile belongs to block (i mod cluster size) of the cluster.  A block
-    // sends every other block that block's columns of its piece, receives its own columns of
-    // theirs, adds them in block order and stores.
-    const uint32_t tile = blockIdx.x / csize;
-    TilePlace place;
-    place.w_row = place.j0 = tile * kRows;
-    place.j_limit = args.n;
-    place.i0 = 0u;
-    place.i_limit = m_live;
-    const uint32_t lane_row = warp * 32u + lane;
-    const uint32_t j = place.j0 + lane_row;
-    if (csize == 1u) {
-        if (warp < kEpilogueWarps) {
-            store_chunk<(uint32_t)NTOK, YT>(args, place, lane_row, j, 0u, vals);
-        }
-        return;
-    }
+    // Token column i of the tile belongs to block (i mod cluster size) of the cluster.  Every
+    // block writes each column of its piece into the owner's shared memory (its own columns
+    // into its own), over the x ring, which is idle once every block's MMAs have finished; the
+    // owner adds the pieces in block order and stores.
     const uint32_t share = ((uint32_t)NTOK + csize - 1u) / csize; // columns per block, at most
-    // every block of the cluster has finished its MMAs: the x rings are free
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
+    Q8_STAMP(4u, threadIdx.x == 0u)
+    const uint32_t lane_row = warp * 32u + lane;
     if (warp < kEpilogueWarps) {
+        const uint32_t lane_taddr = tmem_base + ((warp * 32u) << 16);
         uint32_t owner = 0u;
         uint32_t local = 0u;
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
+            uint32_t v[8];
+            tmem_ld_32x8(lane_taddr + c0, v);
+            tmem_ld_wait();
 #pragma unroll
-        for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
-            if (owner != crank) {
-                const uint32_t at = x_base + ((crank * share + local) * kRows + lane_row) * 4u;
-                st_shared_cluster_f32(mapa_shared(at, owner), __uint_as_float(vals[i]));
-            }
-            if (++owner == csize) {
-                owner = 0u;
-                ++local;
-            }
-        }
-    }
-    __syncwarp();
-    cluster_arrive_release();
-    cluster_wait_acquire();
-    if (warp < kEpilogueWarps) {
-        uint32_t owner = 0u;
-        uint32_t local = 0u;
-#pragma unroll
-        for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
-            if (owner == crank) {
-                float sum = 0.0f;
-                for (uint32_t src = 0; src < csize; ++src) {
-                    const float piece = src == crank
-                        ? __uint_as_float(vals[i])
-                        : ld_shared_f32(x_base + ((src * share + local) * kRows + lane_row) * 4u);
-                    sum = src == 0u ? piece : sum + piece;
+            for (uint32_t i = 0; i < 8u; ++i) {
+                const uint32_t at = r.x_base + ((crank * share + local) * kRows + lane_row) * 4u;
+                st_shared_cluster_f32(mapa_shared(at, owner), __uint_as_float(v[i]));
+                if (++owner == csize) {
+                    owner = 0u;
+                    ++local;
                 }
-                uint32_t one[1] = {__float_as_uint(sum)};
-                store_chunk<1u, YT>(args, place, lane_row, j, i, one);
-            }
-            if (++owner == csize) {
-                owner = 0u;
-                ++local;
             }
         }
+        tc_fence_before_sync();
     }
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    Q8_STAMP(6u, threadIdx.x == 0u)
+    if (warp == kDecMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, S::tmem_columns);
+    }
+    if (warp < kEpilogueWarps) {
+        const uint32_t tile = blockIdx.x / csize;
+        TilePlace place;
+        place.w_row = place.j0 = tile * kRows;
+        place.j_limit = args.n;
+        place.i0 = 0u;
+        place.i_limit = m_live;
+        const uint32_t j = place.j0 + lane_row;
+        uint32_t local = 0u;
+#pragma unroll 1
+        for (uint32_t col = crank; col < (uint32_t)NTOK; col += csize, ++local) {
+            float sum = 0.0f;
+#pragma unroll 1
+            for (uint32_t src = 0; src < csize; ++src) {
+                const float piece = ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u);
+                sum = src == 0u ? piece : sum + piece;
+            }
+            store_one<YT>(args, place, lane_row, j, col, sum);
+        }
+    }
+    Q8_STAMP(7u, threadIdx.x == 0u)
 }
 
 template <int NTOK, typename YT>
@@ -647,9 +764,20 @@ unsigned int decode_grid(unsigned int row_tiles, unsigned int segs, unsigned int
     *cluster = 0u;
 #ifndef Q8_HOST_EMULATION
     if (2u * row_tiles <= sm_count) {
-        unsigned int pieces = sm_count / row_tiles;
-        pieces = pieces > kDecMaxCluster ? kDecMaxCluster : pieces;
+        // two blocks per SM: as many pieces per tile as fill them, each at least one segment
+        unsigned int pieces = 2u * sm_count / row_tiles;
+        unsigned int most = kDecMaxCluster;
+#ifdef Q8_EXPERIMENT
+        if (getenv("Q8_MAX_CLUSTER") != nullptr) {
+            most = (unsigned int)atoi(getenv("Q8_MAX_CLUSTER"));
+        }
+#endif
+        pieces = pieces > most ? most : pieces;
         pieces = pieces > segs ? segs : pieces;
+        // a power of two: clusters of 6 took three times as long to be placed as clusters of 4 or 8
+        while ((pieces & (pieces - 1u)) != 0u) {
+            pieces &= pieces - 1u;
+        }
         *cluster = pieces;
         return row_tiles * pieces;
     }

@@ -82,6 +82,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return done;
 }
 
+// The same question without waiting at all (try_wait may suspend the thread for a while before
+// it answers no).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -194,6 +209,14 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t *v)
           "=r"(v[15])
         : "r"(taddr)
         : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t *v)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 
 // 32 lanes x 32 columns: thread t of the warp writes lane (base lane + t).

@@ -17,6 +17,8 @@
 
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "q8_common.cuh"
 #include "q8_launch.h"
 
@@ -41,6 +43,7 @@ struct StaticDevice {
 };
 
 StaticDevice g_static[Q8_STATIC_DEVICES];
+std::mutex g_static_mutex; // first calls from several host threads set a device up once
 
 // Set-up for the current device: the device address of the array and the SM count.  Runs on
 // the first call on each device (not inside a stream capture: the look-up is not a stream
@@ -56,6 +59,7 @@ cudaError_t static_device(StaticDevice **out)
         return cudaErrorInvalidDevice;
     }
     StaticDevice *slot = &g_static[device];
+    std::lock_guard<std::mutex> guard(g_static_mutex);
     if (!slot->ready) {
         void *address = nullptr;
         err = cudaGetSymbolAddress(&address, q8_static_scratch);
@@ -94,7 +98,7 @@ extern "C" int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type,
                                      const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev, void *y,
                                      int y_dtype)
 {
-    if (type != AOTX_Q8_TYPE_Q8_0) {
+    if (type != AOTX_Q8_TYPE_Q8_0 && !q8::block_type_known(type)) {
         return AOTX_Q8_ERR_TYPE;
     }
     if ((x_dtype != AOTX_Q8_F16 && x_dtype != AOTX_Q8_BF16) || y_dtype < AOTX_Q8_F32 || y_dtype > AOTX_Q8_BF16
@@ -107,6 +111,17 @@ extern "C" int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type,
     }
     if (n == 0u || m == 0u) {
         return AOTX_Q8_OK;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        /* the other block types run on the ordinary cores and use no scratch */
+        if (w == nullptr || x == nullptr || y == nullptr || (k % q8::block_type_run(type)) != 0u
+            || !is_aligned(x, 4u) || !is_aligned(y, y_dtype == AOTX_Q8_F32 ? 4u : 2u)
+            || (m_dev != nullptr && !is_aligned(m_dev, 4u))) {
+            return AOTX_Q8_ERR_ARGUMENT;
+        }
+        cudaError_t err = q8::launch_gemv_any((cudaStream_t)stream, w, type, n, k, x, x_dtype == AOTX_Q8_BF16, m,
+                                              m_dev, y, y_dtype);
+        return err == cudaSuccess ? AOTX_Q8_OK : AOTX_Q8_ERR_CUDA;
     }
     if (w == nullptr || x == nullptr || y == nullptr || !is_aligned(w, 2u) || !is_aligned(x, 4u)
         || !is_aligned(y, y_dtype == AOTX_Q8_F32 ? 4u : 2u) || (m_dev != nullptr && !is_aligned(m_dev, 4u))) {
@@ -136,4 +151,31 @@ extern "C" int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type,
                               y_dtype, 0u, false);
     }
     return err == cudaSuccess ? AOTX_Q8_OK : AOTX_Q8_ERR_CUDA;
+}
+
+extern "C" int aotx_q8_static_status(uint32_t *status, int clear)
+{
+    if (status == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    *status = 0u;
+    StaticDevice *dev = nullptr;
+    if (static_device(&dev) != cudaSuccess) {
+        return AOTX_Q8_ERR_CUDA;
+    }
+    unsigned int *flags = reinterpret_cast<unsigned int *>(dev->base + Q8_STATIC_PARTIAL_BYTES);
+    unsigned int *word = flags + Q8_STATIC_BLOCKS * 4u;
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err == cudaSuccess) {
+        err = cudaMemcpy(status, word, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    }
+    if (err == cudaSuccess && clear && *status != 0u) {
+        /* a launch that was cut short may have left hand-over flags raised: nothing runs now,
+         * so they go back to zero together with the word */
+        err = cudaMemset(flags, 0, (Q8_STATIC_BLOCKS * 4u + 1u) * sizeof(unsigned int));
+    }
+    if (err != cudaSuccess) {
+        return AOTX_Q8_ERR_CUDA;
+    }
+    return *status == 0u ? AOTX_Q8_OK : AOTX_Q8_ERR_DEVICE;
 }

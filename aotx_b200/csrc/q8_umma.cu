@@ -636,10 +636,10 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
         args.w = static_cast<const unsigned char *>(w);
         if (getenv("Q8_TRACE") != nullptr) {
             if (g_trace_base == nullptr) {
-                cudaMalloc((void **)&g_trace_base, 256ull * 160ull * 8ull * 8ull);
-                cudaMemset(g_trace_base, 0, 256ull * 160ull * 8ull * 8ull);
+                cudaMalloc((void **)&g_trace_base, 256ull * 320ull * 8ull * 8ull);
+                cudaMemset(g_trace_base, 0, 256ull * 320ull * 8ull * 8ull);
             }
-            args.trace = g_trace_base + (unsigned long long)(g_trace_launches % 256u) * 160ull * 8ull;
+            args.trace = g_trace_base + (unsigned long long)(g_trace_launches % 256u) * 320ull * 8ull;
             g_trace_launches += 1;
         } else {
             args.trace = nullptr;
@@ -658,10 +658,23 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     }
 #endif
     if (ntok <= 32u) {
-        // one token tile: the decode kernel, two blocks per SM (q8_decode.cu)
+        // one token tile: the decode kernel, two blocks per SM (q8_decode.cu); its unit
+        // arithmetic is 32-bit
+        if (units >= (1ull << 31)) {
+            return cudaErrorNotSupported;
+        }
         unsigned int cluster = 0u;
         const unsigned int decode_blocks = decode_grid((unsigned int)row_tiles, k / kSegK, sm_count,
                                                        scratch.blocks, &cluster);
+#ifdef Q8_EXPERIMENT
+        if (getenv("Q8_NO_SPLIT") != nullptr && cluster != 0u) {
+            cluster = 0u;
+            const unsigned long long all = row_tiles * (k / kSegK);
+            const unsigned int most = 2u * sm_count < scratch.blocks ? 2u * sm_count : scratch.blocks;
+            args.split = 0u;
+            return launch_decode_kernel(stream, tw, tx, args, all < most ? (unsigned int)all : most, 0u, ntok, y_dtype);
+        }
+#endif
         args.split = cluster;
         return launch_decode_kernel(stream, tw, tx, args, decode_blocks, cluster, ntok, y_dtype);
     }
@@ -767,7 +780,7 @@ cudaError_t launch_umma_grouped(cudaStream_t stream, const UmmaScratch &scratch,
 extern "C" unsigned int q8_trace_read(unsigned long long *host)
 {
     if (q8::g_trace_base != nullptr) {
-        cudaMemcpy(host, q8::g_trace_base, 256ull * 160ull * 8ull * 8ull, cudaMemcpyDeviceToHost);
+        cudaMemcpy(host, q8::g_trace_base, 256ull * 320ull * 8ull * 8ull, cudaMemcpyDeviceToHost);
     }
     return q8::g_trace_launches;
 }

@@ -17,7 +17,8 @@ elif os.environ.get("AOTX_Q8_LIBRARY"):
 SYMBOLS = (
     "aotx_q8_init", "aotx_q8_destroy", "aotx_q8_set_path", "aotx_q8_set_overlap", "aotx_q8_last_cuda_error",
     "aotx_q8_device_status", "aotx_q8_dequant", "aotx_q8_matmul", "aotx_q8_moe_route",
-    "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_matmul_peers",
+    "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_static_status",
+    "aotx_q8_matmul_peers",
     "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused", "aotx_q8_hint_next",
 )
 
@@ -84,6 +85,7 @@ def declare_q8(lib):
                                     u32, vp, i32, vp, C.c_size_t]
     lib.aotx_q8_moe_combine.argtypes = [vp, vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, i32]
     lib.aotx_q8_matmul_static.argtypes = [vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32]
+    lib.aotx_q8_static_status.argtypes = [C.POINTER(C.c_uint32), i32]
     lib.aotx_q8_matmul_peers.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), u32,
                                          u32, u32, i32]
     lib.aotx_q8_hint_next.argtypes = [vp, vp, u32, u32, u32]

@@ -230,11 +230,20 @@ int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t
  * AOTX_Q8_ERR_WORKSPACE and enqueues nothing.  It calls no cudaMalloc or cudaFree.  The first
  * call on each device looks the array up (cudaGetSymbolAddress): make that call before any
  * stream capture.  All calls share the array and clear the part that must start at zero; two
- * calls that overlap on the GPU (different streams, no ordering) race on it.
+ * calls that overlap on the GPU (different streams, no ordering) race on it.  First calls made
+ * from several host threads at once are safe (the look-up is under a lock).  The other block
+ * types are served too (they use no scratch).
  * It has no counterpart in the reference. */
 int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type, uint32_t n, uint32_t k,
                           const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev, void *y,
                           int y_dtype);
+
+/* The status word of the fixed array on the current device, the counterpart of
+ * aotx_q8_device_status for aotx_q8_matmul_static: synchronises the device, copies the word to
+ * *status (0 = every wait of every static call ended in time) and, with clear != 0, resets the
+ * word and the hand-over flags a cut-short launch may have left.  Allocates nothing.  Returns
+ * AOTX_Q8_ERR_DEVICE when the word is not zero.  No counterpart in the reference. */
+int aotx_q8_static_status(uint32_t *status, int clear);
 
 #ifdef __cplusplus
 }

@@ -322,6 +322,11 @@ inline uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return done ? 1u : 0u;
 }
 
+inline uint32_t mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    return mbar_try_wait(bar, parity);
+}
+
 inline void fence_proxy_async_smem() {}
 inline void tma_prefetch_desc(const void *) {}
 
@@ -502,6 +507,11 @@ inline void tmem_ld_32x32(uint32_t taddr, uint32_t *v)
 inline void tmem_ld_32x16(uint32_t taddr, uint32_t *v)
 {
     emu_tmem_access(taddr, v, nullptr, 16);
+}
+
+inline void tmem_ld_32x8(uint32_t taddr, uint32_t *v)
+{
+    emu_tmem_access(taddr, v, nullptr, 8);
 }
 
 inline void tmem_st_32x32(uint32_t taddr, const uint32_t *v)

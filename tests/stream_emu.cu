@@ -165,6 +165,7 @@ inline unsigned int warp_of_thread()
 #include "q8_umma.cu"
 #include "q8_wide.cu"
 #include "q8_duo.cu"
+#include "q8_decode.cu"
 
 // the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
 // so one static copy stands for it

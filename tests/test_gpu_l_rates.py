@@ -1,0 +1,87 @@
+"""Rate gates: a product that falls well under its measured rate fails, in the manner of the
+reference's own gates (tests/matrix_test.cu:54-58, 589-681: its gemv and gemm cases fail below a
+fraction of the card's peak).  The floors sit about 15 % under the figures measured on a B200
+with free clocks (1965 MHz); a run that finds the SM clock held well below its maximum is
+skipped, because a locked clock says nothing about the kernels.  Time is CUDA events around a
+captured graph that rotates weight copies larger than L2 in total."""
+import numpy as np
+import pytest
+
+from _util import device_synth_q8_0, torch_mod
+
+pytestmark = pytest.mark.gpu
+
+# (n, k, rows of x, x dtype, floor): floor in GB/s of algorithmic bytes up to 128 rows of x,
+# in TFLOP/s above
+FLOORS = [
+    (4096, 4096, 1, "float16", 1250.0),
+    (4096, 4096, 32, "bfloat16", 1100.0),
+    (6144, 4096, 32, "bfloat16", 1250.0),
+    (28672, 4096, 32, "bfloat16", 2700.0),
+    (4096, 14336, 32, "bfloat16", 1900.0),
+    (151936, 8192, 8, "bfloat16", 4400.0),
+    (4096, 4096, 2048, "bfloat16", 450.0),
+    (28672, 4096, 2048, "bfloat16", 560.0),
+    (4096, 14336, 2048, "bfloat16", 740.0),
+]
+
+
+def _clock_is_free():
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(torch_mod().cuda.current_device())
+        top = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        app = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        return top, app
+    except Exception:
+        return None, None
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import aotx_b200
+    c = aotx_b200.Q8Context(0)
+    yield c
+    assert c.device_status() == 0
+    c.close()
+
+
+@pytest.mark.parametrize("n,k,m,x_name,floor", FLOORS)
+def test_rate_floor(ctx, n, k, m, x_name, floor):
+    torch = torch_mod()
+    weight_bytes = n * (k // 32) * 34
+    copies = min(24, max(2, int(np.ceil(400e6 / weight_bytes))))
+    ws = [device_synth_q8_0(n, k, 5 + c) for c in range(copies)]
+    x = torch.randn(m, k, device="cuda").to(getattr(torch, x_name))
+    y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ctx.matmul(ws[0], n, k, x, y=y)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for w in ws:
+                ctx.matmul(w, n, k, x, y=y)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (10 * copies)
+        best = us if best is None else min(best, us)
+    top, now = _clock_is_free()
+    if m <= 128:
+        rate = (weight_bytes + m * k * 2 + m * n * 2) / best / 1e3
+    else:
+        rate = 2.0 * m * n * k / best / 1e6
+    if rate < floor and top is not None and now is not None and now < 0.8 * top:
+        pytest.skip("SM clock at %d of %d MHz: not a statement about the kernel" % (now, top))
+    assert rate >= floor, "%.1f under the floor %.1f (%.2f us)" % (rate, floor, best)

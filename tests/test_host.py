@@ -152,7 +152,7 @@ def test_argument_checks_need_no_device(built):
     assert lib.aotx_q8_matmul(null, null, one, 8, 8, 64, one, 1, 1, None, one, 0) == 1
     assert lib.aotx_q8_moe_route(null, null, one, one, 1, None, 32, 4, 2, one, one) == 1
     assert lib.aotx_q8_moe_combine(null, null, one, one, one, 1, None, 32, 4, 2, one, 0) == 1
-    assert lib.aotx_q8_matmul_static(null, one, 2, 8, 64, one, 1, 1, None, one, 0) == 2      # type
+    assert lib.aotx_q8_matmul_static(null, one, 99, 8, 64, one, 1, 1, None, one, 0) == 2     # type
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 48, one, 1, 1, None, one, 0) == 1      # k % 32
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 3, 1, None, one, 0) == 1      # x dtype
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 1, 65, None, one, 0) == 5     # rows > 64
