@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libaotx_q8_b200.so")
-SOURCES = ["q8_api.cu", "q8_simt.cu", "q8_umma.cu", "q8_stream.cu", "q8_decode.cu", "q8_wide.cu", "q8_duo.cu", "q8_static.cu", "q8_moe.cu",
+SOURCES = ["q8_api.cu", "q8_simt.cu", "q8_dispatch.cu", "q8_stream.cu", "q8_decode.cu", "q8_wide.cu", "q8_static.cu", "q8_moe.cu",
            "q_generic.cu", "gguf_table.cpp", "gguf_upload.cu"]
 HEADERS = ["q8_common.cuh", "q8_ptx.cuh", "q8_store.cuh", "q8_simt_gemv.cuh", "q8_launch.h", "q8_tile.cuh", "q_blocks.cuh", os.path.join("..", "..", "include", "aotx_q8_b200.h"),
            os.path.join("..", "..", "include", "aotx_gguf_b200.h")]
@@ -70,18 +70,17 @@ def resource_usage():
     return usage
 
 
-EXPERIMENT_LIB = os.path.join(HERE, "libaotx_q8_b200_experiment.so")
+TRACE_LIB = os.path.join(HERE, "libaotx_q8_b200_trace.so")
 
 
-def build_experiment(defines=()):
-    """The library with -DQ8_EXPERIMENT (plus `defines`, e.g. "Q8_RAW_64=4"): the switches and
-    time stamps that the product build leaves out, and the way to the kernels the product build
-    does not dispatch (see the headers of q8_wide.cu, q8_duo.cu and q8_umma.cu for the
-    environment variables).  Loaded instead of the product library when AOTX_Q8_LIBRARY names it
-    (aotx_b200/library.py).  Always rebuilt: the defines are not tracked."""
-    out = os.path.join(OBJ, "experiment")
+def build_trace():
+    """The library with -DQ8_TRACE: the decode kernel writes time stamps (block start, first x
+    segment landed, conversion done, accumulator ready, the two cluster barriers, end) that
+    aotx_b200/timeline.py reads back.  Never the product build; loaded instead of it when
+    AOTX_Q8_LIBRARY=trace (aotx_b200/library.py)."""
+    out = os.path.join(OBJ, "trace")
     os.makedirs(out, exist_ok=True)
-    flags = [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")] + ["-DQ8_EXPERIMENT"] + ["-D" + d for d in defines]
+    flags = [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")] + ["-DQ8_TRACE"]
 
     def one(src):
         obj = os.path.join(out, os.path.splitext(src)[0] + ".o")
@@ -93,9 +92,9 @@ def build_experiment(defines=()):
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         objs = list(pool.map(one, SOURCES))
-    subprocess.run(["nvcc", "-shared", "-o", EXPERIMENT_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+    subprocess.run(["nvcc", "-shared", "-o", TRACE_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
                    check=True)
-    return EXPERIMENT_LIB
+    return TRACE_LIB
 
 
 def build(verbose=False):
@@ -116,7 +115,7 @@ def build(verbose=False):
 
 
 if __name__ == "__main__":
-    if "--experiment" in sys.argv:
-        print(build_experiment([a[2:] for a in sys.argv if a.startswith("-D")]))
+    if "--trace" in sys.argv:
+        print(build_trace())
     else:
         print(build(verbose="-v" in sys.argv))

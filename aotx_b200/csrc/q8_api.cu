@@ -17,7 +17,6 @@ struct aotx_q8_ctx {
     int overlap;
     unsigned int launches;
     q8::UmmaScratch scratch;
-    q8::NextWeights next; /* one-shot hint of aotx_q8_hint_next, taken by the next product */
 };
 
 namespace {
@@ -63,8 +62,6 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     ctx->last_cuda = 0;
     ctx->overlap = 1;
     ctx->launches = 0;
-    ctx->next.w = nullptr;
-    ctx->next.n = ctx->next.k = ctx->next.m = 0;
     cudaError_t err = cudaSetDevice(device);
     int sms = 0;
     if (err == cudaSuccess) {
@@ -138,31 +135,6 @@ extern "C" int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled)
     return AOTX_Q8_OK;
 }
 
-extern "C" int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, uint32_t n_next, uint32_t k_next,
-                                 uint32_t m_next)
-{
-    if (ctx == nullptr) {
-        return AOTX_Q8_ERR_ARGUMENT;
-    }
-    ctx->next.w = w_next;
-    ctx->next.n = n_next;
-    ctx->next.k = k_next;
-    ctx->next.m = m_next;
-    return AOTX_Q8_OK;
-}
-
-namespace {
-
-/* The hint is for one product: whoever launches next takes it, whether its kernel uses it or not. */
-q8::NextWeights take_hint(aotx_q8_ctx *ctx)
-{
-    q8::NextWeights next = ctx->next;
-    ctx->next.w = nullptr;
-    return next;
-}
-
-} // namespace
-
 extern "C" int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx)
 {
     return ctx == nullptr ? 0 : ctx->last_cuda;
@@ -220,8 +192,6 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    /* the hint is for this call, whatever becomes of it */
-    const q8::NextWeights next = take_hint(ctx);
     if (!q8::block_type_known(type)) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -255,7 +225,7 @@ extern "C" int aotx_q8_matmul(aotx_q8_ctx *ctx, void *stream, const void *w, uin
     cudaError_t err;
     if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
         err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m,
-                              m_dev, y, y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, 0u, &next);
+                              m_dev, y, y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, 0u);
     } else {
         err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
     }
@@ -272,7 +242,6 @@ extern "C" int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *
     if (epilogue == AOTX_Q8_EPILOGUE_STORE) {
         return aotx_q8_matmul(ctx, stream, w, type, n, k, x, x_dtype, m, m_dev, y, y_dtype);
     }
-    const q8::NextWeights next = take_hint(ctx);
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -299,7 +268,7 @@ extern "C" int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *
     cudaError_t err;
     if (tensor_ok && ctx->path != AOTX_Q8_PATH_GENERAL) {
         err = q8::launch_umma(s, ctx->scratch, ctx->sm_count, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y,
-                              y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, (unsigned int)epilogue, &next);
+                              y_dtype, ctx->launches++, ctx->overlap != 0, nullptr, (unsigned int)epilogue);
     } else {
         err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype,
                                    (unsigned int)epilogue);
@@ -340,7 +309,6 @@ extern "C" int aotx_q8_moe_ffn(aotx_q8_ctx *ctx, void *stream, const void *w_gat
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -391,7 +359,6 @@ extern "C" int aotx_q8_moe_ffn_fused(aotx_q8_ctx *ctx, void *stream, const void 
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }
@@ -456,7 +423,6 @@ extern "C" int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *
     if (ctx == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
-    (void)take_hint(ctx); /* a hint does not outlive the next product of any kind */
     if (type != AOTX_Q8_TYPE_Q8_0) {
         return AOTX_Q8_ERR_TYPE;
     }

@@ -143,25 +143,6 @@ __device__ __forceinline__ void store_one(const UmmaArgs &args, const TilePlace 
     store_one_any<YT>(args, place, lane_row, j, row, value);
 }
 
-// The units of block b of `blocks`, `units` in all (32-bit arithmetic: the first `units mod
-// blocks` blocks take one unit more), and the block that holds unit `u`.
-__host__ __device__ __forceinline__ void decode_range(uint32_t b, uint32_t blocks, uint32_t units,
-                                                      uint32_t *begin, uint32_t *end)
-{
-    const uint32_t q = units / blocks;
-    const uint32_t rem = units - q * blocks;
-    *begin = b * q + (b < rem ? b : rem);
-    *end = *begin + q + (b < rem ? 1u : 0u);
-}
-
-__host__ __device__ __forceinline__ uint32_t decode_holder(uint32_t u, uint32_t blocks, uint32_t units)
-{
-    const uint32_t q = units / blocks;
-    const uint32_t rem = units - q * blocks;
-    const uint32_t cut = rem * (q + 1u);
-    return u < cut ? u / (q + 1u) : rem + (u - cut) / q;
-}
-
 // Barriers and buffers of a block, as shared-space addresses.
 struct DecodeRings {
     uint32_t x_base, raw_base;
@@ -170,38 +151,25 @@ struct DecodeRings {
 
 // One unit (a 256-weight segment of the block's 128 rows), half H of it: this thread's row from
 // the raw ring into registers, exact dequantisation, 64 packed words into the thread's lane of
-// the A stage.  The four warps of a half hand the stage over together.  The hand-over of a
-// stage is deferred to the next call (`pending` holds its barrier, 0 for none): the stores into
-// tensor memory then complete while the next raw row is being fetched, instead of holding up
-// the warp after every half segment.  convert_flush hands over the last one.
-__device__ __forceinline__ void convert_flush(uint32_t &pending, uint32_t lane)
-{
-    if (pending != 0u) {
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0u) {
-            mbar_arrive(pending);
-        }
-        pending = 0u;
-    }
-}
-
+// the A stage.  The four warps of a half hand the stage over together.  (Handing a stage over
+// one call later, so that the stores into tensor memory overlap the next fetch, was measured
+// and is slower: with three stages the MMA thread then waits for its operand.)
 template <int NTOK, int H>
 __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, uint32_t row, uint32_t lane,
-                                             uint32_t lane_base, uint32_t &pending,
-                                             volatile uint32_t *abort_flag, unsigned int *status)
+                                             uint32_t lane_base, volatile uint32_t *abort_flag,
+                                             unsigned int *status)
 {
     using S = DecodeShape<NTOK>;
     const uint32_t rst = g % S::raw_stages;
     const uint32_t rph = (g / S::raw_stages) & 1u;
-    if (!mbar_wait_hot(r.raw_full + 8u * rst, rph, abort_flag, status)) {
+    // a wait can end differently for the lanes of a warp when the bound runs out for some just as
+    // the phase completes for others: the warp decides together, so that no lane is left behind
+    // at a warp-wide step
+    if (!__all_sync(0xFFFFFFFFu, mbar_wait_hot(r.raw_full + 8u * rst, rph, abort_flag, status))) {
         return false;
     }
     uint32_t raw[36];
     load_raw<H>(r.raw_base + rst * kRawStageBytes + row * kSegBytes, raw);
-    // the stage before this one is complete by now: hand it to the MMA thread
-    convert_flush(pending, lane);
     // this half is in registers: as far as this warp goes, the raw segment may be overwritten
     __syncwarp();
     if (lane == 0u) {
@@ -210,14 +178,19 @@ __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, u
     const uint32_t hh = 2u * g + (uint32_t)H;
     const uint32_t st = hh % S::a_stages;
     const uint32_t ph = (hh / S::a_stages) & 1u;
-    if (!mbar_wait_hot(r.a_empty + 8u * st, ph ^ 1u, abort_flag, status)) {
+    if (!__all_sync(0xFFFFFFFFu, mbar_wait_hot(r.a_empty + 8u * st, ph ^ 1u, abort_flag, status))) {
         return false;
     }
     const uint32_t taddr = lane_base + st * S::a_stage_columns;
     tc_fence_after_sync();
     convert_stage_tmem<H, 0, false>(raw, taddr);
     convert_stage_tmem<H, 1, false>(raw, taddr + kSubK / 2u);
-    pending = r.a_full + 8u * st;
+    tmem_st_wait();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0u) {
+        mbar_arrive(r.a_full + 8u * st);
+    }
     return true;
 }
 
@@ -317,7 +290,6 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    Q8_STAMP(1u, threadIdx.x == 0u)
 
     unsigned int m_live = 0u;
 
@@ -403,10 +375,11 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
                 const uint32_t xst = g % S::x_depth;
                 const uint32_t xph = (g / S::x_depth) & 1u;
-                if (!mbar_wait(r.x_land + 8u * xst, xph, abort_flag, args.status)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(r.x_land + 8u * xst, xph, abort_flag, args.status))) {
                     ok = false;
                     break;
                 }
+                Q8_STAMP(1u, g == 0u && lane == 0u)     // the first x segment has landed
                 if (args.b_bf16 != 0u) {
                     // eight chunks of 16 bytes per lane at a time: the loads go out together, so
                     // their latency is paid once per batch and not once per chunk
@@ -464,11 +437,8 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         umma_commit(r.x_empty + 8u * xst);
                     }
                 }
-                // a wait that ran out raised the block's abort flag: every lane leaves together
-                __syncwarp();
-                if (*abort_flag != 0u) {
-                    ok = false;
-                }
+                // lane 0's waits may have run out: every lane leaves together
+                ok = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
             if (ok && lane == 0u) {
                 umma_commit(r.acc_full + 8u * buf);
@@ -489,13 +459,11 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // this warp owns TMEM lanes [32 cw, +32): its rows of the tile
         const uint32_t lane_base = tmem_base + ((cw * 32u) << 16) + S::a_column0;
         uint32_t g = 0;
-        uint32_t pending = 0u;
         for (uint32_t u = u_begin; u < u_end; ++u, ++g) {
-            if (!convert_unit<NTOK, 0>(r, g, row, lane, lane_base, pending, abort_flag, args.status)) {
+            if (!convert_unit<NTOK, 0>(r, g, row, lane, lane_base, abort_flag, args.status)) {
                 break;
             }
         }
-        convert_flush(pending, lane);
         Q8_STAMP(3u, cw == 0u && lane == 0u)       // conversion of the block's units done
     } else {
         // ------------------------------------------- dequantise, second halves; read sums, store
@@ -510,20 +478,17 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         uint32_t s0 = seg_begin;
         uint32_t g = 0;
         uint32_t tc = 0;
-        uint32_t pending = 0u;
         bool waited = false;
         bool ok = true;
         while (ok) {
             const bool more = u < u_end;
-            if (!more) {
-                convert_flush(pending, lane);
-            }
             if (done < u_end && !split) {
                 const uint32_t buf = tc & 1u;
                 const uint32_t aph = (tc >> 1) & 1u;
                 // between two segments only look; with nothing left to convert, wait
-                const bool ready = more ? mbar_test_wait(r.acc_full + 8u * buf, aph) != 0u
-                                        : mbar_wait(r.acc_full + 8u * buf, aph, abort_flag, args.status);
+                const bool ready = __all_sync(0xFFFFFFFFu, more
+                    ? mbar_test_wait(r.acc_full + 8u * buf, aph) != 0u
+                    : mbar_wait(r.acc_full + 8u * buf, aph, abort_flag, args.status)) != 0;
                 if (!ready && !more) {
                     break;
                 }
@@ -569,7 +534,35 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                     tc_fence_after_sync();
                     float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats + lane_row;
+                    // the other blocks' partial sums, added up in block order; all the loads of one
+                    // block's partial tile go out together (a trip to L2 each would cost more than
+                    // the whole store otherwise)
+                    float others[NTOK];
+                    if (last_cc != blockIdx.x) {
+                        const float *slot = args.partial + (unsigned long long)(blockIdx.x + 1u) * args.tile_floats
+                                          + lane_row;
+#pragma unroll
+                        for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
+                            others[i] = __ldcg(slot + (unsigned long long)i * kRows);
+                        }
+                    }
 #pragma unroll 1
+                    for (unsigned int cc = blockIdx.x + 2u; cc <= last_cc; ++cc) {
+                        const float *slot = args.partial + (unsigned long long)cc * args.tile_floats + lane_row;
+#pragma unroll
+                        for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 16u) {
+                            float a[16];
+#pragma unroll
+                            for (uint32_t i = 0; i < 16u; ++i) {
+                                a[i] = __ldcg(slot + (unsigned long long)(c0 + i) * kRows);
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < 16u; ++i) {
+                                others[c0 + i] += a[i];
+                            }
+                        }
+                    }
+#pragma unroll
                     for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
                         uint32_t v[8];
                         tmem_ld_32x8(lane_taddr + buf * (uint32_t)NTOK + c0, v);
@@ -580,19 +573,10 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                 __stcg(own_slot + (unsigned long long)(c0 + i) * kRows, __uint_as_float(v[i]));
                             }
                         } else {
-                            // add the other blocks' partial sums in block order
-#pragma unroll 1
-                            for (unsigned int cc = blockIdx.x + 1u; cc <= last_cc; ++cc) {
-                                const float *slot = args.partial + (unsigned long long)cc * args.tile_floats
-                                                  + (unsigned long long)c0 * kRows + lane_row;
-                                float a[8];
+                            if (last_cc != blockIdx.x) {
 #pragma unroll
                                 for (uint32_t i = 0; i < 8u; ++i) {
-                                    a[i] = __ldcg(slot + (unsigned long long)i * kRows);
-                                }
-#pragma unroll
-                                for (uint32_t i = 0; i < 8u; ++i) {
-                                    v[i] = __float_as_uint(__uint_as_float(v[i]) + a[i]);
+                                    v[i] = __float_as_uint(__uint_as_float(v[i]) + others[c0 + i]);
                                 }
                             }
                             store_eight<YT>(args, place, lane_row, j, c0, v);
@@ -632,11 +616,10 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (!more) {
                 break;
             }
-            ok = convert_unit<NTOK, 1>(r, g, lane_row, lane, lane_base, pending, abort_flag, args.status);
+            ok = convert_unit<NTOK, 1>(r, g, lane_row, lane, lane_base, abort_flag, args.status);
             ++u;
             ++g;
         }
-        convert_flush(pending, lane);
         if (split) {
             // the block's one piece: wait for its MMAs, the exchange below reads the accumulator
             grid_dependency_wait();
@@ -713,11 +696,19 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         uint32_t local = 0u;
 #pragma unroll 1
         for (uint32_t col = crank; col < (uint32_t)NTOK; col += csize, ++local) {
-            float sum = 0.0f;
-#pragma unroll 1
-            for (uint32_t src = 0; src < csize; ++src) {
-                const float piece = ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u);
-                sum = src == 0u ? piece : sum + piece;
+            // the pieces of this column, fetched together, added in block order
+            float piece[kDecMaxCluster];
+#pragma unroll
+            for (uint32_t src = 0; src < kDecMaxCluster; ++src) {
+                piece[src] = src < csize
+                    ? ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u) : 0.0f;
+            }
+            float sum = piece[0];
+#pragma unroll
+            for (uint32_t src = 1; src < kDecMaxCluster; ++src) {
+                if (src < csize) {
+                    sum += piece[src];
+                }
             }
             store_one<YT>(args, place, lane_row, j, col, sum);
         }
@@ -764,14 +755,10 @@ unsigned int decode_grid(unsigned int row_tiles, unsigned int segs, unsigned int
     *cluster = 0u;
 #ifndef Q8_HOST_EMULATION
     if (2u * row_tiles <= sm_count) {
-        // two blocks per SM: as many pieces per tile as fill them, each at least one segment
-        unsigned int pieces = 2u * sm_count / row_tiles;
+        // At most one block per SM and launch, so that the blocks of the next product find the
+        // second place on every SM free and stage their weights while this product finishes.
+        unsigned int pieces = sm_count / row_tiles;
         unsigned int most = kDecMaxCluster;
-#ifdef Q8_EXPERIMENT
-        if (getenv("Q8_MAX_CLUSTER") != nullptr) {
-            most = (unsigned int)atoi(getenv("Q8_MAX_CLUSTER"));
-        }
-#endif
         pieces = pieces > most ? most : pieces;
         pieces = pieces > segs ? segs : pieces;
         // a power of two: clusters of 6 took three times as long to be placed as clusters of 4 or 8

@@ -129,19 +129,12 @@ struct PeerOut {
     unsigned int ldy;
 };
 
-// The product that follows on the stream (see UmmaArgs::next_w): its weights and shape.
-struct NextWeights {
-    const void *w;
-    unsigned int n, k, m;
-};
-
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                         const void *w, unsigned int n, unsigned int k, const void *x, int x_bf16,
                         unsigned int m, const unsigned int *m_dev, void *y, int y_dtype, unsigned int set,
-                        bool overlap, const PeerOut *out = nullptr, unsigned int epilogue = 0u,
-                        const NextWeights *next = nullptr);
+                        bool overlap, const PeerOut *out = nullptr, unsigned int epilogue = 0u);
 
 // Grouped mode of the decode-regime kernel: tiles from a device table (see q8_tile.cuh).
 struct GroupTile;

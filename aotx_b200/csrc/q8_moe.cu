@@ -20,12 +20,6 @@ namespace q8 {
 
 static unsigned int group_tokens()
 {
-#ifdef Q8_EXPERIMENT
-    const char *env = getenv("Q8_GROUP_TOKENS");
-    if (env != nullptr) {
-        return (unsigned int)atoi(env);
-    }
-#endif
     return 64u;
 }
 

@@ -116,13 +116,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
         : "memory");
 }
 
-// Ask L2 to fetch [addr, addr + bytes) from device memory; nothing waits for it.  Address and
-// size are multiples of 16.
-__device__ __forceinline__ void l2_prefetch_bulk(const void *addr, uint32_t bytes)
-{
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(addr), "r"(bytes) : "memory");
-}
-
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t columns)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),

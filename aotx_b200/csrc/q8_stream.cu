@@ -80,12 +80,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-#ifdef Q8_TRACE
-    unsigned long long t_start = 0;
-    if (args.trace != nullptr && threadIdx.x == 0) {
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
-    }
-#endif
 
     // The next kernel on the stream may start its blocks as this one's finish.  Work that only
     // reads the weights runs ahead of the kernels before this one; everything that reads x or
@@ -116,15 +110,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
     unsigned long long u_begin, u_end;
     unit_range(blockIdx.x, blocks, units, &u_begin, &u_end);
-#ifdef Q8_SWITCHES
-    if ((args.debug & 16u) != 0u && warp == kWeightWarp && lane == 0u && args.group_tiles == nullptr
-        && args.w != nullptr) {
-        // experiment: memory starts moving for this block before its barriers and tensor
-        // memory are set up
-        first_unit_pieces(args.w, (unsigned long long)(args.k / 32u) * 34u, args.n, segs, tok_tiles,
-                          S::raw_stages, blockIdx.x, gridDim.x, L2PrefetchEmit());
-    }
-#endif
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
@@ -158,14 +143,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 0u] = t_start;
-        args.trace[blockIdx.x * 8u + 1u] = t;
-    }
-#endif
 
     if (warp == kWeightWarp) {
         // ---------------------------------------------------------------- raw weight copies
@@ -185,20 +162,11 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         ok = false;
                         break;
                     }
-#ifdef Q8_SWITCHES
-                    if (args.debug & 1u) {
-                        mbar_arrive(raw_full + 8u * st);
-                        continue;
-                    }
-#endif
                     mbar_expect_tx(raw_full + 8u * st, kRawStageBytes);
                     tma_load_2d(raw_base + st * kRawStageBytes, &tmap_w, raw_full + 8u * st,
                                 (int)(s * kSegWords), (int)w_row);
                 }
                 u += (s1 - s0);
-            }
-            if (ok && args.next_w != nullptr) {
-                prefetch_next_units(args);
             }
             // Let every copy this thread started land before the block ends.
             uint32_t local_abort = 0;
@@ -214,17 +182,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             uint32_t g = 0;
             grid_dependency_wait();
             bool ok = true;
-#ifdef Q8_SWITCHES
-            // switch 64: when a row of x is exactly as many segments deep as the ring has stages,
-            // stage j always holds the same segment of x, and consecutive tiles over the same rows
-            // of x (the row tiles of one expert's token tile in the grouped down product) find
-            // it there: the copy is left out and the stage is handed over as it is
-            uint32_t held[S::depth];
-            for (uint32_t i = 0; i < S::depth; ++i) {
-                held[i] = 0xFFFFFFFFu;
-            }
-            const bool reuse = (args.debug & 64u) != 0u && segs == S::depth && args.b_bf16 == 0u;
-#endif
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
                 const uint32_t s0 = (uint32_t)(u % segs);
@@ -238,26 +195,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         ok = false;
                         break;
                     }
-#ifdef Q8_SWITCHES
-                    if (args.debug & 8u) {
-                        mbar_arrive(x_full + 8u * st);
-                        continue;
-                    }
-                    if (reuse) {
-                        bool same = false;
-#pragma unroll
-                        for (uint32_t i = 0; i < S::depth; ++i) {
-                            if (i == st) {
-                                same = held[i] == tok0;
-                                held[i] = tok0;
-                            }
-                        }
-                        if (same) {
-                            mbar_arrive(x_full + 8u * st);
-                            continue;
-                        }
-                    }
-#endif
                     mbar_expect_tx(x_full + 8u * st, S::x_seg_bytes);
 #pragma unroll
                     for (uint32_t j = 0; j < kSubs; ++j) {
@@ -279,11 +216,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0u) {
             // bfloat16 activations were turned into binary16 in shared memory by the converters
             uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
-#ifdef Q8_SWITCHES
-            if ((args.debug & 32u) != 0u && args.b_bf16 != 0u) {
-                idesc = umma_idesc(kRows, (uint32_t)NTOK, 1u, 1u); // both operands stay bfloat16
-            }
-#endif
             uint32_t g = 0;
             uint32_t tc = 0;
             bool ok = true;
@@ -309,12 +241,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         break;
                     }
                     tc_fence_after_sync();
-#ifdef Q8_SWITCHES
-                    if (args.debug & 4u) {
-                        umma_commit(seg_empty + 8u * st);
-                        continue;
-                    }
-#endif
                     const uint32_t a_tmem = tmem_base + S::a_column0 + st * S::a_seg_columns;
 #pragma unroll
                     for (uint32_t j = 0; j < kSubs; ++j) {
@@ -362,14 +288,6 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
                 uint32_t raw[36];
                 const uint32_t raw_row = raw_base + rst * kRawStageBytes + row * kSegBytes;
-#ifdef Q8_SWITCHES
-                if (args.debug & 2u) {
-#pragma unroll
-                    for (int i = 0; i < 36; ++i) {
-                        raw[i] = 0u;
-                    }
-                } else
-#endif
                 if (half_id == 0u) {
                     load_raw<0>(raw_row, raw);
                 } else {
@@ -385,23 +303,9 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     ok = false;
                     break;
                 }
-#ifdef Q8_SWITCHES
-                if (!(args.debug & 2u))
-#endif
                 {
                     const uint32_t taddr = lane_base + st * S::a_seg_columns;
                     tc_fence_after_sync();
-#ifdef Q8_SWITCHES
-                    if ((args.debug & 32u) != 0u && args.b_bf16 != 0u) {
-                        if (half_id == 0u) {
-                            convert_stage_tmem<0, 0, true>(raw, taddr);
-                            convert_stage_tmem<0, 1, true>(raw, taddr + kSubK / 2u);
-                        } else {
-                            convert_stage_tmem<1, 0, true>(raw, taddr);
-                            convert_stage_tmem<1, 1, true>(raw, taddr + kSubK / 2u);
-                        }
-                    } else
-#endif
                     if (half_id == 0u) {
                         convert_stage_tmem<0, 0>(raw, taddr);
                         convert_stage_tmem<0, 1>(raw, taddr + kSubK / 2u);
@@ -412,11 +316,7 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     tmem_st_wait();
                     tc_fence_before_sync();
                 }
-                bool rewrite_x = args.b_bf16 != 0u;
-#ifdef Q8_SWITCHES
-                rewrite_x = rewrite_x && (args.debug & 32u) == 0u;
-#endif
-                if (rewrite_x) {
+                if (args.b_bf16 != 0u) {
                     // One MMA takes both operands in one format: turn this segment's x tile into
                     // binary16 where it lies (the swizzle moves whole 16-byte chunks, so the
                     // conversion is chunk by chunk whatever the layout).
@@ -463,24 +363,10 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 2u] = t;
-    }
-#endif
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, S::tmem_columns);
     }
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && threadIdx.x == 14 * 32) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 3u] = t;
-    }
-#endif
 }
 
 template <int NTOK, typename YT>

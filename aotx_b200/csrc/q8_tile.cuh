@@ -9,17 +9,6 @@
 #include "q8_common.cuh"
 #include "q8_launch.h"
 
-// -DQ8_EXPERIMENT (never the product build) compiles switches that leave out or change one stage
-// of a kernel at a time (UmmaArgs::debug) and time stamps (UmmaArgs::trace).  The tests' host
-// emulation compiles the switches too (not the time stamps), so that a variant can be checked
-// on the host before it first runs on a GPU.
-#if defined(Q8_EXPERIMENT) || defined(Q8_HOST_EMULATION)
-#define Q8_SWITCHES 1
-#endif
-#if defined(Q8_EXPERIMENT) && !defined(Q8_HOST_EMULATION)
-#define Q8_TRACE 1
-#endif
-
 namespace q8 {
 
 constexpr uint32_t kRows = 128;                          // rows of w per tile (MMA M)
@@ -84,26 +73,12 @@ struct UmmaArgs {
     // y holds (residual stream); or, with rows 2p and 2p+1 of w being the gate and up rows of
     // output column p, write silu(gate) * up to column p of a y that is n / 2 wide.
     unsigned int epilogue;
-    // The product that follows this one on the stream, or next_w == null: its weights, rows,
-    // bytes per row, segments per row and token tiles.  Once a block has issued its own last
-    // weight copy it asks L2 for the first `next_units` units that the same block index will
-    // read in that launch (the schedule is a function of these numbers and the grid), so that
-    // memory does not idle while this launch drains and the next one fills its pipeline.
-    const unsigned char *next_w;
-    unsigned long long next_stride;
-    unsigned int next_n;
-    unsigned int next_segs;
-    unsigned int next_tok_tiles;
-    unsigned int next_units;
     // Decode kernel (q8_decode.cu): nonzero when the launch is one cluster of blocks per weight
     // row tile, each block taking one run of the tile's segments; zero for the unit schedule.
     unsigned int split;
-#ifdef Q8_SWITCHES
-    const unsigned char *w; // the weights as a plain pointer (debug & 16: a block warms L2 with its own first units)
-    // 1: no weight copies, 2: no conversion, 4: no MMA, 8: no x copies, 16: see `w`,
-    // 32: bfloat16 activations get bfloat16 weights in tensor memory (x is not rewritten)
-    unsigned int debug;
-    unsigned long long *trace; // [launch][block][4] timestamps, or null
+#ifdef Q8_TRACE
+    // development builds (-DQ8_TRACE): time stamps of the decode kernel, 8 words per block, or null
+    unsigned long long *trace;
 #endif
 };
 
@@ -114,6 +89,25 @@ __host__ __device__ __forceinline__ void unit_range(unsigned int b, unsigned int
 {
     *begin = (unsigned long long)b * units / blocks;
     *end = (unsigned long long)(b + 1u) * units / blocks;
+}
+
+// The decode kernel's form of the same (q8_decode.cu): the units of block b of `blocks`, `units` in all (32-bit arithmetic: the first `units mod
+// blocks` blocks take one unit more), and the block that holds unit `u`.
+__host__ __device__ __forceinline__ void decode_range(uint32_t b, uint32_t blocks, uint32_t units,
+                                                      uint32_t *begin, uint32_t *end)
+{
+    const uint32_t q = units / blocks;
+    const uint32_t rem = units - q * blocks;
+    *begin = b * q + (b < rem ? b : rem);
+    *end = *begin + q + (b < rem ? 1u : 0u);
+}
+
+__host__ __device__ __forceinline__ uint32_t decode_holder(uint32_t u, uint32_t blocks, uint32_t units)
+{
+    const uint32_t q = units / blocks;
+    const uint32_t rem = units - q * blocks;
+    const uint32_t cut = rem * (q + 1u);
+    return u < cut ? u / (q + 1u) : rem + (u - cut) / q;
 }
 
 // A tile that is cut between blocks is finished by block `b`, which holds its first segment.
@@ -138,119 +132,10 @@ __host__ __device__ __forceinline__ unsigned int last_holder(unsigned int b, uns
     return last_cc;
 }
 
-// The weight bytes that block `block` of a grid of `grid` reads first in the product that
-// follows on the stream (UmmaArgs::next_*): its first `next_units` units, each a run of 272
-// bytes in each of the 128 rows of a tile; runs of consecutive segments of one tile come as one
-// piece per row.  `emit(address, bytes)` is called once per piece.
-template <typename Emit>
-__host__ __device__ __forceinline__ void first_unit_pieces(const unsigned char *w, unsigned long long stride,
-                                                           unsigned int n, unsigned int segs,
-                                                           unsigned int tok_tiles, unsigned int limit,
-                                                           unsigned int block, unsigned int grid, Emit emit)
-{
-    const unsigned int row_tiles = (n + kRows - 1u) / kRows;
-    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * segs;
-    const unsigned int blocks = units < grid ? (unsigned int)units : grid;
-    if (block >= blocks) {
-        return;
-    }
-    unsigned long long u, u_end;
-    unit_range(block, blocks, units, &u, &u_end);
-    if (u_end > u + limit) {
-        u_end = u + limit;
-    }
-    while (u < u_end) {
-        const unsigned int tile = (unsigned int)(u / segs);
-        const unsigned int s0 = (unsigned int)(u % segs);
-        const unsigned long long left = u_end - u;
-        const unsigned int s1 = (segs - s0) < left ? segs : (unsigned int)(s0 + left);
-        const unsigned int row0 = (tile / tok_tiles) * kRows;
-        const unsigned int rows = n - row0 < kRows ? n - row0 : kRows;
-        const unsigned char *at = w + (unsigned long long)row0 * stride + (unsigned long long)s0 * kSegBytes;
-        const uint32_t bytes = (s1 - s0) * kSegBytes;
-        for (unsigned int r = 0; r < rows; ++r) {
-            emit(at + (unsigned long long)r * stride, bytes);
-        }
-        u += (s1 - s0);
-    }
-}
-
-template <typename Emit>
-__host__ __device__ __forceinline__ void next_unit_pieces(const UmmaArgs &args, unsigned int block,
-                                                          unsigned int grid, Emit emit)
-{
-    first_unit_pieces(args.next_w, args.next_stride, args.next_n, args.next_segs, args.next_tok_tiles,
-                      args.next_units, block, grid, emit);
-}
-
-struct L2PrefetchEmit {
-    __device__ __forceinline__ void operator()(const unsigned char *at, uint32_t bytes) const
-    {
-        l2_prefetch_bulk(at, bytes);
-    }
-};
-
-// Warm L2 with those pieces.  One thread; nothing waits for the requests.
-__device__ __forceinline__ void prefetch_next_units(const UmmaArgs &args)
-{
-    next_unit_pieces(args, blockIdx.x, gridDim.x, L2PrefetchEmit());
-}
-
-// Dequantise the two blocks of one MMA stage that this thread owns and store them as 8
-// chunks of 16 bytes in the swizzled operand layout.  `raw` holds 36 words: bytes
-// [H * 128, H * 128 + 144) of the thread's 272-byte row segment.  The thread's four blocks
-// start at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
-template <int H, int JJ, bool BF>
-__device__ __forceinline__ void convert_stage(const uint32_t (&raw)[36], uint32_t a_stage, uint32_t row)
-{
-    const uint32_t row_base = a_stage + (row >> 3) * 1024u + (row & 7u) * 128u;
-    const uint32_t phase = row & 7u;
-#pragma unroll
-    for (int jb = 0; jb < 2; ++jb) {
-        const int lb = 2 * JJ + jb;
-        const int byte_off = (H ? 8 : 0) + 34 * lb;
-        const int wi = byte_off / 4;
-        const bool odd = (byte_off % 4) == 2;
-        // scale in both halves of a word
-        uint32_t d_bits = prmt(raw[wi], raw[wi], odd ? 0x3232u : 0x1010u);
-        __half2 d2 = *reinterpret_cast<__half2 *>(&d_bits);
-        const float d = __low2float(d2);
-        (void)d;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint32_t out[4];
-#pragma unroll
-            for (int pp = 0; pp < 4; ++pp) {
-                const int p = 4 * c + pp; // pair index 0..15: weights 2p, 2p+1
-                if (odd) {
-                    // payload starts at the next word boundary
-                    const int word = wi + 1 + p / 2;
-                    uint32_t flipped = raw[word] ^ 0x80808080u;
-                    if constexpr (BF) {
-                        out[pp] = (p % 2) ? dequant_pair_bf16<1>(flipped, d) : dequant_pair_bf16<0>(flipped, d);
-                    } else {
-                        out[pp] = (p % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
-                    }
-                } else {
-                    // payload starts in the high half of the scale's word
-                    const int word = wi + (p + 1) / 2;
-                    uint32_t flipped = raw[word] ^ 0x80808080u;
-                    if constexpr (BF) {
-                        out[pp] = ((p + 1) % 2) ? dequant_pair_bf16<1>(flipped, d)
-                                                : dequant_pair_bf16<0>(flipped, d);
-                    } else {
-                        out[pp] = ((p + 1) % 2) ? dequant_pair<1>(flipped, d2) : dequant_pair<0>(flipped, d2);
-                    }
-                }
-            }
-            const uint32_t kc = (uint32_t)(4 * jb + c);
-            const uint32_t addr = row_base + ((kc ^ phase) << 4);
-            st_shared_v4(addr, out[0], out[1], out[2], out[3]);
-        }
-    }
-}
-
-// The same two blocks as 32 packed words (64 16-bit values in order of k: binary16, or
+// The two blocks of one MMA stage that this thread owns: `raw` holds 36 words, bytes
+// [H * 128, H * 128 + 144) of the thread's 272-byte row segment; the thread's four blocks start
+// at byte 34 * (4H + lb), lb = 0..3, that is at local byte (H ? 8 : 0) + 34 * lb.
+// They become 32 packed words (64 16-bit values in order of k: binary16, or
 // bfloat16 with BF), written to this thread's lane of tensor memory: column c of the stage holds
 // weights 2c and 2c+1 of the stage.
 template <int H, int JJ, bool BF = false>
@@ -429,14 +314,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
     const unsigned long long tile_end = ((unsigned long long)cut_tile + 1ull) * segs;
     float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats;
 
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && wq == 0u && lane == 0u) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 4u] = t;
-        args.trace[blockIdx.x * 8u + 7u] = (owner ? 1u : 0u) | (whole ? 2u : 0u);
-    }
-#endif
     // The other holders of this tile are the blocks right after this one, up to `last_cc`.
     unsigned int last_cc = blockIdx.x;
     if (owner && !whole) {
@@ -458,13 +335,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
         __syncwarp();
     }
 
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && wq == 0u && lane == 0u) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 5u] = t;
-    }
-#endif
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += kChunk) {
         uint32_t v[kChunk];
@@ -508,13 +378,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             store_chunk<kChunk, YT>(args, place, lane_row, j, i0 + c0, v);
         }
     }
-#ifdef Q8_TRACE
-    if (args.trace != nullptr && wq == 0u && lane == 0u) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        args.trace[blockIdx.x * 8u + 6u] = t;
-    }
-#endif
     // The accumulator buffer is free again.
     tc_fence_before_sync();
     __syncwarp();
@@ -593,11 +456,6 @@ unsigned int decode_grid(unsigned int row_tiles, unsigned int segs, unsigned int
 cudaError_t launch_decode_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
                                  const UmmaArgs &args, unsigned int grid, unsigned int cluster, unsigned int ntok,
                                  int y_dtype);
-
-// Host launcher of the two-blocks-per-SM form of the decode-regime kernel (q8_duo.cu), token
-// tiles 16 and 32; `grid` may be up to twice the number of SMs.
-cudaError_t launch_duo_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,
-                              const UmmaArgs &args, unsigned int grid, unsigned int ntok, int y_dtype);
 
 // Host launcher of the second prefill-regime kernel (q8_wide.cu), token tiles of 256.
 cudaError_t launch_wide_kernel(cudaStream_t stream, const CUtensorMap &tw, const CUtensorMap &tx,

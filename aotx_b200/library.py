@@ -5,11 +5,11 @@ import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libaotx_q8_b200.so")
-# AOTX_Q8_LIBRARY=experiment loads the build of `python -m aotx_b200.build --experiment` instead
+# AOTX_Q8_LIBRARY=trace loads the build of `python -m aotx_b200.build --trace` instead
 # (development only: switches, time stamps, kernels the product build does not dispatch); any
 # other value is taken as the path of a library with the same interface.
-if os.environ.get("AOTX_Q8_LIBRARY") == "experiment":
-    LIB_PATH = os.path.join(HERE, "libaotx_q8_b200_experiment.so")
+if os.environ.get("AOTX_Q8_LIBRARY") == "trace":
+    LIB_PATH = os.path.join(HERE, "libaotx_q8_b200_trace.so")
 elif os.environ.get("AOTX_Q8_LIBRARY"):
     LIB_PATH = os.path.abspath(os.environ["AOTX_Q8_LIBRARY"])
 
@@ -19,7 +19,7 @@ SYMBOLS = (
     "aotx_q8_device_status", "aotx_q8_dequant", "aotx_q8_matmul", "aotx_q8_moe_route",
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_static_status",
     "aotx_q8_matmul_peers",
-    "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused", "aotx_q8_hint_next",
+    "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused",
 )
 
 # every symbol include/aotx_gguf_b200.h declares
@@ -88,7 +88,6 @@ def declare_q8(lib):
     lib.aotx_q8_static_status.argtypes = [C.POINTER(C.c_uint32), i32]
     lib.aotx_q8_matmul_peers.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), u32,
                                          u32, u32, i32]
-    lib.aotx_q8_hint_next.argtypes = [vp, vp, u32, u32, u32]
     lib.aotx_q8_matmul_fused.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32, i32]
     lib.aotx_q8_moe_ffn_fused.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
                                           u32, vp, i32, vp, C.c_size_t]

@@ -77,6 +77,28 @@ def _torch():
     return torch
 
 
+def synth_q8_0_device(n, k, seed, device="cuda"):
+    """The same distribution generated on the device (the large tensors of the sharded
+    configurations take seconds there and minutes on the host); a different stream of numbers
+    from `synth_q8_0`.  Returns a uint8 device tensor of n * (k / 32) * 34 bytes at a 256-byte
+    aligned address."""
+    torch = _torch()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    blocks = k // 32
+    t = torch.empty(n * blocks * 34 + 256, dtype=torch.uint8, device=device)
+    off = (-t.data_ptr()) % 256
+    out = t[off:off + n * blocks * 34].view(n, blocks, 34)
+    step = max(1, (1 << 28) // k)
+    for r0 in range(0, n, step):
+        r1 = min(n, r0 + step)
+        q = torch.randint(-127, 128, (r1 - r0, blocks, 32), dtype=torch.int8, device=device, generator=gen)
+        d = (torch.randn((r1 - r0, blocks), device=device, generator=gen).abs() * (0.02 / 127.0)).half()
+        out[r0:r1, :, 2:] = q.view(torch.uint8)
+        out[r0:r1, :, :2] = d.view(torch.uint8).view(r1 - r0, blocks, 2)
+    return out.view(-1)
+
+
 def _dtype_code(dtype):
     torch = _torch()
     return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[dtype]
@@ -155,14 +177,6 @@ class Q8Context:
             _dtype_code(x.dtype), m, m_dev.data_ptr() if m_dev is not None else None,
             y.data_ptr(), _dtype_code(y.dtype)))
         return y
-
-    def hint_next(self, w_next, n=0, k=0, m=0):
-        """Name the product that follows the next one (weights `w_next[n][k]`, batch `m`), so that
-        the next product warms L2 with what that one reads first.  One-shot; None clears it."""
-        if w_next is None:
-            self._check(self.lib.aotx_q8_hint_next(self.handle, None, 0, 0, 0))
-        else:
-            self._check(self.lib.aotx_q8_hint_next(self.handle, w_next.data_ptr(), n, k, m))
 
     def matmul_fused(self, w, n, k, x, epilogue, m=None, m_dev=None, y=None, y_dtype=None, type=Q8_0):
         """The product with the next step of the layer in its store.  EPILOGUE_ADD: `y` is the

@@ -1,19 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the Q8_0 weight-matrix path.
 
-Default workload (`decode_m32_llama3_8b_layer`): one step = the four Q8_0 projections of a
-Llama-3-8B-shaped layer at a batch of 32 rows (fused QKV 4096->6144, O 4096->4096, fused
-gate+up 4096->28672, down 14336->4096), bf16 activations, float sums, bf16 results, on
-seeded synthetic weights (uniform int8, one half scale per 32 weights).  The metric is
-algorithmic bytes moved per second: every weight byte once plus the activations in and the
-results out.  Weight copies rotate between steps so that no step finds its weights in L2.
-
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-Prints one JSON line (rank 0).  `value` is timed with inputs resident in device memory;
-`e2e` runs the same steps through the library call with activations and results in pinned
-host memory, copies inside the timed region.  `--impl reference` times the reference's own
-host implementation of the product on this machine's cores over a bounded sample.
+Without --workload the line covers every configuration of the benchmark:
+
+* one GPU: the headline is the decode layer step (`decode_m32_llama3_8b_layer`: the four Q8_0
+  projections of a Llama-3-8B-shaped layer at a batch of 32 rows - fused QKV 4096->6144, O
+  4096->4096, fused gate+up 4096->28672, down 14336->4096 - bf16 activations, float sums, bf16
+  results), and `configs` holds short measurements of the single-row product, the prefill layer at
+  2048 rows, the routed experts and the LM head, each with its roofline fraction;
+* N > 1 GPUs (one rank per GPU, launched by torchrun): the headline is what shards - the LM head
+  8192 -> 151936 split by output columns over the ranks, every rank storing its slice of y into
+  all ranks' buffers from the kernel's own stores (strong scaling: the total work is fixed) - and
+  `sharded` holds that product at 8 and 64 rows and the expert-parallel routed experts, each with
+  the one-GPU time measured in the same run and the speed-up over it.
+
+All tensors are seeded synthetic (uniform int8, one half scale per 32 weights).  The metric is
+algorithmic bytes moved per second - every weight byte once plus the activations in and the
+results out - or FLOP/s for the prefill layer.  Weight copies rotate between steps so that no
+step finds its weights in L2.  Prints one JSON line (rank 0).  `value` is timed with inputs
+resident in device memory; `e2e` runs the same steps through the library call with activations
+and results in pinned host memory, copies inside the timed region.  `--impl reference` times the
+reference's own host implementation of the product on this machine's cores over a bounded sample.
 """
 import argparse
 import json
@@ -34,6 +43,8 @@ WORKLOADS = {
                                         ("gate_up", 4096, 28672), ("down", 14336, 4096)],
                                    "bfloat16", "bfloat16"),
     "gemv_m1_4096": (1, [("w", 4096, 4096)], "float16", "float16"),
+    # the LM head of configuration 4 on one GPU (the N > 1 headline splits it over the ranks)
+    "lm_head_m8": (8, [("lm_head", 8192, 151936)], "bfloat16", "bfloat16"),
     "decode_m32_gate_up": (32, [("gate_up", 4096, 28672)], "bfloat16", "bfloat16"),
     "prefill_m2048_gate_up": (2048, [("gate_up", 4096, 28672)], "bfloat16", "bfloat16"),
     "prefill_m2048_llama3_8b_layer": (2048, [("qkv", 4096, 6144), ("o", 4096, 4096),
@@ -48,9 +59,10 @@ for _name, _base in FUSED.items():
     WORKLOADS[_name] = WORKLOADS[_base]
 EPILOGUE_OF = {"o": 1, "down": 1, "gate_up": 2}  # AOTX_Q8_EPILOGUE_ADD / _SWIGLU
 
-# DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures
-# summarised under profiles/ (gate+up projection; scaled to the average launch by bytes).
-TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.0565, "decode_m32_gate_up": 1.0565}
+# DRAM bytes (read + write) per algorithmic byte of the dominant kernel: one ncu capture of the
+# gate+up projection at 32 rows, scaled to the average launch by bytes (source named in the line).
+TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.2267, "decode_m32_gate_up": 1.2267}
+TRAFFIC_SOURCE = "profiles/q8_decode_kernel_gate_up_m32.md (28672 x 4096, 32 rows, one launch)"
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up", "prefill_m2048_llama3_8b_layer_fused"}
 
 
@@ -192,18 +204,8 @@ def run_ours(args, rank, world, local_rank):
         t["y"] = torch.zeros(shape, dtype=kind, device="cuda")
         t["y_host"] = torch.empty(shape, dtype=kind).pin_memory()
 
-    def following(i, c):
-        """The product after tensors[i] of step c: steps run with copy c, c + 1, ..."""
-        if i + 1 < len(tensors):
-            t = tensors[i + 1]
-            return t["w"][c], t["n"], t["k"], m
-        t = tensors[0]
-        return t["w"][(c + 1) % copies], t["n"], t["k"], m
-
     def product(i, c):
         t = tensors[i]
-        if args.prefetch_next:
-            ctx.hint_next(*following(i, c))
         if t["mode"]:
             ctx.matmul_fused(t["w"][c], t["n"], t["k"], t["x"], t["mode"], y=t["y"])
         else:
@@ -357,10 +359,11 @@ def run_ours(args, rank, world, local_rank):
         metric, unit = "q8_decode_gemm_hbm_gbs", "GB/s"
     ratio = TRAFFIC_RATIO.get(args.workload)
     roofline["traffic"] = ratio * step_bytes / launches if ratio else None
+    roofline["traffic_source"] = TRAFFIC_SOURCE if ratio else None
     roofline["peak_source"] = peak_kind
     # the nominal figures, for context only (HBM3e 7.7 TB/s; dense bf16 2250 TFLOP/s)
     roofline["frac_of_nominal"] = achieved / (2250.0 if tensor_bound else 7700.0)
-    roofline["kernel"] = "q8_stream_kernel"
+    roofline["kernel"] = "q8_wide_kernel" if tensor_bound else "q8_decode_kernel"
     roofline["launches_timed"] = launches * args.steps
     roofline["avg_launch_us"] = kernel_ms * 1e3
     roofline["bytes_per_launch"] = step_bytes / launches
@@ -379,8 +382,7 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": args.workload, "rows": m, "x": x_name, "y": y_name,
                    "projections": {name: [k, n] for name, k, n in projections},
                    "weight_copies_rotated": copies, "l2": "weight copies rotate; total > 3x L2",
-                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True,
-                   "prefetch_next": bool(args.prefetch_next)},
+                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode, "host_result_matches_device": check},
@@ -388,6 +390,9 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "device_status": status,
     }
+    if world == 1 and args.composite:
+        # the other configurations of the benchmark, measured briefly in the same run
+        line["configs"] = measure_configs(torch, ctx, tensors, copies)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
         try:
@@ -409,97 +414,99 @@ SHARDED = {
 }
 
 
-def run_sharded(args, rank, world, local_rank):
-    """Strong-scaling workloads: the total work is fixed, the ranks split it."""
-    import torch
+def setup_lm_head(torch, ctx, world, rank, m, fused, copies=2):
+    """BASELINE config 4, LM head: rows of w split over the ranks.  Returns (step, bytes, launches,
+    config, result) where result() is the y[m][n] of the last step on this rank."""
     import aotx_b200
-    from aotx_b200.sharded import (ColumnSplit, column_split_on_gpu, expert_parallel_on_gpu, shard_rows)
+    from aotx_b200.sharded import column_split_on_gpu, shard_rows
+    spec = SHARDED["lm_head_colsplit"]
+    n, k = spec["n"], spec["k"]
+    first, last = shard_rows(n, world, rank)
+    shards = [aotx_b200.synth_q8_0_device(last - first, k, 7000 + 10 * rank + c) for c in range(copies)]
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+    state = {}
+    if fused and world > 1:
+        from aotx_b200.sharded import ColumnSplitFused
+        objects = [ColumnSplitFused(ctx, w, n, k, world, rank, m, torch.bfloat16) for w in shards]
 
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = aotx_b200.Q8Context(local_rank)
-    hbm_peak, tensor_peak, peak_kind = measured_peaks()
-    spec = SHARDED[args.workload]
-    copies = 2
-    if args.workload == "lm_head_colsplit":
-        n, k, m = spec["n"], spec["k"], args.rows
-        first, last = shard_rows(n, world, rank)
-        rows = last - first
-        shards = []
-        for c in range(copies):
-            host = aotx_b200.synth_q8_0(rows, k, 7000 + 10 * rank + c)
-            shards.append(torch.from_numpy(host).cuda())
-        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        if args.fused and world > 1:
-            from aotx_b200.sharded import ColumnSplitFused
-            fused = [ColumnSplitFused(ctx, w, n, k, world, rank, m, torch.bfloat16) for w in shards]
-
-            # One barrier per step is enough here even inside a graph: the step rotates over
-            # `copies` >= 2 of these objects, so another barrier of the same ranks lies between
-            # two uses of one object's buffer.
-            def step(c):
-                fused[c].matmul(x, m, opening_barrier=False if copies >= 2 else None)
-        else:
-            splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
-            out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-
-            def step(c):
-                splits[c].matmul(x, m, out=out)
-
-        step_bytes = n * (k // 32) * 34 + m * k * 2 + m * n * 2
-        launches = 1
-        config = {"workload": args.workload, "rows": m, "n": n, "k": k, "x": "bfloat16", "y": "bfloat16",
-                  "parallelism": ("column split x%d, slices stored into peers by the kernel" if args.fused
-                                  else "column split x%d + all-gather") % world}
+        # One barrier per step is enough here even inside a graph: the step rotates over
+        # `copies` >= 2 of these objects, so another barrier of the same ranks lies between
+        # two uses of one object's buffer.
+        def step(c):
+            state["y"] = objects[c].matmul(x, m, opening_barrier=False if copies >= 2 else None)
     else:
-        tokens, experts, used = spec["tokens"], spec["experts"], spec["used"]
-        hidden, ffn = spec["hidden"], spec["ffn"]
-        e0, e1 = shard_rows(experts, world, rank)
-        t0, t1 = shard_rows(tokens, world, rank)
-        local = e1 - e0
-        sets = []
-        for c in range(copies):
-            sets.append(tuple(torch.from_numpy(aotx_b200.synth_q8_0(local * r, kk, 8000 + 100 * c + 10 * rank + i)).cuda()
-                              for i, (r, kk) in enumerate(((ffn, hidden), (ffn, hidden), (hidden, ffn)))))
-        gen = torch.Generator(device="cuda").manual_seed(11)
-        x_all = torch.randn(tokens, hidden, device="cuda", generator=gen).half()
-        router = (torch.randn(experts, hidden, device="cuda", generator=gen) / hidden ** 0.5).float()
-        prob_all, ids_all = ctx.moe_route(x_all, router, used)
-        x_loc, prob, ids = x_all[t0:t1].contiguous(), prob_all[t0:t1].contiguous(), ids_all[t0:t1].contiguous()
-        if world == 1:
-            ws = ctx.moe_workspace(tokens, used, hidden, ffn)
-            out = torch.empty((tokens, hidden), dtype=torch.float32, device="cuda")
-            if args.moe_fused:
-                # gate and up of every expert as one tensor with the rows interleaved
-                both = [torch.from_numpy(aotx_b200.interleave_rows(g.cpu().numpy(), u.cpu().numpy(), hidden,
-                                                                   groups=experts)).cuda()
-                        for g, u, _ in sets]
+        splits = [column_split_on_gpu(ctx, w, n, k, world, rank, y_dtype=torch.bfloat16) for w in shards]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
 
-                def step(c):
-                    ctx.moe_ffn_fused(both[c], sets[c][2], experts, hidden, ffn, x_loc, prob, ids, out=out,
-                                      workspace=ws)
-            else:
-                def step(c):
-                    ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
-        else:
-            eps = [expert_parallel_on_gpu(ctx, *sets[c], experts, used, hidden, ffn, world, rank)
-                   for c in range(copies)]
+        def step(c):
+            state["y"] = splits[c].matmul(x, m, out=out)
+
+    step_bytes = n * (k // 32) * 34 + m * k * 2 + m * n * 2
+    config = {"workload": "lm_head_colsplit", "rows": m, "n": n, "k": k, "x": "bfloat16", "y": "bfloat16",
+              "parallelism": "single" if world == 1 else
+              ("column split x%d, slices stored into peers by the kernel" if fused
+               else "column split x%d + all-gather") % world}
+    return step, step_bytes, 1, config, (lambda: state.get("y")), x
+
+
+def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
+    """BASELINE config 3: Qwen3-30B-A3B-shaped routed experts, expert parallel over the ranks."""
+    import aotx_b200
+    from aotx_b200.sharded import expert_parallel_on_gpu, shard_rows
+    spec = SHARDED["moe_qwen3_30b_a3b"]
+    tokens, experts, used = spec["tokens"], spec["experts"], spec["used"]
+    hidden, ffn = spec["hidden"], spec["ffn"]
+    e0, e1 = shard_rows(experts, world, rank)
+    t0, t1 = shard_rows(tokens, world, rank)
+    local = e1 - e0
+    sets = []
+    for c in range(copies):
+        sets.append(tuple(aotx_b200.synth_q8_0_device(local * r, kk, 8000 + 100 * c + 10 * rank + i)
+                          for i, (r, kk) in enumerate(((ffn, hidden), (ffn, hidden), (hidden, ffn)))))
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    x_all = torch.randn(tokens, hidden, device="cuda", generator=gen).half()
+    router = (torch.randn(experts, hidden, device="cuda", generator=gen) / hidden ** 0.5).float()
+    prob_all, ids_all = ctx.moe_route(x_all, router, used)
+    x_loc, prob, ids = x_all[t0:t1].contiguous(), prob_all[t0:t1].contiguous(), ids_all[t0:t1].contiguous()
+    if world == 1:
+        ws = ctx.moe_workspace(tokens, used, hidden, ffn)
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device="cuda")
+        if moe_fused:
+            # gate and up of every expert as one tensor with the rows interleaved
+            both = [torch.from_numpy(aotx_b200.interleave_rows(g.cpu().numpy(), u.cpu().numpy(), hidden,
+                                                               groups=experts)).cuda()
+                    for g, u, _ in sets]
 
             def step(c):
-                eps[c].ffn(x_loc, prob, ids)
+                ctx.moe_ffn_fused(both[c], sets[c][2], experts, hidden, ffn, x_loc, prob, ids, out=out,
+                                  workspace=ws)
+        else:
+            def step(c):
+                ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
+    else:
+        eps = [expert_parallel_on_gpu(ctx, *sets[c], experts, used, hidden, ffn, world, rank)
+               for c in range(copies)]
 
-        hit = int((torch.bincount(ids_all.reshape(-1).long(), minlength=experts) > 0).sum())
-        slice_bytes = 2 * ffn * (hidden // 32) * 34 + hidden * (ffn // 32) * 34
-        step_bytes = hit * slice_bytes + tokens * hidden * 2 + tokens * hidden * 4
-        launches = 5 if (args.moe_fused and world == 1) else 8
-        config = {"workload": args.workload, "interleaved_gate_up": bool(args.moe_fused and world == 1),
-                  "tokens": tokens, "experts": experts, "used": used,
-                  "hidden": hidden, "ffn": ffn, "experts_hit": hit, "x": "float16", "y": "float32",
-                  "router": "selections made once outside the timed region",
-                  "parallelism": "expert parallel x%d + all-to-all" % world if world > 1 else "single"}
+        def step(c):
+            eps[c].ffn(x_loc, prob, ids)
 
+    hit = int((torch.bincount(ids_all.reshape(-1).long(), minlength=experts) > 0).sum())
+    slice_bytes = 2 * ffn * (hidden // 32) * 34 + hidden * (ffn // 32) * 34
+    step_bytes = hit * slice_bytes + tokens * hidden * 2 + tokens * hidden * 4
+    launches = 5 if (moe_fused and world == 1) else 8
+    config = {"workload": "moe_qwen3_30b_a3b", "interleaved_gate_up": bool(moe_fused and world == 1),
+              "tokens": tokens, "experts": experts, "used": used,
+              "hidden": hidden, "ffn": ffn, "experts_hit": hit, "x": "float16", "y": "float32",
+              "router": "selections made once outside the timed region",
+              "parallelism": "expert parallel x%d + all-to-all" % world if world > 1 else "single"}
+    return step, step_bytes, launches, config
+
+
+def time_steps(torch, step, copies, steps, warmup, world, capture=True):
+    """Warm up, then time `steps` steps that rotate over `copies` weight copies: CUDA events
+    between two barriers, the maximum over the ranks.  Each copy's step is captured into a CUDA
+    graph where that works.  Returns (total ms, captured, run) - `run(c)` replays one step."""
     def barrier():
         if world > 1:
             import torch.distributed as dist
@@ -509,7 +516,7 @@ def run_sharded(args, rank, world, local_rank):
     step(0)
     barrier()
     graphs = None
-    if args.workload == "lm_head_colsplit" or world == 1:
+    if capture:
         try:
             graphs = []
             side = torch.cuda.Stream()
@@ -523,28 +530,62 @@ def run_sharded(args, rank, world, local_rank):
         except Exception:
             graphs = None
     run = (lambda c: graphs[c].replay()) if graphs else step
-    for i in range(max(args.warmup, 3)):
+    for i in range(max(warmup, 3)):
         run(i % copies)
     barrier()
-    sampler = ClockSampler(device_index(local_rank))
-    sampler.start()
     e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0_.record()
-    for i in range(args.steps):
+    for i in range(steps):
         run(i % copies)
     e1_.record()
     barrier()
     total_ms = e0_.elapsed_time(e1_)
-    sampler.stop_flag.set()
-    sampler.join()
-    status = ctx.device_status()
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t[0])
+    return total_ms, bool(graphs), run
+
+
+def leave_together(torch, world):
+    """Graphs that hold captured collectives must go before the process group does; tearing the
+    group down first left every rank waiting at exit."""
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def run_sharded(args, rank, world, local_rank):
+    """Strong-scaling workloads: the total work is fixed, the ranks split it."""
+    import torch
+    import aotx_b200
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = aotx_b200.Q8Context(local_rank)
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    copies = 2
+    if args.workload == "lm_head_colsplit":
+        step, step_bytes, launches, config, _, _ = setup_lm_head(torch, ctx, world, rank, args.rows, args.fused, copies)
+        capture = True
+    else:
+        step, step_bytes, launches, config = setup_moe(torch, ctx, world, rank, args.moe_fused, copies)
+        capture = world == 1
+    sampler = ClockSampler(device_index(local_rank))
+    sampler.start()
+    total_ms, captured, run = time_steps(torch, step, copies, args.steps, args.warmup, world, capture)
+    sampler.stop_flag.set()
+    sampler.join()
+    status = ctx.device_status()
     value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
-    config["cuda_graph"] = bool(graphs)
+    config["cuda_graph"] = captured
     config["l2"] = "two weight copies rotate; each larger than L2 at N=1"
     line = {
         "metric": "q8_decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -558,17 +599,167 @@ def run_sharded(args, rank, world, local_rank):
     }
     if rank == 0:
         print(json.dumps(mark_library(line)), flush=True)
-    # Graphs that hold captured collectives must go before the process group does; tearing the
-    # group down first left every rank waiting at exit.
-    graphs = None
     run = None
-    torch.cuda.synchronize()
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        os._exit(0)
+    leave_together(torch, world)
+
+
+def summary(workload, ms, step_bytes=None, step_flops=None, **more):
+    """One entry of `configs` / `sharded`: time per step and the fraction of the binding roofline."""
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    entry = {"workload": workload, "ms_per_step": ms}
+    if step_flops is not None:
+        achieved = step_flops / (ms * 1e-3) / 1e12
+        entry.update({"achieved": achieved, "unit": "TFLOP/s", "bound": "tensor", "peak": tensor_peak,
+                      "frac": achieved / tensor_peak})
+    else:
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        entry.update({"achieved": achieved, "unit": "GB/s", "bound": "hbm", "peak": hbm_peak,
+                      "frac": achieved / hbm_peak})
+    entry["peak_source"] = peak_kind
+    entry.update(more)
+    return entry
+
+
+# shapes of the brief measurements (module level so that a dry run can shrink them)
+GEMV_SHAPE = {"n": 4096, "k": 4096, "copies": 24}
+PREFILL_ROWS = 2048
+
+
+def measure_configs(torch, ctx, layer, copies, steps=40):
+    """Configurations 0, 2, 3 and the LM head of configuration 4 on this GPU: a few dozen steps
+    each after three warm-up steps, weight copies rotating (larger than L2 in total)."""
+    import aotx_b200
+    out = []
+    # configuration 0: one row of x against 4096 x 4096, half in and out
+    n, k, many = GEMV_SHAPE["n"], GEMV_SHAPE["k"], GEMV_SHAPE["copies"]
+    ws = [aotx_b200.synth_q8_0_device(n, k, 300 + c) for c in range(many)]
+    x = torch.randn(1, k, device="cuda").half()
+    y = torch.empty(1, n, dtype=torch.float16, device="cuda")
+    ms, _, _ = time_steps(torch, lambda c: ctx.matmul(ws[c], n, k, x, y=y), many, many * 8, many, 1)
+    out.append(summary("gemv_m1_4096", ms / (many * 8), step_bytes=n * (k // 32) * 34 + k * 2 + n * 2, rows=1,
+                       us_per_launch=ms / (many * 8) * 1e3))
+    del ws
+    # configuration 2: the same layer at 2048 rows, bfloat16 in and out
+    m = PREFILL_ROWS
+    xs = [torch.randn(m, t["k"], device="cuda").to(torch.bfloat16) for t in layer]
+    ys = [torch.empty(m, t["n"], dtype=torch.bfloat16, device="cuda") for t in layer]
+
+    def prefill(c):
+        for t, xx, yy in zip(layer, xs, ys):
+            ctx.matmul(t["w"][c], t["n"], t["k"], xx, y=yy)
+
+    ms, _, _ = time_steps(torch, prefill, copies, steps, 3, 1)
+    projections = [(t["name"], t["k"], t["n"]) for t in layer]
+    out.append(summary("prefill_m2048_llama3_8b_layer", ms / steps, step_flops=flops(m, projections), rows=m,
+                       tokens_per_s=m * steps / (ms * 1e-3)))
+    del xs, ys
+    # configuration 3: routed experts, 512 tokens, 128 experts, 8 used
+    step, step_bytes, launches, config = setup_moe(torch, ctx, 1, 0)
+    ms, _, run = time_steps(torch, step, 2, steps, 3, 1)
+    out.append(summary("moe_qwen3_30b_a3b", ms / steps, step_bytes=step_bytes, launches_per_step=launches,
+                       experts_hit=config["experts_hit"]))
+    run = step = None
+    # configuration 4: the LM head on one GPU, 8 rows
+    step, step_bytes, launches, config, _, _ = setup_lm_head(torch, ctx, 1, 0, 8, False)
+    ms, _, run = time_steps(torch, step, 2, steps, 3, 1)
+    out.append(summary("lm_head_8192_to_151936_m8", ms / steps, step_bytes=step_bytes, rows=8))
+    run = step = None
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_scaling(args, rank, world, local_rank):
+    """N > 1: what shards.  The headline is the LM head column split at 8 rows (strong scaling,
+    the gather in the kernel's own stores); `sharded` adds 64 rows and the expert-parallel routed
+    experts, each with the one-GPU time of the same run."""
+    import torch
+    import torch.distributed as dist
+    import aotx_b200
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = aotx_b200.Q8Context(local_rank)
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    copies = 2
+    short = max(10, min(args.steps, 100))
+    sharded = {}
+
+    # one-GPU figures first (every rank runs them on its own GPU; rank 0's are reported)
+    single = {}
+    for rows in (8, 64):
+        step, step_bytes, _, _, _, _ = setup_lm_head(torch, ctx, 1, 0, rows, False, copies)
+        ms, _, run = time_steps(torch, step, copies, short, 3, 1)
+        single["lm_head_m%d" % rows] = ms / short
+        run = step = None
+        torch.cuda.empty_cache()
+    step, moe_bytes, _, _ = setup_moe(torch, ctx, 1, 0, False, copies)
+    ms, _, run = time_steps(torch, step, copies, short, 3, 1)
+    single["moe"] = ms / short
+    run = step = None
+    torch.cuda.empty_cache()
+    dist.barrier()
+
+    # the headline: LM head, 8 rows, fused column split
+    step, step_bytes, launches, config, result, x_dev = setup_lm_head(torch, ctx, world, rank, 8, True, copies)
+    sampler = ClockSampler(device_index(local_rank))
+    sampler.start()
+    total_ms, captured, run = time_steps(torch, step, copies, args.steps, args.warmup, world)
+    sampler.stop_flag.set()
+    sampler.join()
+    value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+    # end to end: x from pinned host memory every step, the gathered y back to the host
+    x_host = x_dev.cpu().pin_memory()
+    y_host = torch.empty((8, config["n"]), dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e(c):
+        x_dev.copy_(x_host, non_blocking=True)
+        step(c)
+        y_host.copy_(result(), non_blocking=True)
+
+    e2e_ms, _, run_e2e = time_steps(torch, step_e2e, copies, args.steps, 3, world, capture=False)
+    e2e_value = step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
+    sharded["lm_head_m8"] = summary("lm_head_colsplit", total_ms / args.steps, step_bytes=step_bytes, rows=8,
+                                    one_gpu_ms=single["lm_head_m8"],
+                                    speedup_over_one_gpu=single["lm_head_m8"] / (total_ms / args.steps),
+                                    frac_per_gpu=value / world / hbm_peak)
+    run = run_e2e = None
+
+    step64, bytes64, _, _, _, _ = setup_lm_head(torch, ctx, world, rank, 64, True, copies)
+    ms64, _, run = time_steps(torch, step64, copies, short, 3, world)
+    sharded["lm_head_m64"] = summary("lm_head_colsplit", ms64 / short, step_bytes=bytes64, rows=64,
+                                     one_gpu_ms=single["lm_head_m64"],
+                                     speedup_over_one_gpu=single["lm_head_m64"] / (ms64 / short),
+                                     frac_per_gpu=bytes64 * short / (ms64 * 1e-3) / 1e9 / world / hbm_peak)
+    run = step64 = None
+    torch.cuda.empty_cache()
+
+    step_moe, moe_bytes, _, moe_config = setup_moe(torch, ctx, world, rank, False, copies)
+    ms_moe, _, run = time_steps(torch, step_moe, copies, short, 3, world, capture=False)
+    sharded["moe_expert_parallel"] = summary("moe_qwen3_30b_a3b", ms_moe / short, step_bytes=moe_bytes,
+                                             one_gpu_ms=single["moe"],
+                                             speedup_over_one_gpu=single["moe"] / (ms_moe / short),
+                                             frac_per_gpu=moe_bytes * short / (ms_moe * 1e-3) / 1e9 / world / hbm_peak)
+    run = step_moe = None
+    status = ctx.device_status()
+    config["cuda_graph"] = captured
+    config["l2"] = "two weight copies rotate; the whole tensor is ten times L2"
+    line = {
+        "metric": "q8_decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16/bf16 operands, f32 sums", "data": "synthetic", "config": config,
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": value / world / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                     "kernel": "q8_decode_kernel", "note": "per GPU, whole step including the exchange"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_ms / args.steps,
+                "mode": "eager calls, x up and the gathered y down on rank 0's stream every step"},
+        "sharded": sharded,
+        "gpu_launches": launches * args.steps, "clocks": sampler.summary(), "device_status": status,
+    }
+    if rank == 0:
+        print(json.dumps(mark_library(line)), flush=True)
+    leave_together(torch, world)
 
 
 def cpu_sample(workload, fraction):
@@ -715,21 +906,28 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
-    parser.add_argument("--workload", default="decode_m32_llama3_8b_layer",
-                        choices=sorted(WORKLOADS) + sorted(SHARDED))
+    parser.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(SHARDED),
+                        help="one workload alone; by default the line covers every configuration")
     parser.add_argument("--rows", type=int, default=8, help="rows of x for lm_head_colsplit")
     parser.add_argument("--fused", action="store_true",
                         help="lm_head_colsplit: store the slices into the peers instead of an all-gather")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-configs", action="store_true",
+                        help="one GPU, default workload: leave out the `configs` measurements")
     parser.add_argument("--moe-fused", action="store_true",
                         help="moe_qwen3_30b_a3b on one GPU: interleaved gate+up tensor, gated unit in the store")
-    parser.add_argument("--prefetch-next", action="store_true",
-                        help="name the next projection's weights before each product (aotx_q8_hint_next)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    args.composite = args.workload is None and not args.no_configs
+    if args.workload is None:
+        if world > 1 and args.impl != "reference":
+            run_scaling(args, rank, world, local_rank)
+            return
+        # the reference arm follows the headline: the LM head where the ranks split it
+        args.workload = "lm_head_m8" if world > 1 else "decode_m32_llama3_8b_layer"
     if args.impl == "reference":
         if args.steps > 20:
             args.steps = 20

@@ -87,21 +87,6 @@ int aotx_q8_set_path(aotx_q8_ctx *ctx, int path);
  * overlap off around such a sequence.  No counterpart in the reference. */
 int aotx_q8_set_overlap(aotx_q8_ctx *ctx, int enabled);
 
-/* Name the product that will FOLLOW the next one on the stream: its Q8_0 weights w_next[n][k]
- * and its batch m (the largest, where a device word gives the live one).  The next
- * aotx_q8_matmul / aotx_q8_matmul_fused on this context that runs on the tensor-core kernel
- * then asks L2, from every block once that block has issued its own last weight copy, for the
- * weight bytes the same block index reads first in the named product (about 32 MiB over the
- * whole grid), so that the memory system keeps moving while one launch drains and the following
- * one fills its pipeline.  One-shot: the hint belongs to the next product call of any kind and
- * is forgotten after it; a null w_next clears it; a shape the tensor-core kernel does not take
- * is ignored.  It changes no result; w_next must be valid device memory of n * (k / 32) * 34
- * bytes.  A caller that captures a layer knows the order of its tensors
- * (cuda/model/graph_host.cu:64-96) and can name each next one.  No counterpart in the
- * reference. */
-int aotx_q8_hint_next(aotx_q8_ctx *ctx, const void *w_next, uint32_t n_next, uint32_t k_next,
-                      uint32_t m_next);
-
 /* The last CUDA error code an entry point of this context saw (cudaError_t as int). */
 int aotx_q8_last_cuda_error(const aotx_q8_ctx *ctx);
 

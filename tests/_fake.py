@@ -65,7 +65,6 @@ class FakeContext:
         self.oracle = Oracle()
         self.Q8Error = Q8Error
         self.path = 0
-        self.hint = None
 
     # -- housekeeping -------------------------------------------------------------------
     def close(self):
@@ -82,10 +81,6 @@ class FakeContext:
     def set_overlap(self, enabled):
         pass
 
-    def hint_next(self, w_next, n=0, k=0, m=0):
-        self.hint = None if w_next is None else (n, k, m)
-
-    # -- helpers ------------------------------------------------------------------------
     def _weights(self, kind, w, n, k):
         from aotx_b200.q8 import row_bytes
         w = w.numpy() if hasattr(w, "numpy") else np.asarray(w)
@@ -123,7 +118,6 @@ class FakeContext:
         return out
 
     def matmul(self, w, n, k, x, m=None, m_dev=None, y=None, y_dtype=None, type=8):
-        self.hint = None
         self._check_shape(type, k)
         if self.path == 2 and (type != 8 or k % 256 != 0):
             raise self.Q8Error(4)   # the forced tensor-core kernel cannot take it
@@ -137,7 +131,6 @@ class FakeContext:
         return y
 
     def matmul_fused(self, w, n, k, x, epilogue, m=None, m_dev=None, y=None, y_dtype=None, type=8):
-        self.hint = None
         if epilogue == 0:
             return self.matmul(w, n, k, x, m=m, m_dev=m_dev, y=y, y_dtype=y_dtype, type=type)
         if type != 8:
@@ -189,14 +182,12 @@ class FakeContext:
 
     def moe_ffn(self, w_gate, w_up, w_down, experts, hidden, ffn, x, prob, ids, tokens=None,
                 tokens_dev=None, out=None, out_dtype=None, workspace=None, type=8):
-        self.hint = None
         return self._moe(w_gate.numpy(), w_up.numpy(), w_down.numpy(), experts, hidden, ffn, x, prob, ids,
                          tokens, out, out_dtype)
 
     def moe_ffn_fused(self, w_gate_up, w_down, experts, hidden, ffn, x, prob, ids, tokens=None,
                       tokens_dev=None, out=None, out_dtype=None, workspace=None, type=8):
         from aotx_b200.q8 import row_bytes
-        self.hint = None
         if hidden % 256 or ffn % 256:
             raise self.Q8Error(4)
         rows = w_gate_up.numpy().reshape(-1, row_bytes(hidden))

@@ -56,24 +56,9 @@ def check_product(oracle, w, n, k, x_bits, m, y, bf16=False, full_limit=6e9, spo
 
 
 def device_synth_q8_0(n, k, seed):
-    """Seeded synthetic Q8_0 rows in the benchmark's distribution, generated on the device (the
-    large tensors of the sharded configurations take seconds there and minutes on the host).
-    Returns the device tensor (256-byte aligned) of n * (k / 32) * 34 bytes."""
-    torch = torch_mod()
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(seed)
-    blocks = k // 32
-    t = torch.empty(n * blocks * 34 + 256, dtype=torch.uint8, device="cuda")
-    off = (-t.data_ptr()) % 256
-    out = t[off:off + n * blocks * 34].view(n, blocks, 34)
-    step = max(1, (1 << 28) // k)
-    for r0 in range(0, n, step):
-        r1 = min(n, r0 + step)
-        q = torch.randint(-127, 128, (r1 - r0, blocks, 32), dtype=torch.int8, device="cuda", generator=gen)
-        d = (torch.randn((r1 - r0, blocks), device="cuda", generator=gen).abs() * (0.02 / 127.0)).half()
-        out[r0:r1, :, 2:] = q.view(torch.uint8)
-        out[r0:r1, :, :2] = d.view(torch.uint8).view(r1 - r0, blocks, 2)
-    return out.view(-1)
+    """Seeded synthetic Q8_0 rows in the benchmark's distribution, generated on the device."""
+    import aotx_b200
+    return aotx_b200.synth_q8_0_device(n, k, seed)
 
 
 def check_columns(oracle, w_host, n, k, x_bits, m, y, bf16=True, columns=192, seed=77):

@@ -5,7 +5,7 @@
 // the device has AOTX_EMULATED_SMS multiprocessors (six unless set), so that grids stay small.
 // What this adds to tests/stream_emu.cu, which calls the kernels with arguments the test driver
 // fills in: here the library's own host code fills them in - argument checks and return codes,
-// the choice of kernel, tensor maps, grids, scratch sets, workspaces, the hint for the following
+// the choice of kernel, tensor maps, grids, scratch sets, workspaces, and
 // product, the order of the launches of the routed-expert step.
 //
 // Built as a shared library by tests/test_api_emu.py.
@@ -109,10 +109,3 @@ extern "C" void api_emu_mode(int asynchronous, unsigned int max_delay_us)
     set_mode(asynchronous, max_delay_us);
 }
 
-// Bytes the launches asked L2 for since the last call of this function.
-extern "C" unsigned long long api_emu_l2_bytes()
-{
-    const unsigned long long bytes = q8::l2_requests;
-    q8::l2_requests = 0;
-    return bytes;
-}

@@ -154,7 +154,6 @@ inline void fence()
 #define mbar_arrive ptx_mbar_arrive
 #define ld_acquire_gpu ptx_ld_acquire_gpu
 #define st_release_gpu ptx_st_release_gpu
-#define l2_prefetch_bulk ptx_l2_prefetch_bulk
 #include "q8_common.cuh"
 #undef tmem_ld_32x32
 #undef tmem_ld_32x16
@@ -163,7 +162,6 @@ inline void fence()
 #undef mbar_arrive
 #undef ld_acquire_gpu
 #undef st_release_gpu
-#undef l2_prefetch_bulk
 
 // ... and the stand-ins take the names the tile header calls
 namespace q8 {
@@ -191,7 +189,6 @@ inline void tmem_ld_32x16(uint32_t taddr, uint32_t *v)
 inline void tmem_ld_wait() {}
 inline void tc_fence_before_sync() {}
 inline void mbar_arrive(uint32_t) {}
-inline void l2_prefetch_bulk(const void *, uint32_t) {}
 
 inline uint32_t ld_acquire_gpu(const unsigned int *p)
 {

@@ -370,19 +370,6 @@ inline void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, in
     q8emu::issue(q8emu::copy_engine, [=] { emu_tma_load_2d(dst, map, bar, c0, c1); });
 }
 
-inline unsigned long long l2_requests = 0;
-
-inline void l2_prefetch_bulk(const void *addr, uint32_t bytes)
-{
-    // nothing to warm; the ranges are checked by the caller's test through the count
-    if ((reinterpret_cast<uintptr_t>(addr) & 15u) != 0u || (bytes & 15u) != 0u || bytes == 0u) {
-        q8emu::lane_violations += 1u;
-        q8emu::violation_kinds |= 8u;
-    }
-    std::lock_guard<std::mutex> lock(q8emu::barrier_mutex);
-    l2_requests += bytes;
-}
-
 inline void tmem_alloc(uint32_t smem_result, uint32_t columns)
 {
     // the allocation sits at the top of the 512 columns, so a kernel that takes fewer than all of

@@ -1,9 +1,9 @@
-"""Random-interleaving models of the two kernels' ring protocols (test infrastructure).
+"""Random-interleaving model of the decode-regime kernel's ring protocol (test infrastructure).
 
 The kernels hand stages of shared and tensor memory between warps through mbarriers that are
 waited on by phase parity.  A parity wait cannot tell a phase from the one two phases later,
 so a ring is only safe if no waiter can get two phases ahead of the barrier it polls.  These
-models run the barrier protocol of aotx_b200/csrc/q8_stream.cu and q8_umma.cu (same counts,
+model runs the barrier protocol of aotx_b200/csrc/q8_stream.cu (same counts,
 same parity formulas, same order of waits and arrivals per warp) as cooperating generators
 under a random scheduler, with copies and MMAs completing asynchronously after random delays,
 and record any read of a stage that does not hold the expected piece."""
@@ -103,83 +103,6 @@ def weight_producer(mach, raw, raw_full, raw_empty, pieces):
 
         mach.later(land)
         yield
-
-
-def wide_kernel(seed, raw_stages, mma_stages, x_stages, segments, subs=4):
-    """q8_umma_kernel: A stages in shared memory, one hand-over per 64-deep step."""
-    mach = Machine(seed)
-    raw = [None] * raw_stages
-    raw_full = [Barrier(1) for _ in range(raw_stages)]
-    raw_empty = [Barrier(8) for _ in range(raw_stages)]
-    xs = [None] * x_stages
-    x_full = [Barrier(1) for _ in range(x_stages)]
-    x_empty = [Barrier(1) for _ in range(x_stages)]
-    a_rows = [dict() for _ in range(mma_stages)]
-    a_full = [Barrier(4) for _ in range(mma_stages)]
-    mma_empty = [Barrier(1) for _ in range(mma_stages)]
-    steps = segments * subs
-
-    def x_producer():
-        for q in range(steps):
-            st, ph = q % x_stages, (q // x_stages) & 1
-            while not x_empty[st].passed(ph ^ 1):
-                yield
-            x_full[st].expect(1)
-            xs[st] = ("in flight", q)
-
-            def land(st=st, q=q):
-                xs[st] = q
-                x_full[st].complete(1)
-
-            mach.later(land)
-            yield
-
-    def issuer():
-        for q in range(steps):
-            st, ph = q % mma_stages, (q // mma_stages) & 1
-            xst, xph = q % x_stages, (q // x_stages) & 1
-            while not a_full[st].passed(ph):
-                yield
-            while not x_full[xst].passed(xph):
-                yield
-
-            def execute(st=st, xst=xst, q=q):
-                for w in range(4):
-                    if a_rows[st].get(w) != q:
-                        mach.errors.append(("A stage", q, st, w, a_rows[st].get(w)))
-                if xs[xst] != q:
-                    mach.errors.append(("x stage", q, xs[xst]))
-                mma_empty[st].arrive()
-                x_empty[xst].arrive()
-
-            mach.mma_queue.append(execute)
-            yield
-
-    def converter(cw):
-        half, w = cw >> 2, cw & 3
-        for g in range(segments):
-            rst, rph = g % raw_stages, (g // raw_stages) & 1
-            while not raw_full[rst].passed(rph):
-                yield
-            for _ in range(mach.rnd.randint(0, 3)):
-                yield
-            if raw[rst] != g:
-                mach.errors.append(("raw stage", g, raw[rst], cw))
-            raw_empty[rst].arrive()
-            for jj in range(2):
-                q = g * subs + half * 2 + jj
-                st, ph = q % mma_stages, (q // mma_stages) & 1
-                while not mma_empty[st].passed(ph ^ 1):
-                    yield
-                for _ in range(mach.rnd.randint(0, 4)):
-                    yield
-                a_rows[st][w] = q
-                a_full[st].arrive()
-                yield
-
-    agents = [weight_producer(mach, raw, raw_full, raw_empty, segments), x_producer(), issuer()]
-    agents += [converter(c) for c in range(8)]
-    return mach.run(agents)
 
 
 def stream_kernel(seed, raw_stages, depth, segments, bf16):

@@ -10,8 +10,8 @@
 //   4. last_holder() names exactly the blocks that hold the remaining segments of that tile,
 //      and they are the blocks directly after the owner;
 //   5. no block that takes part is without work;
-//   6. the bytes a launch asks L2 for on behalf of the next product (next_unit_pieces) are
-//      exactly the weight bytes of the first units of the same block index there.
+//   6. the decode kernel's own 32-bit range arithmetic (decode_range, decode_holder in
+//      q8_decode.cu) deals every unit once and names the block that holds a unit.
 //
 // Prints "ok <cases>" and exits 0, or the first violated property and exits 1.
 #include <cstdio>
@@ -116,84 +116,25 @@ static int check(unsigned long long tiles, uint32_t segs, unsigned int grid, boo
     return 0;
 }
 
-// The pieces a launch asks L2 for on behalf of the next product (next_unit_pieces) are exactly
-// the bytes that the same block index reads in its first units there: inside the tensor, on
-// 16-byte boundaries, each (row, segment) of those units once.
-struct RecordEmit {
-    std::vector<std::pair<unsigned long long, uint32_t>> *out;
-    const unsigned char *base;
-    void operator()(const unsigned char *at, uint32_t bytes) const
-    {
-        out->push_back({(unsigned long long)(at - base), bytes});
-    }
-};
-
-static int check_next(unsigned int n, unsigned int k, unsigned int tok_tiles, unsigned int grid, unsigned int limit)
+// The decode kernel's range arithmetic: the ranges of the blocks tile [0, units) in order, none
+// is empty, and decode_holder names the block whose range holds a unit.
+static int check_decode(uint32_t units, uint32_t blocks)
 {
-    static unsigned char anchor[16];
-    UmmaArgs args;
-    args.next_w = anchor;
-    args.next_stride = (unsigned long long)(k / 32u) * 34u;
-    args.next_n = n;
-    args.next_segs = k / kSegK;
-    args.next_tok_tiles = tok_tiles;
-    args.next_units = limit;
-    const unsigned long long total = args.next_stride * n;
-    const unsigned int row_tiles = (n + kRows - 1u) / kRows;
-    const unsigned long long units = (unsigned long long)row_tiles * tok_tiles * args.next_segs;
-    const unsigned int blocks = units < grid ? (unsigned int)units : grid;
-    for (unsigned int b = 0; b < grid; ++b) {
-        std::vector<std::pair<unsigned long long, uint32_t>> pieces;
-        next_unit_pieces(args, b, grid, RecordEmit{&pieces, anchor});
-        if (b >= blocks) {
-            if (!pieces.empty()) {
-                return fail("a block without work in the next launch asks for bytes", n, k, grid, b);
+    uint32_t at = 0;
+    for (uint32_t b = 0; b < blocks; ++b) {
+        uint32_t begin, end;
+        decode_range(b, blocks, units, &begin, &end);
+        if (begin != at || end <= begin) {
+            return fail("decode ranges do not tile the units", units, 0u, blocks, b);
+        }
+        for (uint32_t u = begin; u < end; ++u) {
+            if (decode_holder(u, blocks, units) != b) {
+                return fail("decode_holder names another block", units, u, blocks, b);
             }
-            continue;
         }
-        unsigned long long u0, u1;
-        unit_range(b, blocks, units, &u0, &u1);
-        if (u1 > u0 + limit) {
-            u1 = u0 + limit;
-        }
-        // expected: every (row, segment) of the units [u0, u1)
-        unsigned long long want_bytes = 0, got_bytes = 0;
-        for (unsigned long long u = u0; u < u1; ++u) {
-            const unsigned int tile = (unsigned int)(u / args.next_segs);
-            const unsigned int row0 = (tile / tok_tiles) * kRows;
-            const unsigned int rows = n - row0 < kRows ? n - row0 : kRows;
-            want_bytes += (unsigned long long)rows * kSegBytes;
-        }
-        for (const auto &p : pieces) {
-            if ((p.first % 16ull) != 0ull || (p.second % 16u) != 0u || p.second == 0u || p.first + p.second > total) {
-                return fail("a piece is off the 16-byte grid or outside the tensor", n, k, grid, b);
-            }
-            // the piece lies in one row and covers whole segments of it
-            const unsigned long long row = p.first / args.next_stride;
-            const unsigned long long in_row = p.first % args.next_stride;
-            if ((in_row % kSegBytes) != 0ull || in_row + p.second > args.next_stride || row >= n) {
-                return fail("a piece does not cover whole segments of one row", n, k, grid, b);
-            }
-            // and those segments belong to this block's units
-            for (uint32_t s = 0; s < p.second / kSegBytes; ++s) {
-                const unsigned int seg = (unsigned int)(in_row / kSegBytes) + s;
-                const unsigned int row_tile = (unsigned int)(row / kRows);
-                bool mine = false;
-                for (unsigned int tt = 0; tt < tok_tiles && !mine; ++tt) {
-                    const unsigned long long u = ((unsigned long long)row_tile * tok_tiles + tt) * args.next_segs + seg;
-                    mine = u >= u0 && u < u1;
-                }
-                if (!mine) {
-                    return fail("a piece belongs to another block's units", n, k, grid, b);
-                }
-            }
-            got_bytes += p.second;
-        }
-        if (got_bytes != want_bytes) {
-            return fail("the pieces are not the bytes of the first units", n, k, grid, b);
-        }
+        at = end;
     }
-    return 0;
+    return at == units ? 0 : fail("decode ranges stop short", units, 0u, blocks, 0u);
 }
 
 int main()
@@ -230,18 +171,16 @@ int main()
             }
         }
     }
-    // the next-product pieces: (rows of w, depth, token tiles) x grid x unit limit
-    const unsigned int next_shapes[][3] = {{6144, 4096, 1}, {4096, 4096, 1}, {28672, 4096, 1}, {4096, 14336, 1},
-                                           {151936, 8192, 1}, {130, 256, 1}, {4736, 4096, 3}, {28672, 4096, 16},
-                                           {100, 512, 2}};
-    for (const auto &shape : next_shapes) {
-        for (unsigned int grid : {148u, 132u, 7u}) {
-            for (unsigned int limit : {1u, 6u, 40u}) {
-                if (check_next(shape[0], shape[1], shape[2], grid, limit) != 0) {
-                    return 1;
-                }
-                cases += 1;
+    // the decode kernel's ranges: two blocks per SM and odd grids
+    for (uint32_t blocks : {1u, 2u, 7u, 148u, 160u, 264u, 296u}) {
+        for (uint32_t units : {1u, 2u, 5u, 147u, 296u, 297u, 512u, 768u, 1792u, 3584u, 37984u}) {
+            if (units < blocks) {
+                continue;
             }
+            if (check_decode(units, blocks) != 0) {
+                return 1;
+            }
+            cases += 1;
         }
     }
     std::printf("ok %llu\n", cases);

@@ -75,6 +75,20 @@ inline float shfl_xor(float value, unsigned int mask)
     return value;
 }
 
+// __all_sync over the whole warp: true when every lane's predicate is
+inline int vote_all(int predicate)
+{
+    const unsigned int lane = thread_index.x % 32u;
+    warp->slot[lane] = predicate ? 1u : 0u;
+    warp->barrier.wait();
+    int all = 1;
+    for (unsigned int i = 0; i < 32u; ++i) {
+        all &= warp->slot[i] != 0u;
+    }
+    warp->barrier.wait();
+    return all;
+}
+
 inline float uint_as_float(uint32_t bits)
 {
     float value;
@@ -131,6 +145,7 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define gridDim (emu::grid_dim)
 #define __shfl_xor_sync(mask, value, lanes) emu::shfl_xor((value), (lanes))
 #define __syncwarp() emu::warp->barrier.wait()
+#define __all_sync(mask, predicate) emu::vote_all(predicate)
 #define __syncthreads() emu::block_barrier->wait()
 #define __uint_as_float(bits) emu::uint_as_float(bits)
 #define __float_as_uint(value) emu::float_as_uint(value)
@@ -162,9 +177,8 @@ inline unsigned int warp_of_thread()
 } // namespace q8emu
 
 #include "q8_stream.cu"
-#include "q8_umma.cu"
+#include "q8_dispatch.cu"
 #include "q8_wide.cu"
-#include "q8_duo.cu"
 #include "q8_decode.cu"
 
 // the routed-expert kernels keep their tables in static shared memory: one block runs at a time,
@@ -247,20 +261,14 @@ static void make_maps(const unsigned char *w, uint32_t w_rows, uint32_t k, const
     std::memcpy(tx, &map_x, sizeof map_x);
 }
 
-// the switches of an experiment build (UmmaArgs::debug) for the launches that follow
-static unsigned int switches = 0;
-// which decode-regime kernel the launches that follow run: 0 the one that ships (q8_stream.cu),
-// 1 the two-blocks-per-SM form (q8_duo.cu; token tiles of 16 and 32)
+// which decode-regime kernel the launches that follow run: 0 the one-block-per-SM kernel
+// (q8_stream.cu), 1 the two-blocks-per-SM kernel (q8_decode.cu; token tiles of 16 and 32, one
+// token tile, unit schedule - a cluster launch is not modelled)
 static unsigned int decode_form = 0;
 
 extern "C" void stream_emu_form(unsigned int form)
 {
     decode_form = form;
-}
-
-extern "C" void stream_emu_switches(unsigned int debug)
-{
-    switches = debug;
 }
 
 // column-split mode for the launches that follow (UmmaArgs::peers, y_peer, col0): the product's
@@ -292,7 +300,8 @@ static unsigned int run_stream(const CUtensorMap &tw, const CUtensorMap &tx, Umm
     if (decode_form == 0u) {
         ended = run_grid(grid, kThreads, [&] { q8_stream_kernel<NTOK, YT>(tw, tx, args); });
     } else if constexpr (NTOK <= 32) {
-        ended = run_grid(grid, kDuoThreads, [&] { q8_duo_kernel<NTOK, YT>(tw, tx, args); });
+        args.split = 0u;
+        ended = run_grid(grid, kDecThreads, [&] { q8_decode_kernel<NTOK, YT>(tw, tx, args); });
     }
     status |= ended;
     for (unsigned int flag : flags) {
@@ -324,16 +333,12 @@ static void set_mode(int asynchronous, uint32_t max_delay_us)
 }
 
 // One product, arguments as launch_umma fills them.  x: binary16 or bfloat16 [m][k]; y: float
-// [m][ldy] (epilogue 0, 1) or [m][n / 2] (epilogue 2).  next_*: the product that follows on the
-// stream, whose first units each block asks the L2 for; *l2_bytes receives the bytes asked for.
+// [m][ldy] (epilogue 0, 1) or [m][n / 2] (epilogue 2).
 extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
                                    uint32_t m, const unsigned int *m_dev, float *y, uint32_t ldy, uint32_t epilogue,
-                                   uint32_t grid, uint32_t ntok, const unsigned char *next_w, uint32_t next_n,
-                                   uint32_t next_k, uint32_t next_m, uint32_t next_units,
-                                   unsigned long long *l2_bytes, int asynchronous, uint32_t max_delay_us)
+                                   uint32_t grid, uint32_t ntok, int asynchronous, uint32_t max_delay_us)
 {
     set_mode(asynchronous, max_delay_us);
-    q8::l2_requests = 0;
     CUtensorMap tw, tx;
     make_maps(w, n, k, x, m, ntok, &tw, &tx);
     const unsigned long long units = (unsigned long long)((n + kRows - 1u) / kRows) * ((m + ntok - 1u) / ntok) * (k / kSegK);
@@ -350,32 +355,17 @@ extern "C" unsigned int stream_emu(const unsigned char *w, uint32_t n, uint32_t 
     args.b_bf16 = x_bf16 ? 1u : 0u;
     args.ldy = ldy;
     args.epilogue = epilogue;
-    args.debug = switches;
-    args.w = w;
     args.peers = peer_count;
     args.col0 = peer_col0;
     for (unsigned int i = 0; i < 8u; ++i) {
         args.y_peer[i] = peer_buffer[i];
     }
-    if (next_w != nullptr) {
-        args.next_w = next_w;
-        args.next_stride = (unsigned long long)(next_k / 32u) * 34u;
-        args.next_n = next_n;
-        args.next_segs = next_k / kSegK;
-        args.next_tok_tiles = (next_m + ntok - 1u) / ntok;
-        args.next_units = next_units;
-    }
-    const unsigned int status = run_stream_tile<float>(ntok, tw, tx, args, grid);
-    if (l2_bytes != nullptr) {
-        *l2_bytes = q8::l2_requests;
-    }
-    return status;
+    return run_stream_tile<float>(ntok, tw, tx, args, grid);
 }
 
-// One product on a prefill-regime kernel (whole waves of tiles dealt round-robin and the last
-// partial wave cut into units), arguments as launch_umma fills them for it.  y: float [m][n].
-// form 0: both operands from shared memory (q8_umma.cu; ntok 64 or 256); form 1: the weights in
-// tensor memory (q8_wide.cu; ntok 256).
+// One product on the prefill-regime kernel (q8_wide.cu: token tiles of 256, whole waves of tiles
+// dealt round-robin and the last partial wave cut into units), arguments as launch_umma fills
+// them for it.  y: float [m][n].
 template <int NTOK, typename Kernel>
 static unsigned int run_prefill(Kernel kernel, const CUtensorMap &tw, const CUtensorMap &tx, UmmaArgs args,
                                 unsigned int grid)
@@ -396,10 +386,11 @@ static unsigned int run_prefill(Kernel kernel, const CUtensorMap &tw, const CUte
     return status;
 }
 
-extern "C" unsigned int umma_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
+extern "C" unsigned int wide_emu(const unsigned char *w, uint32_t n, uint32_t k, const void *x, int x_bf16,
                                  uint32_t m, const unsigned int *m_dev, float *y, uint32_t epilogue, uint32_t grid,
-                                 uint32_t ntok, int asynchronous, uint32_t max_delay_us, uint32_t form)
+                                 int asynchronous, uint32_t max_delay_us)
 {
+    const uint32_t ntok = 256u;
     set_mode(asynchronous, max_delay_us);
     CUtensorMap tw, tx;
     make_maps(w, n, k, x, m, ntok, &tw, &tx);
@@ -417,16 +408,7 @@ extern "C" unsigned int umma_emu(const unsigned char *w, uint32_t n, uint32_t k,
     args.b_bf16 = x_bf16 ? 1u : 0u;
     args.ldy = epilogue == kEpilogueSwiglu ? n / 2u : n;
     args.epilogue = epilogue;
-    if (form == 1u && ntok == 256u) {
-        return run_prefill<256>(q8_wide_kernel<float>, tw, tx, args, grid);
-    }
-    if (form == 0u && ntok == 64u) {
-        return run_prefill<64>(q8_umma_kernel<64, float>, tw, tx, args, grid);
-    }
-    if (form == 0u && ntok == 256u) {
-        return run_prefill<256>(q8_umma_kernel<256, float>, tw, tx, args, grid);
-    }
-    return 0xFFFFu;
+    return run_prefill<256>(q8_wide_kernel<float>, tw, tx, args, grid);
 }
 
 // Grouped mode, arguments as launch_umma_grouped fills them.
@@ -456,7 +438,6 @@ static unsigned int run_grouped(const unsigned char *w_stacked, uint32_t total_r
     args.row_map = row_map;
     args.ldy = ldy;
     args.epilogue = epilogue;
-    args.debug = switches;
     return run_stream_tile<YT>(ntok, tw, tx, args, grid);
 }
 

@@ -5,7 +5,7 @@ with six emulated multiprocessors.  tests/test_stream_emu.py checks the kernels 
 its own driver fills in; here the library's host code fills them in, so these tests cover what
 lies between the ABI and a launch: argument checks and return codes, the choice of kernel,
 tensor maps (through a stand-in of the encoder that refuses what the driver refuses), grids,
-scratch sets alternating between launches, workspaces, the hint for the following product, and
+scratch sets alternating between launches, workspaces, and
 the order of the launches of the routed-expert step.  Results are checked against the oracle."""
 import ctypes as C
 import os
@@ -80,7 +80,6 @@ def api(tmp_path_factory):
     lib = C.CDLL(path)
     library.declare_q8(lib)
     lib.api_emu_status.restype = C.c_uint
-    lib.api_emu_l2_bytes.restype = C.c_ulonglong
     lib.api_emu_mode.argtypes = [C.c_int, C.c_uint]
     for name in library.SYMBOLS:
         assert hasattr(lib, name), name
@@ -188,58 +187,6 @@ def test_fused_stores_on_both_kernel_families(api, n, k, m):
     got = act[:m].astype(np.float64)
     assert (np.abs(got - want) <= 2.0 ** -10 * np.abs(want) + 1e-6).all()
     assert (act[m:] == np.float16(9.0)).all() and np.abs(want).max() > 0.1
-
-
-def pieces_bytes(n, k, m, limit, grid):
-    """Bytes of the first `limit` units of every block of the launch that follows (its token tile
-    from its batch as the library picks it)."""
-    ntok = 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
-    segs, tok_tiles = k // 256, -(-m // ntok)
-    units = -(-n // 128) * tok_tiles * segs
-    blocks = min(units, grid)
-    total = 0
-    for b in range(blocks):
-        u, end = b * units // blocks, (b + 1) * units // blocks
-        end = min(end, u + limit)
-        while u < end:
-            tile, s0 = divmod(u, segs)
-            s1 = min(segs, s0 + (end - u))
-            total += min(128, n - (tile // tok_tiles) * 128) * (s1 - s0) * 272
-            u += s1 - s0
-    return total
-
-
-def test_hint_for_the_following_product(api, oracle):
-    """aotx_q8_hint_next: the next product's launch asks L2 for the first units of the product
-    named in the hint, block by block as that launch will read them; the hint is used once, any
-    product consumes it, and a hint the tensor-core kernel cannot follow is dropped."""
-    import aotx_b200
-    n, k, m = 700, 1024, 20
-    w = aotx_b200.synth_q8_0(n, k, 51)
-    n2, k2 = 900, 768
-    w2 = aotx_b200.synth_q8_0(n2, k2, 52)
-    x = inputs(m, k, 53)
-    y = np.zeros((m, n), np.float32)
-    api.lib.api_emu_l2_bytes()
-    assert api.lib.aotx_q8_hint_next(api.ctx, w2.ctypes.data, n2, k2, m) == OK
-    api.matmul(w, n, k, x, y)
-    asked = api.lib.api_emu_l2_bytes()
-    # 32 MiB over six emulated SMs is more than every block's whole share: all of w2 once
-    assert asked == pieces_bytes(n2, k2, m, 10 ** 9, 6) == n2 * (k2 // 32) * 34
-    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
-    api.matmul(w, n, k, x, y)
-    assert api.lib.api_emu_l2_bytes() == 0                      # used once
-    # consumed by a product of another kind (the any-shape kernel asks for nothing)
-    assert api.lib.aotx_q8_hint_next(api.ctx, w2.ctypes.data, n2, k2, m) == OK
-    w96 = aotx_b200.synth_q8_0(20, 96, 1)
-    api.matmul(w96, 20, 96, inputs(5, 96, 2), np.zeros((5, 20), np.float32))
-    api.matmul(w, n, k, x, y)
-    assert api.lib.api_emu_l2_bytes() == 0
-    # a following product the tensor-core kernel does not take: no requests
-    assert api.lib.aotx_q8_hint_next(api.ctx, w96.ctypes.data, 20, 96, 5) == OK
-    api.matmul(w, n, k, x, y)
-    assert api.lib.api_emu_l2_bytes() == 0
-    assert api.lib.aotx_q8_hint_next(None, w2.ctypes.data, n2, k2, m) == ERR_ARGUMENT
 
 
 def test_dequantisation_of_every_block_type(api, oracle):

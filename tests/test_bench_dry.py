@@ -74,6 +74,10 @@ class DryCuda:
     def is_available():
         return True
 
+    @staticmethod
+    def empty_cache():
+        pass
+
 
 class DryTorch(_fake.FakeTorch):
     cuda = DryCuda()
@@ -87,8 +91,13 @@ class DryTorch(_fake.FakeTorch):
         return real_torch.randn(*args, **kwargs)
 
 
+def _host_synth(n, k, seed, device="cuda"):
+    """The device-side generator of the harness, on the host for the dry run."""
+    import aotx_b200
+    return real_torch.from_numpy(aotx_b200.synth_q8_0(n, k, seed))
+
+
 @pytest.mark.parametrize("workload,extra", [("decode_m32_llama3_8b_layer", []),
-                                            ("decode_m32_llama3_8b_layer", ["--prefetch-next"]),
                                             ("decode_m32_llama3_8b_layer_fused", []),
                                             ("prefill_m2048_llama3_8b_layer", [])])
 def test_default_benchmark_path_runs_to_its_json_line(monkeypatch, capsys, workload, extra):
@@ -104,6 +113,7 @@ def test_default_benchmark_path_runs_to_its_json_line(monkeypatch, capsys, workl
     monkeypatch.setattr(real_torch.Tensor, "pin_memory", lambda self, *a, **k: self)
     monkeypatch.setattr(bench, "reference_gpu_baseline", lambda name: {"unavailable": "dry run"})
     monkeypatch.setattr(bench, "cpu_baseline", lambda name, budget_s: {"value": 0.0, "kind": "dry run"})
+    monkeypatch.setattr(aotx_b200, "synth_q8_0_device", _host_synth)
     monkeypatch.setattr(sys, "argv", ["bench.py", "--steps", "3", "--warmup", "1", "--workload", workload] + extra)
     bench.main()
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
@@ -118,7 +128,6 @@ def test_default_benchmark_path_runs_to_its_json_line(monkeypatch, capsys, workl
     assert line["config"]["workload"] == workload and line["steps"] == 3 and line["n_gpus"] == 1
     assert line["gpu_launches"] == 4 * 3
     assert line["e2e"]["host_result_matches_device"] is True
-    assert line["config"]["prefetch_next"] == bool(extra)
 
 
 @pytest.mark.parametrize("workload,extra", [("lm_head_colsplit", ["--rows", "4"]),
@@ -134,6 +143,7 @@ def test_sharded_workloads_run_on_one_rank(monkeypatch, capsys, workload, extra)
     monkeypatch.setitem(sys.modules, "torch", fake)
     monkeypatch.setattr(aotx_b200, "Q8Context", _fake.FakeContext)
     monkeypatch.setattr(real_torch.Tensor, "cuda", lambda self, *a, **k: self)
+    monkeypatch.setattr(aotx_b200, "synth_q8_0_device", _host_synth)
     monkeypatch.setattr(sys, "argv", ["bench.py", "--steps", "2", "--warmup", "1", "--workload", workload] + extra)
     bench.main()
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
@@ -141,6 +151,37 @@ def test_sharded_workloads_run_on_one_rank(monkeypatch, capsys, workload, extra)
     assert line["value"] > 0 and "roofline" in line and "clocks" in line
     if workload.startswith("moe"):
         assert line["config"]["interleaved_gate_up"] == bool(extra)
+
+
+def test_default_line_covers_every_configuration(monkeypatch, capsys):
+    """No --workload on one GPU: the decode layer as the headline and a `configs` entry for the
+    single-row product, the prefill layer, the routed experts and the LM head."""
+    import aotx_b200
+    bench = importlib.import_module("bench")
+    small = [("qkv", 256, 96), ("o", 256, 64), ("gate_up", 256, 128), ("down", 512, 64)]
+    monkeypatch.setitem(bench.WORKLOADS, "decode_m32_llama3_8b_layer", (8, small, "bfloat16", "bfloat16"))
+    monkeypatch.setitem(bench.SHARDED, "lm_head_colsplit", {"n": 200, "k": 256})
+    monkeypatch.setitem(bench.SHARDED, "moe_qwen3_30b_a3b",
+                        {"tokens": 12, "experts": 4, "used": 2, "hidden": 256, "ffn": 256})
+    monkeypatch.setattr(bench, "GEMV_SHAPE", {"n": 64, "k": 256, "copies": 2})
+    monkeypatch.setattr(bench, "PREFILL_ROWS", 40)
+    monkeypatch.setitem(sys.modules, "torch", DryTorch())
+    monkeypatch.setattr(aotx_b200, "Q8Context", _fake.FakeContext)
+    monkeypatch.setattr(real_torch.Tensor, "cuda", lambda self, *a, **k: self)
+    monkeypatch.setattr(real_torch.Tensor, "pin_memory", lambda self, *a, **k: self)
+    monkeypatch.setattr(bench, "reference_gpu_baseline", lambda name: {"unavailable": "dry run"})
+    monkeypatch.setattr(bench, "cpu_baseline", lambda name, budget_s: {"value": 0.0, "kind": "dry run"})
+    monkeypatch.setattr(aotx_b200, "synth_q8_0_device", _host_synth)
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--steps", "3", "--warmup", "1"])
+    bench.main()
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["config"]["workload"] == "decode_m32_llama3_8b_layer" and line["n_gpus"] == 1
+    names = [entry["workload"] for entry in line["configs"]]
+    assert names == ["gemv_m1_4096", "prefill_m2048_llama3_8b_layer", "moe_qwen3_30b_a3b",
+                     "lm_head_8192_to_151936_m8"]
+    for entry in line["configs"]:
+        for key in ("ms_per_step", "achieved", "unit", "bound", "frac", "peak"):
+            assert key in entry, key
 
 
 def test_smoke_entry_runs_on_the_stand_in(monkeypatch, capsys):

@@ -50,35 +50,3 @@ def test_routed_experts_repeat_bit_identically(ctx):
     torch.cuda.synchronize()
     for other in outs[1:]:
         assert torch.equal(other, outs[0])
-
-
-def test_naming_the_next_product_changes_no_result(ctx):
-    """aotx_q8_hint_next only warms L2: products with and without it are the same bits, whatever
-    is named - a large tensor, a small one, one at a misaligned address or with a depth the
-    tensor-core kernel does not take (both ignored), the tensor itself - and a hint that a
-    product of another kind takes is gone afterwards."""
-    import aotx_b200
-    torch = torch_mod()
-    n, k, m = 6144, 4096, 32
-    w = dev_weights(aotx_b200.synth_q8_0(n, k, 28))
-    other = dev_weights(aotx_b200.synth_q8_0(28672, 4096, 29))
-    x, _ = x_bf16_bits(m, k, 30)
-    xd = x.cuda()
-    plain = ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16)
-    stride = aotx_b200.row_bytes(4096)
-    hints = [(other, 28672, 4096, 32), (other, 28672, 4096, 2048), (other, 130, 4096, 1),
-             (other[stride + 2:], 100, 4096, 32), (other, 1000, 4128, 32), (w, n, k, m),
-             (other, 7168, 16384, 32)]
-    for hinted in hints:
-        ctx.hint_next(*hinted)
-        again = ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16)
-        torch.cuda.synchronize()
-        assert torch.equal(again, plain)
-    ctx.hint_next(*hints[0])
-    ctx.hint_next(None)                                            # cleared
-    assert torch.equal(ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16), plain)
-    ctx.hint_next(*hints[0])
-    small = ctx.matmul(dev_weights(aotx_b200.synth_q8_0(80, 128, 1)), 80, 128, xd[:, :128].contiguous())
-    torch.cuda.synchronize()                                       # the general kernel took the hint
-    assert torch.equal(ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16), plain) and bool(torch.isfinite(small).all())
-    assert ctx.device_status() == 0

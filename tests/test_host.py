@@ -157,7 +157,6 @@ def test_argument_checks_need_no_device(built):
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 3, 1, None, one, 0) == 1      # x dtype
     assert lib.aotx_q8_matmul_static(null, one, 8, 8, 64, one, 1, 65, None, one, 0) == 5     # rows > 64
     assert lib.aotx_q8_matmul_static(null, one, 8, 0, 64, one, 1, 1, None, one, 0) == 0      # nothing to do
-    assert lib.aotx_q8_hint_next(null, one, 8, 256, 1) == 1
     assert lib.aotx_q8_matmul_fused(null, null, one, 8, 8, 64, one, 1, 1, None, one, 0, 1) == 1
     assert lib.aotx_q8_moe_ffn_fused(null, null, one, one, 8, 4, 256, 256, one, one, one, 1, None, 2, one, 0,
                                      one, 1 << 30) == 1

@@ -10,10 +10,14 @@ from aotx_b200 import build as builder
 # the kernels a product, a dequantisation or the routed-expert step launches on the shipped paths
 HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_build_kernel",
        "q8_gather_rows_kernel", "q8_swiglu_kernel", "q8_expert_sum_kernel", "q_dequant_any_kernel")
-# any-shape fallbacks (shapes the tensor-core kernels do not take) and kernels no shipped path reaches
+# any-shape fallbacks (shapes the tensor-core kernels do not take), the prefill kernel, and the
+# decode kernel for batches of up to 32 rows: its converter loop spills nothing; what it spills
+# is in the once-per-tile path where the owner of a cut tile holds another block's 32 partial
+# sums while it reads its own (two blocks of 80 registers share an SM)
 SMALL_SPILLS = {"q8_gemv_simt_kernel": 32, "q8_gemv_simt_fused_kernel": 64, "q_gemv_any_kernel": 16,
                 "q8_expert_feed_kernel": 64, "q8_expert_down_kernel": 64,
-                "q8_wide_kernel": 16, "q8_duo_kernel": 0, "q8_umma_kernel": 0}
+                "q8_wide_kernel": 16, "q8_decode_kernel": 256, "store_eight_any": 64, "store_one_any": 64,
+                "mbar_wait": 0}
 
 
 @pytest.fixture(scope="module")
@@ -45,9 +49,9 @@ def test_every_other_kernel_is_listed_with_its_bound(usage):
 
 def test_register_budgets(usage):
     """One block of 480 threads per SM: at most 128 registers a thread (65536 / 480 rounded down
-    to the allocation unit); the two-blocks-per-SM kernel: 352 threads twice, at most 88."""
+    to the allocation unit); the two-blocks-per-SM kernel: 352 threads twice, at most 80."""
     for name, use in usage.items():
-        if "q8_stream_kernel" in name or "q8_wide_kernel" in name or "q8_umma_kernel" in name:
+        if "q8_stream_kernel" in name or "q8_wide_kernel" in name:
             assert use["registers"] <= 128, (name, use)
-        if "q8_duo_kernel" in name:
-            assert use["registers"] <= 88, (name, use)
+        if "q8_decode_kernel" in name:
+            assert use["registers"] <= 80, (name, use)

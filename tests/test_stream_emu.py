@@ -6,7 +6,7 @@ tensor memory as an array, the MMA in float.  The results are checked against th
 this covers on a machine without a GPU what only the GPU tests covered before: the five warp
 roles and their rings, the byte arithmetic of the dequantisation into tensor memory, the operand
 layouts, the bfloat16 path, the unit schedule with tiles cut between blocks, the live batch word,
-the three store modes and the L2 requests for the following product.  In the asynchronous mode
+the three store modes.  In the asynchronous mode
 the copies and the tensor-core work complete later, in order, on threads of their own with random
 delays, so a buffer reused too early would give wrong numbers; and a copy that never lands (made
 on the host) checks that every wait is bounded: the block raises its status bit, lets its other
@@ -44,11 +44,9 @@ def emu(tmp_path_factory):
     assert done.returncode == 0, done.stderr[-3000:]
     lib = C.CDLL(path)
     vp, u32 = C.c_void_p, C.c_uint32
-    lib.stream_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, u32,
-                               vp, C.c_int, u32]
+    lib.stream_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, u32, C.c_int, u32]
     lib.stream_emu.restype = C.c_uint
     lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
-    lib.stream_emu_switches.argtypes = [C.c_uint]
     lib.stream_emu_form.argtypes = [C.c_uint]
     lib.stream_emu_copies.restype = C.c_longlong
     lib.stream_emu_peers.argtypes = [C.c_uint, vp, C.c_uint]
@@ -56,31 +54,25 @@ def emu(tmp_path_factory):
     lib.stream_emu_moe.argtypes = [vp, vp, vp, vp, u32, u32, u32, vp, vp, u32, vp, u32, u32, u32, vp, vp, vp,
                                    C.c_int, u32]
     lib.stream_emu_moe.restype = C.c_uint
-    lib.umma_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, u32, C.c_int, u32, u32]
-    lib.umma_emu.restype = C.c_uint
+    lib.wide_emu.argtypes = [vp, u32, u32, vp, C.c_int, u32, vp, vp, u32, u32, C.c_int, u32]
+    lib.wide_emu.restype = C.c_uint
 
-    def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, following=None, delay_us=None, lost_copy=-1,
-            expect=0, switches=0, form=0):
+    def run(w, n, k, x, y, bf16=0, live=None, mode=0, grid=5, ntok=16, delay_us=None, lost_copy=-1, expect=0,
+            form=0):
         """delay_us: None runs copies and MMAs at once in the issuing thread, a number runs them
         later on engine threads with random delays up to that many microseconds."""
         m = x.shape[0]
-        requested = C.c_ulonglong(0)
-        nw, nn, nk, nm, units = following if following is not None else (None, 0, 0, 0, 0)
         lib.stream_emu_faults(lost_copy, 10.0 if lost_copy < 0 else 0.5)
-        lib.stream_emu_switches(switches)
         lib.stream_emu_form(form)
         status = lib.stream_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, m,
                                 live.ctypes.data if live is not None else None, y.ctypes.data, y.shape[1], mode,
-                                grid, ntok, nw.ctypes.data if nw is not None else None, nn, nk, nm, units,
-                                C.byref(requested), 0 if delay_us is None else 1, delay_us or 0)
-        lib.stream_emu_switches(0)
+                                grid, ntok, 0 if delay_us is None else 1, delay_us or 0)
         lib.stream_emu_form(0)
         if expect is not None:
             assert status == expect, hex(status)
-        return requested.value if expect == 0 else status
+        return status
 
-    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None, form=0,
-            switches=0):
+    def moe(wg, wu, both, wd, experts, hidden, ffn, x, ids, live=None, tile=64, grid=5, delay_us=None):
         """The routed-expert step; returns proj [tokens][used][hidden], act and the sorted pairs."""
         tokens, used = ids.shape
         proj = np.full((tokens * used, hidden), GUARD, np.float32)
@@ -88,24 +80,19 @@ def emu(tmp_path_factory):
         pair = np.full(tokens * used, 0xFFFFFFFF, np.uint32)
         ptr = lambda a: a.ctypes.data if a is not None else None
         lib.stream_emu_faults(-1, 10.0)
-        lib.stream_emu_form(form)
-        lib.stream_emu_switches(switches)
         status = lib.stream_emu_moe(ptr(wg), ptr(wu), ptr(both), ptr(wd), experts, hidden, ffn, x.ctypes.data,
                                     ids.ctypes.data, tokens, ptr(live), used, tile, grid, proj.ctypes.data,
                                     act.ctypes.data, pair.ctypes.data, 0 if delay_us is None else 1, delay_us or 0)
-        lib.stream_emu_form(0)
-        lib.stream_emu_switches(0)
         run.copies = lib.stream_emu_copies()
         assert status == 0, hex(status)
         return proj.reshape(tokens, used, hidden), act, pair
 
-    def wide(w, n, k, x, y, bf16=0, mode=0, grid=3, ntok=256, delay_us=None, form=0, live=None):
-        """A prefill-regime kernel: form 0 operands from shared memory, form 1 weights in tensor
-        memory."""
+    def wide(w, n, k, x, y, bf16=0, mode=0, grid=3, delay_us=None, live=None):
+        """The prefill-regime kernel (token tiles of 256, weights in tensor memory)."""
         lib.stream_emu_faults(-1, 10.0)
-        status = lib.umma_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, x.shape[0],
+        status = lib.wide_emu(w.ctypes.data, n, k, x.ctypes.data, bf16, x.shape[0],
                               live.ctypes.data if live is not None else None, y.ctypes.data, mode, grid,
-                              ntok, 0 if delay_us is None else 1, delay_us or 0, form)
+                              0 if delay_us is None else 1, delay_us or 0)
         assert status == 0, hex(status)
 
     def peers(buffers, col0):
@@ -255,42 +242,6 @@ def test_gated_unit_over_row_pairs(emu, n, k, m, grid, ntok):
     assert np.abs(want).max() > 0.1
 
 
-def pieces_bytes(n, k, m, ntok, limit, grid):
-    """Bytes of the first `limit` units of every block of a launch of `grid` blocks over w[n][k]."""
-    segs = k // SEG_K
-    tok_tiles = -(-m // ntok)
-    units = -(-n // ROWS) * tok_tiles * segs
-    blocks = min(units, grid)
-    total = 0
-    for b in range(blocks):
-        u, end = b * units // blocks, (b + 1) * units // blocks
-        end = min(end, u + limit)
-        while u < end:
-            tile, s0 = divmod(u, segs)
-            s1 = min(segs, s0 + (end - u))
-            row0 = (tile // tok_tiles) * ROWS
-            total += min(ROWS, n - row0) * (s1 - s0) * SEG_BYTES
-            u += s1 - s0
-    return total
-
-
-@pytest.mark.parametrize("limit", [1, 2, 5])
-def test_requests_for_the_following_product(emu, oracle, limit):
-    import aotx_b200
-    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
-    w = aotx_b200.synth_q8_0(n, k, 51)
-    n2, k2 = 200, 768
-    w2 = aotx_b200.synth_q8_0(n2, k2, 52)
-    x = inputs(m, k, 53)
-    y = np.zeros((m, n), np.float32)
-    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, following=(w2, n2, k2, m, limit))
-    assert asked == pieces_bytes(n2, k2, m, ntok, limit, grid)
-    assert asked > 0
-    # and the product itself is what it is without the requests
-    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
-    assert emu(w, n, k, x, y, grid=grid, ntok=ntok) == 0
-
-
 def moe_case(oracle, tokens, experts, used, hidden, ffn, seed):
     import aotx_b200
     wg = aotx_b200.synth_q8_0(experts * ffn, hidden, seed)
@@ -370,62 +321,23 @@ def test_routed_experts_live_batch_and_selections_outside_the_table(emu, oracle)
     assert sorted(pair.tolist())[:-1] == [p for p in range(tokens * used) if p != 3 * used + 1]
 
 
-@pytest.mark.parametrize("n,k,m,grid,ntok,delay", [(300, 1024, 300, 5, 256, None), (520, 1024, 300, 3, 256, 0),
-                                                   (520, 1024, 300, 3, 256, 50), (300, 512, 70, 4, 64, 50)])
-def test_prefill_regime_kernel(emu, oracle, n, k, m, grid, ntok, delay):
-    """The kernel with both operands in shared memory and token tiles of 256 rows
-    (aotx_b200/csrc/q8_umma.cu), which the library does not dispatch because repeated launches on
-    the GPU differed in a few outputs.  Run whole on the host - whole waves of tiles dealt
-    round-robin, the partial wave cut into units, three operand stages shared between the two
-    converter halves, operations completing later - its results equal the oracle's and repeat bit
-    for bit, so its rings and schedule are sound and the fault lies in what the stand-ins do not
-    model (how the hardware orders the converters' shared-memory stores against the tensor
-    core's reads)."""
-    import aotx_b200
-    w = aotx_b200.synth_q8_0(n, k, 7)
-    x = inputs(m, k, 8)
-    want = oracle.product(w, n, k, x.view(np.uint16), m)
-    runs = []
-    for _ in range(2):
-        y = np.full((m + 1, n), GUARD, np.float32)
-        emu.wide(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay)
-        assert oracle.diff(y[:m], want)[0] == 0
-        assert (y[m:] == GUARD).all()
-        runs.append(y)
-    assert np.array_equal(runs[0], runs[1])
-
-
-def test_prefill_regime_kernel_bfloat16(emu, oracle):
-    import aotx_b200
-    import torch
-    n, k, m = 260, 768, 270
-    w = aotx_b200.synth_q8_0(n, k, 9)
-    xb = torch.from_numpy(inputs(m, k, 10).astype(np.float32)).to(torch.bfloat16)
-    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
-    y = np.zeros((m, n), np.float32)
-    emu.wide(w, n, k, bits, y, bf16=1, grid=4, delay_us=20)
-    # weights rounded to bfloat16 here (one MMA takes both operands in one format)
-    want = oracle.product(w, n, k, bits, m, bf16=True)
-    assert oracle.diff(y, want)[0] == 0
-
-
 @pytest.mark.parametrize("n,k,m,grid,delay", [(300, 1024, 300, 5, None), (520, 1024, 300, 3, 50),
                                               (390, 1024, 520, 4, 20), (128, 256, 257, 2, 0)])
 def test_prefill_kernel_with_weights_in_tensor_memory(emu, oracle, n, k, m, grid, delay):
-    """The second 256-row kernel (aotx_b200/csrc/q8_wide.cu; not dispatched by the product build):
+    """The prefill-regime kernel (aotx_b200/csrc/q8_wide.cu, batches above 128 rows):
     one accumulator, two segments of weights in tensor memory, x in boxes of 64 columns through a
     ring of its own, whole waves of tiles and a partial wave cut into units."""
     import aotx_b200
     w = aotx_b200.synth_q8_0(n, k, 17)
     x = inputs(m, k, 18)
     y = np.full((m + 1, n), GUARD, np.float32)
-    emu.wide(w, n, k, x, y[:m], grid=grid, delay_us=delay, form=1)
+    emu.wide(w, n, k, x, y[:m], grid=grid, delay_us=delay)
     assert oracle.diff(y[:m], oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
     assert (y[m:] == GUARD).all()
     # the live batch word and the add store
     live = m - 70
     part = np.full((m, n), GUARD, np.float32)
-    emu.wide(w, n, k, x, part, grid=grid, delay_us=delay, form=1, live=np.array([live], np.uint32))
+    emu.wide(w, n, k, x, part, grid=grid, delay_us=delay, live=np.array([live], np.uint32))
     assert (part[live:] == GUARD).all()
     if -(-live // 256) == -(-m // 256):
         assert np.array_equal(part[:live], y[:live])       # same tiles, same cuts, same sums
@@ -433,7 +345,7 @@ def test_prefill_kernel_with_weights_in_tensor_memory(emu, oracle, n, k, m, grid
         assert np.abs(part[:live] - y[:live]).max() <= 1e-5 * np.abs(y[:m]).max()
     y0 = np.random.default_rng(19).standard_normal((m, n)).astype(np.float32)
     added = y0.copy()
-    emu.wide(w, n, k, x, added, mode=1, grid=grid, delay_us=delay, form=1)
+    emu.wide(w, n, k, x, added, mode=1, grid=grid, delay_us=delay)
     assert np.array_equal(added, y0 + y[:m])
 
 
@@ -445,80 +357,35 @@ def test_prefill_kernel_with_weights_in_tensor_memory_bfloat16(emu, oracle):
     xb = torch.from_numpy(inputs(m, k, 10).astype(np.float32)).to(torch.bfloat16)
     bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
     y = np.zeros((m, n), np.float32)
-    emu.wide(w, n, k, bits, y, bf16=1, grid=4, delay_us=20, form=1)
+    emu.wide(w, n, k, bits, y, bf16=1, grid=4, delay_us=20)
     want = oracle.product(w, n, k, bits, m, bf16=True)
     assert oracle.diff(y, want)[0] == 0
-    # bit for bit the sums of the first form, which rounds the weights to bfloat16 the same way
-    first = np.zeros((m, n), np.float32)
-    emu.wide(w, n, k, bits, first, bf16=1, grid=4, form=0)
-    assert np.array_equal(first, y)
 
 
-@pytest.mark.parametrize("n,k,m,grid,ntok", [(200, 512, 9, 3, 16), (300, 1024, 30, 5, 32), (260, 768, 50, 4, 64),
-                                             (130, 512, 100, 5, 128)])
-def test_switch_bfloat16_weights_in_tensor_memory(emu, oracle, n, k, m, grid, ntok):
-    """Switch 32 of an experiment build: with bfloat16 activations the weights go to tensor memory
-    as bfloat16 (one rounding of the exact q * d) and both MMA operands are bfloat16, so the x
-    tile is never rewritten in shared memory.  Against the oracle's product over
-    bfloat16-rounded weights."""
-    import aotx_b200
-    import torch
-    w = aotx_b200.synth_q8_0(n, k, 11)
-    xb = torch.from_numpy(inputs(m, k, 12).astype(np.float32)).to(torch.bfloat16)
-    bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
-    y = np.full((m + 1, n), GUARD, np.float32)
-    emu(w, n, k, bits, y[:m], bf16=1, grid=grid, ntok=ntok, switches=32, delay_us=20)
-    want = oracle.product(w, n, k, bits, m, bf16=True)
-    assert oracle.diff(y[:m], want)[0] == 0
-    assert (y[m:] == GUARD).all()
-    # and within the product tolerance of the form that ships (binary16 weights, x converted)
-    ships = np.zeros((m, n), np.float32)
-    emu(w, n, k, bits, ships, bf16=1, grid=grid, ntok=ntok)
-    assert np.abs(ships - y[:m]).max() <= 1e-2 * np.abs(ships).max() + 1e-3
-    # binary16 activations are not touched by the switch
-    x16 = inputs(m, k, 13)
-    a = np.zeros((m, n), np.float32)
-    b = np.zeros((m, n), np.float32)
-    emu(w, n, k, x16, a, grid=grid, ntok=ntok)
-    emu(w, n, k, x16, b, grid=grid, ntok=ntok, switches=32)
-    assert np.array_equal(a, b)
-
-
-def test_switch_block_warms_l2_with_its_own_first_units(emu, oracle):
-    """Switch 16: before its barriers and tensor memory are set up, a block asks L2 for the
-    first units it will copy.  The bytes asked for are those of its first raw stages."""
-    import aotx_b200
-    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
-    w = aotx_b200.synth_q8_0(n, k, 51)
-    x = inputs(m, k, 53)
-    y = np.zeros((m, n), np.float32)
-    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, switches=16)
-    assert asked == pieces_bytes(n, k, m, ntok, 5, grid)       # five raw stages at this tile width
-    assert oracle.diff(y, oracle.product(w, n, k, x.view(np.uint16), m))[0] == 0
-
-
-# ---- the two-blocks-per-SM form of the decode-regime kernel (aotx_b200/csrc/q8_duo.cu; form=1) ----
+# ---- the decode kernel for batches of up to 32 rows (aotx_b200/csrc/q8_decode.cu; form=1), on its
+# ---- unit schedule (a cluster launch is not modelled by the emulation)
 
 @pytest.mark.parametrize("n,k,m,grid,ntok,delay", [(200, 512, 5, 3, 16, None), (300, 1024, 20, 5, 32, 100),
-                                                   (384, 2048, 33, 11, 16, 30), (128, 256, 1, 1, 16, None),
-                                                   (1000, 512, 7, 9, 16, 0), (140, 512, 70, 5, 32, 20),
+                                                   (384, 2048, 12, 11, 16, 30), (128, 256, 1, 1, 16, None),
+                                                   (1000, 512, 7, 9, 16, 0), (140, 512, 30, 5, 32, 20),
                                                    (300, 1536, 12, 18, 16, None)])
-def test_duo_product_against_the_oracle(emu, oracle, n, k, m, grid, ntok, delay):
+def test_decode_kernel_against_the_oracle(emu, oracle, n, k, m, grid, ntok, delay):
     import aotx_b200
     w = aotx_b200.synth_q8_0(n, k, n + k)
     x = inputs(m, k, m)
-    y = np.full((m + 2, n), GUARD, np.float32)
-    emu(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay, form=1)
-    want = oracle.product(w, n, k, x.view(np.uint16), m)
-    assert oracle.diff(y[:m], want)[0] == 0
-    assert (y[m:] == GUARD).all()
-    # the same tiles, units and order of sums as the kernel that ships: the same bits
-    ships = np.zeros((m, n), np.float32)
-    emu(w, n, k, x, ships, grid=grid, ntok=ntok)
-    assert np.array_equal(ships, y[:m])
+    runs = []
+    for _ in range(2):
+        y = np.full((m + 2, n), GUARD, np.float32)
+        emu(w, n, k, x, y[:m], grid=grid, ntok=ntok, delay_us=delay, form=1)
+        want = oracle.product(w, n, k, x.view(np.uint16), m)
+        assert oracle.diff(y[:m], want)[0] == 0
+        assert (y[m:] == GUARD).all()
+        runs.append(y)
+    # the sums run in a fixed order whatever the timing: the same bits every time
+    assert np.array_equal(runs[0], runs[1])
 
 
-def test_duo_bfloat16_live_batch_and_fused_stores(emu, oracle):
+def test_decode_kernel_bfloat16_live_batch_and_fused_stores(emu, oracle):
     import aotx_b200
     import torch
     n, k, m, grid, ntok = 300, 1024, 20, 5, 32
@@ -527,6 +394,7 @@ def test_duo_bfloat16_live_batch_and_fused_stores(emu, oracle):
     bits = np.ascontiguousarray(xb.view(torch.int16).numpy().view(np.uint16))
     y = np.full((m + 1, n), GUARD, np.float32)
     emu(w, n, k, bits, y[:m], bf16=1, grid=grid, ntok=ntok, form=1, delay_us=30)
+    # binary16 weights; the bfloat16 x tile is turned into binary16 where it lies
     assert oracle.diff(y[:m], oracle.product(w, n, k, bits, m, bf16=True))[0] == 0
     assert (y[m:] == GUARD).all()
     x = inputs(m, k, 33, scale=4.0)
@@ -549,7 +417,7 @@ def test_duo_bfloat16_live_batch_and_fused_stores(emu, oracle):
 
 
 @pytest.mark.parametrize("lost,delay", [(0, None), (3, 50), (11, None)])
-def test_duo_a_copy_that_never_lands(emu, lost, delay):
+def test_decode_kernel_a_copy_that_never_lands(emu, lost, delay):
     import aotx_b200
     n, k, m, grid, ntok = 300, 2048, 20, 5, 32
     w = aotx_b200.synth_q8_0(n, k, 5)
@@ -559,34 +427,6 @@ def test_duo_a_copy_that_never_lands(emu, lost, delay):
     assert status & 1
     assert status & ~0x103 == 0, hex(status)
     assert (y[m:] == GUARD).all()
-
-
-def test_duo_requests_for_the_following_product(emu, oracle):
-    import aotx_b200
-    n, k, m, grid, ntok = 300, 1024, 5, 6, 16
-    w = aotx_b200.synth_q8_0(n, k, 51)
-    w2 = aotx_b200.synth_q8_0(200, 768, 52)
-    x = inputs(m, k, 53)
-    y = np.zeros((m, n), np.float32)
-    asked = emu(w, n, k, x, y, grid=grid, ntok=ntok, following=(w2, 200, 768, m, 2), form=1)
-    assert asked == pieces_bytes(200, 768, m, ntok, 2, grid)
-
-
-@pytest.mark.parametrize("tile,fused", [(16, False), (32, True)])
-def test_duo_routed_experts(emu, oracle, tile, fused):
-    import aotx_b200
-    tokens, experts, used, hidden, ffn = 40, 3, 2, 512, 256
-    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 120 + tile)
-    both = aotx_b200.interleave_rows(wg, wu, hidden, groups=experts) if fused else None
-    proj, act, pair = emu.moe(None if fused else wg, None if fused else wu, both, wd, experts, hidden, ffn, x, ids,
-                              tile=tile, grid=7, delay_us=20, form=1)
-    ships, _, _ = emu.moe(None if fused else wg, None if fused else wu, both, wd, experts, hidden, ffn, x, ids,
-                          tile=tile, grid=7)
-    assert np.array_equal(proj, ships)
-    got = oracle.ordered_sum(np.ascontiguousarray(proj.transpose(1, 0, 2)), prob, ids)
-    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
-    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
-    assert ok, (err, bound)
 
 
 @pytest.mark.parametrize("form", [0, 1])
@@ -648,26 +488,6 @@ def test_table_build_is_a_stable_sort_with_exact_tables(emu, tokens, used, exper
     assert counts.tolist() == [len(want_feed), len(want_down)]
     assert feed[:len(want_feed)].tolist() == [list(t) for t in want_feed]
     assert down[:len(want_down)].tolist() == [list(t) for t in want_down]
-
-
-def test_switch_x_tile_kept_across_row_tiles(emu, oracle):
-    """Switch 64 of an experiment build: in the grouped down product of a layer whose expert
-    width is three segments (768), the three x stages hold a token tile's whole rows, and the
-    row tiles that follow over the same token tile take them as they are.  Same bits, fewer
-    copies."""
-    tokens, experts, used, hidden, ffn = 40, 3, 2, 256, 768
-    wg, wu, wd, x, prob, ids = moe_case(oracle, tokens, experts, used, hidden, ffn, 140)
-    plain, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=64, grid=3)
-    copies_plain = emu.copies
-    kept, _, _ = emu.moe(wg, wu, None, wd, experts, hidden, ffn, x, ids, tile=64, grid=3, switches=64, delay_us=20)
-    assert np.array_equal(kept, plain)
-    # down: 3 experts x 2 row tiles x 3 segments x 4 boxes of x; with the switch each block copies a
-    # token tile's segments once
-    assert emu.copies < copies_plain
-    got = oracle.ordered_sum(np.ascontiguousarray(kept.transpose(1, 0, 2)), prob, ids)
-    want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x.view(np.uint16), prob, ids)
-    ok, err, bound = oracle.within_bound(got, want.astype(np.float64))
-    assert ok, (err, bound)
 
 
 def test_benchmark_projection_at_full_size_and_grid(emu, oracle):
