@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libaotx_q8_b200.so")
-SOURCES = ["q8_api.cu", "q8_simt.cu", "q8_dispatch.cu", "q8_stream.cu", "q8_decode.cu", "q8_wide.cu", "q8_static.cu", "q8_moe.cu",
+SOURCES = ["q8_api.cu", "q8_simt.cu", "q8_dispatch.cu", "q8_stream.cu", "q8_decode.cu", "q8_wide.cu", "q8_static.cu", "q8_moe.cu", "q8_peers.cu",
            "q_generic.cu", "gguf_table.cpp", "gguf_upload.cu"]
 HEADERS = ["q8_common.cuh", "q8_ptx.cuh", "q8_store.cuh", "q8_simt_gemv.cuh", "q8_launch.h", "q8_tile.cuh", "q_blocks.cuh", os.path.join("..", "..", "include", "aotx_q8_b200.h"),
            os.path.join("..", "..", "include", "aotx_gguf_b200.h")]

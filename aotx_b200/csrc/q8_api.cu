@@ -452,3 +452,37 @@ extern "C" int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *
                                       ctx->overlap != 0, &out);
     return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
 }
+
+extern "C" int aotx_q8_peer_barrier(aotx_q8_ctx *ctx, void *stream, void *const *flag_arrays, uint32_t peers,
+                                    uint32_t rank, uint32_t *step_word)
+{
+    if (ctx == nullptr || flag_arrays == nullptr || step_word == nullptr || peers == 0u || peers > 8u
+        || rank >= peers || !aligned(step_word, 4u)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    for (uint32_t i = 0; i < peers; ++i) {
+        if (flag_arrays[i] == nullptr || !aligned(flag_arrays[i], 4u)) {
+            return AOTX_Q8_ERR_ARGUMENT;
+        }
+    }
+    cudaError_t err = q8::launch_peer_barrier((cudaStream_t)stream, flag_arrays, peers, rank, step_word,
+                                              ctx->scratch.status);
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}
+
+extern "C" int aotx_q8_matmul_colsplit(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                                       uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                                       void *const *y_peers, void *const *flag_arrays, uint32_t peers,
+                                       uint32_t rank, uint32_t ldy, uint32_t col0, int y_dtype,
+                                       uint32_t *step_word)
+{
+    if (ctx == nullptr || flag_arrays == nullptr || step_word == nullptr || rank >= peers) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    int code = aotx_q8_matmul_peers(ctx, stream, w, type, n, k, x, x_dtype, m, m_dev, y_peers, peers, ldy, col0,
+                                    y_dtype);
+    if (code != AOTX_Q8_OK) {
+        return code;
+    }
+    return aotx_q8_peer_barrier(ctx, stream, flag_arrays, peers, rank, step_word);
+}

@@ -2,41 +2,45 @@
 // tile of 16 or 32): y[i][j] = sum_c x[i][c] * half(q[j][c] * d[j][c / 32]), float sums.
 //
 // HBM-bound: a launch moves n * (k / 32) * 34 bytes of weights once, whatever the batch.  What
-// decides the time of the 18 to 125 MB products of a decode step is not the steady stream but
-// the ends of a launch, so the kernel is built around three things:
-//   * two blocks fit on one SM (352 threads, 88 registers, about 102 KB of shared memory, half
-//     of the tensor memory each).  With programmatic dependent launch the blocks of the next
-//     product start beside the blocks of this one and stream and dequantise their first weights
-//     while this product finishes; only x, the live batch and the stores wait for it;
+// decides the time of the 18 to 125 MB products of a decode step is not only the steady stream
+// but the ends of a launch, so the kernel is built around these things:
+//   * two blocks fit on one SM (352 threads, 80 registers, about 103 KB of shared memory, half
+//     of the tensor memory each): while one block stores, or waits for the launch before it, the
+//     other block's copies are in flight, and with programmatic dependent launch the blocks of
+//     the next product start as soon as a place is free and stream and dequantise their first
+//     weights while this product finishes; only x, the live batch and the stores wait for it;
 //   * when the weight tensor has few row tiles (n up to about 9000), a tile is cut along k over
-//     a CLUSTER of up to 8 blocks, one piece each, and the pieces are summed through
-//     distributed shared memory: every block sends each other block its slice of the token
-//     columns, adds what it receives in block order and stores its own columns.  No global
-//     scratch, no flags to poll, and every block stores a share of the tile;
+//     a CLUSTER of 2, 4 or 8 blocks, one piece each, and the pieces are summed through
+//     distributed shared memory: every block writes each token column of its piece into the
+//     shared memory of the block that owns the column, the owner adds the pieces in block order
+//     and stores.  No global scratch, no flags to poll, and every block stores a share of the
+//     tile;
 //   * larger tensors run as (tile, segment) units dealt evenly over 2 blocks per SM.  A tile cut
 //     between blocks belongs to the block that holds its first segment, which is that block's
-//     last piece; the other holders publish their partial sums at the start of their ranges, and
-//     the owner fetches and adds them while its own last MMAs still run.
+//     last piece; the other holders publish their partial sums at the start of their ranges;
+//   * successive MMAs of a piece go to 64 / NTOK accumulators in turn, which the store adds up:
+//     an MMA of this shape does little work but takes about 0.1 us from issue to completion, and
+//     MMAs into one accumulator run one after the other;
+//   * the code is kept small (a short launch fetches its code cold, at its start and again at
+//     its end): the accumulator is read and stored in chunks of 8 columns inside ordinary loops,
+//     the store with every option (add, gated unit, several output buffers, row map) is one
+//     out-of-line function beside a short inline path for the plain store, and a wait is out of
+//     line too, except in the converters' loop.
 //
 // Inside a block (11 warps): warp 8 issues bulk tensor copies of raw weight segments
-// [128 rows x 272 B] into a two-deep ring; warps 0-7 are converters, thread = row, warps 4-7 for
-// the first half of every 256-weight segment and warps 0-3 for the second: nine 16-byte shared
-// loads, exact dequantisation in registers, tcgen05.st of 64 packed words into the thread's lane
-// of tensor memory; warp 10 issues tcgen05.mma 128 x NTOK x 16 with A from tensor memory and
-// B = the x tile in shared memory (128-byte swizzle), and first turns a bfloat16 x tile into
-// binary16 where it lies (one MMA takes both operands in one format; exact for magnitudes in
-// [2^-14, 65504], saturating above); warp 9 copies x tiles.  Warps 0-3 also read a finished
-// accumulator and store: between two segments they look whether the MMAs of the piece before
-// have completed, so the conversion never waits for a store.  The schedule never depends on the
-// live batch (one token tile), so the batch word is read only when storing, after the launches
-// before this one finished.  Every wait on a barrier or flag is bounded and raises a status bit
-// when it runs out.
-//
-// A short launch fetches its code cold, at its start and again at its end, so the code is kept
-// small: the accumulator is read and stored in chunks of 8 columns inside ordinary loops, the
-// store with every option (add, gated unit, several output buffers, row map) is one out-of-line
-// function beside a short inline path for the plain store, and the slow part of a wait is out of
-// line too.
+// [128 rows x 272 B] into a two-deep ring; warps 4-7 are converters, thread = row: nine 16-byte
+// shared loads per half segment, exact dequantisation in registers, tcgen05.st of 64 packed
+// words into the thread's lane of tensor memory (three half-segment stages), and - for bfloat16
+// activations - a few 16-byte chunks of the segment's x tile turned into binary16 where it
+// lies (one MMA takes both operands in one format; exact for magnitudes in [2^-14, 65504],
+// saturating above); warp 10 issues tcgen05.mma 128 x NTOK x 16 with A from tensor memory and
+// B = the x tile in shared memory (128-byte swizzle); warp 9 copies x tiles; warps 0-3 read the
+// sums and store.  The schedule never depends on the live batch (one token tile), so the batch
+// word is read only by the storing warps, after the launches before this one finished.  Every
+// wait on a barrier or flag is bounded and raises a status bit when it runs out; after a wait
+// the lanes of a warp vote, so that a wait that ends differently for two lanes (the bound runs
+// out for one just as the phase completes for another) cannot leave a lane behind at a
+// warp-wide step.
 //
 // Reference kernels replaced: ptx/gemv_q8.ptx:18-223, cuda/model/gemv.cuh:33-145 (and the
 // three-node switch of cuda/model/graph_host.cu:31-39 for these batches).
@@ -64,13 +68,18 @@ struct DecodeShape {
     static constexpr uint32_t a_stages = 3;                          // half segments of A in tensor memory
     static constexpr uint32_t x_sub_bytes = NTOK * kSubK * 2;        // one [NTOK x 64] swizzled box
     static constexpr uint32_t x_seg_bytes = kSubs * x_sub_bytes;     // four boxes = 256 weights deep
-    static constexpr uint32_t a_column0 = 64;                        // after the two accumulators
+    // The 64 accumulator columns hold 64 / NTOK sums of one piece: successive MMAs go to them in
+    // turn and the store adds them up.  An MMA of this shape does little work but takes about
+    // 0.1 us from issue to completion, and MMAs into one accumulator run one after the other, so
+    // a single sum holds the whole block to sixteen such latencies per segment.
+    static constexpr uint32_t chains = 64 / NTOK;
+    static constexpr uint32_t a_column0 = 64;                        // after the accumulators
     static constexpr uint32_t a_stage_columns = kSegK / 4;           // 64 words per row per half segment
     static constexpr uint32_t tmem_columns = 256;
     static constexpr uint32_t x_offset = 0;
     static constexpr uint32_t raw_offset = x_offset + x_depth * x_seg_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
-    static constexpr uint32_t bar_count = 2 * raw_stages + 2 * x_depth + 2 * a_stages + 4 + 1;
+    static constexpr uint32_t bar_count = 2 * raw_stages + 3 * x_depth + 2 * a_stages + 4 + 1;
     static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
     // what a block receives from the other blocks of its cluster lies over the x ring, which is
     // idle by then: per sending block its share of the token columns, 128 floats each
@@ -146,8 +155,26 @@ __device__ __forceinline__ void store_one(const UmmaArgs &args, const TilePlace 
 // Barriers and buffers of a block, as shared-space addresses.
 struct DecodeRings {
     uint32_t x_base, raw_base;
-    uint32_t raw_full, raw_empty, x_land, x_empty, a_full, a_empty, acc_full, acc_empty;
+    uint32_t raw_full, raw_empty, x_land, x_full, x_empty, a_full, a_empty, acc_full, acc_empty;
 };
+
+// Eight columns of a finished piece: the 64 / NTOK sums the MMAs went to in turn, added up.
+template <int NTOK>
+__device__ __forceinline__ void load_sums(uint32_t taddr, uint32_t (&v)[8])
+{
+    tmem_ld_32x8(taddr, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (uint32_t c = 1; c < 64u / (uint32_t)NTOK; ++c) {
+        uint32_t more[8];
+        tmem_ld_32x8(taddr + c * (uint32_t)NTOK, more);
+        tmem_ld_wait();
+#pragma unroll
+        for (uint32_t i = 0; i < 8u; ++i) {
+            v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(more[i]));
+        }
+    }
+}
 
 // One unit (a 256-weight segment of the block's 128 rows), half H of it: this thread's row from
 // the raw ring into registers, exact dequantisation, 64 packed words into the thread's lane of
@@ -156,7 +183,7 @@ struct DecodeRings {
 // and is slower: with three stages the MMA thread then waits for its operand.)
 template <int NTOK, int H>
 __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, uint32_t row, uint32_t lane,
-                                             uint32_t lane_base, volatile uint32_t *abort_flag,
+                                             uint32_t lane_base, bool b_bf16, volatile uint32_t *abort_flag,
                                              unsigned int *status)
 {
     using S = DecodeShape<NTOK>;
@@ -170,10 +197,13 @@ __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, u
     }
     uint32_t raw[36];
     load_raw<H>(r.raw_base + rst * kRawStageBytes + row * kSegBytes, raw);
-    // this half is in registers: as far as this warp goes, the raw segment may be overwritten
-    __syncwarp();
-    if (lane == 0u) {
-        mbar_arrive(r.raw_empty + 8u * rst);
+    if (H == 1) {
+        // both halves are in registers by now: as far as this warp goes, the raw segment may be
+        // overwritten
+        __syncwarp();
+        if (lane == 0u) {
+            mbar_arrive(r.raw_empty + 8u * rst);
+        }
     }
     const uint32_t hh = 2u * g + (uint32_t)H;
     const uint32_t st = hh % S::a_stages;
@@ -190,6 +220,28 @@ __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, u
     __syncwarp();
     if (lane == 0u) {
         mbar_arrive(r.a_full + 8u * st);
+    }
+    if (b_bf16) {
+        // One MMA takes both operands in one format: the 256 converter threads turn the unit's
+        // x segment into binary16 where it lies, a few 16-byte chunks each (the swizzle moves
+        // whole chunks, so the conversion is chunk by chunk whatever the layout).  After the
+        // weights, so that the conversion of weights never waits for x.
+        const uint32_t xst = g % S::x_depth;
+        const uint32_t xph = (g / S::x_depth) & 1u;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_hot(r.x_land + 8u * xst, xph, abort_flag, status))) {
+            return false;
+        }
+        const uint32_t x_seg = r.x_base + xst * S::x_seg_bytes;
+        const uint32_t me = (uint32_t)H * 128u + row;
+#pragma unroll
+        for (uint32_t c = 0; c < S::x_seg_bytes / 16u / 256u; ++c) {
+            bf16_chunk_to_f16_inplace(x_seg + 16u * (me + 256u * c));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0u) {
+            mbar_arrive(r.x_full + 8u * xst);
+        }
     }
     return true;
 }
@@ -209,7 +261,8 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     r.raw_full = bar_base;
     r.raw_empty = r.raw_full + 8u * S::raw_stages;
     r.x_land = r.raw_empty + 8u * S::raw_stages;  // the copy of an x segment is complete
-    r.x_empty = r.x_land + 8u * S::x_depth;
+    r.x_full = r.x_land + 8u * S::x_depth;        // ... and, for bfloat16 activations, turned into binary16
+    r.x_empty = r.x_full + 8u * S::x_depth;
     r.a_full = r.x_empty + 8u * S::x_depth;
     r.a_empty = r.a_full + 8u * S::a_stages;
     r.acc_full = r.a_empty + 8u * S::a_stages;
@@ -258,10 +311,11 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < S::raw_stages; ++i) {
             mbar_init(r.raw_full + 8u * i, 1u);
-            mbar_init(r.raw_empty + 8u * i, 2u * kDecConvertWarps);
+            mbar_init(r.raw_empty + 8u * i, kDecConvertWarps);
         }
         for (uint32_t i = 0; i < S::x_depth; ++i) {
             mbar_init(r.x_land + 8u * i, 1u);
+            mbar_init(r.x_full + 8u * i, 2u * kDecConvertWarps);
             mbar_init(r.x_empty + 8u * i, 1u);
         }
         for (uint32_t i = 0; i < S::a_stages; ++i) {
@@ -356,10 +410,7 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else if (warp == kDecMmaWarp) {
         // ---------------------------------------------------------------- MMA issue
-        // Lane 0 issues the MMAs.  For bfloat16 activations the whole warp first turns the x
-        // segment into binary16 where it lies (the swizzle moves whole 16-byte chunks, so the
-        // conversion is chunk by chunk whatever the layout); the MMAs it issued for the segment
-        // before run on the tensor core meanwhile.
+        // Lane 0 issues the MMAs.
         const uint32_t idesc = umma_idesc(kRows, (uint32_t)NTOK, 0u, 0u);
         uint32_t g = 0;
         uint32_t tc = 0;
@@ -368,43 +419,21 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         for (uint32_t u = u_begin; ok && u < u_end; ++tc) {
             const uint32_t left = u_end - u;
             const uint32_t s1 = (segs - s0) < left ? segs : s0 + left;
-            const uint32_t buf = tc & 1u;
-            const uint32_t aph = (tc >> 1) & 1u;
-            const uint32_t d_tmem = tmem_base + buf * (uint32_t)NTOK;
-            uint32_t accumulate = 0u;
+            const uint32_t aph = tc & 1u;
+            uint32_t chain = 0u;
+            uint32_t started = 0u;   // bit c: sum c holds MMAs of this piece already
             for (uint32_t s = s0; ok && s < s1; ++s, ++g) {
                 const uint32_t xst = g % S::x_depth;
                 const uint32_t xph = (g / S::x_depth) & 1u;
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait(r.x_land + 8u * xst, xph, abort_flag, args.status))) {
-                    ok = false;
-                    break;
-                }
-                Q8_STAMP(1u, g == 0u && lane == 0u)     // the first x segment has landed
-                if (args.b_bf16 != 0u) {
-                    // eight chunks of 16 bytes per lane at a time: the loads go out together, so
-                    // their latency is paid once per batch and not once per chunk
-                    const uint32_t x_seg = r.x_base + xst * S::x_seg_bytes + 16u * lane;
-#pragma unroll 1
-                    for (uint32_t c0 = 0; c0 < S::x_seg_bytes / 16u; c0 += 256u) {
-                        uint32_t w[8][4];
-#pragma unroll
-                        for (uint32_t i = 0; i < 8u; ++i) {
-                            ld_shared_v4(x_seg + 16u * (c0 + 32u * i), w[i][0], w[i][1], w[i][2], w[i][3]);
-                        }
-#pragma unroll
-                        for (uint32_t i = 0; i < 8u; ++i) {
-#pragma unroll
-                            for (uint32_t e = 0; e < 4u; ++e) {
-                                w[i][e] = bf16x2_to_f16x2(w[i][e]);
-                            }
-                            st_shared_v4(x_seg + 16u * (c0 + 32u * i), w[i][0], w[i][1], w[i][2], w[i][3]);
-                        }
-                    }
-                    fence_proxy_async_smem();
-                }
-                __syncwarp();
                 if (lane == 0u) {
-                    if (s == s0 && !mbar_wait(r.acc_empty + 8u * buf, aph ^ 1u, abort_flag, args.status)) {
+                    // the x segment has landed and, where it was bfloat16, the converters have
+                    // turned it into binary16
+                    if (!mbar_wait((args.b_bf16 != 0u ? r.x_full : r.x_land) + 8u * xst, xph, abort_flag,
+                                   args.status)) {
+                        ok = false;
+                    }
+                    Q8_STAMP(1u, g == 0u)                   // the first x segment is ready
+                    if (ok && s == s0 && !mbar_wait(r.acc_empty, aph ^ 1u, abort_flag, args.status)) {
                         ok = false;
                     }
 #pragma unroll 1
@@ -426,9 +455,10 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
                             for (uint32_t kk = 0; kk < kSubK / 16u; ++kk) {
                                 // 16 values: 8 columns of A, 32 bytes along the swizzled row of x
-                                umma_f16_ts(d_tmem, a_tmem + jl * (kSubK / 2u) + 8u * kk, b_desc + 2u * kk, idesc,
-                                            accumulate);
-                                accumulate = 1u;
+                                umma_f16_ts(tmem_base + chain * (uint32_t)NTOK, a_tmem + jl * (kSubK / 2u) + 8u * kk,
+                                            b_desc + 2u * kk, idesc, (started >> chain) & 1u);
+                                started |= 1u << chain;
+                                chain = chain + 1u == S::chains ? 0u : chain + 1u;
                             }
                         }
                         umma_commit(r.a_empty + 8u * st);
@@ -441,7 +471,7 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 ok = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
             if (ok && lane == 0u) {
-                umma_commit(r.acc_full + 8u * buf);
+                umma_commit(r.acc_full);
             }
             u += (s1 - s0);
             s0 = 0u;
@@ -453,181 +483,147 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_wait(drain_bar, 0u, &local_abort, nullptr);
         }
     } else if (warp >= kDecConvertWarp0) {
-        // ---------------------------------------------------------------- dequantise, first halves
+        // ---------------------------------------------------------------- dequantise
         const uint32_t cw = warp - kDecConvertWarp0;
         const uint32_t row = cw * 32u + lane;
         // this warp owns TMEM lanes [32 cw, +32): its rows of the tile
         const uint32_t lane_base = tmem_base + ((cw * 32u) << 16) + S::a_column0;
         uint32_t g = 0;
         for (uint32_t u = u_begin; u < u_end; ++u, ++g) {
-            if (!convert_unit<NTOK, 0>(r, g, row, lane, lane_base, abort_flag, args.status)) {
+            if (!convert_unit<NTOK, 0>(r, g, row, lane, lane_base, args.b_bf16 != 0u, abort_flag, args.status)
+                || !convert_unit<NTOK, 1>(r, g, row, lane, lane_base, args.b_bf16 != 0u, abort_flag, args.status)) {
                 break;
             }
         }
         Q8_STAMP(3u, cw == 0u && lane == 0u)       // conversion of the block's units done
     } else {
-        // ------------------------------------------- dequantise, second halves; read sums, store
+        // ---------------------------------------------------------------- read sums, store
         const uint32_t wq = warp;
         const uint32_t lane_row = wq * 32u + lane;
         const uint32_t lane_taddr = tmem_base + ((wq * 32u) << 16);
-        const uint32_t lane_base = lane_taddr + S::a_column0;
-        // conversion runs ahead of the MMAs; `done` is the first unit of the piece to store next
-        uint32_t u = u_begin;
-        uint32_t done = u_begin;
-        uint32_t tile = tile_begin;   // of the piece to store next
-        uint32_t s0 = seg_begin;
-        uint32_t g = 0;
-        uint32_t tc = 0;
-        bool waited = false;
-        bool ok = true;
-        while (ok) {
-            const bool more = u < u_end;
-            if (done < u_end && !split) {
-                const uint32_t buf = tc & 1u;
-                const uint32_t aph = (tc >> 1) & 1u;
-                // between two segments only look; with nothing left to convert, wait
-                const bool ready = __all_sync(0xFFFFFFFFu, more
-                    ? mbar_test_wait(r.acc_full + 8u * buf, aph) != 0u
-                    : mbar_wait(r.acc_full + 8u * buf, aph, abort_flag, args.status)) != 0;
-                if (!ready && !more) {
+        grid_dependency_wait();
+        m_live = args.m_max;
+        if (args.m_dev != nullptr) {
+            const unsigned int live = *args.m_dev;
+            m_live = live < m_live ? live : m_live;
+        }
+        if (!split) {
+            uint32_t tile = tile_begin;
+            uint32_t s0 = seg_begin;
+            uint32_t tc = 0;
+            for (uint32_t done = u_begin; done < u_end; ++tc) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(r.acc_full, tc & 1u, abort_flag, args.status))) {
                     break;
                 }
-                if (ready) {
-                    if (!waited) {
-                        grid_dependency_wait();
-                        m_live = args.m_max;
-                        if (args.m_dev != nullptr) {
-                            const unsigned int live = *args.m_dev;
-                            m_live = live < m_live ? live : m_live;
-                        }
-                        waited = true;
-                    }
-                    const uint32_t left = u_end - done;
-                    const uint32_t s1 = (segs - s0) < left ? segs : s0 + left;
-                    const bool owner = s0 == 0u;
-                    const bool whole = owner && s1 == segs;
-                    TilePlace place;
-                    place.w_row = place.j0 = tile * kRows;
-                    place.j_limit = args.n;
-                    place.i0 = 0u;
-                    place.i_limit = m_live;
-                    const uint32_t j = place.j0 + lane_row;
-                    unsigned int last_cc = blockIdx.x;
-                    if (owner && !whole) {
-                        // The other holders of this tile are the blocks right after this one; they
-                        // met it at the start of their ranges and have published their partial sums.
-                        last_cc = decode_holder((tile + 1u) * segs - 1u, blocks, units);
-                        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
-                            const unsigned int cc = base + lane;
-                            if (cc <= last_cc) {
-                                const unsigned int *flag = args.flags + 4u * cc + wq;
-                                const long long begin = clock64();
-                                while (ld_acquire_gpu(flag) == 0u) {
-                                    if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
-                                        atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
-                                        break;
-                                    }
+                const uint32_t left = u_end - done;
+                const uint32_t s1 = (segs - s0) < left ? segs : s0 + left;
+                const bool owner = s0 == 0u;
+                const bool whole = owner && s1 == segs;
+                TilePlace place;
+                place.w_row = place.j0 = tile * kRows;
+                place.j_limit = args.n;
+                place.i0 = 0u;
+                place.i_limit = m_live;
+                const uint32_t j = place.j0 + lane_row;
+                unsigned int last_cc = blockIdx.x;
+                if (owner && !whole) {
+                    // The other holders of this tile are the blocks right after this one; they
+                    // met it at the start of their ranges and have published their partial sums.
+                    last_cc = decode_holder((tile + 1u) * segs - 1u, blocks, units);
+                    for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+                        const unsigned int cc = base + lane;
+                        if (cc <= last_cc) {
+                            const unsigned int *flag = args.flags + 4u * cc + wq;
+                            const long long begin = clock64();
+                            while (ld_acquire_gpu(flag) == 0u) {
+                                if (clock64() - begin > Q8_WAIT_CYCLES || *abort_flag != 0u) {
+                                    atomicOr(args.status, Q8_DEV_FLAG_TIMEOUT);
+                                    break;
                                 }
                             }
                         }
-                        __syncwarp();
                     }
-                    tc_fence_after_sync();
-                    float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats + lane_row;
-                    // the other blocks' partial sums, added up in block order; all the loads of one
-                    // block's partial tile go out together (a trip to L2 each would cost more than
-                    // the whole store otherwise)
-                    float others[NTOK];
-                    if (last_cc != blockIdx.x) {
-                        const float *slot = args.partial + (unsigned long long)(blockIdx.x + 1u) * args.tile_floats
-                                          + lane_row;
-#pragma unroll
-                        for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
-                            others[i] = __ldcg(slot + (unsigned long long)i * kRows);
+                    __syncwarp();
+                }
+                tc_fence_after_sync();
+                float *own_slot = args.partial + (unsigned long long)blockIdx.x * args.tile_floats + lane_row;
+                // the other blocks' partial sums, added up in block order; all the loads of one
+                // block's partial tile go out together (a trip to L2 each would cost more than
+                // the whole store otherwise)
+                float others[NTOK];
+                if (last_cc != blockIdx.x) {
+                    const float *slot = args.partial + (unsigned long long)(blockIdx.x + 1u) * args.tile_floats
+                                      + lane_row;
+    #pragma unroll
+                    for (uint32_t i = 0; i < (uint32_t)NTOK; ++i) {
+                        others[i] = __ldcg(slot + (unsigned long long)i * kRows);
+                    }
+                }
+    #pragma unroll 1
+                for (unsigned int cc = blockIdx.x + 2u; cc <= last_cc; ++cc) {
+                    const float *slot = args.partial + (unsigned long long)cc * args.tile_floats + lane_row;
+    #pragma unroll
+                    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 16u) {
+                        float a[16];
+    #pragma unroll
+                        for (uint32_t i = 0; i < 16u; ++i) {
+                            a[i] = __ldcg(slot + (unsigned long long)(c0 + i) * kRows);
+                        }
+    #pragma unroll
+                        for (uint32_t i = 0; i < 16u; ++i) {
+                            others[c0 + i] += a[i];
                         }
                     }
-#pragma unroll 1
-                    for (unsigned int cc = blockIdx.x + 2u; cc <= last_cc; ++cc) {
-                        const float *slot = args.partial + (unsigned long long)cc * args.tile_floats + lane_row;
-#pragma unroll
-                        for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 16u) {
-                            float a[16];
-#pragma unroll
-                            for (uint32_t i = 0; i < 16u; ++i) {
-                                a[i] = __ldcg(slot + (unsigned long long)(c0 + i) * kRows);
-                            }
-#pragma unroll
-                            for (uint32_t i = 0; i < 16u; ++i) {
-                                others[c0 + i] += a[i];
-                            }
+                }
+    #pragma unroll
+                for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
+                    uint32_t v[8];
+                    load_sums<NTOK>(lane_taddr + c0, v);
+                    if (!owner) {
+    #pragma unroll
+                        for (uint32_t i = 0; i < 8u; ++i) {
+                            __stcg(own_slot + (unsigned long long)(c0 + i) * kRows, __uint_as_float(v[i]));
                         }
-                    }
-#pragma unroll
-                    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
-                        uint32_t v[8];
-                        tmem_ld_32x8(lane_taddr + buf * (uint32_t)NTOK + c0, v);
-                        tmem_ld_wait();
-                        if (!owner) {
-#pragma unroll
+                    } else {
+                        if (last_cc != blockIdx.x) {
+    #pragma unroll
                             for (uint32_t i = 0; i < 8u; ++i) {
-                                __stcg(own_slot + (unsigned long long)(c0 + i) * kRows, __uint_as_float(v[i]));
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) + others[c0 + i]);
                             }
-                        } else {
-                            if (last_cc != blockIdx.x) {
-#pragma unroll
-                                for (uint32_t i = 0; i < 8u; ++i) {
-                                    v[i] = __float_as_uint(__uint_as_float(v[i]) + others[c0 + i]);
-                                }
-                            }
-                            store_eight<YT>(args, place, lane_row, j, c0, v);
                         }
+                        store_eight<YT>(args, place, lane_row, j, c0, v);
                     }
-                    // The accumulator buffer is free again.
-                    tc_fence_before_sync();
+                }
+                // The accumulator buffer is free again.
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0u) {
+                    mbar_arrive(r.acc_empty);
+                }
+                if (!owner) {
+                    // Publish this warp's quarter of the partial tile; every lane makes its own
+                    // stores visible first.
+                    __threadfence();
                     __syncwarp();
                     if (lane == 0u) {
-                        mbar_arrive(r.acc_empty + 8u * buf);
+                        st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
                     }
-                    if (!owner) {
-                        // Publish this warp's quarter of the partial tile; every lane makes its own
-                        // stores visible first.
-                        __threadfence();
-                        __syncwarp();
-                        if (lane == 0u) {
-                            st_release_gpu(args.flags + 4u * blockIdx.x + wq, 1u);
-                        }
-                    } else if (!whole) {
-                        // Hand the consumed slots back for the next launch that uses this set
-                        // (ordered by the end of the kernel).
-                        for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
-                            const unsigned int cc = base + lane;
-                            if (cc <= last_cc) {
-                                *reinterpret_cast<volatile unsigned int *>(args.flags + 4u * cc + wq) = 0u;
-                            }
+                } else if (!whole) {
+                    // Hand the consumed slots back for the next launch that uses this set
+                    // (ordered by the end of the kernel).
+                    for (unsigned int base = blockIdx.x + 1u; base <= last_cc; base += 32u) {
+                        const unsigned int cc = base + lane;
+                        if (cc <= last_cc) {
+                            *reinterpret_cast<volatile unsigned int *>(args.flags + 4u * cc + wq) = 0u;
                         }
                     }
-                    done += (s1 - s0);
-                    s0 = 0u;
-                    ++tile;
-                    ++tc;
-                    continue;
                 }
+                done += (s1 - s0);
+                s0 = 0u;
+                ++tile;
             }
-            if (!more) {
-                break;
-            }
-            ok = convert_unit<NTOK, 1>(r, g, lane_row, lane, lane_base, abort_flag, args.status);
-            ++u;
-            ++g;
-        }
-        if (split) {
+        } else {
             // the block's one piece: wait for its MMAs, the exchange below reads the accumulator
-            grid_dependency_wait();
-            m_live = args.m_max;
-            if (args.m_dev != nullptr) {
-                const unsigned int live = *args.m_dev;
-                m_live = live < m_live ? live : m_live;
-            }
             mbar_wait(r.acc_full, 0u, abort_flag, args.status);
             tc_fence_after_sync();
             Q8_STAMP(5u, wq == 0u && lane == 0u)
@@ -663,8 +659,7 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
             uint32_t v[8];
-            tmem_ld_32x8(lane_taddr + c0, v);
-            tmem_ld_wait();
+            load_sums<NTOK>(lane_taddr + c0, v);
 #pragma unroll
             for (uint32_t i = 0; i < 8u; ++i) {
                 const uint32_t at = r.x_base + ((crank * share + local) * kRows + lane_row) * 4u;
@@ -755,10 +750,16 @@ unsigned int decode_grid(unsigned int row_tiles, unsigned int segs, unsigned int
     *cluster = 0u;
 #ifndef Q8_HOST_EMULATION
     if (2u * row_tiles <= sm_count) {
-        // At most one block per SM and launch, so that the blocks of the next product find the
-        // second place on every SM free and stage their weights while this product finishes.
-        unsigned int pieces = sm_count / row_tiles;
+        // As many pieces per tile as fill two blocks per SM.  (One block per SM and launch, so
+        // that the next product's blocks always find a free place, was measured and is slower:
+        // half as many blocks convert.)
+        unsigned int pieces = 2u * sm_count / row_tiles;
         unsigned int most = kDecMaxCluster;
+#ifdef Q8_TRACE
+        if (getenv("Q8_ONE_PER_SM") != nullptr) {
+            pieces = sm_count / row_tiles;   // development builds: the other placement, for comparison
+        }
+#endif
         pieces = pieces > most ? most : pieces;
         pieces = pieces > segs ? segs : pieces;
         // a power of two: clusters of 6 took three times as long to be placed as clusters of 4 or 8

@@ -169,7 +169,12 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
         g_trace_launches += 1;
     }
 #endif
-    if (ntok <= 32u) {
+#ifdef Q8_TRACE
+    const bool decode_kernel = getenv("Q8_DECODE") == nullptr || atoi(getenv("Q8_DECODE")) != 0;
+#else
+    const bool decode_kernel = true;
+#endif
+    if (ntok <= 32u && decode_kernel) {
         // one token tile: the decode kernel, two blocks per SM (q8_decode.cu); its unit
         // arithmetic is 32-bit
         if (units >= (1ull << 31)) {

@@ -129,6 +129,11 @@ struct PeerOut {
     unsigned int ldy;
 };
 
+// The barrier between the ranks of a column-split product (q8_peers.cu): flag_arrays[r] is rank
+// r's array of `peers` words as this GPU addresses it, step_word this rank's own counter.
+cudaError_t launch_peer_barrier(cudaStream_t stream, void *const *flag_arrays, unsigned int peers,
+                                unsigned int rank, unsigned int *step_word, unsigned int *status);
+
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.
 cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,

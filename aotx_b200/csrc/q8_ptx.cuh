@@ -261,6 +261,20 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int *p)
     return v;
 }
 
+// The same at system scope: a word that another GPU of the box writes or reads through a
+// peer-mapped address.
+__device__ __forceinline__ uint32_t ld_acquire_sys(const unsigned int *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned int *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void st_release_gpu(unsigned int *p, uint32_t v)
 {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -19,7 +19,7 @@ SYMBOLS = (
     "aotx_q8_device_status", "aotx_q8_dequant", "aotx_q8_matmul", "aotx_q8_moe_route",
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_static_status",
     "aotx_q8_matmul_peers",
-    "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused",
+    "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused", "aotx_q8_peer_barrier", "aotx_q8_matmul_colsplit",
 )
 
 # every symbol include/aotx_gguf_b200.h declares
@@ -88,6 +88,9 @@ def declare_q8(lib):
     lib.aotx_q8_static_status.argtypes = [C.POINTER(C.c_uint32), i32]
     lib.aotx_q8_matmul_peers.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), u32,
                                          u32, u32, i32]
+    lib.aotx_q8_peer_barrier.argtypes = [vp, vp, C.POINTER(vp), u32, u32, vp]
+    lib.aotx_q8_matmul_colsplit.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, C.POINTER(vp), C.POINTER(vp),
+                                            u32, u32, u32, u32, i32, vp]
     lib.aotx_q8_matmul_fused.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32, i32]
     lib.aotx_q8_moe_ffn_fused.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
                                           u32, vp, i32, vp, C.c_size_t]

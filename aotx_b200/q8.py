@@ -205,6 +205,24 @@ class Q8Context:
             m_dev.data_ptr() if m_dev is not None else None, array, len(y_ptrs), ldy, col0,
             _dtype_code(y_dtype)))
 
+    def peer_barrier(self, flag_ptrs, rank, step_word):
+        """The library's own barrier between the ranks of a column split: `flag_ptrs` are the
+        device addresses of every rank's flag array (own and peer-mapped), `step_word` a uint32
+        device tensor of this rank (zero at the start)."""
+        array = (C.c_void_p * len(flag_ptrs))(*[C.c_void_p(int(p)) for p in flag_ptrs])
+        self._check(self.lib.aotx_q8_peer_barrier(self.handle, self._stream(), array, len(flag_ptrs), rank,
+                                                  step_word.data_ptr()))
+
+    def matmul_colsplit(self, w, n, k, x, m, y_ptrs, flag_ptrs, rank, ldy, col0, y_dtype, step_word, m_dev=None,
+                        type=Q8_0):
+        """`matmul_peers` followed by `peer_barrier`: one call per rank and step."""
+        ys = (C.c_void_p * len(y_ptrs))(*[C.c_void_p(int(p)) for p in y_ptrs])
+        flags = (C.c_void_p * len(flag_ptrs))(*[C.c_void_p(int(p)) for p in flag_ptrs])
+        self._check(self.lib.aotx_q8_matmul_colsplit(
+            self.handle, self._stream(), w.data_ptr(), type, n, k, x.data_ptr(), _dtype_code(x.dtype), m,
+            m_dev.data_ptr() if m_dev is not None else None, ys, flags, len(y_ptrs), rank, ldy, col0,
+            _dtype_code(y_dtype), step_word.data_ptr()))
+
     def matmul_host(self, w, n, k, x_host, y_host, x_dev, y_dev):
         """The same product with the activations and the result in pinned host memory: copy
         in, multiply, copy out, all on the current stream (weights stay resident on the

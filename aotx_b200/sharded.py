@@ -85,10 +85,19 @@ class ColumnSplit:
 class ExpertParallel:
     """Routed feed-forward step with experts placed on ranks.
 
-    `experts(x_pairs, local_expert_of_pair) -> proj[pairs][hidden]` (float) runs the expert
-    products of this rank for the pairs it received (on GPUs: `Q8Context.moe_ffn` with one
-    selection per row and weight 1).  `combine(proj[tokens][used][hidden], prob, ids) -> out`
-    is the rank-ordered weighted sum (`Q8Context.moe_combine`)."""
+    `experts(x_rows, local_expert_of_row) -> proj[rows][hidden]` (float) runs the expert products
+    of this rank for the rows it received; a row whose expert number lies outside
+    [0, local experts) is padding and its result is never read (on GPUs: `Q8Context.moe_ffn` with
+    one selection per row and weight 1, which leaves such rows out).  `combine(proj[tokens][used]
+    [hidden], prob, ids) -> out` is the rank-ordered weighted sum (`Q8Context.moe_combine`).
+
+    Every buffer of the exchange has a fixed size (room for all of a rank's pairs towards every
+    destination), the counts never come to the host, and the padding carries an expert number
+    that names no expert, so the whole step is a fixed sequence of device operations and can be
+    captured in a CUDA graph.  A selection outside the expert table (ids >= experts_total) is
+    dropped on every rank alike and adds nothing to its token's sum, as on one GPU."""
+
+    PADDING = 0x7FFFFFF0  # an expert number no rank holds
 
     def __init__(self, experts_total, used, hidden, world, rank, experts, combine, group=None):
         self.experts_total, self.used, self.hidden = experts_total, used, hidden
@@ -103,45 +112,49 @@ class ExpertParallel:
         ids: [tokens_local][used] int32.  Returns out[tokens_local][hidden]."""
         import torch
         dist = _dist()
+        world = self.world
         tokens = x.shape[0]
         pairs = tokens * self.used
         flat = ids.reshape(-1).long()
-        owner = torch.empty_like(flat)
-        base, extra = divmod(self.experts_total, self.world)
+        valid = (flat >= 0) & (flat < self.experts_total)
+        base, extra = divmod(self.experts_total, world)
         edge = extra * (base + 1)
-        low = flat < edge
-        owner[low] = flat[low] // (base + 1)
-        if base > 0:
-            owner[~low] = extra + (flat[~low] - edge) // base
+        owner_low = flat // (base + 1)
+        owner_high = extra + (flat - edge) // max(base, 1)
+        owner = torch.where(flat < edge, owner_low, owner_high)
+        owner = torch.where(valid, owner, torch.full_like(owner, world))      # bucket `world`: dropped
         # pairs grouped by destination rank, stable, so that the way back is the inverse
         order = torch.argsort(owner, stable=True)
-        send_counts = torch.bincount(owner, minlength=self.world)
-        recv_counts = torch.empty_like(send_counts)
-        if self.world > 1:
-            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        owner_sorted = owner[order]
+        counts = torch.zeros(world + 1, dtype=torch.long, device=x.device)
+        counts.scatter_add_(0, owner, torch.ones_like(owner))
+        starts = torch.cumsum(counts, 0) - counts
+        place = torch.arange(pairs, device=x.device) - starts[owner_sorted]    # position within its destination
+        keep = owner_sorted < world
+        slot = torch.where(keep, owner_sorted * pairs + place, torch.full_like(place, world * pairs))
+        # one segment of `pairs` rows per destination (and one spare row that takes what is dropped)
+        rows_out = x.new_zeros((world * pairs + 1, self.hidden))
+        expert_out = torch.full((world * pairs + 1,), self.PADDING, dtype=torch.int32, device=x.device)
+        rows_out[slot] = x[order // self.used]
+        expert_out[slot] = torch.where(keep, flat[order], torch.full_like(flat, self.PADDING)).to(torch.int32)
+        rows_out, expert_out = rows_out[:world * pairs], expert_out[:world * pairs]
+        if world > 1:
+            rows_in = torch.empty_like(rows_out)
+            expert_in = torch.empty_like(expert_out)
+            dist.all_to_all_single(rows_in, rows_out, group=self.group)
+            dist.all_to_all_single(expert_in, expert_out, group=self.group)
         else:
-            recv_counts.copy_(send_counts)
-        send_list = send_counts.tolist()
-        recv_list = recv_counts.tolist()
-        rows_out = x[(order // self.used)]
-        expert_out = flat[order].to(torch.int32)
-        got = int(sum(recv_list))
-        rows_in = x.new_empty((got, self.hidden))
-        expert_in = expert_out.new_empty((got,))
-        if self.world > 1:
-            dist.all_to_all_single(rows_in, rows_out.contiguous(), recv_list, send_list, group=self.group)
-            dist.all_to_all_single(expert_in, expert_out.contiguous(), recv_list, send_list, group=self.group)
-        else:
-            rows_in.copy_(rows_out)
-            expert_in.copy_(expert_out)
+            rows_in, expert_in = rows_out, expert_out
         proj_in = self.experts(rows_in, expert_in - self.first)
-        proj_back = proj_in.new_empty((pairs, self.hidden))
-        if self.world > 1:
-            dist.all_to_all_single(proj_back, proj_in.contiguous(), send_list, recv_list, group=self.group)
+        if world > 1:
+            proj_back = torch.empty_like(proj_in)
+            dist.all_to_all_single(proj_back, proj_in.contiguous(), group=self.group)
         else:
-            proj_back.copy_(proj_in)
-        proj = proj_back.new_empty((pairs, self.hidden))
-        proj[order] = proj_back
+            proj_back = proj_in
+        # the result of a pair that was dropped is zero; the others come back from their slot
+        spare = torch.cat([proj_back, proj_back.new_zeros((1, self.hidden))])
+        proj = proj_back.new_zeros((pairs, self.hidden))
+        proj[order] = spare[slot]
         return self.combine(proj.reshape(tokens, self.used, self.hidden), prob, ids)
 
 
@@ -164,14 +177,19 @@ def expert_parallel_on_gpu(ctx, w_gate, w_up, w_down, experts_total, used, hidde
     first, last = shard_rows(experts_total, world, rank)
     local = last - first
 
+    state = {}
+
     def experts(rows, local_expert):
+        # every row carries one selection with weight 1; padding rows name no local expert and
+        # are left out of the products (their result rows are never read)
         count = rows.shape[0]
-        if count == 0:
-            return torch.zeros((0, hidden), dtype=torch.float32, device=rows.device)
-        ones = torch.ones((count, local), dtype=torch.float32, device=rows.device)
+        if "ones" not in state or state["ones"].shape[0] != count:
+            state["ones"] = torch.ones((count, local), dtype=torch.float32, device=rows.device)
+            state["workspace"] = ctx.moe_workspace(count, 1, hidden, ffn)
+            state["out"] = torch.zeros((count, hidden), dtype=torch.float32, device=rows.device)
         ids = local_expert.to(torch.int32).reshape(count, 1).contiguous()
-        return ctx.moe_ffn(w_gate, w_up, w_down, local, hidden, ffn, rows.contiguous(), ones, ids,
-                           tokens=count)
+        return ctx.moe_ffn(w_gate, w_up, w_down, local, hidden, ffn, rows.contiguous(), state["ones"], ids,
+                           tokens=count, out=state["out"], workspace=state["workspace"])
 
     def combine(proj, prob, ids):
         return ctx.moe_combine(proj.contiguous(), prob, ids)
@@ -180,12 +198,16 @@ def expert_parallel_on_gpu(ctx, w_gate, w_up, w_down, experts_total, used, hidde
 
 
 class ColumnSplitFused:
-    """Column-split projection whose gather happens in the product's own stores.
+    """Column-split projection whose gather happens in the product's own stores
+    (`aotx_q8_matmul_colsplit`).
 
-    y lives in symmetric memory (`torch.distributed._symmetric_memory`): every rank can store
-    into every rank's copy.  The kernel of rank r writes its column slice of each tile into all
-    copies (plain stores over NVLink, no multicast loads), and one device-side barrier orders
-    the ranks before anyone reads y.
+    y and a small array of flag words live in symmetric memory
+    (`torch.distributed._symmetric_memory`, used only to allocate and exchange the addresses):
+    every rank can store into every rank's copy.  The kernel of rank r writes its column slice of
+    each tile into all copies (plain stores over NVLink, no multicast loads), and the library's
+    own barrier - each rank writes a step number into its word of every rank's flag array and
+    waits, with a bound, until its own array has reached it - orders the ranks before anyone
+    reads y.  No library kernel sits on the step's path.
 
     There are two copies of y, used by alternate steps, and that is what makes one barrier per
     step enough: a rank that writes the buffer of step s + 2 has passed the barrier of step
@@ -211,13 +233,24 @@ class ColumnSplitFused:
         self.first, self.last = shard_rows(n, world, rank)
         self.y_dtype = y_dtype
         group = group if group is not None else dist.group.WORLD
-        self.y = symm.empty((2, m_max, n), dtype=y_dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.y = symm.empty((2, m_max, n), dtype=y_dtype, device=device)
         self.handle = symm.rendezvous(self.y, group)
         half = m_max * n * self.y.element_size()
         self.ptrs = [[int(p) + which * half for p in self.handle.buffer_ptrs] for which in (0, 1)]
+        # one flag word per source rank, and this rank's step counter
+        self.flags = symm.empty((max(world, 8),), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flag_handle = symm.rendezvous(self.flags, group)
+        self.flag_ptrs = [int(p) for p in self.flag_handle.buffer_ptrs]
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=device)
         self.step = 0
-        # nobody stores into a peer before every rank has its buffers
+        torch.cuda.synchronize()
+        # nobody stores into a peer before every rank has its buffers and zeroed flags (set-up only)
         self.handle.barrier(channel=0)
+
+    def barrier(self):
+        self.ctx.peer_barrier(self.flag_ptrs, self.rank, self.step_word)
 
     def matmul(self, x, m, opening_barrier=None):
         import torch
@@ -226,8 +259,7 @@ class ColumnSplitFused:
         if opening_barrier is None:
             opening_barrier = torch.cuda.is_current_stream_capturing()
         if opening_barrier:
-            self.handle.barrier(channel=which ^ 1)
-        self.ctx.matmul_peers(self.w_local, self.last - self.first, self.k, x, m, self.ptrs[which], self.n,
-                              self.first, self.y_dtype)
-        self.handle.barrier(channel=which)
+            self.barrier()
+        self.ctx.matmul_colsplit(self.w_local, self.last - self.first, self.k, x, m, self.ptrs[which],
+                                 self.flag_ptrs, self.rank, self.n, self.first, self.y_dtype, self.step_word)
         return self.y[which, :m]

@@ -207,6 +207,29 @@ int aotx_q8_matmul_peers(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t
                          uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
                          void *const *y_peers, uint32_t peers, uint32_t ldy, uint32_t col0, int y_dtype);
 
+/* The barrier that ends a column-split step, the library's own: flag_arrays[r] is rank r's array
+ * of `peers` 32-bit words (zero at the start; device memory that every rank can store into, as
+ * this GPU addresses it), step_word a word of this rank's own device memory (zero at the start)
+ * that the call counts up, so that a call captured in a CUDA graph arrives with a new number on
+ * every replay.  One small kernel: it writes the step number into this rank's word of every
+ * rank's array (ordinary system-scope stores, after a system-scope fence over what this GPU
+ * stored before) and waits until all words of its own array have reached it.  The wait is
+ * bounded (about two seconds of SM clock): when it runs out, AOTX_Q8_DEVICE_FLAG_TIMEOUT is
+ * raised in the context's status word and the kernel ends.  Every rank calls it the same number
+ * of times.  No counterpart in the reference (single GPU). */
+int aotx_q8_peer_barrier(aotx_q8_ctx *ctx, void *stream, void *const *flag_arrays, uint32_t peers,
+                         uint32_t rank, uint32_t *step_word);
+
+/* aotx_q8_matmul_peers followed by aotx_q8_peer_barrier on the same stream: one call per rank
+ * and step for a projection split by output columns (LM head, 70B-class FFN).  After it, on
+ * every rank, y holds all columns.  This is the form that replaces "product, then all-gather of
+ * the slices": the gather happens in the kernel's own stores, over NVLink, while the weights
+ * stream.  No counterpart in the reference. */
+int aotx_q8_matmul_colsplit(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t type, uint32_t n,
+                            uint32_t k, const void *x, int x_dtype, uint32_t m, const uint32_t *m_dev,
+                            void *const *y_peers, void *const *flag_arrays, uint32_t peers, uint32_t rank,
+                            uint32_t ldy, uint32_t col0, int y_dtype, uint32_t *step_word);
+
 /* The product without a context, for callers that cannot allocate device memory (a frozen
  * memory plan, a process whose device footprint must not grow, a plug-in that only gets a
  * stream and buffers).  Same arguments and result as aotx_q8_matmul; the scratch the kernel

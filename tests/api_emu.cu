@@ -92,6 +92,7 @@ static inline cudaError_t emulated_malloc(void **out, size_t bytes)
 #include "q8_simt.cu"
 #include "q_generic.cu"
 #include "q8_static.cu"
+#include "q8_peers.cu"
 #include "q8_api.cu"
 
 // Status bits the emulation itself raised since the last call of this function (work in flight at

@@ -517,6 +517,16 @@ inline uint32_t ld_acquire_gpu(const unsigned int *p)
     return reinterpret_cast<const std::atomic<unsigned int> *>(p)->load(std::memory_order_acquire);
 }
 
+inline uint32_t ld_acquire_sys(const unsigned int *p)
+{
+    return reinterpret_cast<const std::atomic<unsigned int> *>(p)->load(std::memory_order_acquire);
+}
+
+inline void st_release_sys(unsigned int *p, uint32_t v)
+{
+    reinterpret_cast<std::atomic<unsigned int> *>(p)->store(v, std::memory_order_release);
+}
+
 inline void st_release_gpu(unsigned int *p, uint32_t v)
 {
     reinterpret_cast<std::atomic<unsigned int> *>(p)->store(v, std::memory_order_release);

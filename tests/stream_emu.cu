@@ -154,6 +154,7 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define __ldcg(p) (*(p))
 #define __stcg(p, v) (*(p) = (v))
 #define __threadfence() std::atomic_thread_fence(std::memory_order_seq_cst)
+#define __threadfence_system() std::atomic_thread_fence(std::memory_order_seq_cst)
 #define blockDim (emu::block_dim)
 #define atomicAdd(word, value) emu::atomic_add((word), (value))
 #define Q8_HOST_EMULATION 1

@@ -328,3 +328,34 @@ def test_column_split_entry_point(api, oracle):
     for y in (mine, theirs):
         assert oracle.diff(y[:m, col0:col0 + n], want)[0] == 0
         assert (y[:m, :col0] == GUARD).all() and (y[:m, col0 + n:] == GUARD).all() and (y[m:] == GUARD).all()
+
+
+def test_peer_barrier_passes_when_every_rank_arrived_and_gives_up_when_one_never_does(api):
+    """aotx_q8_peer_barrier for rank 0 of two: it writes the step number into its word of both
+    flag arrays; with rank 1's word already there it passes, and the step word counts up; with a
+    rank that never arrives the bounded wait runs out, the flag-timeout bit is raised and the
+    call still returns (the failure is made on the host: a word nothing writes)."""
+    lib = api.lib
+    lib.stream_emu_faults.argtypes = [C.c_longlong, C.c_double]
+    mine = np.zeros(2, np.uint32)
+    theirs = np.zeros(2, np.uint32)
+    step = np.zeros(1, np.uint32)
+    arrays = (C.c_void_p * 2)(mine.ctypes.data, theirs.ctypes.data)
+    mine[1] = 1                                          # rank 1 has arrived for step 1
+    assert lib.aotx_q8_peer_barrier(api.ctx, None, arrays, 2, 0, step.ctypes.data) == OK
+    assert step[0] == 1 and mine[0] == 1 and theirs[0] == 1 and theirs[1] == 0
+    status = C.c_uint32(9)
+    assert lib.aotx_q8_device_status(api.ctx, C.byref(status), 1) == OK and status.value == 0
+    # step 2: rank 1 never arrives
+    lib.stream_emu_faults(-1, 0.3)
+    try:
+        assert lib.aotx_q8_peer_barrier(api.ctx, None, arrays, 2, 0, step.ctypes.data) == OK
+    finally:
+        lib.stream_emu_faults(-1, 10.0)
+    assert step[0] == 2 and theirs[0] == 2
+    assert lib.aotx_q8_device_status(api.ctx, C.byref(status), 1) != OK and status.value & 2
+    assert lib.aotx_q8_device_status(api.ctx, C.byref(status), 1) == OK and status.value == 0
+    # arguments
+    assert lib.aotx_q8_peer_barrier(api.ctx, None, arrays, 2, 2, step.ctypes.data) == 1
+    assert lib.aotx_q8_peer_barrier(api.ctx, None, arrays, 9, 0, step.ctypes.data) == 1
+    assert lib.aotx_q8_peer_barrier(api.ctx, None, arrays, 2, 0, None) == 1

@@ -41,7 +41,7 @@ def _column_worker(rank, world, port, n, k, m, result):
     dist.destroy_process_group()
 
 
-def _expert_worker(rank, world, port, result):
+def _expert_worker(rank, world, port, bad, result):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -60,25 +60,44 @@ def _expert_worker(rank, world, port, result):
     prob_all, ids_all = oracle.route(x_all.view(np.uint16), router, used)
     prob_all = prob_all.astype(np.float32)
     want = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x_all.view(np.uint16), prob_all, ids_all, threads=1)
+    if bad:
+        # a selection outside the expert table on every rank's share of the tokens: it adds nothing,
+        # the token's sum is that of its other selections in their order
+        ids_all = ids_all.copy()
+        for t in range(1, tokens_all, 4):
+            kept = np.ascontiguousarray(np.delete(ids_all[t], 1).reshape(1, used - 1))
+            want[t] = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x_all[t:t + 1].view(np.uint16),
+                                     prob_all[t:t + 1], kept, threads=1)[0]
+            ids_all[t, 1] = experts + 5
     t0, t1 = shard_rows(tokens_all, world, rank)
     e0, e1 = shard_rows(experts, world, rank)
     seen = []
 
     def run_experts(rows, local_expert):
-        # this rank only ever sees its own experts
-        seen.extend((local_expert + e0).tolist())
-        count = rows.shape[0]
-        ids = (local_expert + e0).numpy().astype(np.uint32).reshape(count, 1)
-        ones = np.ones((count, experts), np.float32)
-        if count == 0:
-            return torch.zeros((0, hidden))
-        out = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, rows.numpy().view(np.uint16), ones, ids,
-                             threads=1)
+        # rows that name one of this rank's experts are real; the others are padding of the
+        # fixed-size exchange and their results are never read
+        local = local_expert.numpy().astype(np.int64)
+        real = (local >= 0) & (local < e1 - e0)
+        seen.extend((local[real] + e0).tolist())
+        out = np.zeros((rows.shape[0], hidden), np.float32)
+        if real.any():
+            ids = (local[real] + e0).astype(np.uint32).reshape(-1, 1)
+            ones = np.ones((int(real.sum()), experts), np.float32)
+            picked = np.ascontiguousarray(rows.numpy()[real])
+            out[real] = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, picked.view(np.uint16), ones, ids,
+                                       threads=1)
         return torch.from_numpy(out)
 
     def combine(proj, prob, ids):
-        out = oracle.ordered_sum(np.ascontiguousarray(proj.numpy().transpose(1, 0, 2)), prob.numpy(),
-                                 ids.numpy().view(np.uint32))
+        # a selection that names no expert adds nothing: its projection rows are zero and its
+        # weight is taken as that of expert 0, so the sum does not change... except that adding a
+        # signed zero may not be the identity for -0.0; the kernel skips the rank instead
+        picks = ids.numpy().view(np.uint32)
+        out = np.zeros((proj.shape[0], proj.shape[2]), np.float32)
+        for t in range(proj.shape[0]):
+            good = [r for r in range(picks.shape[1]) if picks[t, r] < experts]
+            one = np.ascontiguousarray(proj.numpy()[t:t + 1, good].transpose(1, 0, 2))
+            out[t] = oracle.ordered_sum(one, prob.numpy()[t:t + 1], np.ascontiguousarray(picks[t:t + 1, good]))[0]
         return torch.from_numpy(out)
 
     ep = ExpertParallel(experts, used, hidden, world, rank, run_experts, combine)
@@ -121,7 +140,9 @@ def test_column_split_all_gather(world, n):
     assert result == {r: True for r in range(world)}
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_expert_parallel_all_to_all(world):
-    result = _spawn(_expert_worker, world)
+@pytest.mark.parametrize("world,bad", [(2, False), (3, False), (2, True)])
+def test_expert_parallel_all_to_all(world, bad):
+    """`bad`: some selections name no expert; every rank drops them alike and the exchange keeps
+    its fixed shape."""
+    result = _spawn(_expert_worker, world, bad)
     assert result == {r: True for r in range(world)}
