@@ -1,5 +1,5 @@
 """The sharded paths on real GPUs (needs two): every rank's result equals the single-GPU
-result of the same library."""
+result of the same library to float rounding, and the oracle's within the product bound."""
 import os
 import socket
 import sys
@@ -43,6 +43,10 @@ def _worker(rank, world, port, result):
     # a different split of the rows changes where tiles are cut between blocks, hence the
     # order of a few float additions: equal to float rounding, not bit for bit
     ok = ok and bool((y - want).abs().max() <= 1e-4 * want.abs().max())
+    from oracle.binding import Oracle
+    oracle = Oracle()
+    x_bits = x.cpu().numpy().view(np.uint16)
+    ok = ok and oracle.diff(y.cpu().numpy(), oracle.product(w, n, k, x_bits, m))[0] == 0
     # the same split with the gather fused into the product's stores (symmetric memory)
     from aotx_b200.sharded import ColumnSplitFused
     nf, kf = 3072, 1024
@@ -56,6 +60,7 @@ def _worker(rank, world, port, result):
     wantf = ctx.matmul(torch.from_numpy(wf).cuda(), nf, kf, xf)
     torch.cuda.synchronize()
     ok = ok and bool((yf - wantf).abs().max() <= 1e-4 * wantf.abs().max())
+    ok = ok and oracle.diff(yf.cpu().numpy(), oracle.product(wf, nf, kf, np.ascontiguousarray(x_bits[:, :kf]), m))[0] == 0
     # expert parallel
     experts, used, hidden, ffn, tokens_all = 16, 4, 512, 256, 40
     wg = aotx_b200.synth_q8_0(experts * ffn, hidden, 1)
@@ -77,6 +82,9 @@ def _worker(rank, world, port, result):
     out = ep.ffn(x_all[t0:t1].contiguous(), prob[t0:t1].contiguous(), ids[t0:t1].contiguous())
     torch.cuda.synchronize()
     ok = ok and bool((out - full[t0:t1]).abs().max() <= 1e-4 * full.abs().max())
+    want_moe = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x_all[t0:t1].cpu().numpy().view(np.uint16),
+                              prob[t0:t1].cpu().numpy(), ids[t0:t1].cpu().numpy().view(np.uint32))
+    ok = ok and oracle.within_bound(out.cpu().numpy(), want_moe.astype(np.float64))[0]
     ok = ok and ctx.device_status() == 0
     result[rank] = ok
     dist.destroy_process_group()
