@@ -486,3 +486,108 @@ extern "C" int aotx_q8_matmul_colsplit(aotx_q8_ctx *ctx, void *stream, const voi
     }
     return aotx_q8_peer_barrier(ctx, stream, flag_arrays, peers, rank, step_word);
 }
+
+// The split of `total` experts over `parts` GPUs: the first total % parts hold one more.
+static void expert_range(uint32_t total, uint32_t parts, uint32_t rank, uint32_t *first, uint32_t *last)
+{
+    const uint32_t share = total / parts;
+    const uint32_t extra = total % parts;
+    *first = rank * share + (rank < extra ? rank : extra);
+    *last = *first + share + (rank < extra ? 1u : 0u);
+}
+
+extern "C" size_t aotx_q8_moe_ep_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidden, uint32_t ffn,
+                                                 uint32_t peers)
+{
+    if (peers == 0u || peers > 8u) {
+        return 0u;
+    }
+    const size_t all = (size_t)tokens * peers;
+    return q8::moe_workspace_layout((unsigned int)all, used, hidden, ffn, kMaxExperts).bytes
+         + (all * used * sizeof(uint32_t) + 255u) / 256u * 256u;
+}
+
+extern "C" int aotx_q8_moe_ep(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up,
+                              const void *w_down, uint32_t type, uint32_t experts_total, uint32_t hidden,
+                              uint32_t ffn, const void *const *x_of_rank, const uint32_t *const *ids_of_rank,
+                              const float *prob, uint32_t tokens, uint32_t used, float *const *proj_of_rank,
+                              void *const *flag_arrays, uint32_t peers, uint32_t rank, uint32_t *step_word,
+                              void *out, int out_dtype, void *workspace, size_t workspace_bytes)
+{
+    if (ctx == nullptr || peers == 0u || peers > 8u || rank >= peers || x_of_rank == nullptr
+        || ids_of_rank == nullptr || proj_of_rank == nullptr || flag_arrays == nullptr || step_word == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (type != AOTX_Q8_TYPE_Q8_0) {
+        return AOTX_Q8_ERR_TYPE;
+    }
+    uint32_t first = 0u, last = 0u;
+    expert_range(experts_total, peers, rank, &first, &last);
+    const uint32_t local = last - first;
+    if (experts_total == 0u || local == 0u || local > kMaxExperts || used == 0u || used > experts_total
+        || hidden == 0u || ffn == 0u || !dtype_out(out_dtype)
+        || (unsigned long long)tokens * peers * used >= (1ull << 31)) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (tokens == 0u) {
+        return AOTX_Q8_OK;
+    }
+    if (w_gate == nullptr || w_up == nullptr || w_down == nullptr || prob == nullptr || out == nullptr) {
+        return AOTX_Q8_ERR_ARGUMENT;
+    }
+    for (uint32_t q = 0; q < peers; ++q) {
+        if (x_of_rank[q] == nullptr || ids_of_rank[q] == nullptr || proj_of_rank[q] == nullptr
+            || !aligned(x_of_rank[q], 16u) || !aligned(proj_of_rank[q], 16u)) {
+            return AOTX_Q8_ERR_ARGUMENT;
+        }
+    }
+    /* the expert-parallel step runs on the grouped tensor-core products only */
+    if (ctx->path == AOTX_Q8_PATH_GENERAL
+        || !q8::moe_grouped_supports(w_gate, w_up, w_down, x_of_rank[rank], hidden, ffn, local)) {
+        return AOTX_Q8_ERR_UNSUPPORTED;
+    }
+    const uint32_t all = tokens * peers;
+    q8::MoeWorkspace ws = q8::moe_workspace_layout(all, used, hidden, ffn, kMaxExperts);
+    const size_t ids_bytes = ((size_t)all * used * sizeof(uint32_t) + 255u) / 256u * 256u;
+    if (workspace == nullptr || !aligned(workspace, 256u) || workspace_bytes < ws.bytes + ids_bytes) {
+        return AOTX_Q8_ERR_WORKSPACE;
+    }
+    unsigned char *base = static_cast<unsigned char *>(workspace);
+    uint32_t *ids_all = reinterpret_cast<uint32_t *>(base + ws.bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+
+    /* every GPU's x and selections of this step are in place, and every GPU is done with the
+       projections of the step before */
+    cudaError_t err = q8::launch_peer_barrier(s, flag_arrays, peers, rank, step_word, ctx->scratch.status);
+    if (err == cudaSuccess) {
+        err = q8::launch_collect_ids(s, ids_of_rank, peers, tokens * used, first, ids_all);
+    }
+    if (err == cudaSuccess) {
+        q8::RowParts rows = {};
+        for (uint32_t q = 0; q < peers; ++q) {
+            rows.base[q] = x_of_rank[q];
+        }
+        rows.parts = peers;
+        rows.rows_per_part = tokens;
+        err = q8::launch_moe_grouped(s, ctx->scratch, ctx->sm_count, &ctx->launches, ctx->overlap != 0, w_gate,
+                                     w_up, w_down, local, hidden, ffn, x_of_rank[rank], ids_all, all, nullptr, used,
+                                     base, ws, &rows, proj_of_rank[rank]);
+    }
+    /* every GPU has written the projections of its experts */
+    if (err == cudaSuccess) {
+        err = q8::launch_peer_barrier(s, flag_arrays, peers, rank, step_word, ctx->scratch.status);
+    }
+    if (err == cudaSuccess) {
+        q8::ProjParts from = {};
+        for (uint32_t q = 0; q < peers; ++q) {
+            from.base[q] = proj_of_rank[q];
+        }
+        from.parts = peers;
+        from.share = experts_total / peers;
+        from.extra = experts_total % peers;
+        from.first_pair = rank * tokens * used;
+        err = q8::launch_expert_sum_parts(s, from, prob, ids_of_rank[rank], tokens, nullptr, hidden, experts_total,
+                                          used, out, out_dtype);
+    }
+    return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
+}

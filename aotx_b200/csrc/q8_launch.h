@@ -98,6 +98,25 @@ cudaError_t launch_route(cudaStream_t stream, const void *x, const float *router
                          const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                          unsigned int used, float *prob, unsigned int *ids);
 
+// Expert parallel (several GPUs, each holding a run of the experts; q8_api.cu aotx_q8_moe_ep).
+// Where the rows of x of all GPUs' tokens lie: rows_per_part rows in each of `parts` arrays
+// (own and peer-mapped); parts <= 1: one array.
+struct RowParts {
+    const void *base[8];
+    unsigned int parts;
+    unsigned int rows_per_part;
+};
+// Where the projections of this GPU's pairs lie: in the array of the GPU that holds the pair's
+// expert (the experts dealt to `parts` GPUs, the first `extra` of them holding share + 1, the
+// others share), at row first_pair + pair; parts <= 1: one array, first_pair 0.
+struct ProjParts {
+    const float *base[8];
+    unsigned int parts;
+    unsigned int share;
+    unsigned int extra;
+    unsigned int first_pair;
+};
+
 cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, const void *w_up,
                                      const void *w_down, unsigned int hidden, unsigned int ffn,
                                      const void *x, const unsigned int *ids, unsigned int experts,
@@ -108,6 +127,10 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
                               const unsigned int *ids, unsigned int tokens,
                               const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                               unsigned int used, void *out, int out_dtype);
+cudaError_t launch_expert_sum_parts(cudaStream_t stream, const ProjParts &proj, const float *prob,
+                                    const unsigned int *ids, unsigned int tokens,
+                                    const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                                    unsigned int used, void *out, int out_dtype);
 
 // The streaming tensor-core product.  Scratch, in two sets that alternate between launches:
 // `partial` holds one float tile of 128 x token_tile per block of the grid, `flags` four words
@@ -164,7 +187,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
                                const void *w_down, unsigned int experts, unsigned int hidden,
                                unsigned int ffn, const void *x, const unsigned int *ids, unsigned int tokens,
                                const unsigned int *tokens_dev, unsigned int used, unsigned char *workspace,
-                               const MoeWorkspace &ws);
+                               const MoeWorkspace &ws, const RowParts *x_parts = nullptr, float *proj_out = nullptr);
 
 cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scratch, unsigned int sm_count,
                                      unsigned int *launches, bool overlap, const void *w_gate_up,
@@ -172,6 +195,11 @@ cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scr
                                      unsigned int ffn, const void *x, const unsigned int *ids,
                                      unsigned int tokens, const unsigned int *tokens_dev, unsigned int used,
                                      unsigned char *workspace, const MoeWorkspace &ws);
+
+// ids_all[q * count + i] = ids_of_rank[q][i] - first_expert for the `parts` arrays of `count`
+// selections each: an expert of another GPU becomes a number that names no local expert.
+cudaError_t launch_collect_ids(cudaStream_t stream, const unsigned int *const *ids_of_rank, unsigned int parts,
+                               unsigned int count, unsigned int first_expert, unsigned int *ids_all);
 
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m);
 

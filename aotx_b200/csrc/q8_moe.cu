@@ -18,9 +18,13 @@ namespace q8 {
 #define Q8_GROUP_MAX_EXPERTS 256u
 #define Q8_GROUP_TOKENS_MAX 64u /* largest token tile of the grouped products */
 
+#ifndef Q8_GROUP_TOKENS
+#define Q8_GROUP_TOKENS 64u /* token tile of the grouped products */
+#endif
+
 static unsigned int group_tokens()
 {
-    return 64u;
+    return Q8_GROUP_TOKENS;
 }
 
 // One block.  Counts the pairs of every expert, places each pair in its expert's run of
@@ -28,6 +32,12 @@ static unsigned int group_tokens()
 // with it the token tile it lands in and the points where that tile's sums are cut between
 // blocks, is a function of the selections alone, so the results repeat bit for bit from run to
 // run), and writes the two tile tables.
+//
+// Every warp takes one contiguous run of the pairs.  Pass 1 counts, per warp and expert, the
+// warp's pairs (lanes that name the same expert find each other with a match); a scan over the
+// warps turns the counts into each warp's first place within the expert; pass 2 walks the
+// same run again and places the pairs, lanes in order within a step, steps in order within
+// the warp, warps in order within the expert.
 __global__ void __launch_bounds__(Q8_GROUP_THREADS)
 q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_max,
                       const unsigned int *tokens_dev, unsigned int used, unsigned int experts,
@@ -37,13 +47,13 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
 {
     __shared__ unsigned int count[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int offset[Q8_GROUP_MAX_EXPERTS];
-    __shared__ unsigned int cursor[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int feed_base[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int down_base[Q8_GROUP_MAX_EXPERTS];
     __shared__ unsigned int placed;
-    // one round of the placement: the expert of every thread's pair, and per warp and expert
-    // first the number of its pairs in this round, then the place of the warp's first one
-    __shared__ unsigned int round_expert[Q8_GROUP_THREADS];
+    __shared__ unsigned int scan_pairs[Q8_GROUP_MAX_EXPERTS];
+    __shared__ unsigned int scan_tiles[Q8_GROUP_MAX_EXPERTS];
+    // per warp and expert: first the number of the warp's pairs, then the next free place of
+    // the warp within the expert's run
     __shared__ unsigned int warp_place[Q8_GROUP_THREADS / 32u][Q8_GROUP_MAX_EXPERTS];
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
@@ -56,93 +66,110 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
     const unsigned int warp = threadIdx.x >> 5;
     const unsigned int lane = threadIdx.x & 31u;
     const unsigned int warps = blockDim.x >> 5;
-    for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
-        count[e] = 0u;
-        cursor[e] = 0u;
+    // the warp's run of pairs, a whole number of steps of 32
+    const unsigned int per_warp = ((pairs + warps - 1u) / warps + 31u) / 32u * 32u;
+    const unsigned int run_begin = warp * per_warp < pairs ? warp * per_warp : pairs;
+    const unsigned int run_end = run_begin + per_warp < pairs ? run_begin + per_warp : pairs;
+    const unsigned int none = 0xFFFFFFFFu;
+
+    for (unsigned int e = lane; e < experts; e += 32u) {
+        warp_place[warp][e] = 0u;
     }
-    __syncthreads();
+    __syncwarp();
     // A selection outside the expert table is left out of both passes (its result row is then
     // never written), rather than indexing past the tables.
-    for (unsigned int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        unsigned int e = ids[p];
-        if (e < experts) {
-            atomicAdd(&count[e], 1u);
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0u) {
-        unsigned int at = 0u;
-        unsigned int feed = 0u;
-        unsigned int down = 0u;
-        for (unsigned int e = 0u; e < experts; ++e) {
-            offset[e] = at;
-            feed_base[e] = feed;
-            down_base[e] = down;
-            unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
-            at += count[e];
-            feed += tok_tiles * feed_rows;
-            down += tok_tiles * down_rows;
-        }
-        counts[0] = feed;
-        counts[1] = down;
-        placed = at;
-    }
-    __syncthreads();
-    // Placement, blockDim pairs per round, in order of the pair index: a pair's place is its
-    // expert's offset + the pairs of that expert in earlier rounds (cursor) + those in lower
-    // warps of this round + those in lower lanes of its own warp.
-    for (unsigned int first = 0u; first < pairs; first += blockDim.x) {
-        const unsigned int p = first + threadIdx.x;
-        unsigned int e = p < pairs ? ids[p] : 0xFFFFFFFFu;
+    for (unsigned int first = run_begin; first < run_end; first += 32u) {
+        const unsigned int p = first + lane;
+        unsigned int e = p < run_end ? ids[p] : none;
         if (e >= experts) {
-            e = 0xFFFFFFFFu;
+            e = none;
         }
-        round_expert[threadIdx.x] = e;
-        for (unsigned int i = lane; i < experts; i += 32u) {
-            warp_place[warp][i] = 0u;
+        const unsigned int same = __match_any_sync(0xFFFFFFFFu, e);
+        if (e != none && (same & ((1u << lane) - 1u)) == 0u) {
+            warp_place[warp][e] += (unsigned int)__popc(same); // the lowest lane speaks for the expert
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
+        unsigned int running = 0u;
+        for (unsigned int w = 0u; w < warps; ++w) {
+            const unsigned int here = warp_place[w][e];
+            warp_place[w][e] = running;
+            running += here;
+        }
+        count[e] = running;
+    }
+    __syncthreads();
+    // running totals over the experts of the pairs and of the token tiles (a scan in shared
+    // memory, one thread per expert): an expert's first place and first table entries
+    {
+        const unsigned int e = threadIdx.x;
+        const unsigned int mine = e < experts ? count[e] : 0u;
+        const unsigned int mine_tiles = (mine + tile_tokens - 1u) / tile_tokens;
+        if (e < Q8_GROUP_MAX_EXPERTS) {
+            scan_pairs[e] = mine;
+            scan_tiles[e] = mine_tiles;
         }
         __syncthreads();
-        unsigned int below = 0u;
-        unsigned int same = 0u;
-        if (e != 0xFFFFFFFFu) {
-            for (unsigned int i = 0u; i < 32u; ++i) {
-                const unsigned int other = round_expert[warp * 32u + i];
-                same += other == e ? 1u : 0u;
-                below += (other == e && i < lane) ? 1u : 0u;
+        for (unsigned int step = 1u; step < Q8_GROUP_MAX_EXPERTS; step <<= 1) {
+            unsigned int add_pairs = 0u;
+            unsigned int add_tiles = 0u;
+            if (e < Q8_GROUP_MAX_EXPERTS && e >= step) {
+                add_pairs = scan_pairs[e - step];
+                add_tiles = scan_tiles[e - step];
             }
+            __syncthreads();
+            if (e < Q8_GROUP_MAX_EXPERTS) {
+                scan_pairs[e] += add_pairs;
+                scan_tiles[e] += add_tiles;
+            }
+            __syncthreads();
+        }
+        if (e < experts) {
+            offset[e] = scan_pairs[e] - mine;
+            feed_base[e] = (scan_tiles[e] - mine_tiles) * feed_rows;
+            down_base[e] = (scan_tiles[e] - mine_tiles) * down_rows;
+            if (e == experts - 1u) {
+                counts[0] = scan_tiles[e] * feed_rows;
+                counts[1] = scan_tiles[e] * down_rows;
+                placed = scan_pairs[e];
+            }
+        }
+    }
+    __syncthreads();
+    for (unsigned int first = run_begin; first < run_end; first += 32u) {
+        const unsigned int p = first + lane;
+        unsigned int e = p < run_end ? ids[p] : none;
+        if (e >= experts) {
+            e = none;
+        }
+        const unsigned int same = __match_any_sync(0xFFFFFFFFu, e);
+        const unsigned int below = (unsigned int)__popc(same & ((1u << lane) - 1u));
+        const unsigned int base = e != none ? warp_place[warp][e] : 0u;
+        __syncwarp();
+        if (e != none) {
+            sorted_pair[offset[e] + base + below] = p;
             if (below == 0u) {
-                warp_place[warp][e] = same; // the first lane with this expert speaks for the warp
+                warp_place[warp][e] = base + (unsigned int)__popc(same);
             }
         }
-        __syncthreads();
-        for (unsigned int i = threadIdx.x; i < experts; i += blockDim.x) {
-            unsigned int running = cursor[i];
-            for (unsigned int w = 0u; w < warps; ++w) {
-                const unsigned int here = warp_place[w][i];
-                warp_place[w][i] = running;
-                running += here;
-            }
-            cursor[i] = running;
-        }
-        __syncthreads();
-        if (e != 0xFFFFFFFFu) {
-            sorted_pair[offset[e] + warp_place[warp][e] + below] = p;
-        }
-        __syncthreads();
+        __syncwarp();
     }
     // the places that pairs left out would have taken name no pair (the gather skips them)
     for (unsigned int at = placed + threadIdx.x; at < pairs; at += blockDim.x) {
         sorted_pair[at] = 0xFFFFFFFFu;
     }
-    for (unsigned int e = threadIdx.x; e < experts; e += blockDim.x) {
-        unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
+    // the tile tables: a warp per expert, a lane per weight row tile
+    for (unsigned int e = warp; e < experts; e += warps) {
+        const unsigned int tok_tiles = (count[e] + tile_tokens - 1u) / tile_tokens;
         for (unsigned int tt = 0u; tt < tok_tiles; ++tt) {
-            unsigned int tok0 = offset[e] + tt * tile_tokens;
+            const unsigned int tok0 = offset[e] + tt * tile_tokens;
             unsigned int tok_limit = offset[e] + count[e];
             if (tok_limit > tok0 + tile_tokens) {
                 tok_limit = tok0 + tile_tokens;
             }
-            for (unsigned int r = 0u; r < feed_rows; ++r) {
+            for (unsigned int r = lane; r < feed_rows; r += 32u) {
                 GroupTile t;
                 t.w_row = e * ffn + r * kRows;
                 t.j0 = r * kRows;
@@ -151,7 +178,7 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
                 t.tok_limit = tok_limit;
                 tiles_feed[feed_base[e] + tt * feed_rows + r] = t;
             }
-            for (unsigned int r = 0u; r < down_rows; ++r) {
+            for (unsigned int r = lane; r < down_rows; r += 32u) {
                 GroupTile t;
                 t.w_row = e * hidden + r * kRows;
                 t.j0 = r * kRows;
@@ -165,7 +192,9 @@ q8_group_build_kernel(const unsigned int *__restrict__ ids, unsigned int tokens_
 }
 
 // x_sorted[i] = x[sorted_pair[i] / used], rows of `hidden` halves, 16 bytes per thread step.
-__global__ void q8_gather_rows_kernel(const uint4 *__restrict__ x, const unsigned int *__restrict__ sorted_pair,
+// Expert parallel: token t is row t % rows_per_part of array t / rows_per_part (the tokens of
+// all GPUs, each GPU's in its own array, read through peer-mapped addresses).
+__global__ void q8_gather_rows_kernel(const __grid_constant__ RowParts x, const unsigned int *__restrict__ sorted_pair,
                                       unsigned int tokens_max, const unsigned int *tokens_dev,
                                       unsigned int used, unsigned int row_chunks, uint4 *__restrict__ out)
 {
@@ -180,11 +209,45 @@ __global__ void q8_gather_rows_kernel(const uint4 *__restrict__ x, const unsigne
         if (p >= pairs) {
             continue; // no pair here: a selection outside the expert table was left out
         }
-        const unsigned int t = p / used;
+        unsigned int t = p / used;
+        const uint4 *from = static_cast<const uint4 *>(x.base[0]);
+        if (x.parts > 1u) {
+            from = static_cast<const uint4 *>(x.base[t / x.rows_per_part]);
+            t = t % x.rows_per_part;
+        }
         for (unsigned int c = threadIdx.x; c < row_chunks; c += blockDim.x) {
-            out[(size_t)i * row_chunks + c] = x[(size_t)t * row_chunks + c];
+            out[(size_t)i * row_chunks + c] = from[(size_t)t * row_chunks + c];
         }
     }
+}
+
+// ids_all[q * count + i] = ids_of_rank[q][i] - first: the selections of every GPU's tokens,
+// numbered from this GPU's first expert (unsigned: an expert below it wraps to a number that
+// names no local expert, like one above the last).
+struct IdParts {
+    const unsigned int *base[8];
+};
+
+__global__ void q8_collect_ids_kernel(const __grid_constant__ IdParts ids, unsigned int parts, unsigned int count,
+                                      unsigned int first, unsigned int *__restrict__ ids_all)
+{
+    const unsigned int total = parts * count;
+    for (unsigned int at = blockIdx.x * blockDim.x + threadIdx.x; at < total; at += gridDim.x * blockDim.x) {
+        const unsigned int q = at / count;
+        ids_all[at] = ids.base[q][at - q * count] - first;
+    }
+}
+
+cudaError_t launch_collect_ids(cudaStream_t stream, const unsigned int *const *ids_of_rank, unsigned int parts,
+                               unsigned int count, unsigned int first_expert, unsigned int *ids_all)
+{
+    IdParts ids = {};
+    for (unsigned int q = 0; q < parts && q < 8u; ++q) {
+        ids.base[q] = ids_of_rank[q];
+    }
+    const unsigned int total = parts * count;
+    const unsigned int grid = (total + 255u) / 256u < 148u * 4u ? (total + 255u) / 256u : 148u * 4u;
+    return launch_kernel(q8_collect_ids_kernel, grid, 256, 0, stream, ids, parts, count, first_expert, ids_all);
 }
 
 // act = half(silu(gate) * up), silu(g) = g / (1 + exp(-g))  (cuda/model/norm.cu:92-105)
@@ -256,7 +319,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
                                const void *w_down, unsigned int experts, unsigned int hidden,
                                unsigned int ffn, const void *x, const unsigned int *ids, unsigned int tokens,
                                const unsigned int *tokens_dev, unsigned int used, unsigned char *workspace,
-                               const MoeWorkspace &ws)
+                               const MoeWorkspace &ws, const RowParts *x_parts, float *proj_out)
 {
     const unsigned int pairs = tokens * used;
     const unsigned int tile_tokens = group_tokens();
@@ -268,7 +331,13 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
     float *gate = reinterpret_cast<float *>(workspace + ws.gate);
     float *up = reinterpret_cast<float *>(workspace + ws.up);
     __half *act = reinterpret_cast<__half *>(workspace + ws.act);
-    float *proj = reinterpret_cast<float *>(workspace + ws.proj);
+    float *proj = proj_out != nullptr ? proj_out : reinterpret_cast<float *>(workspace + ws.proj);
+    RowParts rows = {};
+    rows.base[0] = x;
+    rows.parts = 1u;
+    if (x_parts != nullptr) {
+        rows = *x_parts;
+    }
 
     cudaError_t err = launch_kernel(q8_group_build_kernel, 1, Q8_GROUP_THREADS, 0, stream, ids, tokens, tokens_dev,
                                     used, experts, ffn, hidden, sorted_pair, tiles_feed, tiles_down, counts,
@@ -277,7 +346,7 @@ cudaError_t launch_moe_grouped(cudaStream_t stream, const UmmaScratch &scratch, 
         return err;
     }
     const unsigned int wave = pairs < 148u * 16u ? pairs : 148u * 16u;
-    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, static_cast<const uint4 *>(x), sorted_pair, tokens,
+    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, rows, sorted_pair, tokens,
                         tokens_dev, used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
     if (err != cudaSuccess) {
         return err;
@@ -332,7 +401,10 @@ cudaError_t launch_moe_grouped_fused(cudaStream_t stream, const UmmaScratch &scr
         return err;
     }
     const unsigned int wave = pairs < 148u * 16u ? pairs : 148u * 16u;
-    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, static_cast<const uint4 *>(x), sorted_pair, tokens,
+    RowParts rows = {};
+    rows.base[0] = x;
+    rows.parts = 1u;
+    err = launch_kernel(q8_gather_rows_kernel, wave, 128, 0, stream, rows, sorted_pair, tokens,
                         tokens_dev, used, hidden / 8u, reinterpret_cast<uint4 *>(x_sorted));
     if (err != cudaSuccess) {
         return err;

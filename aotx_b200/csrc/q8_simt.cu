@@ -245,13 +245,20 @@ q8_expert_down_kernel(const unsigned char *__restrict__ w_down, unsigned int hid
 // out[t][d] = the ordered sum over ranks: rank 0 gives fmul(proj, p); each later rank adds
 // fmul(proj, p) with a separate rounding of the product and of the sum.  A thread carries
 // WIDTH neighbouring columns (WIDTH = 4: one 16-byte load of proj per rank); every column's
-// chain of roundings is the one written above whatever the width.
+// chain of roundings is the one written above whatever the width.  The loads of up to eight
+// ranks go out together before the chain of additions starts.
+//
+// `from` says where a pair's projection lies: in one array [tokens][used][hidden], or - expert
+// parallel - in the array of the GPU that holds the pair's expert (experts dealt to `parts`
+// GPUs as shard_rows deals rows: the first `extra` of them one expert more), at the row of
+// the pair among all GPUs' pairs (first_pair + t * used + r).
 template <typename YT, unsigned int WIDTH>
-__global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float *__restrict__ prob,
+__global__ void q8_expert_sum_kernel(const __grid_constant__ ProjParts from, const float *__restrict__ prob,
                                      const unsigned int *__restrict__ ids, unsigned int tokens_max,
                                      const unsigned int *tokens_dev, unsigned int hidden,
                                      unsigned int experts, unsigned int used, YT *__restrict__ out)
 {
+    constexpr unsigned int kTogether = 8u;
     unsigned int tokens = tokens_max;
     if (tokens_dev != nullptr) {
         unsigned int live = *tokens_dev;
@@ -264,34 +271,53 @@ __global__ void q8_expert_sum_kernel(const float *__restrict__ proj, const float
             for (unsigned int i = 0; i < WIDTH; ++i) {
                 sum[i] = 0.0f;
             }
-            for (unsigned int r = 0; r < used; ++r) {
-                unsigned int expert = ids[(size_t)t * used + r];
-                // a selection outside the expert table has no probability and no projection
-                // (the product kernels leave it out): it adds nothing
-                float value[WIDTH];
+            for (unsigned int r0 = 0; r0 < used; r0 += kTogether) {
+                float value[kTogether][WIDTH];
+                float p[kTogether];
 #pragma unroll
-                for (unsigned int i = 0; i < WIDTH; ++i) {
-                    value[i] = 0.0f;
-                }
-                if (expert < experts) {
-                    float p = prob[(size_t)t * experts + expert];
-                    const float *from = proj + ((size_t)t * used + r) * hidden + d;
-                    if (WIDTH == 4u) {
-                        float4 four = *reinterpret_cast<const float4 *>(from);
-                        value[0] = __fmul_rn(four.x, p);
-                        value[1 % WIDTH] = __fmul_rn(four.y, p);
-                        value[2 % WIDTH] = __fmul_rn(four.z, p);
-                        value[3 % WIDTH] = __fmul_rn(four.w, p);
-                    } else {
+                for (unsigned int q = 0; q < kTogether; ++q) {
+                    const unsigned int r = r0 + q;
+                    const unsigned int expert = r < used ? ids[(size_t)t * used + r] : 0xFFFFFFFFu;
+                    // a selection outside the expert table has no probability and no projection
+                    // (the product kernels leave it out): it adds nothing
+                    p[q] = 0.0f;
 #pragma unroll
-                        for (unsigned int i = 0; i < WIDTH; ++i) {
-                            value[i] = __fmul_rn(from[i], p);
+                    for (unsigned int i = 0; i < WIDTH; ++i) {
+                        value[q][i] = 0.0f;
+                    }
+                    if (expert < experts) {
+                        p[q] = prob[(size_t)t * experts + expert];
+                        const float *base = from.base[0];
+                        if (from.parts > 1u) {
+                            const unsigned int cut = from.extra * (from.share + 1u);
+                            const unsigned int owner = expert < cut ? expert / (from.share + 1u)
+                                                                    : from.extra + (expert - cut) / from.share;
+                            base = from.base[owner];
+                        }
+                        const float *row = base + ((size_t)from.first_pair + (size_t)t * used + r) * hidden + d;
+                        if (WIDTH == 4u) {
+                            const float4 four = *reinterpret_cast<const float4 *>(row);
+                            value[q][0] = four.x;
+                            value[q][1 % WIDTH] = four.y;
+                            value[q][2 % WIDTH] = four.z;
+                            value[q][3 % WIDTH] = four.w;
+                        } else {
+#pragma unroll
+                            for (unsigned int i = 0; i < WIDTH; ++i) {
+                                value[q][i] = row[i];
+                            }
                         }
                     }
                 }
 #pragma unroll
-                for (unsigned int i = 0; i < WIDTH; ++i) {
-                    sum[i] = (r == 0u) ? value[i] : __fadd_rn(sum[i], value[i]);
+                for (unsigned int q = 0; q < kTogether; ++q) {
+                    if (r0 + q < used) {
+#pragma unroll
+                        for (unsigned int i = 0; i < WIDTH; ++i) {
+                            const float term = __fmul_rn(value[q][i], p[q]);
+                            sum[i] = (r0 + q == 0u) ? term : __fadd_rn(sum[i], term);
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -414,7 +440,7 @@ cudaError_t launch_expert_pairs_simt(cudaStream_t stream, const void *w_gate, co
 }
 
 template <typename YT>
-static cudaError_t expert_sum_launch(bool wide, unsigned int grid, cudaStream_t stream, const float *proj,
+static cudaError_t expert_sum_launch(bool wide, unsigned int grid, cudaStream_t stream, const ProjParts &proj,
                                      const float *prob, const unsigned int *ids, unsigned int tokens,
                                      const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
                                      unsigned int used, void *out)
@@ -427,17 +453,20 @@ static cudaError_t expert_sum_launch(bool wide, unsigned int grid, cudaStream_t 
                          hidden, experts, used, static_cast<YT *>(out));
 }
 
-cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
-                              const unsigned int *ids, unsigned int tokens,
-                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
-                              unsigned int used, void *out, int out_dtype)
+cudaError_t launch_expert_sum_parts(cudaStream_t stream, const ProjParts &proj, const float *prob,
+                                    const unsigned int *ids, unsigned int tokens,
+                                    const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                                    unsigned int used, void *out, int out_dtype)
 {
     if (tokens == 0u) {
         return cudaSuccess;
     }
     unsigned int grid = tokens < 148u * 8u ? tokens : 148u * 8u;
     // 16-byte loads of proj need rows of a multiple of four floats on a 16-byte boundary
-    const bool wide = (hidden % 4u) == 0u && (reinterpret_cast<uintptr_t>(proj) & 15u) == 0u;
+    bool wide = (hidden % 4u) == 0u;
+    for (unsigned int i = 0; i < (proj.parts > 1u ? proj.parts : 1u); ++i) {
+        wide = wide && (reinterpret_cast<uintptr_t>(proj.base[i]) & 15u) == 0u;
+    }
     if (out_dtype == 0) {
         return expert_sum_launch<float>(wide, grid, stream, proj, prob, ids, tokens, tokens_dev, hidden, experts,
                                         used, out);
@@ -451,6 +480,18 @@ cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const floa
                                                 experts, used, out);
     }
     return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_expert_sum(cudaStream_t stream, const float *proj, const float *prob,
+                              const unsigned int *ids, unsigned int tokens,
+                              const unsigned int *tokens_dev, unsigned int hidden, unsigned int experts,
+                              unsigned int used, void *out, int out_dtype)
+{
+    ProjParts one = {};
+    one.base[0] = proj;
+    one.parts = 1u;
+    return launch_expert_sum_parts(stream, one, prob, ids, tokens, tokens_dev, hidden, experts, used, out,
+                                   out_dtype);
 }
 
 } // namespace q8

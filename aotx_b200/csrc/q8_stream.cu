@@ -149,12 +149,18 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0u) {
             uint32_t g = 0;
             bool ok = true;
+            // the table entry of a tile is fetched one tile ahead: a trip to memory at every
+            // change of tile would leave the ring of copies idle for that long
+            TilePlace ahead = tile_place<NTOK>(args, (uint32_t)(u_begin / segs), tok_tiles, m);
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
                 const uint32_t s0 = (uint32_t)(u % segs);
                 const unsigned long long left = u_end - u;
                 const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t w_row = tile_place<NTOK>(args, tile, tok_tiles, m).w_row;
+                const uint32_t w_row = ahead.w_row;
+                if (u + (s1 - s0) < u_end) {
+                    ahead = tile_place<NTOK>(args, tile + 1u, tok_tiles, m);
+                }
                 for (uint32_t s = s0; s < s1; ++s, ++g) {
                     const uint32_t st = g % S::raw_stages;
                     const uint32_t ph = (g / S::raw_stages) & 1u;
@@ -182,12 +188,16 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             uint32_t g = 0;
             grid_dependency_wait();
             bool ok = true;
+            TilePlace ahead = tile_place<NTOK>(args, (uint32_t)(u_begin / segs), tok_tiles, m);
             for (unsigned long long u = u_begin; ok && u < u_end;) {
                 const uint32_t tile = (uint32_t)(u / segs);
                 const uint32_t s0 = (uint32_t)(u % segs);
                 const unsigned long long left = u_end - u;
                 const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
-                const uint32_t tok0 = tile_place<NTOK>(args, tile, tok_tiles, m).i0;
+                const uint32_t tok0 = ahead.i0;   // fetched one tile ahead, as the weight copies do
+                if (u + (s1 - s0) < u_end) {
+                    ahead = tile_place<NTOK>(args, tile + 1u, tok_tiles, m);
+                }
                 for (uint32_t s = s0; s < s1; ++s, ++g) {
                     const uint32_t st = g % S::depth;
                     const uint32_t ph = (g / S::depth) & 1u;
@@ -350,12 +360,14 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t s1 = (segs - s0) < left ? segs : (uint32_t)(s0 + left);
             const uint32_t buf = tc & 1u;
             const uint32_t aph = (tc >> 1) & 1u;
+            // where the tile goes (a table entry in grouped mode): asked for before the wait
+            const TilePlace place = tile_place<NTOK>(args, tile, tok_tiles, m);
             if (!mbar_wait(acc_full + 8u * buf, aph, abort_flag, args.status)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, tile, tile, s0, s1, segs,
+            epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, place, tile, s0, s1, segs,
                                      tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
             u += (s1 - s0);
         }

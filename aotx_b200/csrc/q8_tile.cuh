@@ -266,11 +266,19 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlac
         const uint32_t copies = args.peers == 0u ? 1u : args.peers;
         for (uint32_t peer = 0; peer < copies; ++peer) {
             YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
+            // the rows of y first, all loads together: a load of the map between two stores
+            // would wait for the store before it (the map could alias y for all the compiler knows)
+            uint32_t row_of[COUNT];
+#pragma unroll
+            for (uint32_t i = 0; i < COUNT; ++i) {
+                const uint32_t row_x = first_row + i;
+                row_of[i] = (args.row_map != nullptr && row_x < place.i_limit) ? __ldg(args.row_map + row_x) : row_x;
+            }
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
                 const uint32_t row_x = first_row + i;
                 if (row_x < place.i_limit) {
-                    const uint32_t row_y = args.row_map != nullptr ? args.row_map[row_x] : row_x;
+                    const uint32_t row_y = row_of[i];
                     const size_t at = (size_t)row_y * args.ldy + col;
                     if (args.epilogue == kEpilogueAdd) {
                         // y is the float residual stream: one rounded add, as the separate
@@ -291,7 +299,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlac
 // in the same order.
 template <int NTOK, typename YT, bool PAIRS = true>
 __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t taddr_acc, uint32_t wq,
-                                               uint32_t lane, uint32_t tile, uint32_t cut_tile, uint32_t s0,
+                                               uint32_t lane, const TilePlace &place, uint32_t cut_tile, uint32_t s0,
                                                uint32_t s1,
                                                uint32_t segs, uint32_t tok_tiles,
                                                unsigned long long units, unsigned int blocks,
@@ -299,7 +307,6 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                                                uint32_t acc_empty_bar)
 {
     constexpr uint32_t kChunk = NTOK < 32 ? 16 : 32;
-    const TilePlace place = tile_place<NTOK>(args, tile, tok_tiles, m);
     const uint32_t lane_row = wq * 32u + lane;
     const uint32_t j = place.j0 + lane_row;              // row of w = column of y
     const uint32_t i0 = place.i0;                        // first row of x of the tile
@@ -335,8 +342,10 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
         __syncwarp();
     }
 
+    // columns at and beyond the tile's live rows hold nothing that is ever stored
+    const uint32_t live_cols = place.i_limit > place.i0 ? place.i_limit - place.i0 : 0u;
 #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += kChunk) {
+    for (uint32_t c0 = 0; c0 < (uint32_t)NTOK && c0 < live_cols; c0 += kChunk) {
         uint32_t v[kChunk];
         if (kChunk == 32u) {
             tmem_ld_32x32(taddr + c0, v);

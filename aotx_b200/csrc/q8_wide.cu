@@ -351,7 +351,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 break;
             }
             tc_fence_after_sync();
-            epilogue_piece<NTOK, YT>(args, tmem_base, wq, lane, tile,
+            epilogue_piece<NTOK, YT>(args, tmem_base, wq, lane, tile_place<NTOK>(args, tile, tok_tiles, m),
                                      tile >= first_work.sk_tile0 ? tile - first_work.sk_tile0 : 0u, s0, s1, segs,
                                      tok_tiles, units, blocks, m, abort_flag, acc_empty);
         }

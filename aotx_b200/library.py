@@ -20,6 +20,7 @@ SYMBOLS = (
     "aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ffn", "aotx_q8_moe_combine", "aotx_q8_matmul_static", "aotx_q8_static_status",
     "aotx_q8_matmul_peers",
     "aotx_q8_matmul_fused", "aotx_q8_moe_ffn_fused", "aotx_q8_peer_barrier", "aotx_q8_matmul_colsplit",
+    "aotx_q8_moe_ep_workspace_bytes", "aotx_q8_moe_ep",
 )
 
 # every symbol include/aotx_gguf_b200.h declares
@@ -81,6 +82,7 @@ def declare_q8(lib):
     lib.aotx_q8_moe_route.argtypes = [vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, vp]
     lib.aotx_q8_moe_workspace_bytes.argtypes = [u32, u32, u32, u32]
     lib.aotx_q8_moe_workspace_bytes.restype = C.c_size_t
+    lib.aotx_q8_moe_ep_workspace_bytes.restype = C.c_size_t
     lib.aotx_q8_moe_ffn.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
                                     u32, vp, i32, vp, C.c_size_t]
     lib.aotx_q8_moe_combine.argtypes = [vp, vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, i32]
@@ -94,9 +96,12 @@ def declare_q8(lib):
     lib.aotx_q8_matmul_fused.argtypes = [vp, vp, vp, u32, u32, u32, vp, i32, u32, vp, vp, i32, i32]
     lib.aotx_q8_moe_ffn_fused.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, u32, vp,
                                           u32, vp, i32, vp, C.c_size_t]
+    lib.aotx_q8_moe_ep_workspace_bytes.argtypes = [u32, u32, u32, u32, u32]
+    lib.aotx_q8_moe_ep.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, C.POINTER(vp), C.POINTER(vp), vp, u32, u32,
+                                   C.POINTER(vp), C.POINTER(vp), u32, u32, vp, vp, i32, vp, C.c_size_t]
     for name in SYMBOLS:
         fn = getattr(lib, name)
-        if name != "aotx_q8_moe_workspace_bytes":
+        if name not in ("aotx_q8_moe_workspace_bytes", "aotx_q8_moe_ep_workspace_bytes"):
             fn.restype = i32
 
 

@@ -286,6 +286,24 @@ class Q8Context:
             _dtype_code(out.dtype), workspace.data_ptr(), workspace.numel()))
         return out
 
+    def moe_ep_workspace(self, tokens, used, hidden, ffn, peers):
+        torch = _torch()
+        size = self.lib.aotx_q8_moe_ep_workspace_bytes(tokens, used, hidden, ffn, peers)
+        return torch.empty(size, dtype=torch.uint8, device=self.device)
+
+    def moe_ep(self, w_gate, w_up, w_down, experts_total, hidden, ffn, x_ptrs, ids_ptrs, prob, tokens, used,
+               proj_ptrs, flag_ptrs, rank, step_word, out, workspace, type=Q8_0):
+        """The expert-parallel routed step of this rank (aotx_q8_moe_ep): `x_ptrs`, `ids_ptrs`,
+        `proj_ptrs`, `flag_ptrs` are device addresses of every rank's arrays (own and
+        peer-mapped); w_* hold this rank's experts."""
+        table = lambda ptrs: (C.c_void_p * len(ptrs))(*[C.c_void_p(int(p)) for p in ptrs])
+        self._check(self.lib.aotx_q8_moe_ep(
+            self.handle, self._stream(), w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), type,
+            experts_total, hidden, ffn, table(x_ptrs), table(ids_ptrs), prob.data_ptr(), tokens, used,
+            table(proj_ptrs), table(flag_ptrs), len(flag_ptrs), rank, step_word.data_ptr(), out.data_ptr(),
+            _dtype_code(out.dtype), workspace.data_ptr(), workspace.numel()))
+        return out
+
     def moe_combine(self, proj, prob, ids, tokens=None, tokens_dev=None, out=None, out_dtype=None):
         """aotx_model_expert_add over all ranks: proj is float [tokens][used][hidden]."""
         torch = _torch()

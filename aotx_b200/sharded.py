@@ -263,3 +263,53 @@ class ColumnSplitFused:
         self.ctx.matmul_colsplit(self.w_local, self.last - self.first, self.k, x, m, self.ptrs[which],
                                  self.flag_ptrs, self.rank, self.n, self.first, self.y_dtype, self.step_word)
         return self.y[which, :m]
+
+
+class ExpertParallelFused:
+    """The routed step with experts placed on ranks and the exchange folded into the library's
+    own kernels (`aotx_q8_moe_ep`): no all-to-all, no staging buffers, no library collective.
+
+    Every rank keeps its tokens' activations and selections, and the projections of its experts,
+    in symmetric memory (`torch.distributed._symmetric_memory`, used only to allocate and to
+    exchange the addresses).  Per step and rank, one call: barrier, gather of the rows of the
+    pairs that name a local expert straight from the GPU that holds the token, the grouped
+    products, barrier, and the rank-ordered sum that reads every pair's projection from the GPU
+    that computed it (plain loads over NVLink).  The first barrier of step s + 1 is also what
+    keeps a fast rank from overwriting projections that a peer still sums: it is passed only
+    when every rank has finished step s."""
+
+    def __init__(self, ctx, w_gate, w_up, w_down, experts_total, used, hidden, ffn, world, rank, tokens,
+                 group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.ctx = ctx
+        self.w = (w_gate, w_up, w_down)
+        self.experts_total, self.used, self.hidden, self.ffn = experts_total, used, hidden, ffn
+        self.world, self.rank, self.tokens = world, rank, tokens
+        group = group if group is not None else dist.group.WORLD
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.x = symm.empty((tokens, hidden), dtype=torch.float16, device=device)
+        self.ids = symm.empty((tokens, used), dtype=torch.int32, device=device)
+        self.proj = symm.empty((world * tokens * used, hidden), dtype=torch.float32, device=device)
+        self.flags = symm.empty((max(world, 8),), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.proj.zero_()
+        handles = [symm.rendezvous(t, group) for t in (self.x, self.ids, self.proj, self.flags)]
+        self.x_ptrs, self.ids_ptrs, self.proj_ptrs, self.flag_ptrs = (
+            [int(p) for p in h.buffer_ptrs] for h in handles)
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.workspace = ctx.moe_ep_workspace(tokens, used, hidden, ffn, world)
+        self.out = torch.empty((tokens, hidden), dtype=torch.float32, device=device)
+        torch.cuda.synchronize()
+        # nobody signals a peer before every rank has its buffers and zeroed flags (set-up only)
+        handles[0].barrier(channel=0)
+
+    def ffn(self, x, prob, ids):
+        """x: [tokens][hidden] half, prob: [tokens][experts_total] float, ids: [tokens][used]
+        int32 - this rank's tokens.  Returns out[tokens][hidden] (valid until the next call)."""
+        self.x.copy_(x)
+        self.ids.copy_(ids)
+        return self.ctx.moe_ep(*self.w, self.experts_total, self.hidden, self.ffn, self.x_ptrs, self.ids_ptrs,
+                               prob, self.tokens, self.used, self.proj_ptrs, self.flag_ptrs, self.rank,
+                               self.step_word, self.out, self.workspace)

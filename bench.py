@@ -453,7 +453,7 @@ def setup_lm_head(torch, ctx, world, rank, m, fused, copies=2):
 def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
     """BASELINE config 3: Qwen3-30B-A3B-shaped routed experts, expert parallel over the ranks."""
     import aotx_b200
-    from aotx_b200.sharded import expert_parallel_on_gpu, shard_rows
+    from aotx_b200.sharded import shard_rows
     spec = SHARDED["moe_qwen3_30b_a3b"]
     tokens, experts, used = spec["tokens"], spec["experts"], spec["used"]
     hidden, ffn = spec["hidden"], spec["ffn"]
@@ -485,7 +485,10 @@ def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
             def step(c):
                 ctx.moe_ffn(*sets[c], experts, hidden, ffn, x_loc, prob, ids, out=out, workspace=ws)
     else:
-        eps = [expert_parallel_on_gpu(ctx, *sets[c], experts, used, hidden, ffn, world, rank)
+        # the exchange folded into the library's kernels (aotx_q8_moe_ep): rows and projections
+        # are read straight from the GPU that holds them, two barriers of the library's own
+        from aotx_b200.sharded import ExpertParallelFused
+        eps = [ExpertParallelFused(ctx, *sets[c], experts, used, hidden, ffn, world, rank, t1 - t0)
                for c in range(copies)]
 
         def step(c):
@@ -494,12 +497,15 @@ def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
     hit = int((torch.bincount(ids_all.reshape(-1).long(), minlength=experts) > 0).sum())
     slice_bytes = 2 * ffn * (hidden // 32) * 34 + hidden * (ffn // 32) * 34
     step_bytes = hit * slice_bytes + tokens * hidden * 2 + tokens * hidden * 4
-    launches = 5 if (moe_fused and world == 1) else 8
+    # one GPU: table, gather, gate, up, gated unit, down, sum (interleaved: one product and no
+    # gated-unit kernel less); expert parallel adds two barriers and the collection of the ids
+    launches = (5 if moe_fused else 7) if world == 1 else 10
     config = {"workload": "moe_qwen3_30b_a3b", "interleaved_gate_up": bool(moe_fused and world == 1),
               "tokens": tokens, "experts": experts, "used": used,
               "hidden": hidden, "ffn": ffn, "experts_hit": hit, "x": "float16", "y": "float32",
               "router": "selections made once outside the timed region",
-              "parallelism": "expert parallel x%d + all-to-all" % world if world > 1 else "single"}
+              "parallelism": ("expert parallel x%d, rows and projections read from the peers by the "
+                              "library's kernels" % world) if world > 1 else "single"}
     return step, step_bytes, launches, config
 
 

@@ -230,6 +230,38 @@ int aotx_q8_matmul_colsplit(aotx_q8_ctx *ctx, void *stream, const void *w, uint3
                             void *const *y_peers, void *const *flag_arrays, uint32_t peers, uint32_t rank,
                             uint32_t ldy, uint32_t col0, int y_dtype, uint32_t *step_word);
 
+/* The routed-expert step over several GPUs of one box (expert parallel), one call per rank and
+ * step.  The experts are dealt to the ranks in runs (rank r holds experts [r * E / peers ...) as
+ * aotx_gguf_row_range deals rows: the first E % peers ranks hold one more); w_gate / w_up /
+ * w_down are this rank's experts only.  Every rank has `tokens` tokens of its own:
+ * x_of_rank[q] ([tokens][hidden] binary16) and ids_of_rank[q] ([tokens][used], expert numbers
+ * of the whole table) are rank q's activations and selections, proj_of_rank[q]
+ * ([peers * tokens * used][hidden] float) the array in which rank q leaves the projections of
+ * its experts - all as this GPU addresses them (peer-mapped or symmetric memory; q == rank:
+ * this GPU's own).  prob ([tokens][experts_total]) and out ([tokens][hidden]) are this rank's.
+ *
+ * The call is the single-GPU step with the exchange folded into its kernels: after the
+ * library's barrier (every rank's x and ids are in place) the gather that sorts the rows by
+ * expert reads each row straight from the memory of the GPU that holds the token, the grouped
+ * products run on the pairs that name one of this rank's experts, a second barrier follows, and
+ * the rank-ordered weighted sum reads each pair's projection straight from the GPU that
+ * computed it.  A row of x crosses NVLink once per remote pair, a projection once; there is no
+ * staging buffer, no padding, no library collective and no count ever comes to the host, so the
+ * step is a fixed sequence of kernels (CUDA-graph capturable).  The result equals the
+ * single-GPU step's to float rounding (an expert sees the same pairs in the same order; where a
+ * tile's depth is cut between blocks differs with the number of local experts).  flag_arrays /
+ * step_word: as for aotx_q8_peer_barrier (two barriers per call).  Workspace:
+ * aotx_q8_moe_ep_workspace_bytes.  Needs the tensor-core path (hidden, ffn multiples of 256).
+ * No counterpart in the reference (single GPU). */
+size_t aotx_q8_moe_ep_workspace_bytes(uint32_t tokens, uint32_t used, uint32_t hidden, uint32_t ffn,
+                                      uint32_t peers);
+int aotx_q8_moe_ep(aotx_q8_ctx *ctx, void *stream, const void *w_gate, const void *w_up, const void *w_down,
+                   uint32_t type, uint32_t experts_total, uint32_t hidden, uint32_t ffn,
+                   const void *const *x_of_rank, const uint32_t *const *ids_of_rank, const float *prob,
+                   uint32_t tokens, uint32_t used, float *const *proj_of_rank, void *const *flag_arrays,
+                   uint32_t peers, uint32_t rank, uint32_t *step_word, void *out, int out_dtype,
+                   void *workspace, size_t workspace_bytes);
+
 /* The product without a context, for callers that cannot allocate device memory (a frozen
  * memory plan, a process whose device footprint must not grow, a plug-in that only gets a
  * stream and buffers).  Same arguments and result as aotx_q8_matmul; the scratch the kernel

@@ -89,6 +89,20 @@ inline int vote_all(int predicate)
     return all;
 }
 
+// __match_any_sync over the whole warp: the lanes whose value equals this lane's
+inline unsigned int match_any(unsigned int value)
+{
+    const unsigned int lane = thread_index.x % 32u;
+    warp->slot[lane] = value;
+    warp->barrier.wait();
+    unsigned int same = 0u;
+    for (unsigned int i = 0; i < 32u; ++i) {
+        same |= (warp->slot[i] == value ? 1u : 0u) << i;
+    }
+    warp->barrier.wait();
+    return same;
+}
+
 inline float uint_as_float(uint32_t bits)
 {
     float value;
@@ -146,12 +160,15 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define __shfl_xor_sync(mask, value, lanes) emu::shfl_xor((value), (lanes))
 #define __syncwarp() emu::warp->barrier.wait()
 #define __all_sync(mask, predicate) emu::vote_all(predicate)
+#define __match_any_sync(mask, value) emu::match_any(value)
+#define __popc(bits) __builtin_popcount(bits)
 #define __syncthreads() emu::block_barrier->wait()
 #define __uint_as_float(bits) emu::uint_as_float(bits)
 #define __float_as_uint(value) emu::float_as_uint(value)
 #define clock64() emu::clock_now()
 #define atomicOr(word, bits) emu::atomic_or((word), (bits))
 #define __ldcg(p) (*(p))
+#define __ldg(p) (*(p))
 #define __stcg(p, v) (*(p) = (v))
 #define __threadfence() std::atomic_thread_fence(std::memory_order_seq_cst)
 #define __threadfence_system() std::atomic_thread_fence(std::memory_order_seq_cst)
@@ -250,12 +267,12 @@ void emulate_grid(dim3 grid, unsigned int threads, const std::function<void()> &
 
 // The two tensor maps as the host launch code encodes them (launch_umma, launch_umma_grouped).
 static void make_maps(const unsigned char *w, uint32_t w_rows, uint32_t k, const void *x, uint32_t x_rows,
-                      uint32_t ntok, CUtensorMap *tw, CUtensorMap *tx)
+                      uint32_t x_box_rows, CUtensorMap *tw, CUtensorMap *tx)
 {
     static_assert(sizeof(q8emu::TensorMap) <= sizeof(CUtensorMap), "the stand-in fits the real type");
     const uint64_t row_b = (uint64_t)(k / 32u) * 34u;
     q8emu::TensorMap map_w = {w, {row_b / 4u, w_rows}, row_b, {kSegWords, kRows}, 4u, 0u};
-    q8emu::TensorMap map_x = {static_cast<const unsigned char *>(x), {k, x_rows}, (uint64_t)k * 2u, {kSubK, ntok}, 2u, 1u};
+    q8emu::TensorMap map_x = {static_cast<const unsigned char *>(x), {k, x_rows}, (uint64_t)k * 2u, {kSubK, x_box_rows}, 2u, 1u};
     std::memset(tw, 0, sizeof *tw);
     std::memset(tx, 0, sizeof *tx);
     std::memcpy(tw, &map_w, sizeof map_w);
@@ -466,8 +483,11 @@ extern "C" unsigned int stream_emu_moe(const unsigned char *w_gate, const unsign
         q8_group_build_kernel(ids, tokens, tokens_dev, used, experts, fused ? 2u * ffn : ffn, hidden, sorted_pair,
                               tiles_feed.data(), tiles_down.data(), counts, tile_tokens);
     });
+    RowParts rows = {};
+    rows.base[0] = x;
+    rows.parts = 1u;
     status |= run_grid(pairs < 3u ? pairs : 3u, 128u, [&] {
-        q8_gather_rows_kernel(static_cast<const uint4 *>(x), sorted_pair, tokens, tokens_dev, used, hidden / 8u,
+        q8_gather_rows_kernel(rows, sorted_pair, tokens, tokens_dev, used, hidden / 8u,
                               reinterpret_cast<uint4 *>(x_sorted.data()));
     });
     if (fused) {

@@ -85,6 +85,23 @@ def _worker(rank, world, port, result):
     want_moe = oracle.moe_ffn(wg, wu, wd, experts, hidden, ffn, x_all[t0:t1].cpu().numpy().view(np.uint16),
                               prob[t0:t1].cpu().numpy(), ids[t0:t1].cpu().numpy().view(np.uint32))
     ok = ok and oracle.within_bound(out.cpu().numpy(), want_moe.astype(np.float64))[0]
+    # the same step with the exchange folded into the library's kernels (aotx_q8_moe_ep), three
+    # steps in a row over two sets of inputs (the buffers are reused from step to step)
+    from aotx_b200.sharded import ExpertParallelFused
+    fused_ep = ExpertParallelFused(ctx, torch.from_numpy(wg[e0 * sg:e1 * sg].copy()).cuda(),
+                                   torch.from_numpy(wu[e0 * sg:e1 * sg].copy()).cuda(),
+                                   torch.from_numpy(wd[e0 * sd:e1 * sd].copy()).cuda(), experts, used, hidden,
+                                   ffn, world, rank, t1 - t0)
+    x_other = (x_all * 0.5).contiguous()
+    prob_o, ids_o = ctx.moe_route(x_other, router, used)
+    full_o = ctx.moe_ffn(torch.from_numpy(wg).cuda(), torch.from_numpy(wu).cuda(), torch.from_numpy(wd).cuda(),
+                         experts, hidden, ffn, x_other, prob_o, ids_o)
+    for xs, ps, sel, want_full in ((x_all, prob, ids, full), (x_other, prob_o, ids_o, full_o),
+                                   (x_all, prob, ids, full)):
+        got = fused_ep.ffn(xs[t0:t1].contiguous(), ps[t0:t1].contiguous(), sel[t0:t1].contiguous()).clone()
+        torch.cuda.synchronize()
+        ok = ok and bool((got - want_full[t0:t1]).abs().max() <= 1e-4 * want_full.abs().max())
+    ok = ok and oracle.within_bound(got.cpu().numpy(), want_moe.astype(np.float64))[0]
     ok = ok and ctx.device_status() == 0
     result[rank] = ok
     dist.destroy_process_group()

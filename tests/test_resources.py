@@ -9,7 +9,8 @@ from aotx_b200 import build as builder
 
 # the kernels a product, a dequantisation or the routed-expert step launches on the shipped paths
 HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_build_kernel",
-       "q8_gather_rows_kernel", "q8_swiglu_kernel", "q8_expert_sum_kernel", "q_dequant_any_kernel")
+       "q8_gather_rows_kernel", "q8_collect_ids_kernel", "q8_swiglu_kernel", "q8_expert_sum_kernel",
+       "q_dequant_any_kernel")
 # any-shape fallbacks (shapes the tensor-core kernels do not take), the prefill kernel, and the
 # decode kernel for batches of up to 32 rows: its converter loop spills nothing; what it spills
 # is in the once-per-tile path where the owner of a cut tile holds another block's 32 partial
@@ -17,7 +18,7 @@ HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_bui
 SMALL_SPILLS = {"q8_gemv_simt_kernel": 32, "q8_gemv_simt_fused_kernel": 64, "q_gemv_any_kernel": 16,
                 "q8_expert_feed_kernel": 64, "q8_expert_down_kernel": 64,
                 "q8_wide_kernel": 16, "q8_decode_kernel": 256, "store_eight_any": 64, "store_one_any": 64,
-                "mbar_wait": 0}
+                "mbar_wait": 0, "q8_peer_barrier_kernel": 0}
 
 
 @pytest.fixture(scope="module")
