@@ -61,7 +61,7 @@ EPILOGUE_OF = {"o": 1, "down": 1, "gate_up": 2}  # AOTX_Q8_EPILOGUE_ADD / _SWIGL
 
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel: one ncu capture of the
 # gate+up projection at 32 rows, scaled to the average launch by bytes (source named in the line).
-TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.2267, "decode_m32_gate_up": 1.2267}
+TRAFFIC_RATIO = {"decode_m32_llama3_8b_layer": 1.2168, "decode_m32_gate_up": 1.2168}
 TRAFFIC_SOURCE = "profiles/q8_decode_kernel_gate_up_m32.md (28672 x 4096, 32 rows, one launch)"
 TENSOR_BOUND = {"prefill_m2048_llama3_8b_layer", "prefill_m2048_gate_up", "prefill_m2048_llama3_8b_layer_fused"}
 
@@ -641,9 +641,16 @@ def measure_configs(torch, ctx, layer, copies, steps=40):
     ws = [aotx_b200.synth_q8_0_device(n, k, 300 + c) for c in range(many)]
     x = torch.randn(1, k, device="cuda").half()
     y = torch.empty(1, n, dtype=torch.float16, device="cuda")
-    ms, _, _ = time_steps(torch, lambda c: ctx.matmul(ws[c], n, k, x, y=y), many, many * 8, many, 1)
+    # one captured graph holds a launch per weight copy (as the reference's decode graph holds
+    # a layer's products): a graph of a single 13 us kernel would time the graph launches
+
+    def gemv(c):
+        for w in ws:
+            ctx.matmul(w, n, k, x, y=y)
+
+    ms, _, _ = time_steps(torch, gemv, 1, 8, 3, 1)
     out.append(summary("gemv_m1_4096", ms / (many * 8), step_bytes=n * (k // 32) * 34 + k * 2 + n * 2, rows=1,
-                       us_per_launch=ms / (many * 8) * 1e3))
+                       us_per_launch=ms / (many * 8) * 1e3, launches_per_graph=many))
     del ws
     # configuration 2: the same layer at 2048 rows, bfloat16 in and out
     m = PREFILL_ROWS
