@@ -1,14 +1,14 @@
-// The decode-regime kernel of the Q8_0 product (token tiles of 16 to 128 rows of x): the
-// weights stream through once at memory speed, whatever the batch.  Batches above 128 rows run
-// on it too, as several token tiles of 128.
+// The decode-regime kernel of the Q8_0 product with one block per SM: token tiles of 64 and 128
+// rows of x (batches of 33 to 128 rows) and the grouped products of the routed experts.  The
+// weights stream through once at memory speed, whatever the batch.  Batches of up to 32 rows
+// run on the two-blocks-per-SM form (q8_decode.cu), batches above 128 on q8_wide.cu.
 //
-// Same tiling and unit schedule as the kernel in q8_umma.cu (128 rows of w by NTOK rows of
-// x, depth in segments of 256 weights, units dealt evenly over one persistent block per SM),
-// but built around two facts of this regime:
+// Tiles of 128 rows of w by NTOK rows of x, depth in segments of 256 weights, (tile, segment)
+// units dealt evenly over one persistent block per SM.  Built around two facts of this regime:
 //   * the dequantised weight tile never touches shared memory: each converter thread owns one
 //     row, writes its 64-weight pieces straight into its lane of tensor memory with
 //     tcgen05.st, and the MMA reads A from there.  Shared memory then holds only raw bytes in
-//     flight (a deep ring of 34 KB segments) and the small x tiles;
+//     flight (a ring of 34 KB segments) and the x tiles;
 //   * a hand-off between warps costs far more than the MMAs of one 64-weight step at these
 //     widths, so every ring is handed over once per 256-weight segment (16 MMAs), not once
 //     per step.
@@ -25,8 +25,8 @@
 namespace q8 {
 
 // Stage counts of the 64-row token tile (the routed-expert products and batches of 33 to 64
-// rows), open to -D for experiments: fewer x / A stages leave room for more raw segments in
-// flight.  The static checks below hold the budget.
+// rows).  Measured against 2 x / A stages with 4 raw segments in flight: 3 and 3 is faster.
+// The static checks below hold the budget.
 #ifndef Q8_DEPTH_64
 #define Q8_DEPTH_64 3
 #endif

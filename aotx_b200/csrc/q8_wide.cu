@@ -1,16 +1,14 @@
-// The prefill-regime kernel, second form (token tiles of 256 rows of x, dequantised weights in
-// tensor memory).  NOT DISPATCHED by the product build: written after the first form
-// (q8_umma.cu, both operands in shared memory) showed run-to-run differences on the GPU, checked
-// so far only on the tests' host emulation; a build with -DQ8_EXPERIMENT reaches it with
-// Q8_WIDE_TILE=2 in the environment.
+// The prefill-regime kernel: batches above 128 rows of x, as token tiles of 256 rows, the
+// dequantised weights in tensor memory.  It replaced an earlier form with both operands in
+// shared memory, whose results differed in a few outputs from launch to launch on the GPU.
 //
-// What it takes from the two kernels that exist:
+// What it takes from the two kernels it descends from:
 //   * from the decode-regime kernel (q8_stream.cu): a converter thread owns one row of the weight
 //     tile and writes its dequantised 64-weight pieces straight into its lane of tensor memory
 //     (tcgen05.st); the MMA reads A from there.  No thread ever writes an MMA operand into shared
 //     memory, so nothing depends on how stores by ordinary threads are ordered against reads by
-//     the tensor core - the one thing the first form does that the decode-regime kernel does not;
-//   * from the first form: the tile is 128 rows of w by 256 rows of x, so one pass of
+//     the tensor core - the one thing the earlier form did that the decode-regime kernel does not;
+//   * from the earlier form: the tile is 128 rows of w by 256 rows of x, so one pass of
 //     dequantisation feeds twice the MMA work of a 128-row token tile; x comes in boxes of
 //     [256 x 64] through a ring of its own (a whole 256-deep segment of x would be 128 KB);
 //     whole waves of tiles are dealt round-robin and only the last partial wave is cut into

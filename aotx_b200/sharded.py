@@ -285,7 +285,7 @@ class ExpertParallelFused:
         import torch.distributed._symmetric_memory as symm
         self.ctx = ctx
         self.w = (w_gate, w_up, w_down)
-        self.experts_total, self.used, self.hidden, self.ffn = experts_total, used, hidden, ffn
+        self.experts_total, self.used, self.hidden, self.ffn_rows = experts_total, used, hidden, ffn
         self.world, self.rank, self.tokens = world, rank, tokens
         group = group if group is not None else dist.group.WORLD
         device = torch.device("cuda", torch.cuda.current_device())
@@ -310,6 +310,6 @@ class ExpertParallelFused:
         int32 - this rank's tokens.  Returns out[tokens][hidden] (valid until the next call)."""
         self.x.copy_(x)
         self.ids.copy_(ids)
-        return self.ctx.moe_ep(*self.w, self.experts_total, self.hidden, self.ffn, self.x_ptrs, self.ids_ptrs,
+        return self.ctx.moe_ep(*self.w, self.experts_total, self.hidden, self.ffn_rows, self.x_ptrs, self.ids_ptrs,
                                prob, self.tokens, self.used, self.proj_ptrs, self.flag_ptrs, self.rank,
                                self.step_word, self.out, self.workspace)
