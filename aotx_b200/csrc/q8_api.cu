@@ -23,6 +23,7 @@ namespace {
 
 const unsigned int kMaxTokenTile = 256u;
 const unsigned int kMaxExperts = 256u; /* cuda/model/kinds_data.h:36 */
+const unsigned int kMaxRouteHidden = 10240u; /* the router keeps four rows of x as floats in 160 KB of shared memory */
 
 int cuda_fail(aotx_q8_ctx *ctx, cudaError_t err)
 {
@@ -145,6 +146,21 @@ extern "C" int aotx_q8_device_status(aotx_q8_ctx *ctx, uint32_t *status, int cle
     if (ctx == nullptr || status == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
     }
+    /* the context's device, whatever the caller's current one is; put back afterwards */
+    int before = -1;
+    cudaGetDevice(&before);
+    if (before != ctx->device) {
+        cudaSetDevice(ctx->device);
+    }
+    struct Back {
+        int device, ours;
+        ~Back()
+        {
+            if (device >= 0 && device != ours) {
+                cudaSetDevice(device);
+            }
+        }
+    } back = {before, ctx->device};
     cudaError_t err = cudaDeviceSynchronize();
     if (err == cudaSuccess) {
         err = cudaMemcpy(status, ctx->scratch.status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
@@ -289,6 +305,9 @@ extern "C" int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f
     }
     if (x_f16 == nullptr || router == nullptr || prob == nullptr || ids == nullptr) {
         return AOTX_Q8_ERR_ARGUMENT;
+    }
+    if (hidden > kMaxRouteHidden) {
+        return AOTX_Q8_ERR_UNSUPPORTED; /* four rows of x as floats must fit in shared memory */
     }
     cudaError_t err = q8::launch_route((cudaStream_t)stream, x_f16, router, tokens, tokens_dev, hidden,
                                        experts, used, prob, ids);
@@ -466,7 +485,7 @@ extern "C" int aotx_q8_peer_barrier(aotx_q8_ctx *ctx, void *stream, void *const 
         }
     }
     cudaError_t err = q8::launch_peer_barrier((cudaStream_t)stream, flag_arrays, peers, rank, step_word,
-                                              ctx->scratch.status);
+                                              ctx->scratch.status, ctx->overlap != 0);
     return err == cudaSuccess ? AOTX_Q8_OK : cuda_fail(ctx, err);
 }
 

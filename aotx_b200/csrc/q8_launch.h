@@ -155,7 +155,8 @@ struct PeerOut {
 // The barrier between the ranks of a column-split product (q8_peers.cu): flag_arrays[r] is rank
 // r's array of `peers` words as this GPU addresses it, step_word this rank's own counter.
 cudaError_t launch_peer_barrier(cudaStream_t stream, void *const *flag_arrays, unsigned int peers,
-                                unsigned int rank, unsigned int *step_word, unsigned int *status);
+                                unsigned int rank, unsigned int *step_word, unsigned int *status,
+                                bool overlap = false);
 
 // Returns cudaErrorNotSupported when the shape is outside what the kernel takes
 // (k % 256 != 0, unaligned pointers); the caller then uses the general kernel.

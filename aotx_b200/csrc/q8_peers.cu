@@ -24,6 +24,13 @@ __global__ void q8_peer_barrier_kernel(PeerFlags flags, unsigned int peers, unsi
                                        unsigned int *step_word, unsigned int *status)
 {
     __shared__ unsigned int step_shared;
+    // Launched with the programmatic attribute, this kernel starts while the product before it
+    // still runs and lets the product after it start as well (that one streams weights and
+    // touches nothing else before its own wait): the launch gaps either side of the barrier and
+    // the next product's pipeline fill overlap the wait for the peers.  Everything this kernel
+    // does comes after the work before it has completed.
+    grid_launch_dependents();
+    grid_dependency_wait();
     if (threadIdx.x == 0) {
         step_shared = *step_word + 1u;
     }
@@ -51,12 +58,27 @@ __global__ void q8_peer_barrier_kernel(PeerFlags flags, unsigned int peers, unsi
 }
 
 cudaError_t launch_peer_barrier(cudaStream_t stream, void *const *flag_arrays, unsigned int peers,
-                                unsigned int rank, unsigned int *step_word, unsigned int *status)
+                                unsigned int rank, unsigned int *step_word, unsigned int *status, bool overlap)
 {
     PeerFlags flags = {};
     for (unsigned int i = 0; i < 8u; ++i) {
         flags.of_rank[i] = i < peers ? static_cast<unsigned int *>(flag_arrays[i]) : nullptr;
     }
+#ifndef Q8_HOST_EMULATION
+    if (overlap) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 1, 1);
+        config.blockDim = dim3(32, 1, 1);
+        config.stream = stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        return cudaLaunchKernelEx(&config, q8_peer_barrier_kernel, flags, peers, rank, step_word, status);
+    }
+#endif
+    (void)overlap;
     return launch_kernel(q8_peer_barrier_kernel, dim3(1, 1, 1), 32u, 0, stream, flags, peers, rank, step_word,
                          status);
 }

@@ -26,6 +26,7 @@ reference's own host implementation of the product on this machine's cores over 
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -221,16 +222,22 @@ def run_ours(args, rank, world, local_rank):
             product(i, c)
             t["y_host"].copy_(t["y"], non_blocking=True)
 
-    # One graph per weight copy: the step is launch-bound on the host otherwise.
+    # Captured graphs: the step is launch-bound on the host otherwise.  A graph holds `group`
+    # consecutive steps over rotating weight copies (the reference's decode graph holds a whole
+    # forward pass): inside a graph a product overlaps the tail of the one before it, as it does
+    # in a model; between two graph launches it cannot.
     step(0)
     torch.cuda.synchronize()
+    group = steps_per_graph(args.steps)
+    distinct = copies // math.gcd(copies, group)
     graphs = []
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
-        for c in range(copies):
+        for j in range(distinct):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
-                step(c)
+                for i in range(group):
+                    step((j * group + i) % copies)
             graphs.append(g)
     torch.cuda.synchronize()
 
@@ -241,20 +248,19 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     for i in range(max(args.warmup, 3)):
-        graphs[i % copies].replay()
+        graphs[i % distinct].replay()
     barrier()
 
     sampler = ClockSampler(device_index(local_rank))
     sampler.start()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    for i in range(args.steps):
-        starts[i].record()
-        graphs[i % copies].replay()
-        stops[i].record()
+    first = torch.cuda.Event(enable_timing=True)
+    last = torch.cuda.Event(enable_timing=True)
+    first.record()
+    for i in range(args.steps // group):
+        graphs[i % distinct].replay()
+    last.record()
     barrier()
-    total_ms = starts[0].elapsed_time(stops[-1])
-    step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    total_ms = first.elapsed_time(last)
     # A short timed region gives the sampler nothing to see: keep the same load running,
     # untimed, until it has a few samples under load.
     extended = False
@@ -264,7 +270,7 @@ def run_ours(args, rank, world, local_rank):
         i = 0
         while time.time() < deadline:
             for _ in range(50):
-                graphs[i % copies].replay()
+                graphs[i % distinct].replay()
                 i += 1
             torch.cuda.synchronize()
     sampler.stop_flag.set()
@@ -341,7 +347,7 @@ def run_ours(args, rank, world, local_rank):
     step_flops = flops(m, projections)
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     launches = len(projections)
-    kernel_ms = statistics.mean(step_ms) / launches
+    kernel_ms = total_ms / args.steps / launches
     tensor_bound = args.workload in TENSOR_BOUND
     if tensor_bound:
         achieved = step_flops / launches / (kernel_ms * 1e-3) / 1e12
@@ -382,7 +388,8 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": args.workload, "rows": m, "x": x_name, "y": y_name,
                    "projections": {name: [k, n] for name, k, n in projections},
                    "weight_copies_rotated": copies, "l2": "weight copies rotate; total > 3x L2",
-                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True},
+                   "parallelism": "replicas" if world > 1 else "single", "cuda_graph": True,
+                   "steps_per_graph": group},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode, "host_result_matches_device": check},
@@ -447,7 +454,8 @@ def setup_lm_head(torch, ctx, world, rank, m, fused, copies=2):
               "parallelism": "single" if world == 1 else
               ("column split x%d, slices stored into peers by the kernel" if fused
                else "column split x%d + all-gather") % world}
-    return step, step_bytes, 1, config, (lambda: state.get("y")), x
+    # launches per step: the product and, where the slices go to the peers, the barrier
+    return step, step_bytes, 2 if (fused and world > 1) else 1, config, (lambda: state.get("y")), x
 
 
 def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
@@ -509,40 +517,60 @@ def setup_moe(torch, ctx, world, rank, moe_fused=False, copies=2):
     return step, step_bytes, launches, config
 
 
-def time_steps(torch, step, copies, steps, warmup, world, capture=True):
+def steps_per_graph(steps, most=4):
+    """How many consecutive steps one captured graph holds: as many as divide `steps` exactly
+    (so that exactly `steps` steps are timed), up to `most`."""
+    for group in range(most, 1, -1):
+        if steps % group == 0:
+            return group
+    return 1
+
+
+def time_steps(torch, step, copies, steps, warmup, world, capture=True, group=1):
     """Warm up, then time `steps` steps that rotate over `copies` weight copies: CUDA events
-    between two barriers, the maximum over the ranks.  Each copy's step is captured into a CUDA
-    graph where that works.  Returns (total ms, captured, run) - `run(c)` replays one step."""
+    between two barriers, the maximum over the ranks.  The steps are captured into CUDA graphs
+    where that works, `group` consecutive steps to a graph (the reference's decode graph holds a
+    whole forward pass; inside one graph consecutive launches overlap as they do in a model,
+    between two graph launches they do not); `steps` must be a multiple of `group`.  Returns
+    (total ms, captured, run) - `run(i)` runs the i-th group of steps."""
     def barrier():
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
         torch.cuda.synchronize()
 
+    assert steps % group == 0
     step(0)
     barrier()
     graphs = None
+    distinct = copies // math.gcd(copies, group)   # graphs after which the rotation repeats
     if capture:
         try:
             graphs = []
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
-                for c in range(copies):
+                for j in range(distinct):
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=side):
-                        step(c)
+                        for i in range(group):
+                            step((j * group + i) % copies)
                     graphs.append(g)
             torch.cuda.synchronize()
         except Exception:
             graphs = None
-    run = (lambda c: graphs[c].replay()) if graphs else step
+
+    def eager(j):
+        for i in range(group):
+            step((j * group + i) % copies)
+
+    run = (lambda j: graphs[j % distinct].replay()) if graphs else eager
     for i in range(max(warmup, 3)):
-        run(i % copies)
+        run(i)
     barrier()
     e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0_.record()
-    for i in range(steps):
-        run(i % copies)
+    for i in range(steps // group):
+        run(i)
     e1_.record()
     barrier()
     total_ms = e0_.elapsed_time(e1_)
@@ -661,20 +689,20 @@ def measure_configs(torch, ctx, layer, copies, steps=40):
         for t, xx, yy in zip(layer, xs, ys):
             ctx.matmul(t["w"][c], t["n"], t["k"], xx, y=yy)
 
-    ms, _, _ = time_steps(torch, prefill, copies, steps, 3, 1)
+    ms, _, _ = time_steps(torch, prefill, copies, steps, 3, 1, group=steps_per_graph(steps))
     projections = [(t["name"], t["k"], t["n"]) for t in layer]
     out.append(summary("prefill_m2048_llama3_8b_layer", ms / steps, step_flops=flops(m, projections), rows=m,
                        tokens_per_s=m * steps / (ms * 1e-3)))
     del xs, ys
     # configuration 3: routed experts, 512 tokens, 128 experts, 8 used
     step, step_bytes, launches, config = setup_moe(torch, ctx, 1, 0)
-    ms, _, run = time_steps(torch, step, 2, steps, 3, 1)
+    ms, _, run = time_steps(torch, step, 2, steps, 3, 1, group=steps_per_graph(steps))
     out.append(summary("moe_qwen3_30b_a3b", ms / steps, step_bytes=step_bytes, launches_per_step=launches,
                        experts_hit=config["experts_hit"]))
     run = step = None
     # configuration 4: the LM head on one GPU, 8 rows
     step, step_bytes, launches, config, _, _ = setup_lm_head(torch, ctx, 1, 0, 8, False)
-    ms, _, run = time_steps(torch, step, 2, steps, 3, 1)
+    ms, _, run = time_steps(torch, step, 2, steps, 3, 1, group=steps_per_graph(steps))
     out.append(summary("lm_head_8192_to_151936_m8", ms / steps, step_bytes=step_bytes, rows=8))
     run = step = None
     torch.cuda.empty_cache()
@@ -701,12 +729,12 @@ def run_scaling(args, rank, world, local_rank):
     single = {}
     for rows in (8, 64):
         step, step_bytes, _, _, _, _ = setup_lm_head(torch, ctx, 1, 0, rows, False, copies)
-        ms, _, run = time_steps(torch, step, copies, short, 3, 1)
+        ms, _, run = time_steps(torch, step, copies, short, 3, 1, group=steps_per_graph(short))
         single["lm_head_m%d" % rows] = ms / short
         run = step = None
         torch.cuda.empty_cache()
     step, moe_bytes, _, _ = setup_moe(torch, ctx, 1, 0, False, copies)
-    ms, _, run = time_steps(torch, step, copies, short, 3, 1)
+    ms, _, run = time_steps(torch, step, copies, short, 3, 1, group=steps_per_graph(short))
     single["moe"] = ms / short
     run = step = None
     torch.cuda.empty_cache()
@@ -716,7 +744,8 @@ def run_scaling(args, rank, world, local_rank):
     step, step_bytes, launches, config, result, x_dev = setup_lm_head(torch, ctx, world, rank, 8, True, copies)
     sampler = ClockSampler(device_index(local_rank))
     sampler.start()
-    total_ms, captured, run = time_steps(torch, step, copies, args.steps, args.warmup, world)
+    group = steps_per_graph(args.steps)
+    total_ms, captured, run = time_steps(torch, step, copies, args.steps, args.warmup, world, group=group)
     sampler.stop_flag.set()
     sampler.join()
     value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
@@ -738,7 +767,7 @@ def run_scaling(args, rank, world, local_rank):
     run = run_e2e = None
 
     step64, bytes64, _, _, _, _ = setup_lm_head(torch, ctx, world, rank, 64, True, copies)
-    ms64, _, run = time_steps(torch, step64, copies, short, 3, world)
+    ms64, _, run = time_steps(torch, step64, copies, short, 3, world, group=steps_per_graph(short))
     sharded["lm_head_m64"] = summary("lm_head_colsplit", ms64 / short, step_bytes=bytes64, rows=64,
                                      one_gpu_ms=single["lm_head_m64"],
                                      speedup_over_one_gpu=single["lm_head_m64"] / (ms64 / short),
@@ -747,7 +776,7 @@ def run_scaling(args, rank, world, local_rank):
     torch.cuda.empty_cache()
 
     step_moe, moe_bytes, _, moe_config = setup_moe(torch, ctx, world, rank, False, copies)
-    ms_moe, _, run = time_steps(torch, step_moe, copies, short, 3, world, capture=False)
+    ms_moe, moe_captured, run = time_steps(torch, step_moe, copies, short, 3, world, group=steps_per_graph(short))
     sharded["moe_expert_parallel"] = summary("moe_qwen3_30b_a3b", ms_moe / short, step_bytes=moe_bytes,
                                              one_gpu_ms=single["moe"],
                                              speedup_over_one_gpu=single["moe"] / (ms_moe / short),
@@ -755,7 +784,9 @@ def run_scaling(args, rank, world, local_rank):
     run = step_moe = None
     status = ctx.device_status()
     config["cuda_graph"] = captured
+    config["steps_per_graph"] = group
     config["l2"] = "two weight copies rotate; the whole tensor is ten times L2"
+    sharded["moe_expert_parallel"]["cuda_graph"] = moe_captured
     line = {
         "metric": "q8_decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
@@ -904,10 +935,14 @@ def run_reference(args, rank, world):
         "impl": "reference",
         "metric": "q8_prefill_gemm_tflops" if tensor_bound else "q8_decode_gemm_hbm_gbs",
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmups,
-        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True,
+        # the same names as this arm's own line at this N (the LM head is split over the ranks there)
+        "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "f64 sums over f16", "data": "synthetic",
-        "config": {"workload": args.workload, "rows": m, "x": "float16", "y": "float64",
-                   "projections": {name: [k, n] for name, k, n in projections}},
+        "config": ({"workload": "lm_head_colsplit", "rows": m, "n": projections[0][2], "k": projections[0][1],
+                    "x": "float16", "y": "float64", "parallelism": "host cores of rank 0"} if world > 1 else
+                   {"workload": args.workload, "rows": m, "x": "float16", "y": "float64",
+                    "projections": {name: [k, n] for name, k, n in projections}}),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }

