@@ -111,13 +111,51 @@ static __device__ __noinline__ void store_eight_any(const UmmaArgs &args, const 
     store_chunk<8u, YT>(args, place, lane_row, j, first_row, v);
 }
 
+// The column-split store: the same eight sums into every GPU's copy of y.  Everything the
+// stores need is in registers before the first of them (behind a call the compiler must assume
+// that a store may have changed the argument block, and would fetch it again after each one),
+// and a sum is rounded once, not once per copy.
+template <typename YT>
+static __device__ __noinline__ void store_eight_peers(const UmmaArgs &args, uint32_t i_limit, uint32_t j,
+                                                      uint32_t first_row, uint32_t (&v)[8])
+{
+    const uint32_t peers = args.peers;
+    const size_t ldy = args.ldy;
+    const size_t col = args.col0 + j;
+    YT *out[8];
+#pragma unroll
+    for (uint32_t p = 0; p < 8u; ++p) {
+        out[p] = static_cast<YT *>(args.y_peer[p]);
+    }
+    float value[8];
+#pragma unroll
+    for (uint32_t i = 0; i < 8u; ++i) {
+        value[i] = __uint_as_float(v[i]);
+    }
+#pragma unroll
+    for (uint32_t p = 0; p < 8u; ++p) {
+        if (p < peers) {
+#pragma unroll
+            for (uint32_t i = 0; i < 8u; ++i) {
+                if (first_row + i < i_limit) {
+                    store_out<YT>(out[p], (size_t)(first_row + i) * ldy + col, value[i]);
+                }
+            }
+        }
+    }
+}
+
 // Eight finished sums of column j of y, rows first_row .. first_row + 7 of x.
 template <typename YT>
 __device__ __forceinline__ void store_eight(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
                                             uint32_t j, uint32_t first_row, uint32_t (&v)[8])
 {
-    if (args.epilogue == kEpilogueStore && args.peers == 0u && args.row_map == nullptr) {
-        if (j < place.j_limit) {
+    if (args.epilogue == kEpilogueStore && args.row_map == nullptr) {
+        if (j < place.j_limit && first_row < place.i_limit) {
+            if (args.peers != 0u) {
+                store_eight_peers<YT>(args, place.i_limit, j, first_row, v);
+                return;
+            }
             YT *y = static_cast<YT *>(args.y);
 #pragma unroll
             for (uint32_t i = 0; i < 8u; ++i) {

@@ -247,47 +247,69 @@ template <uint32_t COUNT, typename YT>
 __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
                                             uint32_t j, uint32_t first_row, uint32_t (&v)[COUNT])
 {
-    YT *y = static_cast<YT *>(args.y);
-    const bool swiglu = args.epilogue == kEpilogueSwiglu;
+    // Everything the stores need is read before the first of them: where this runs behind a
+    // call, the compiler must assume that a store may have changed the argument block and
+    // would fetch a field again after every store (measured: 7 us per copy of y and launch).
+    const uint32_t epilogue = args.epilogue;
+    const uint32_t peers = args.peers;
+    const size_t ldy = args.ldy;
+    const uint32_t col0 = args.col0;
+    const unsigned int *row_map = args.row_map;
+    const uint32_t i_limit = place.i_limit;
+    const uint32_t j_limit = place.j_limit;
+    const bool swiglu = epilogue == kEpilogueSwiglu;
+    float value[COUNT];
+#pragma unroll
+    for (uint32_t i = 0; i < COUNT; ++i) {
+        value[i] = __uint_as_float(v[i]);
+    }
     if (swiglu) {
         // Gate and up sums of one output column sit in neighbouring lanes.  The arithmetic is
         // that of the separate kernel (cuda/model/norm.cu:92-105).
 #pragma unroll
         for (uint32_t i = 0; i < COUNT; ++i) {
-            const float mine = __uint_as_float(v[i]);
+            const float mine = value[i];
             const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1u);
             const float unit = mine / (1.0f + expf(-mine));
-            v[i] = __float_as_uint(unit * other);
+            value[i] = unit * other;
         }
     }
-    const bool writes = j < place.j_limit && (!swiglu || (lane_row & 1u) == 0u);
-    const uint32_t col = swiglu ? ((args.col0 + j) >> 1) : (args.col0 + j);
-    if (writes) {
-        const uint32_t copies = args.peers == 0u ? 1u : args.peers;
-        for (uint32_t peer = 0; peer < copies; ++peer) {
-            YT *out = args.peers == 0u ? y : static_cast<YT *>(args.y_peer[peer]);
-            // the rows of y first, all loads together: a load of the map between two stores
-            // would wait for the store before it (the map could alias y for all the compiler knows)
-            uint32_t row_of[COUNT];
+    const bool writes = j < j_limit && (!swiglu || (lane_row & 1u) == 0u);
+    if (!writes) {
+        return;
+    }
+    const size_t col = swiglu ? ((col0 + j) >> 1) : (col0 + j);
+    // the rows of y, all loads of the map together
+    uint32_t row_of[COUNT];
+#pragma unroll
+    for (uint32_t i = 0; i < COUNT; ++i) {
+        const uint32_t row_x = first_row + i;
+        row_of[i] = (row_map != nullptr && row_x < i_limit) ? __ldg(row_map + row_x) : row_x;
+    }
+    const uint32_t copies = peers == 0u ? 1u : peers;
+    for (uint32_t peer = 0; peer < copies; ++peer) {
+        YT *out = static_cast<YT *>(peers == 0u ? args.y : args.y_peer[peer]);
+        if (epilogue == kEpilogueAdd) {
+            // y is the float residual stream: one rounded add, as the separate kernel does it
+            // (cuda/model/norm.cu:78-89).  The old values are fetched together, then added and
+            // stored: one at a time each fetch would wait behind the store before it.
+            float *sums = reinterpret_cast<float *>(out);
+            float before[COUNT];
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
-                const uint32_t row_x = first_row + i;
-                row_of[i] = (args.row_map != nullptr && row_x < place.i_limit) ? __ldg(args.row_map + row_x) : row_x;
+                before[i] = first_row + i < i_limit ? sums[(size_t)row_of[i] * ldy + col] : 0.0f;
             }
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
-                const uint32_t row_x = first_row + i;
-                if (row_x < place.i_limit) {
-                    const uint32_t row_y = row_of[i];
-                    const size_t at = (size_t)row_y * args.ldy + col;
-                    if (args.epilogue == kEpilogueAdd) {
-                        // y is the float residual stream: one rounded add, as the separate
-                        // kernel does it (cuda/model/norm.cu:78-89)
-                        float *sum = reinterpret_cast<float *>(out) + at;
-                        *sum = *sum + __uint_as_float(v[i]);
-                    } else {
-                        store_out<YT>(out, at, __uint_as_float(v[i]));
-                    }
+                if (first_row + i < i_limit) {
+                    sums[(size_t)row_of[i] * ldy + col] = before[i] + value[i];
+                }
+            }
+        } else {
+#pragma unroll
+            for (uint32_t i = 0; i < COUNT; ++i) {
+                if (first_row + i < i_limit) {
+                    store_out<YT>(out, (size_t)row_of[i] * ldy + col, value[i]);
                 }
             }
         }

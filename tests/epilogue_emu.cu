@@ -141,6 +141,7 @@ inline void fence()
 #define __float_as_uint(value) emu::float_as_uint(value)
 #define clock64() emu::clock_now()
 #define atomicOr(word, bits) emu::atomic_or((word), (bits))
+#define __ldg(p) (*(p))
 #define __ldcg(p) emu::load_global(p)
 #define __stcg(p, v) emu::store_global((p), (v))
 #define __threadfence() emu::fence()
@@ -282,7 +283,7 @@ static void run_launch(const float *w, uint32_t n, uint32_t k, const float *x, u
                     }
                     emu::accumulator = acc.data();
                     emu::accumulator_columns = NTOK;
-                    epilogue_piece<NTOK, float>(args, 0u, t / 32u, t % 32u, tile, tile, s0, s1, segs, tok_tiles, units,
+                    epilogue_piece<NTOK, float>(args, 0u, t / 32u, t % 32u, tile_place<NTOK>(args, tile, tok_tiles, m), tile, s0, s1, segs, tok_tiles, units,
                                                 blocks, m, &abort_flag, 0u);
                     u += (s1 - s0);
                 }

@@ -190,6 +190,8 @@ inline void launch2(Index grid, unsigned int threads, const std::function<void()
 // ---- the kernel sources as host code --------------------------------------------------------
 #undef __global__
 #define __global__
+#undef __grid_constant__
+#define __grid_constant__
 #undef __device__
 #define __device__
 #undef __host__
@@ -343,13 +345,16 @@ extern "C" void emu_expert_sum(const float *proj, const float *prob, const unsig
                                const unsigned int *tokens_dev, uint32_t hidden, uint32_t experts, uint32_t used,
                                float *out, uint32_t width, uint32_t grid)
 {
+    q8::ProjParts from = {};
+    from.base[0] = proj;
+    from.parts = 1u;
     if (width == 4u) {
         emu::launch(grid, 256, [=] {
-            q8::q8_expert_sum_kernel<float, 4u>(proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
+            q8::q8_expert_sum_kernel<float, 4u>(from, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
         });
     } else {
         emu::launch(grid, 256, [=] {
-            q8::q8_expert_sum_kernel<float, 1u>(proj, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
+            q8::q8_expert_sum_kernel<float, 1u>(from, prob, ids, tokens, tokens_dev, hidden, experts, used, out);
         });
     }
 }
