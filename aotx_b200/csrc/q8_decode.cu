@@ -169,25 +169,32 @@ __device__ __forceinline__ void store_eight(const UmmaArgs &args, const TilePlac
     store_eight_any<YT>(args, place, lane_row, j, first_row, v);
 }
 
+// Four finished sums of column j of y that lie `step` rows of x apart (the columns of a tile
+// that one block of a cluster stores).
 template <typename YT>
-static __device__ __noinline__ void store_one_any(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
-                                                  uint32_t j, uint32_t row, float value)
+static __device__ __noinline__ void store_four_any(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                                   uint32_t j, uint32_t first_row, uint32_t step, uint32_t (&v)[4])
 {
-    uint32_t one[1] = {__float_as_uint(value)};
-    store_chunk<1u, YT>(args, place, lane_row, j, row, one);
+    store_chunk<4u, YT>(args, place, lane_row, j, first_row, v, step);
 }
 
 template <typename YT>
-__device__ __forceinline__ void store_one(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
-                                          uint32_t j, uint32_t row, float value)
+__device__ __forceinline__ void store_four(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
+                                           uint32_t j, uint32_t first_row, uint32_t step, uint32_t (&v)[4])
 {
     if (args.epilogue == kEpilogueStore && args.peers == 0u && args.row_map == nullptr) {
-        if (j < place.j_limit && row < place.i_limit) {
-            store_out<YT>(static_cast<YT *>(args.y), (size_t)row * args.ldy + j, value);
+        if (j < place.j_limit) {
+            YT *y = static_cast<YT *>(args.y);
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) {
+                if (first_row + i * step < place.i_limit) {
+                    store_out<YT>(y, (size_t)(first_row + i * step) * args.ldy + j, __uint_as_float(v[i]));
+                }
+            }
         }
         return;
     }
-    store_one_any<YT>(args, place, lane_row, j, row, value);
+    store_four_any<YT>(args, place, lane_row, j, first_row, step, v);
 }
 
 // Barriers and buffers of a block, as shared-space addresses.
@@ -728,22 +735,30 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t j = place.j0 + lane_row;
         uint32_t local = 0u;
 #pragma unroll 1
-        for (uint32_t col = crank; col < (uint32_t)NTOK; col += csize, ++local) {
-            // the pieces of this column, fetched together, added in block order
-            float piece[kDecMaxCluster];
+        for (uint32_t col0 = crank; col0 < (uint32_t)NTOK; col0 += 4u * csize) {
+            // four of this block's columns at a time, so that a store which has to fetch
+            // first (residual add) has four fetches in flight
+            uint32_t sums[4];
 #pragma unroll
-            for (uint32_t src = 0; src < kDecMaxCluster; ++src) {
-                piece[src] = src < csize
-                    ? ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u) : 0.0f;
-            }
-            float sum = piece[0];
+            for (uint32_t q = 0; q < 4u; ++q, ++local) {
+                // the pieces of this column, fetched together, added in block order (a column
+                // past the tile reads slots nobody wrote and is dropped by the store)
+                float piece[kDecMaxCluster];
 #pragma unroll
-            for (uint32_t src = 1; src < kDecMaxCluster; ++src) {
-                if (src < csize) {
-                    sum += piece[src];
+                for (uint32_t src = 0; src < kDecMaxCluster; ++src) {
+                    piece[src] = (src < csize && col0 + q * csize < (uint32_t)NTOK)
+                        ? ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u) : 0.0f;
                 }
+                float sum = piece[0];
+#pragma unroll
+                for (uint32_t src = 1; src < kDecMaxCluster; ++src) {
+                    if (src < csize) {
+                        sum += piece[src];
+                    }
+                }
+                sums[q] = __float_as_uint(sum);
             }
-            store_one<YT>(args, place, lane_row, j, col, sum);
+            store_four<YT>(args, place, lane_row, j, col0, csize, sums);
         }
     }
     Q8_STAMP(7u, threadIdx.x == 0u)

@@ -243,9 +243,11 @@ __device__ __forceinline__ TilePlace tile_place(const UmmaArgs &args, uint32_t t
 // holds, or - with rows 2p and 2p+1 of w the gate and up rows of output column p - store
 // silu(gate) * up in column p.  Every lane of the warp calls this together (the gated unit
 // exchanges values between neighbouring lanes).  `lane_row` is the row within the tile.
+// `row_step`: the sums belong to rows first_row, first_row + row_step, ... of x.
 template <uint32_t COUNT, typename YT>
 __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlace &place, uint32_t lane_row,
-                                            uint32_t j, uint32_t first_row, uint32_t (&v)[COUNT])
+                                            uint32_t j, uint32_t first_row, uint32_t (&v)[COUNT],
+                                            uint32_t row_step = 1u)
 {
     // Everything the stores need is read before the first of them: where this runs behind a
     // call, the compiler must assume that a store may have changed the argument block and
@@ -283,7 +285,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlac
     uint32_t row_of[COUNT];
 #pragma unroll
     for (uint32_t i = 0; i < COUNT; ++i) {
-        const uint32_t row_x = first_row + i;
+        const uint32_t row_x = first_row + i * row_step;
         row_of[i] = (row_map != nullptr && row_x < i_limit) ? __ldg(row_map + row_x) : row_x;
     }
     const uint32_t copies = peers == 0u ? 1u : peers;
@@ -297,18 +299,18 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlac
             float before[COUNT];
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
-                before[i] = first_row + i < i_limit ? sums[(size_t)row_of[i] * ldy + col] : 0.0f;
+                before[i] = first_row + i * row_step < i_limit ? sums[(size_t)row_of[i] * ldy + col] : 0.0f;
             }
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
-                if (first_row + i < i_limit) {
+                if (first_row + i * row_step < i_limit) {
                     sums[(size_t)row_of[i] * ldy + col] = before[i] + value[i];
                 }
             }
         } else {
 #pragma unroll
             for (uint32_t i = 0; i < COUNT; ++i) {
-                if (first_row + i < i_limit) {
+                if (first_row + i * row_step < i_limit) {
                     store_out<YT>(out, (size_t)row_of[i] * ldy + col, value[i]);
                 }
             }

@@ -758,7 +758,7 @@ def run_scaling(args, rank, world, local_rank):
         step(c)
         y_host.copy_(result(), non_blocking=True)
 
-    e2e_ms, _, run_e2e = time_steps(torch, step_e2e, copies, args.steps, 3, world, capture=False)
+    e2e_ms, e2e_captured, run_e2e = time_steps(torch, step_e2e, copies, args.steps, 3, world, group=group)
     e2e_value = step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
     sharded["lm_head_m8"] = summary("lm_head_colsplit", total_ms / args.steps, step_bytes=step_bytes, rows=8,
                                     one_gpu_ms=single["lm_head_m8"],
@@ -797,7 +797,8 @@ def run_scaling(args, rank, world, local_rank):
                      "kernel": "q8_decode_kernel", "note": "per GPU, whole step including the exchange"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_ms / args.steps,
-                "mode": "eager calls, x up and the gathered y down on rank 0's stream every step"},
+                "mode": ("captured graphs" if e2e_captured else "eager calls")
+                + ", x up from pinned host memory and the gathered y down to it on every rank, every step"},
         "sharded": sharded,
         "gpu_launches": launches * args.steps, "clocks": sampler.summary(), "device_status": status,
     }

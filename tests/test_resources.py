@@ -17,7 +17,7 @@ HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_bui
 # sums while it reads its own (two blocks of 80 registers share an SM)
 SMALL_SPILLS = {"q8_gemv_simt_kernel": 32, "q8_gemv_simt_fused_kernel": 64, "q_gemv_any_kernel": 16,
                 "q8_expert_feed_kernel": 64, "q8_expert_down_kernel": 64,
-                "q8_wide_kernel": 16, "q8_decode_kernel": 256, "store_eight_any": 64, "store_one_any": 64,
+                "q8_wide_kernel": 16, "q8_decode_kernel": 256, "store_eight_any": 64, "store_four_any": 64, "store_eight_peers": 64,
                 "mbar_wait": 0, "q8_peer_barrier_kernel": 0}
 
 
