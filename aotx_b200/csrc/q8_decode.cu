@@ -243,6 +243,7 @@ __device__ __forceinline__ bool convert_unit(const DecodeRings &r, uint32_t g, u
     uint32_t raw[36];
     load_raw<H>(r.raw_base + rst * kRawStageBytes + row * kSegBytes, raw);
     if (H == 1) {
+        raw_words_present(raw, status);
         // both halves are in registers by now: as far as this warp goes, the raw segment may be
         // overwritten
         __syncwarp();

@@ -178,6 +178,27 @@ __device__ __forceinline__ void load_raw(uint32_t raw_row, uint32_t (&raw)[36])
     }
 }
 
+// Before a warp hands a raw stage back to the copying thread, every lane must HAVE the words of
+// its row, not merely have asked for them: the hand-over lets the next bulk copy overwrite the
+// stage from its first rows on, and a load still on its way then reads the next segment's bytes
+// (seen on the GPU as one weight row of a tile wrong in one launch in forty, lanes 0 to 3 only,
+// and only in the one kernel variant whose instruction order left the loads unconsumed).  The
+// vote needs a value computed from all 36 words of every lane, so it cannot issue before the
+// loads have returned; it is true about once in 2^64 loads, and then does nothing.
+__device__ __forceinline__ void raw_words_present(const uint32_t (&raw)[36], unsigned int *status)
+{
+    uint32_t all = raw[0];
+    uint32_t odd = raw[1];
+#pragma unroll
+    for (int i = 2; i < 36; i += 2) {
+        all ^= raw[i];
+        odd += raw[i + 1];
+    }
+    if (__any_sync(0xFFFFFFFFu, all == 0x5F3759DFu && odd == 0x9E3779B9u)) {
+        atomicOr(status, 0u);
+    }
+}
+
 // The order of work of one block: first its share [u, u_end) of the units of the tiles that
 // are cut between blocks (tile ids from sk_tile0), then whole tiles dp_first + i * dp_stride.
 struct WorkIter {

@@ -300,6 +300,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 } else {
                     load_raw<1>(raw_row, raw);
                 }
+                raw_words_present(raw, args.status);
                 __syncwarp();
                 if (lane == 0u) {
                     mbar_arrive(raw_empty + 8u * rst);

@@ -140,6 +140,8 @@ inline void fence()
 #define __uint_as_float(bits) emu::uint_as_float(bits)
 #define __float_as_uint(value) emu::float_as_uint(value)
 #define clock64() emu::clock_now()
+// only the store side runs here: the converters' vote is never reached
+#define __any_sync(mask, predicate) (predicate)
 #define atomicOr(word, bits) emu::atomic_or((word), (bits))
 #define __ldg(p) (*(p))
 #define __ldcg(p) emu::load_global(p)

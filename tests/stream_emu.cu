@@ -160,6 +160,7 @@ inline unsigned int atomic_or(unsigned int *word, unsigned int bits)
 #define __shfl_xor_sync(mask, value, lanes) emu::shfl_xor((value), (lanes))
 #define __syncwarp() emu::warp->barrier.wait()
 #define __all_sync(mask, predicate) emu::vote_all(predicate)
+#define __any_sync(mask, predicate) (!emu::vote_all(!(predicate)))
 #define __match_any_sync(mask, value) emu::match_any(value)
 #define __popc(bits) __builtin_popcount(bits)
 #define __syncthreads() emu::block_barrier->wait()

@@ -34,6 +34,26 @@ def test_bf16_product_repeats_bit_identically(ctx, n, k, m):
         assert torch.equal(other, outs[0])
 
 
+@pytest.mark.parametrize("x_name", ["bfloat16", "float16"])
+def test_prefill_kernel_repeats_bit_identically_many_times(ctx, x_name):
+    """Sixty launches of the prefill kernel at 28672 x 4096 x 2048.  This is the probe that
+    caught a raw stage handed back to the copying thread before a warp's shared-memory loads
+    had returned: about one launch in forty had one weight row of one tile wrong, bfloat16
+    only.  Six launches, as above, would have passed nine times in ten."""
+    from _util import device_synth_q8_0
+    torch = torch_mod()
+    n, k, m = 28672, 4096, 2048
+    w = device_synth_q8_0(n, k, 77)
+    xd = torch.randn(m, k, device="cuda").to(getattr(torch, x_name))
+    first = ctx.matmul(w, n, k, xd, y_dtype=torch.float32)
+    for _ in range(6):
+        outs = [ctx.matmul(w, n, k, xd, y_dtype=torch.float32) for _ in range(10)]
+        torch.cuda.synchronize()
+        for other in outs:
+            assert torch.equal(other, first)
+        del outs
+
+
 def test_routed_experts_repeat_bit_identically(ctx):
     """Grouped mode (tile table, scattered stores) on a shape where most experts are hit."""
     import aotx_b200

@@ -163,6 +163,19 @@ def test_argument_checks_need_no_device(built):
     small = lib.aotx_q8_moe_workspace_bytes(8, 2, 256, 256)
     large = lib.aotx_q8_moe_workspace_bytes(512, 8, 2048, 768)
     assert 0 < small < large and large % 256 == 0
+    # the entries for several GPUs
+    table = (C.c_void_p * 8)(*[C.c_void_p(256)] * 8)
+    assert lib.aotx_q8_peer_barrier(null, null, table, 2, 0, one) == 1
+    assert lib.aotx_q8_matmul_colsplit(null, null, one, 8, 8, 256, one, 1, 1, None, table, table, 2, 0, 16, 0, 0,
+                                       one) == 1
+    assert lib.aotx_q8_moe_ep(null, null, one, one, one, 8, 16, 512, 256, table, table, one, 4, 2, table, table, 2,
+                              0, one, one, 0, one, 1 << 30) == 1
+    assert lib.aotx_q8_moe_ep_workspace_bytes(4, 2, 512, 256, 0) == 0
+    assert lib.aotx_q8_moe_ep_workspace_bytes(4, 2, 512, 256, 9) == 0
+    two = lib.aotx_q8_moe_ep_workspace_bytes(64, 8, 2048, 768, 2)
+    eight = lib.aotx_q8_moe_ep_workspace_bytes(64, 8, 2048, 768, 8)
+    assert lib.aotx_q8_moe_workspace_bytes(128, 8, 2048, 768) < two < eight
+    assert lib.aotx_q8_static_status(None, 0) != 0
 
 
 def test_interleaved_rows_layout():
