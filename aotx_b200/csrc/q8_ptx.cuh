@@ -43,6 +43,16 @@ __device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t &a, uint32_
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
 }
 
+__device__ __forceinline__ void st_shared_b32(uint32_t addr, uint32_t value)
+{
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_b16(uint32_t addr, uint32_t value)
+{
+    asm volatile("{ .reg .b16 h; cvt.u16.u32 h, %1; st.shared.b16 [%0], h; }" ::"r"(addr), "r"(value) : "memory");
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");

@@ -48,7 +48,13 @@ struct StreamShape {
     static constexpr uint32_t raw_offset = x_offset + depth * x_seg_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 3 * depth + 4 + 1;
-    static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    // after the barriers: the storing warps' staging buffer (store_chunk_staged)
+    // (token tiles of 64 and 128; the smaller ones, which only a development build reaches,
+    // have no room for it beside their five raw stages)
+    static constexpr uint32_t stage_offset = bar_offset + 256;
+    static constexpr uint32_t stage_bytes = NTOK >= 64 ? kEpilogueWarps * kStoreStageBytes : 0;
+    static constexpr uint32_t smem_bytes = stage_offset + stage_bytes + 1024;
+    static_assert(bar_count * 8 + 16 <= 256, "barriers and the two words after them");
     static_assert(smem_bytes <= 227u * 1024u, "one block's shared memory");
     static_assert(a_column0 >= 2u * NTOK && a_column0 + depth * a_seg_columns <= tmem_columns,
                   "two accumulators, then the A segments, within the allocation");
@@ -369,7 +375,8 @@ q8_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
             tc_fence_after_sync();
             epilogue_piece<NTOK, YT>(args, tmem_base + buf * (uint32_t)NTOK, wq, lane, place, tile, s0, s1, segs,
-                                     tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf);
+                                     tok_tiles, units, blocks, m, abort_flag, acc_empty + 8u * buf,
+                                     S::stage_bytes != 0u ? smem0 + S::stage_offset : 0u);
             u += (s1 - s0);
         }
     }

@@ -339,6 +339,80 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &args, const TilePlac
     }
 }
 
+// The bits of one result in the output type (the low 16 bits for the 16-bit types).
+template <typename YT>
+__device__ __forceinline__ uint32_t out_bits(float v);
+template <>
+__device__ __forceinline__ uint32_t out_bits<float>(float v)
+{
+    return __float_as_uint(v);
+}
+template <>
+__device__ __forceinline__ uint32_t out_bits<__half>(float v)
+{
+    return (uint32_t)__half_as_ushort(__float2half_rn(v));
+}
+template <>
+__device__ __forceinline__ uint32_t out_bits<__nv_bfloat16>(float v)
+{
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+constexpr uint32_t kStoreStageBytes = 4096;   // per storing warp: 32 rows of x by 32 columns of y, floats
+
+// Whether a tile's plain store can go through the staging buffer: whole 16-byte pieces of rows
+// of y, all of the tile's 128 columns inside the tensor.
+template <typename YT>
+__device__ __forceinline__ bool staged_store_fits(const UmmaArgs &args, const TilePlace &place, uint32_t stage)
+{
+    return stage != 0u && args.epilogue == kEpilogueStore && args.peers == 0u && args.col0 == 0u
+        && place.j0 + kRows <= place.j_limit && (place.j0 % 8u) == 0u
+        && (((size_t)args.ldy * sizeof(YT)) % 16u) == 0u && (reinterpret_cast<uintptr_t>(args.y) % 16u) == 0u;
+}
+
+// 32 rows of x by this warp's 32 columns of y: every lane holds one column.  A store of a
+// column is 32 instructions that each write one 2- or 4-byte value per lane into a different
+// row of y, and the one-block-per-SM kernels spent a quarter to two fifths of their time in
+// them (prefill gate+up 839 us with the stores, 498 us without).  Here the warp turns its
+// 32 x 32 piece round in shared memory (its own 4 KB, no other warp involved) and writes rows:
+// 16 bytes per lane, 4 (16-bit) or 8 (float) instructions instead of 32.
+template <typename YT>
+__device__ __forceinline__ void store_chunk_staged(const UmmaArgs &args, const TilePlace &place, uint32_t stage_warp,
+                                                   uint32_t lane, uint32_t first_col, uint32_t first_row,
+                                                   const uint32_t (&v)[32])
+{
+    constexpr uint32_t kRowBytes = 32u * sizeof(YT);          // this warp's part of a row of y
+    constexpr uint32_t kLanesPerRow = kRowBytes / 16u;         // 4 or 8
+    constexpr uint32_t kRowsPerStep = 32u / kLanesPerRow;      // 8 or 4
+    const unsigned int *row_map = args.row_map;
+    const size_t ldy = args.ldy;
+    const uint32_t i_limit = place.i_limit;
+    unsigned char *y = static_cast<unsigned char *>(args.y);
+#pragma unroll
+    for (uint32_t i = 0; i < 32u; ++i) {
+        const uint32_t bits = out_bits<YT>(__uint_as_float(v[i]));
+        if (sizeof(YT) == 4) {
+            st_shared_b32(stage_warp + i * kRowBytes + lane * 4u, bits);
+        } else {
+            st_shared_b16(stage_warp + i * kRowBytes + lane * 2u, bits);
+        }
+    }
+    __syncwarp();
+    const uint32_t part = lane % kLanesPerRow;
+#pragma unroll
+    for (uint32_t step = 0; step < 32u / kRowsPerStep; ++step) {
+        const uint32_t r = step * kRowsPerStep + lane / kLanesPerRow;
+        const uint32_t row_x = first_row + r;
+        uint4 piece;
+        ld_shared_v4(stage_warp + r * kRowBytes + part * 16u, piece.x, piece.y, piece.z, piece.w);
+        if (row_x < i_limit) {
+            const uint32_t row_y = row_map != nullptr ? __ldg(row_map + row_x) : row_x;
+            *reinterpret_cast<uint4 *>(y + ((size_t)row_y * ldy + first_col) * sizeof(YT) + part * 16u) = piece;
+        }
+    }
+    __syncwarp();
+}
+
 // PAIRS: the owner of a cut tile keeps the partial sums of two blocks in flight at a time (the
 // kernels with 128 registers a thread); without it one block's at a time, the same additions
 // in the same order.
@@ -349,9 +423,11 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                                                uint32_t segs, uint32_t tok_tiles,
                                                unsigned long long units, unsigned int blocks,
                                                unsigned int m, volatile uint32_t *abort_flag,
-                                               uint32_t acc_empty_bar)
+                                               uint32_t acc_empty_bar, uint32_t stage = 0u)
 {
     constexpr uint32_t kChunk = NTOK < 32 ? 16 : 32;
+    // `stage`: 4 x kStoreStageBytes of shared memory for the storing warps (0: none)
+    const bool staged = kChunk == 32u && staged_store_fits<YT>(args, place, stage);
     const uint32_t lane_row = wq * 32u + lane;
     const uint32_t j = place.j0 + lane_row;              // row of w = column of y
     const uint32_t i0 = place.i0;                        // first row of x of the tile
@@ -427,6 +503,13 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
                         sum += a1[i];
                     }
                     v[i] = __float_as_uint(sum);
+                }
+            }
+            if constexpr (kChunk == 32u) {
+                if (staged) {
+                    store_chunk_staged<YT>(args, place, stage + wq * kStoreStageBytes, lane, place.j0 + wq * 32u,
+                                           i0 + c0, v);
+                    continue;
                 }
             }
             store_chunk<kChunk, YT>(args, place, lane_row, j, i0 + c0, v);

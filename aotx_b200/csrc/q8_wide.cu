@@ -43,7 +43,10 @@ struct WideShape {
     static constexpr uint32_t raw_offset = x_offset + x_stages * x_stage_bytes;
     static constexpr uint32_t bar_offset = raw_offset + raw_stages * kRawStageBytes;
     static constexpr uint32_t bar_count = 2 * raw_stages + 2 * x_stages + 2 * a_stages + 2 + 1;
-    static constexpr uint32_t smem_bytes = bar_offset + bar_count * 8 + 16 + 1024;
+    // after the barriers: the storing warps' staging buffer (store_chunk_staged)
+    static constexpr uint32_t stage_offset = bar_offset + 256;
+    static constexpr uint32_t smem_bytes = stage_offset + kEpilogueWarps * kStoreStageBytes + 1024;
+    static_assert(bar_count * 8 + 16 <= 256, "barriers and the two words after them");
     static_assert(smem_bytes <= 227u * 1024u, "one block's shared memory");
     static_assert(a_column0 >= ntok && a_column0 + a_stages * a_seg_columns <= tmem_columns,
                   "the accumulator, then the A segments, within the allocation");
@@ -352,7 +355,7 @@ q8_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             tc_fence_after_sync();
             epilogue_piece<NTOK, YT>(args, tmem_base, wq, lane, tile_place<NTOK>(args, tile, tok_tiles, m),
                                      tile >= first_work.sk_tile0 ? tile - first_work.sk_tile0 : 0u, s0, s1, segs,
-                                     tok_tiles, units, blocks, m, abort_flag, acc_empty);
+                                     tok_tiles, units, blocks, m, abort_flag, acc_empty, smem0 + S::stage_offset);
         }
     }
 

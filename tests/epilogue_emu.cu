@@ -157,6 +157,9 @@ inline void fence()
 #define mbar_arrive ptx_mbar_arrive
 #define ld_acquire_gpu ptx_ld_acquire_gpu
 #define st_release_gpu ptx_st_release_gpu
+#define ld_shared_v4 ptx_ld_shared_v4
+#define st_shared_b32 ptx_st_shared_b32
+#define st_shared_b16 ptx_st_shared_b16
 #include "q8_common.cuh"
 #undef tmem_ld_32x32
 #undef tmem_ld_32x16
@@ -165,6 +168,9 @@ inline void fence()
 #undef mbar_arrive
 #undef ld_acquire_gpu
 #undef st_release_gpu
+#undef ld_shared_v4
+#undef st_shared_b32
+#undef st_shared_b16
 
 // ... and the stand-ins take the names the tile header calls
 namespace q8 {
@@ -188,6 +194,15 @@ inline void tmem_ld_32x16(uint32_t taddr, uint32_t *v)
 {
     emu_tmem_read(taddr, v, 16);
 }
+
+// the row-wise store through a staging buffer is not driven here (no buffer is handed in); the
+// whole-kernel emulation (tests/stream_emu.cu) runs it
+inline void ld_shared_v4(uint32_t, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d)
+{
+    a = b = c = d = 0u;
+}
+inline void st_shared_b32(uint32_t, uint32_t) {}
+inline void st_shared_b16(uint32_t, uint32_t) {}
 
 inline void tmem_ld_wait() {}
 inline void tc_fence_before_sync() {}

@@ -276,6 +276,17 @@ inline void ld_shared_v4(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, u
     a = w[0], b = w[1], c = w[2], d = w[3];
 }
 
+inline void st_shared_b32(uint32_t addr, uint32_t value)
+{
+    std::memcpy(q8emu::shared_at(addr), &value, 4);
+}
+
+inline void st_shared_b16(uint32_t addr, uint32_t value)
+{
+    const uint16_t low = (uint16_t)value;
+    std::memcpy(q8emu::shared_at(addr), &low, 2);
+}
+
 inline void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     const uint32_t w[4] = {a, b, c, d};
