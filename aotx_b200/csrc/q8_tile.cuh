@@ -365,8 +365,11 @@ constexpr uint32_t kStoreStageBytes = 4096;   // per storing warp: 32 rows of x 
 template <typename YT>
 __device__ __forceinline__ bool staged_store_fits(const UmmaArgs &args, const TilePlace &place, uint32_t stage)
 {
-    return stage != 0u && args.epilogue == kEpilogueStore && args.peers == 0u && args.col0 == 0u
-        && place.j0 + kRows <= place.j_limit && (place.j0 % 8u) == 0u
+    return stage != 0u
+        && (args.epilogue == kEpilogueStore || args.epilogue == kEpilogueSwiglu
+            || (args.epilogue == kEpilogueAdd && sizeof(YT) == 4))
+        && args.peers == 0u && args.col0 == 0u
+        && place.j0 + kRows <= place.j_limit && (place.j0 % 16u) == 0u
         && (((size_t)args.ldy * sizeof(YT)) % 16u) == 0u && (reinterpret_cast<uintptr_t>(args.y) % 16u) == 0u;
 }
 
@@ -376,38 +379,75 @@ __device__ __forceinline__ bool staged_store_fits(const UmmaArgs &args, const Ti
 // them (prefill gate+up 839 us with the stores, 498 us without).  Here the warp turns its
 // 32 x 32 piece round in shared memory (its own 4 KB, no other warp involved) and writes rows:
 // 16 bytes per lane, 4 (16-bit) or 8 (float) instructions instead of 32.
-template <typename YT>
+// GATED: the warp's 32 sums of a row are 16 gate / up pairs in neighbouring lanes and become 16
+// values silu(gate) * up (the arithmetic of cuda/model/norm.cu:92-105), held by the even lanes;
+// first_col then counts columns of the narrower y.
+template <typename YT, bool GATED>
 __device__ __forceinline__ void store_chunk_staged(const UmmaArgs &args, const TilePlace &place, uint32_t stage_warp,
                                                    uint32_t lane, uint32_t first_col, uint32_t first_row,
                                                    const uint32_t (&v)[32])
 {
-    constexpr uint32_t kRowBytes = 32u * sizeof(YT);          // this warp's part of a row of y
-    constexpr uint32_t kLanesPerRow = kRowBytes / 16u;         // 4 or 8
-    constexpr uint32_t kRowsPerStep = 32u / kLanesPerRow;      // 8 or 4
+    constexpr uint32_t kColumns = GATED ? 16u : 32u;
+    constexpr uint32_t kRowBytes = kColumns * sizeof(YT);      // this warp's part of a row of y
+    constexpr uint32_t kLanesPerRow = kRowBytes / 16u;         // 2, 4 or 8
+    constexpr uint32_t kRowsPerStep = 32u / kLanesPerRow;      // 16, 8 or 4
     const unsigned int *row_map = args.row_map;
     const size_t ldy = args.ldy;
     const uint32_t i_limit = place.i_limit;
     unsigned char *y = static_cast<unsigned char *>(args.y);
+    const uint32_t column = GATED ? lane / 2u : lane;
 #pragma unroll
     for (uint32_t i = 0; i < 32u; ++i) {
-        const uint32_t bits = out_bits<YT>(__uint_as_float(v[i]));
-        if (sizeof(YT) == 4) {
-            st_shared_b32(stage_warp + i * kRowBytes + lane * 4u, bits);
-        } else {
-            st_shared_b16(stage_warp + i * kRowBytes + lane * 2u, bits);
+        float value = __uint_as_float(v[i]);
+        if (GATED) {
+            const float other = __shfl_xor_sync(0xFFFFFFFFu, value, 1u);
+            value = value / (1.0f + expf(-value)) * other;
+        }
+        const uint32_t bits = out_bits<YT>(value);
+        if (!GATED || (lane & 1u) == 0u) {
+            if (sizeof(YT) == 4) {
+                st_shared_b32(stage_warp + i * kRowBytes + column * 4u, bits);
+            } else {
+                st_shared_b16(stage_warp + i * kRowBytes + column * 2u, bits);
+            }
         }
     }
     __syncwarp();
     const uint32_t part = lane % kLanesPerRow;
+    constexpr uint32_t kSteps = 32u / kRowsPerStep;
+    const bool adds = !GATED && sizeof(YT) == 4 && args.epilogue == kEpilogueAdd;
+    uint4 *at[kSteps];
 #pragma unroll
-    for (uint32_t step = 0; step < 32u / kRowsPerStep; ++step) {
-        const uint32_t r = step * kRowsPerStep + lane / kLanesPerRow;
-        const uint32_t row_x = first_row + r;
-        uint4 piece;
-        ld_shared_v4(stage_warp + r * kRowBytes + part * 16u, piece.x, piece.y, piece.z, piece.w);
+    for (uint32_t step = 0; step < kSteps; ++step) {
+        const uint32_t row_x = first_row + step * kRowsPerStep + lane / kLanesPerRow;
+        at[step] = nullptr;
         if (row_x < i_limit) {
             const uint32_t row_y = row_map != nullptr ? __ldg(row_map + row_x) : row_x;
-            *reinterpret_cast<uint4 *>(y + ((size_t)row_y * ldy + first_col) * sizeof(YT) + part * 16u) = piece;
+            at[step] = reinterpret_cast<uint4 *>(y + ((size_t)row_y * ldy + first_col) * sizeof(YT) + part * 16u);
+        }
+    }
+    // y as the float residual stream: one rounded add per value, as the separate kernel does it
+    // (cuda/model/norm.cu:78-89); the old values are fetched together, before the first store
+    uint4 before[kSteps];
+    if (adds) {
+#pragma unroll
+        for (uint32_t step = 0; step < kSteps; ++step) {
+            before[step] = at[step] != nullptr ? *at[step] : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+#pragma unroll
+    for (uint32_t step = 0; step < kSteps; ++step) {
+        const uint32_t r = step * kRowsPerStep + lane / kLanesPerRow;
+        uint4 piece;
+        ld_shared_v4(stage_warp + r * kRowBytes + part * 16u, piece.x, piece.y, piece.z, piece.w);
+        if (adds) {
+            piece.x = __float_as_uint(__uint_as_float(before[step].x) + __uint_as_float(piece.x));
+            piece.y = __float_as_uint(__uint_as_float(before[step].y) + __uint_as_float(piece.y));
+            piece.z = __float_as_uint(__uint_as_float(before[step].z) + __uint_as_float(piece.z));
+            piece.w = __float_as_uint(__uint_as_float(before[step].w) + __uint_as_float(piece.w));
+        }
+        if (at[step] != nullptr) {
+            *at[step] = piece;
         }
     }
     __syncwarp();
@@ -507,8 +547,13 @@ __device__ __forceinline__ void epilogue_piece(const UmmaArgs &args, uint32_t ta
             }
             if constexpr (kChunk == 32u) {
                 if (staged) {
-                    store_chunk_staged<YT>(args, place, stage + wq * kStoreStageBytes, lane, place.j0 + wq * 32u,
-                                           i0 + c0, v);
+                    if (args.epilogue == kEpilogueSwiglu) {
+                        store_chunk_staged<YT, true>(args, place, stage + wq * kStoreStageBytes, lane,
+                                                     (place.j0 + wq * 32u) / 2u, i0 + c0, v);
+                    } else {
+                        store_chunk_staged<YT, false>(args, place, stage + wq * kStoreStageBytes, lane,
+                                                      place.j0 + wq * 32u, i0 + c0, v);
+                    }
                     continue;
                 }
             }

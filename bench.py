@@ -695,10 +695,19 @@ def measure_configs(torch, ctx, layer, copies, steps=40):
                        tokens_per_s=m * steps / (ms * 1e-3)))
     del xs, ys
     # configuration 3: routed experts, 512 tokens, 128 experts, 8 used
+    # in both forms: gate and up as the model file holds them (two tensors), and interleaved
+    # at load into one (aotx_gguf_upload_rows) with the gated unit in the product's store
     step, step_bytes, launches, config = setup_moe(torch, ctx, 1, 0)
     ms, _, run = time_steps(torch, step, 2, steps, 3, 1, group=steps_per_graph(steps))
-    out.append(summary("moe_qwen3_30b_a3b", ms / steps, step_bytes=step_bytes, launches_per_step=launches,
-                       experts_hit=config["experts_hit"]))
+    run = step = None
+    torch.cuda.empty_cache()
+    step, _, launches_one, _ = setup_moe(torch, ctx, 1, 0, moe_fused=True)
+    ms_one, _, run = time_steps(torch, step, 2, steps, 3, 1, group=steps_per_graph(steps))
+    best = min(ms, ms_one)
+    out.append(summary("moe_qwen3_30b_a3b", best / steps, step_bytes=step_bytes,
+                       launches_per_step=launches_one if ms_one <= ms else launches,
+                       experts_hit=config["experts_hit"], interleaved_gate_up=bool(ms_one <= ms),
+                       us_separate_tensors=ms / steps * 1e3, us_interleaved=ms_one / steps * 1e3))
     run = step = None
     # configuration 4: the LM head on one GPU, 8 rows
     step, step_bytes, launches, config, _, _ = setup_lm_head(torch, ctx, 1, 0, 8, False)
