@@ -688,11 +688,14 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
 
     // ------------------------------------------------------------ sum of a cluster's pieces
-    // Token column i of the tile belongs to block (i mod cluster size) of the cluster.  Every
-    // block writes each column of its piece into the owner's shared memory (its own columns
-    // into its own), over the x ring, which is idle once every block's MMAs have finished; the
-    // owner adds the pieces in block order and stores.
-    const uint32_t share = ((uint32_t)NTOK + csize - 1u) / csize; // columns per block, at most
+    // The token columns of the tile are dealt to the blocks of the cluster in runs: block o owns
+    // columns [o * share, (o + 1) * share).  Every block writes the columns of its piece into
+    // their owners' shared memory (its own into its own), over the x ring, which is idle once
+    // every block's MMAs have finished: per sending block and row of w the owner's `share` sums
+    // lie next to each other, so a thread sends them 16 bytes at a time (a store into another
+    // block's shared memory costs the same for one float as for four).  The owner adds the
+    // pieces in block order and stores.
+    const uint32_t share = (uint32_t)NTOK / csize;   // 2 to 32: the cluster size is a power of two up to 8
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
@@ -700,19 +703,25 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t lane_row = warp * 32u + lane;
     if (warp < kEpilogueWarps) {
         const uint32_t lane_taddr = tmem_base + ((warp * 32u) << 16);
-        uint32_t owner = 0u;
-        uint32_t local = 0u;
+        const uint32_t mine = r.x_base + (crank * kRows + lane_row) * share * 4u;   // in the owner's memory
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < (uint32_t)NTOK; c0 += 8u) {
             uint32_t v[8];
             load_sums<NTOK>(lane_taddr + c0, v);
+            if (share >= 4u) {
 #pragma unroll
-            for (uint32_t i = 0; i < 8u; ++i) {
-                const uint32_t at = r.x_base + ((crank * share + local) * kRows + lane_row) * 4u;
-                st_shared_cluster_f32(mapa_shared(at, owner), __uint_as_float(v[i]));
-                if (++owner == csize) {
-                    owner = 0u;
-                    ++local;
+                for (uint32_t h = 0; h < 8u; h += 4u) {
+                    const uint32_t col = c0 + h;
+                    st_shared_cluster_v4_f32(mapa_shared(mine + (col % share) * 4u, col / share),
+                                             __uint_as_float(v[h]), __uint_as_float(v[h + 1u]),
+                                             __uint_as_float(v[h + 2u]), __uint_as_float(v[h + 3u]));
+                }
+            } else {
+#pragma unroll
+                for (uint32_t h = 0; h < 8u; h += 2u) {
+                    const uint32_t col = c0 + h;
+                    st_shared_cluster_v2_f32(mapa_shared(mine + (col % share) * 4u, col / share),
+                                             __uint_as_float(v[h]), __uint_as_float(v[h + 1u]));
                 }
             }
         }
@@ -734,32 +743,44 @@ q8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         place.i0 = 0u;
         place.i_limit = m_live;
         const uint32_t j = place.j0 + lane_row;
-        uint32_t local = 0u;
+        const uint32_t width = share < 4u ? share : 4u;
 #pragma unroll 1
-        for (uint32_t col0 = crank; col0 < (uint32_t)NTOK; col0 += 4u * csize) {
-            // four of this block's columns at a time, so that a store which has to fetch
-            // first (residual add) has four fetches in flight
-            uint32_t sums[4];
+        for (uint32_t local = 0; local < share; local += 4u) {
+            // up to four of this block's columns at a time: the pieces of every sending block,
+            // fetched together, added in block order
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (uint32_t q = 0; q < 4u; ++q, ++local) {
-                // the pieces of this column, fetched together, added in block order (a column
-                // past the tile reads slots nobody wrote and is dropped by the store)
-                float piece[kDecMaxCluster];
+            for (uint32_t src = 0; src < kDecMaxCluster; ++src) {
+                if (src < csize) {
+                    const uint32_t at = r.x_base + ((src * kRows + lane_row) * share + local) * 4u;
+                    float piece[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (share >= 4u) {
+                        uint32_t w0, w1, w2, w3;
+                        ld_shared_v4(at, w0, w1, w2, w3);
+                        piece[0] = __uint_as_float(w0);
+                        piece[1] = __uint_as_float(w1);
+                        piece[2] = __uint_as_float(w2);
+                        piece[3] = __uint_as_float(w3);
+                    } else {
+                        piece[0] = ld_shared_f32(at);
+                        piece[1] = ld_shared_f32(at + 4u);
+                    }
 #pragma unroll
-                for (uint32_t src = 0; src < kDecMaxCluster; ++src) {
-                    piece[src] = (src < csize && col0 + q * csize < (uint32_t)NTOK)
-                        ? ld_shared_f32(r.x_base + ((src * share + local) * kRows + lane_row) * 4u) : 0.0f;
-                }
-                float sum = piece[0];
-#pragma unroll
-                for (uint32_t src = 1; src < kDecMaxCluster; ++src) {
-                    if (src < csize) {
-                        sum += piece[src];
+                    for (uint32_t q = 0; q < 4u; ++q) {
+                        sum[q] = src == 0u ? piece[q] : sum[q] + piece[q];
                     }
                 }
-                sums[q] = __float_as_uint(sum);
             }
-            store_four<YT>(args, place, lane_row, j, col0, csize, sums);
+            uint32_t sums[4];
+#pragma unroll
+            for (uint32_t q = 0; q < 4u; ++q) {
+                sums[q] = __float_as_uint(sum[q]);
+            }
+            // only this block's columns: a run of two leaves the other two of the four out
+            TilePlace run = place;
+            const uint32_t first = crank * share + local;
+            run.i_limit = place.i_limit < first + width ? place.i_limit : first + width;
+            store_four<YT>(args, run, lane_row, j, first, 1u, sums);
         }
     }
     Q8_STAMP(7u, threadIdx.x == 0u)

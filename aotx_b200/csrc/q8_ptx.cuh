@@ -330,6 +330,17 @@ __device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v)
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+__device__ __forceinline__ void st_shared_cluster_v4_f32(uint32_t addr, float a, float b, float c, float d)
+{
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_shared_cluster_v2_f32(uint32_t addr, float a, float b)
+{
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+
 __device__ __forceinline__ float ld_shared_f32(uint32_t addr)
 {
     float v;

@@ -556,6 +556,18 @@ inline void st_shared_cluster_f32(uint32_t addr, float v)
     std::memcpy(q8emu::shared_at(addr), &v, sizeof v);
 }
 
+inline void st_shared_cluster_v4_f32(uint32_t addr, float a, float b, float c, float d)
+{
+    const float w[4] = {a, b, c, d};
+    std::memcpy(q8emu::shared_at(addr), w, sizeof w);
+}
+
+inline void st_shared_cluster_v2_f32(uint32_t addr, float a, float b)
+{
+    const float w[2] = {a, b};
+    std::memcpy(q8emu::shared_at(addr), w, sizeof w);
+}
+
 inline float ld_shared_f32(uint32_t addr)
 {
     float v;
