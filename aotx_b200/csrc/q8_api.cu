@@ -23,6 +23,7 @@ namespace {
 
 const unsigned int kMaxTokenTile = 256u;
 const unsigned int kMaxExperts = 256u; /* cuda/model/kinds_data.h:36 */
+const size_t kActivationCopyBytes = 8u << 20; /* 128 rows of x at a depth of 32768 */
 const unsigned int kMaxRouteHidden = 10240u; /* the router keeps four rows of x as floats in 160 KB of shared memory */
 
 int cuda_fail(aotx_q8_ctx *ctx, cudaError_t err)
@@ -94,10 +95,15 @@ extern "C" int aotx_q8_init(aotx_q8_ctx **out, int device)
     if (err == cudaSuccess) {
         err = cudaMemset(ctx->scratch.flags, 0, flag_bytes + sizeof(unsigned int));
     }
+    if (err == cudaSuccess) {
+        ctx->scratch.x16_bytes = kActivationCopyBytes;
+        err = cudaMalloc(&ctx->scratch.x16, kActivationCopyBytes);
+    }
     if (err != cudaSuccess) {
         int code = cuda_fail(ctx, err);
         cudaFree(ctx->scratch.partial);
         cudaFree(ctx->scratch.flags);
+        cudaFree(ctx->scratch.x16);
         delete ctx;
         return code;
     }
@@ -114,6 +120,7 @@ extern "C" int aotx_q8_destroy(aotx_q8_ctx *ctx)
     cudaSetDevice(ctx->device);
     cudaFree(ctx->scratch.partial);
     cudaFree(ctx->scratch.flags);
+    cudaFree(ctx->scratch.x16);
     delete ctx;
     return AOTX_Q8_OK;
 }

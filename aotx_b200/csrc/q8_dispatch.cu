@@ -65,6 +65,21 @@ unsigned int umma_token_tile(unsigned int m)
     return 128u;
 }
 
+// x as binary16, 16 bytes a step (the conversion the kernels apply to an x tile in shared
+// memory: exact between 2^-14 and 65504, saturating above).
+__global__ void q8_x_to_f16_kernel(const uint4 *__restrict__ x, unsigned long long chunks, uint4 *__restrict__ out)
+{
+    for (unsigned long long at = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; at < chunks;
+         at += (unsigned long long)gridDim.x * blockDim.x) {
+        uint4 v = x[at];
+        v.x = bf16x2_to_f16x2(v.x);
+        v.y = bf16x2_to_f16x2(v.y);
+        v.z = bf16x2_to_f16x2(v.z);
+        v.w = bf16x2_to_f16x2(v.w);
+        out[at] = v;
+    }
+}
+
 bool umma_supports(const void *w, unsigned int n, unsigned int k, const void *x, unsigned int m)
 {
     if (n == 0u || m == 0u || k == 0u || (k % kSegK) != 0u) {
@@ -90,6 +105,22 @@ cudaError_t launch_umma(cudaStream_t stream, const UmmaScratch &scratch, unsigne
     }
     const unsigned int ntok = umma_token_tile(m);
     const unsigned long long row_b = row_bytes(k);
+    // bfloat16 activations at 33 to 128 rows: the one-block-per-SM kernel would turn every x
+    // tile into binary16 in shared memory, in every block and for every weight row tile, as many
+    // bytes again as the weights; one pass over x into the context's copy does it once
+    if (x_bf16 && ntok >= 64u && ntok <= 128u && scratch.x16 != nullptr
+        && (unsigned long long)m * k * 2ull <= scratch.x16_bytes) {
+        const unsigned long long chunks = (unsigned long long)m * k / 8ull;
+        const unsigned int blocks = (unsigned int)((chunks + 255ull) / 256ull < 4ull * sm_count
+                                                       ? (chunks + 255ull) / 256ull : 4ull * sm_count);
+        cudaError_t turned = launch_kernel(q8_x_to_f16_kernel, blocks, 256, 0, stream,
+                                           static_cast<const uint4 *>(x), chunks, static_cast<uint4 *>(scratch.x16));
+        if (turned != cudaSuccess) {
+            return turned;
+        }
+        x = scratch.x16;
+        x_bf16 = 0;
+    }
 
     CUtensorMap tw, tx;
     {

@@ -141,6 +141,10 @@ struct UmmaScratch {
     unsigned int *status;
     unsigned int blocks;          // blocks the scratch was sized for
     unsigned long long tile_floats; // floats per block in `partial`
+    // room for a binary16 copy of bfloat16 activations (batches of 33 to 128 rows: one pass
+    // over x before the product instead of a rewrite of every x tile by every block); may be null
+    void *x16 = nullptr;
+    unsigned long long x16_bytes = 0;
 };
 
 // Column-split output: the product is columns [col0, col0 + n) of a y with row stride ldy,

@@ -137,7 +137,7 @@ extern "C" int aotx_q8_matmul_static(void *stream, const void *w, uint32_t type,
         cudaError_t err = q8::launch_gemv_simt(s, w, n, k, x, x_dtype == AOTX_Q8_BF16, m, m_dev, y, y_dtype);
         return err == cudaSuccess ? AOTX_Q8_OK : AOTX_Q8_ERR_CUDA;
     }
-    q8::UmmaScratch scratch;
+    q8::UmmaScratch scratch = {};
     scratch.partial = reinterpret_cast<float *>(dev->base);
     scratch.flags = reinterpret_cast<unsigned int *>(dev->base + Q8_STATIC_PARTIAL_BYTES);
     scratch.status = scratch.flags + Q8_STATIC_BLOCKS * 4u;

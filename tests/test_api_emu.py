@@ -126,10 +126,13 @@ def test_matmul_against_the_oracle(api, oracle, n, k, m):
         assert np.abs(part[:rows] - y[:rows]).max() <= 1e-5 * np.abs(y[:m]).max()
 
 
-def test_matmul_bfloat16_in_and_out(api, oracle):
+@pytest.mark.parametrize("m", [20, 50, 100])
+def test_matmul_bfloat16_in_and_out(api, oracle, m):
+    """20 rows: the x tiles are turned into binary16 in shared memory; 50 and 100 rows: x is
+    turned once per launch into the context's binary16 copy before the product."""
     import aotx_b200
     import torch
-    n, k, m = 300, 1024, 20
+    n, k = 300, 1024
     w = aotx_b200.synth_q8_0(n, k, 3)
     bits, xb = bf16_bits(inputs(m, k, 4))
     y = np.zeros((m, n), np.uint16)

@@ -10,6 +10,7 @@ from aotx_b200 import build as builder
 # the kernels a product, a dequantisation or the routed-expert step launches on the shipped paths
 HOT = ("q8_stream_kernel", "q8_dequant_kernel", "q8_route_kernel", "q8_group_build_kernel",
        "q8_gather_rows_kernel", "q8_collect_ids_kernel", "q8_swiglu_kernel", "q8_expert_sum_kernel",
+       "q8_x_to_f16_kernel",
        "q_dequant_any_kernel")
 # any-shape fallbacks (shapes the tensor-core kernels do not take), the prefill kernel, and the
 # decode kernel for batches of up to 32 rows: its converter loop spills nothing; what it spills
