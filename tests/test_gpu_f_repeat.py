@@ -54,6 +54,24 @@ def test_prefill_kernel_repeats_bit_identically_many_times(ctx, x_name):
         del outs
 
 
+@pytest.mark.parametrize("m,x_name", [(64, "bfloat16"), (128, "bfloat16"), (100, "float16")])
+def test_mid_batch_kernel_repeats_bit_identically_many_times(ctx, m, x_name):
+    """Forty launches of the one-block-per-SM kernel at 28672 x 4096 (row-wise stores through
+    the warps' staging buffers; bfloat16 x turned into binary16 by the pass before the product)."""
+    from _util import device_synth_q8_0
+    torch = torch_mod()
+    n, k = 28672, 4096
+    w = device_synth_q8_0(n, k, 78)
+    xd = torch.randn(m, k, device="cuda").to(getattr(torch, x_name))
+    first = ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16)
+    for _ in range(2):
+        outs = [ctx.matmul(w, n, k, xd, y_dtype=torch.bfloat16) for _ in range(20)]
+        torch.cuda.synchronize()
+        for other in outs:
+            assert torch.equal(other, first)
+        del outs
+
+
 def test_routed_experts_repeat_bit_identically(ctx):
     """Grouped mode (tile table, scattered stores) on a shape where most experts are hit."""
     import aotx_b200
@@ -66,7 +84,15 @@ def test_routed_experts_repeat_bit_identically(ctx):
     x = dev(rng.standard_normal((tokens, hidden)).astype(np.float16))
     router = dev(rng.standard_normal((experts, hidden)).astype(np.float32) / np.float32(np.sqrt(hidden)))
     prob, ids = ctx.moe_route(x, router, used)
-    outs = [ctx.moe_ffn(wg, wu, wd, experts, hidden, ffn, x, prob, ids).clone() for _ in range(5)]
+    outs = [ctx.moe_ffn(wg, wu, wd, experts, hidden, ffn, x, prob, ids).clone() for _ in range(30)]
+    torch.cuda.synchronize()
+    for other in outs[1:]:
+        assert torch.equal(other, outs[0])
+    # the interleaved form (gated unit in the row-wise store of the gate+up product)
+    both = dev_weights(aotx_b200.interleave_rows(aotx_b200.synth_q8_0(experts * ffn, hidden, 71),
+                                                 aotx_b200.synth_q8_0(experts * ffn, hidden, 72), hidden,
+                                                 groups=experts))
+    outs = [ctx.moe_ffn_fused(both, wd, experts, hidden, ffn, x, prob, ids).clone() for _ in range(30)]
     torch.cuda.synchronize()
     for other in outs[1:]:
         assert torch.equal(other, outs[0])
